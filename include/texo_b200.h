@@ -1,0 +1,75 @@
+/*
+ * C ABI of the B200 quantized-matmul library.
+ *
+ * Two packagings of the same three operators are built:
+ *
+ *   libmm_int8.so, libmm_int4.so, libdequantization.so
+ *       each exports the single symbol `solve` with exactly the prototype the reference's
+ *       per-operator harness declares, so tests/mm_int8.cpp, tests/mm_int4.cpp and
+ *       tests/dequantization.cpp of frezcirno/Texo link against them unchanged.
+ *
+ *   libtexo_b200.so
+ *       all three in one library; the sources are compiled with -Dsolve=<name>, the
+ *       reference's own convention for co-linking operators (its Makefile:129-148), giving
+ *       the texo_*_solve names below.
+ *
+ * Common contract (reference docs/operators.md:9-12, src/mm_int8.cu:530-592): every pointer
+ * is a DEVICE pointer owned by the caller, row-major and contiguous; inputs are never
+ * written; the output is fully overwritten and nothing outside it is touched; work is
+ * issued asynchronously on the legacy default stream of the current device and the
+ * functions return void - poll cudaGetLastError() and synchronise before reading results.
+ * Scratch memory is owned by the library (per device, grow-only, never freed).  Calls are
+ * not thread-safe.
+ */
+#ifndef TEXO_B200_H
+#define TEXO_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- combined library: libtexo_b200.so ---------------------------------------------- */
+
+/* INT8 zero-point/scale matmul.  Replaces `solve` of the reference's src/mm_int8.cu:530-535
+ * (declared by its harness at tests/mm_int8.cpp:5-6).  A [M,K], B [K,N], C [M,N] int8.
+ *   C = clamp(rint(float(sum_k (A-zA)(B-zB)) * scale_A * scale_B / scale_C) + zC, -128, 127)
+ * with the FP32 operation order of src/mm_int8.cu:12-25.  M, N > 0; K >= 0; with K == 0,
+ * A and B may be null and C is filled with clamp(zero_point_C).  Any byte alignment. */
+void texo_mm_int8_solve(const int8_t* A, const int8_t* B, int8_t* C, int M, int N, int K,
+                        float scale_A, float scale_B, float scale_C, int zero_point_A,
+                        int zero_point_B, int zero_point_C);
+
+/* W4A16 weight-only matmul.  Replaces `solve` of the reference's src/mm_int4.cu:386-390
+ * (tests/mm_int4.cpp:7-8).  x [M,K] fp16, w_q [N,K/2] uint8 (high nibble = even k, value =
+ * nibble - 8), scales [N,K/group_size] fp16, y [M,N] fp16; fp16 passed as 16-bit words.
+ * M <= 0 or N <= 0 is a no-op (src/mm_int4.cu:391-392). */
+void texo_mm_int4_solve(const void* x, const uint8_t* w_q, const void* scales, void* y, int M,
+                        int N, int K, int group_size);
+
+/* Tile-scale dequantization.  Replaces `solve` of the reference's
+ * src/dequantization.cu:40-43 (tests/dequantization.cpp:4).  X, Y [M,N] fp32,
+ * S [ceil(M/T), ceil(N/T)] fp32; Y = X * S[m/T][n/T]. */
+void texo_dequantization_solve(const float* X, const float* S, float* Y, int M, int N, int T);
+
+/* ---- diagnostics (no counterpart in the reference, whose operators return void and keep no
+ * error state; see reference tests/test_utils.h:11-17 for its only error handling) ------- */
+
+/* Which device path the last mm_int8 call took: 1 generic, 2 tensor (tcgen05), 3 skinny. */
+int texo_mm_int8_last_path(void);
+/* Force a path for the following calls (0 = automatic).  A forced path is still skipped
+ * when its preconditions do not hold.  Also settable with TEXO_MM_INT8_PATH. */
+void texo_mm_int8_force_path(int path);
+/* Reads and clears the error state of the current device: 0 = none, 1-5 = a bounded
+ * device-side wait gave up (kernel returned early, results invalid), 16 = bad argument,
+ * 17 = tensor-map creation failed (call fell back to the generic path).  Synchronises. */
+int texo_mm_int8_status(void);
+
+int texo_mm_int4_last_path(void);
+int texo_mm_int4_status(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TEXO_B200_H */

@@ -1,0 +1,53 @@
+"""ctypes binding of libtexo_b200.so (the combined C-ABI library).
+
+There is no CPU fallback: if the library is missing it is built with nvcc, and if that is
+impossible the import of the operators fails with an error.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+from . import build as _build
+
+_LIB = None
+
+_c_int = ctypes.c_int
+_c_float = ctypes.c_float
+_c_ptr = ctypes.c_void_p
+
+_SIGNATURES = {
+    # name: (restype, argtypes)
+    "texo_mm_int8_solve": (None, [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int,
+                                  _c_float, _c_float, _c_float, _c_int, _c_int, _c_int]),
+    "texo_mm_int4_solve": (None, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int]),
+    "texo_dequantization_solve": (None, [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int]),
+    "texo_mm_int8_last_path": (_c_int, []),
+    "texo_mm_int8_force_path": (None, [_c_int]),
+    "texo_mm_int8_status": (_c_int, []),
+    "texo_mm_int4_last_path": (_c_int, []),
+    "texo_mm_int4_status": (_c_int, []),
+}
+
+
+def library_path() -> str:
+    return _build.lib_path("texo_b200")
+
+
+def load() -> ctypes.CDLL:
+    """Load (building first if needed) the combined library; raises if unavailable."""
+    global _LIB
+    if _LIB is not None:
+        return _LIB
+    path = library_path()
+    if not os.path.exists(path):
+        _build.build()
+    if not os.path.exists(path):
+        raise RuntimeError(f"texo_b200: CUDA library {path} is missing and could not be built")
+    lib = ctypes.CDLL(path)
+    for name, (restype, argtypes) in _SIGNATURES.items():
+        fn = getattr(lib, name)  # AttributeError here means a stale or foreign library
+        fn.restype = restype
+        fn.argtypes = argtypes
+    _LIB = lib
+    return lib

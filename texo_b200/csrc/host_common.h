@@ -1,0 +1,131 @@
+// Host-side state shared by the three operators: a per-device context holding the
+// grow-only scratch buffer, the device status word and cached device attributes, and the
+// driver entry point used to encode TMA tensor maps.
+//
+// Contract inherited from the reference operators (src/mm_int8.cu:500-509, docs/operators.md
+// :9-12 of frezcirno/Texo): work is issued on the legacy default stream of the current
+// device, asynchronously, and the scratch is callee-owned, process-static and never freed.
+// Unlike the reference, the state is kept per device, so one process may drive several GPUs
+// (one after another; calls are still not thread-safe).
+#pragma once
+#include <cstddef>
+#include <cstdint>
+#include <cstdio>
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+namespace texo {
+
+constexpr int MAX_DEVICES = 64;
+
+struct DeviceCtx {
+  bool ready = false;
+  int device = -1;
+  int sm_count = 0;
+  int cc_major = 0;
+  void* scratch = nullptr;
+  size_t scratch_bytes = 0;
+  int* status = nullptr;  // 64 ints of device memory; word 0 = first error code
+};
+
+inline int& host_status() {
+  static int value = 0;
+  return value;
+}
+
+inline void note_host_error(int code) {
+  if (host_status() == 0) host_status() = code;
+}
+
+inline DeviceCtx& device_ctx() {
+  static DeviceCtx table[MAX_DEVICES];
+  int device = 0;
+  cudaGetDevice(&device);
+  if (device < 0 || device >= MAX_DEVICES) device = 0;
+  DeviceCtx& ctx = table[device];
+  if (!ctx.ready) {
+    ctx.device = device;
+    cudaDeviceGetAttribute(&ctx.sm_count, cudaDevAttrMultiProcessorCount, device);
+    cudaDeviceGetAttribute(&ctx.cc_major, cudaDevAttrComputeCapabilityMajor, device);
+    if (cudaMalloc(&ctx.status, 64 * sizeof(int)) == cudaSuccess)
+      cudaMemset(ctx.status, 0, 64 * sizeof(int));
+    ctx.ready = true;
+  }
+  return ctx;
+}
+
+// Grow-only scratch (first call / growth allocates; steady state does not).
+inline void* device_scratch(DeviceCtx& ctx, size_t bytes) {
+  if (bytes > ctx.scratch_bytes) {
+    if (ctx.scratch) cudaFree(ctx.scratch);
+    ctx.scratch = nullptr;
+    ctx.scratch_bytes = 0;
+    // Round up so that slowly growing shapes do not reallocate on every call.
+    size_t want = (bytes + (size_t(1) << 20) - 1) & ~((size_t(1) << 20) - 1);
+    if (cudaMalloc(&ctx.scratch, want) != cudaSuccess) {
+      cudaGetLastError();
+      std::fprintf(stderr, "texo_b200: scratch allocation of %zu bytes failed\n", want);
+      return nullptr;
+    }
+    ctx.scratch_bytes = want;
+  }
+  return ctx.scratch;
+}
+
+// Reads and clears the status: device word (blocking copy) or, if that is clean, the last
+// host-side error.  0 = no error.  Codes are listed in ptx.cuh.
+inline int read_and_clear_status() {
+  DeviceCtx& ctx = device_ctx();
+  int code = 0;
+  if (ctx.status) {
+    cudaMemcpy(&code, ctx.status, sizeof(int), cudaMemcpyDeviceToHost);
+    if (code != 0) cudaMemset(ctx.status, 0, sizeof(int));
+  }
+  if (code == 0) code = host_status();
+  host_status() = 0;
+  return code;
+}
+
+using TensorMapEncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                       const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                       const cuuint32_t*, CUtensorMapInterleave,
+                                       CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                       CUtensorMapFloatOOBfill);
+
+inline TensorMapEncodeFn tensor_map_encoder() {
+  static TensorMapEncodeFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* entry = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &entry, cudaEnableDefault, &result) ==
+            cudaSuccess &&
+        result == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<TensorMapEncodeFn>(entry);
+    else
+      cudaGetLastError();
+  }
+  return fn;
+}
+
+// Row-major 2-D tensor [rows, cols] of `elem_bytes` elements; box = box_rows x box_cols.
+// Out-of-range parts of a box read as zero.  Returns false if the driver rejects it (base
+// not 16-byte aligned, row pitch not a multiple of 16 bytes, ...).
+inline bool make_tensor_map_2d(CUtensorMap* map, CUtensorMapDataType type, size_t elem_bytes,
+                               const void* base, uint64_t rows, uint64_t cols,
+                               uint64_t row_pitch_bytes, uint32_t box_rows, uint32_t box_cols,
+                               CUtensorMapSwizzle swizzle) {
+  TensorMapEncodeFn encode = tensor_map_encoder();
+  if (!encode) return false;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {row_pitch_bytes};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t elem_strides[2] = {1, 1};
+  (void)elem_bytes;
+  return encode(map, type, 2, const_cast<void*>(base), dims, strides, box, elem_strides,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace texo

@@ -1,0 +1,543 @@
+// INT8 zero-point/scale quantized matmul for B200 (sm_100a).
+//
+//   C[m,n] = clamp(rint(float(sum_k (A[m,k]-zA)(B[k,n]-zB)) * sA * sB / sC) + zC, -128, 127)
+//
+// Drop-in for the operator of frezcirno/Texo src/mm_int8.cu:530-592: same
+// `extern "C" void solve(...)` symbol, argument order (M, N, K), device pointers, legacy
+// default stream, asynchronous, output fully overwritten.  The FP32 epilogue keeps the
+// operation order of src/mm_int8.cu:12-25, which is what makes results bit-identical.
+//
+// Three device paths, chosen per call:
+//   * tensor path  - persistent, warp-specialised tcgen05 kernel: TMA loads A (K-major) and B
+//                    straight from its row-major [K,N] layout (an N-major UMMA operand, so no
+//                    transposed copy of B is ever made), kind::i8 MMAs accumulate int32 in
+//                    TMEM (two 128x256 accumulators, so the drain of tile i overlaps the
+//                    MMAs of tile i+1), eight epilogue warps apply the zero-point identity
+//                       sum (a-zA)(b-zB) = sum ab - zB*rowsum(A) - zA*colsum(B) + K*zA*zB
+//                    and requantise.  Needs 16-byte aligned A/B and K % 16 == N % 16 == 0.
+//   * skinny path  - M <= 32 (decode): HBM-bound; weights stream through the same TMA/UMMA
+//                    machinery with the roles of the operands swapped (weights are the
+//                    128-row operand, activations the narrow one) and the K range split over
+//                    CTAs so all SMs pull on HBM; colsum(B) falls out of an extra all-ones
+//                    activation row, so B is read exactly once.
+//   * generic path - any shape, any byte alignment, K = 0, K >= 2^17: SIMT dp4a tiles with
+//                    int64 totals.
+#include <algorithm>
+#include <cstdint>
+#include <cstdlib>
+#include <type_traits>
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include "host_common.h"
+#include "ptx.cuh"
+
+namespace texo {
+namespace i8 {
+
+// ------------------------------------------------------------------ epilogue
+// FP32 requantisation; the operation order is contractual (no reassociation, no
+// reciprocal, IEEE division, ties-to-even rounding).
+__device__ __forceinline__ int requantize(float dot, float sa, float sb, float sc, float zc) {
+  float acc = __fdiv_rn(__fmul_rn(__fmul_rn(dot, sa), sb), sc);
+  acc = __fadd_rn(rintf(acc), zc);
+  acc = fminf(fmaxf(acc, -128.f), 127.f);
+  return __float2int_rn(acc);
+}
+
+struct Quant {
+  float sa, sb, sc;
+  int za, zb, zc;
+};
+
+// -------------------------------------------------------------- generic path
+constexpr int GT = 64;        // output tile edge
+constexpr int GK = 64;        // k bytes per smem tile
+constexpr int GKW = GK / 4;   // packed words per row
+constexpr int G_THREADS = 256;
+constexpr int G_FLUSH_TILES = 512;  // 512 * 64 = 2^15 k per int32 accumulation window
+
+__global__ void __launch_bounds__(G_THREADS)
+    generic_kernel(const int8_t* __restrict__ A, const int8_t* __restrict__ B,
+                   int8_t* __restrict__ C, int M, int N, int K, Quant q) {
+  __shared__ int As[GT][GKW + 1];  // As[m][kw]: four consecutive k of row m
+  __shared__ int Bs[GT][GKW + 1];  // Bs[n][kw]: four consecutive k of column n
+  const int t = threadIdx.x;
+  const int row0 = blockIdx.y * GT, col0 = blockIdx.x * GT;
+  const int ty = t / 16, tx = t % 16;
+
+  int acc[4][4] = {}, ra[4] = {}, cb[4] = {};
+  long long tot[4][4] = {}, tra[4] = {}, tcb[4] = {};
+  const int tiles_k = (K + GK - 1) / GK;
+  int since_flush = 0;
+
+  for (int kt = 0; kt < tiles_k; ++kt) {
+    const int k0 = kt * GK;
+    {
+      // A: thread -> row t/4, sixteen k bytes starting at (t%4)*16
+      const int r = t / 4, kb = (t % 4) * 16;
+      const int m = row0 + r;
+      const int8_t* src = A + size_t(m) * K + k0 + kb;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        unsigned word = 0;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int k = k0 + kb + w * 4 + e;
+          const unsigned v = (m < M && k < K) ? uint8_t(src[w * 4 + e]) : 0u;
+          word |= v << (8 * e);
+        }
+        As[r][kb / 4 + w] = int(word);
+      }
+    }
+    {
+      // B: thread -> four k rows (t/16)*4.., four columns (t%16)*4..
+      const int kw = t / 16, nb = (t % 16) * 4;
+      unsigned word[4] = {0, 0, 0, 0};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int k = k0 + kw * 4 + e;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int n = col0 + nb + j;
+          const unsigned v = (k < K && n < N) ? uint8_t(B[size_t(k) * N + n]) : 0u;
+          word[j] |= v << (8 * e);
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) Bs[nb + j][kw] = int(word[j]);
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kw = 0; kw < GKW; ++kw) {
+      int a[4], b[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[i] = As[ty * 4 + i][kw];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) b[j] = Bs[tx * 4 + j][kw];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        ra[i] = __dp4a(a[i], 0x01010101, ra[i]);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = __dp4a(a[i], b[j], acc[i][j]);
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) cb[j] = __dp4a(b[j], 0x01010101, cb[j]);
+    }
+    __syncthreads();
+    if (++since_flush == G_FLUSH_TILES || kt + 1 == tiles_k) {
+      since_flush = 0;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        tra[i] += ra[i];
+        ra[i] = 0;
+        tcb[i] += cb[i];
+        cb[i] = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          tot[i][j] += acc[i][j];
+          acc[i][j] = 0;
+        }
+      }
+    }
+  }
+
+  const long long offset = (long long)K * q.za * q.zb;
+  const float zc = float(q.zc);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int m = row0 + ty * 4 + i;
+    if (m >= M) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = col0 + tx * 4 + j;
+      if (n >= N) continue;
+      const long long dot = tot[i][j] - (long long)q.zb * tra[i] - (long long)q.za * tcb[j] + offset;
+      C[size_t(m) * N + n] = int8_t(requantize(float(dot), q.sa, q.sb, q.sc, zc));
+    }
+  }
+}
+
+// ------------------------------------------------------------ sums pre-pass
+// row_sum[m] = sum_k A[m,k]; one warp per row, 16-byte loads (A 16-byte aligned, K % 16 == 0).
+__global__ void __launch_bounds__(256)
+    row_sums_kernel(const int8_t* __restrict__ A, int* __restrict__ row_sum, int M, int K) {
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  const int m = blockIdx.x * 8 + warp;
+  if (m >= M) return;
+  const int4* a = reinterpret_cast<const int4*>(A + size_t(m) * K);
+  int acc = 0;
+  for (int i = lane; i < K / 16; i += 32) {
+    const int4 v = __ldg(a + i);
+    acc = __dp4a(v.x, 0x01010101, acc);
+    acc = __dp4a(v.y, 0x01010101, acc);
+    acc = __dp4a(v.z, 0x01010101, acc);
+    acc = __dp4a(v.w, 0x01010101, acc);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if (lane == 0) row_sum[m] = acc;
+}
+
+// col_sum[n] += sum over a 128-row K chunk of B[k,n]; 256 columns per block, 16 columns per
+// thread (B 16-byte aligned, N % 16 == 0).  col_sum must be zero on entry.
+constexpr int CS_ROWS = 128;
+__global__ void __launch_bounds__(256)
+    col_sums_kernel(const int8_t* __restrict__ B, int* __restrict__ col_sum, int K, int N) {
+  __shared__ int part[16][256 + 1];
+  const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
+  const int n = blockIdx.x * 256 + tx * 16;
+  const int k0 = blockIdx.y * CS_ROWS, k1 = min(K, k0 + CS_ROWS);
+  int acc[16] = {};
+  if (n < N) {
+    for (int k = k0 + ty; k < k1; k += 16) {
+      const int4 v = __ldg(reinterpret_cast<const int4*>(B + size_t(k) * N + n));
+      const int w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        acc[i * 4 + 0] = __dp4a(w[i], 0x00000001, acc[i * 4 + 0]);
+        acc[i * 4 + 1] = __dp4a(w[i], 0x00000100, acc[i * 4 + 1]);
+        acc[i * 4 + 2] = __dp4a(w[i], 0x00010000, acc[i * 4 + 2]);
+        acc[i * 4 + 3] = __dp4a(w[i], 0x01000000, acc[i * 4 + 3]);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 16; ++i) part[ty][tx * 16 + i] = acc[i];
+  __syncthreads();
+  const int c = threadIdx.x;
+  int sum = 0;
+#pragma unroll
+  for (int r = 0; r < 16; ++r) sum += part[r][c];
+  const int col = blockIdx.x * 256 + c;
+  if (col < N && sum != 0) atomicAdd(&col_sum[col], sum);
+}
+
+// --------------------------------------------------------------- tensor path
+constexpr int BM = 128, BN = 256, BK = 128;  // CTA tile; BK bytes = one 128-byte swizzle row of A
+constexpr int UMMA_K = 32;                   // K per kind::i8 instruction
+constexpr int STAGES = 4;
+constexpr int A_STAGE_BYTES = BM * BK;          // 16 KiB: 128 rows x 128 k-bytes
+constexpr int B_BOX_BYTES = BK * 128;           // 16 KiB: 128 k-rows x 128 n-bytes
+constexpr int B_STAGE_BYTES = B_BOX_BYTES * 2;  // two boxes side by side cover BN = 256
+constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+constexpr int ACC_COLS = BN;  // TMEM columns per accumulator (int32 per column per lane)
+constexpr int TMEM_COLS = 2 * ACC_COLS;
+constexpr int EPI_WARPS = 8;
+constexpr int MMA_THREADS = 64 + EPI_WARPS * 32;
+constexpr int GROUP_M = 8;  // tile-row group walked column by column (L2 reuse)
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+
+struct Barriers {
+  uint64_t full[STAGES];
+  uint64_t empty[STAGES];
+  uint64_t acc_full[2];
+  uint64_t acc_empty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
+  const int group_tiles = GROUP_M * tiles_n;
+  const int first_m = tile / group_tiles * GROUP_M;
+  const int group_m = min(tiles_m - first_m, GROUP_M);
+  const int in_group = tile % group_tiles;
+  tm = first_m + in_group % group_m;
+  tn = in_group / group_m;
+}
+
+// WIDE = false: |dot| < 2^31 (K <= 33025), zero-point identity in wrapping 32-bit;
+// WIDE = true: 64-bit.
+template <bool WIDE>
+__global__ void __launch_bounds__(MMA_THREADS, 1)
+    umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                int8_t* __restrict__ C, const int* __restrict__ row_sum,
+                const int* __restrict__ col_sum, int M, int N, int K, Quant q, int tiles_m,
+                int tiles_n, int c_vector_ok, int* status) {
+  extern __shared__ uint8_t smem_raw[];
+  // SWIZZLE_128B tiles want 1024-byte alignment.
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~uintptr_t(1023));
+  Barriers* bars = reinterpret_cast<Barriers*>(smem + STAGES * STAGE_BYTES);
+  volatile int* abort_flag = &bars->abort_flag;
+
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  const int num_tiles = tiles_m * tiles_n;
+  const int num_kb = (K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&bars->full[s], 1);
+      mbar_init(&bars->empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&bars->acc_full[b], 1);
+      mbar_init(&bars->acc_empty[b], EPI_WARPS);
+    }
+    bars->abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&map_a);
+    tma_prefetch_desc(&map_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(&bars->tmem_base, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = bars->tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      int tm, tn;
+      tile_coords(tile, tiles_m, tiles_n, tm, tn);
+      for (int kb = 0; kb < num_kb && ok; ++kb) {
+        if (lane == 0) {
+          ok = mbar_wait(&bars->empty[stage], phase ^ 1, abort_flag, status, STATUS_TIMEOUT_EMPTY);
+          if (ok) {
+            uint8_t* sa = smem + stage * STAGE_BYTES;
+            uint8_t* sb = sa + A_STAGE_BYTES;
+            mbar_arrive_expect_tx(&bars->full[stage], STAGE_BYTES);
+            tma_load_2d(sa, &map_a, &bars->full[stage], kb * BK, tm * BM);
+            tma_load_2d(sb, &map_b, &bars->full[stage], tn * BN, kb * BK);
+            tma_load_2d(sb + B_BOX_BYTES, &map_b, &bars->full[stage], tn * BN + 128, kb * BK);
+          }
+        }
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (++stage == STAGES) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------------- MMA issuer
+    // A: K-major, 128-byte swizzle: rows 128 B apart, 8-row groups 1024 B apart (SBO).
+    // B: N-major, 128-byte swizzle: k rows 128 B apart, 8-row k groups 1024 B apart (SBO),
+    //    the second 128-column box B_BOX_BYTES further on (LBO).
+    constexpr uint32_t IDESC = umma_idesc(/*D=s32*/ 2, /*A=s8*/ 1, /*B=s8*/ 1, /*A K-major*/ 0,
+                                          /*B N-major*/ 1, BM, BN);
+    int stage = 0;
+    uint32_t phase = 0;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      if (lane == 0) {
+        ok = mbar_wait(&bars->acc_empty[acc], acc_phase ^ 1, abort_flag, status,
+                       STATUS_TIMEOUT_TMEM_EMPTY);
+        tc_fence_after_sync();
+      }
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      const uint32_t tmem_d = tmem_base + acc * ACC_COLS;
+      for (int kb = 0; kb < num_kb && ok; ++kb) {
+        if (lane == 0) {
+          ok = mbar_wait(&bars->full[stage], phase, abort_flag, status, STATUS_TIMEOUT_FULL);
+          if (ok) {
+            tc_fence_after_sync();
+            const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
+            const uint32_t sb = sa + A_STAGE_BYTES;
+#pragma unroll
+            for (int j = 0; j < BK / UMMA_K; ++j) {
+              const uint64_t da = smem_desc(sa + j * UMMA_K, 16, 1024, SMEM_SWIZZLE_128B);
+              const uint64_t db =
+                  smem_desc(sb + j * UMMA_K * 128, B_BOX_BYTES, 1024, SMEM_SWIZZLE_128B);
+              umma_i8(tmem_d, da, db, IDESC, (kb | j) != 0);
+            }
+            umma_commit(&bars->empty[stage]);  // stage reusable once these MMAs have read it
+          }
+        }
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (++stage == STAGES) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+      if (lane == 0 && ok) umma_commit(&bars->acc_full[acc]);
+      __syncwarp();
+      if (++acc == 2) {
+        acc = 0;
+        acc_phase ^= 1;
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue
+    const int ew = warp - 2;
+    const int quarter = warp % 4;  // TMEM lanes this warp may read: 32*quarter .. +31
+    const int half = ew / 4;       // which 128 of the 256 accumulator columns
+    using Wide = typename std::conditional<WIDE, long long, unsigned>::type;
+    using Signed = typename std::conditional<WIDE, long long, int>::type;
+    const Wide offset = Wide(K) * Wide(q.za) * Wide(q.zb);
+    const float zc = float(q.zc);
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      int tm, tn;
+      tile_coords(tile, tiles_m, tiles_n, tm, tn);
+      ok = mbar_wait(&bars->acc_full[acc], acc_phase, abort_flag, status,
+                     STATUS_TIMEOUT_TMEM_FULL);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const int m = tm * BM + quarter * 32 + lane;
+      const bool row_ok = m < M;
+      Wide row_term = offset;
+      if (row_ok && q.zb != 0) row_term -= Wide(q.zb) * Wide(row_sum[m]);
+      int8_t* c_row = C + size_t(row_ok ? m : 0) * N;
+#pragma unroll 1
+      for (int chunk = 0; chunk < 4; ++chunk) {
+        const int col = half * 128 + chunk * 32;
+        const int n0 = tn * BN + col;
+        uint32_t v[32];
+        tmem_ld_32x32(tmem_base + acc * ACC_COLS + col + (uint32_t(quarter * 32) << 16), v);
+        tmem_ld_wait();
+        if (n0 >= N) continue;  // warp-uniform
+        uint32_t packed[8];
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+          int4 cs = make_int4(0, 0, 0, 0);
+          // col_sum is padded to a multiple of BN, so this never reads out of bounds.
+          if (q.za != 0) cs = __ldg(reinterpret_cast<const int4*>(col_sum + n0 + g * 4));
+          const int csv[4] = {cs.x, cs.y, cs.z, cs.w};
+          uint32_t word = 0;
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const Wide dot = Wide(Signed(int(v[g * 4 + e]))) + row_term - Wide(q.za) * Wide(csv[e]);
+            const int r = requantize(float(Signed(dot)), q.sa, q.sb, q.sc, zc);
+            word |= uint32_t(r & 0xff) << (8 * e);
+          }
+          packed[g] = word;
+        }
+        if (row_ok) {
+          if (c_vector_ok && n0 + 32 <= N) {
+            int4* dst = reinterpret_cast<int4*>(c_row + n0);
+            dst[0] = make_int4(packed[0], packed[1], packed[2], packed[3]);
+            dst[1] = make_int4(packed[4], packed[5], packed[6], packed[7]);
+          } else {
+            for (int e = 0; e < 32 && n0 + e < N; ++e)
+              c_row[n0 + e] = int8_t((packed[e / 4] >> (8 * (e % 4))) & 0xff);
+          }
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->acc_empty[acc]);
+      if (++acc == 2) {
+        acc = 0;
+        acc_phase ^= 1;
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ------------------------------------------------------------------ dispatch
+enum Path { PATH_AUTO = 0, PATH_GENERIC = 1, PATH_TENSOR = 2, PATH_SKINNY = 3 };
+
+inline int& forced_path() {
+  static int path = [] {
+    const char* env = std::getenv("TEXO_MM_INT8_PATH");
+    return env ? std::atoi(env) : 0;
+  }();
+  return path;
+}
+
+inline int& last_path() {
+  static int path = 0;
+  return path;
+}
+
+static void launch_generic(const int8_t* A, const int8_t* B, int8_t* C, int M, int N, int K,
+                           const Quant& q) {
+  dim3 grid((N + GT - 1) / GT, (M + GT - 1) / GT);
+  generic_kernel<<<grid, G_THREADS>>>(A, B, C, M, N, K, q);
+  last_path() = PATH_GENERIC;
+}
+
+static bool tensor_path_ok(const int8_t* A, const int8_t* B, int M, int N, int K) {
+  (void)M;
+  return K > 0 && K < (1 << 17) && K % 16 == 0 && N % 16 == 0 &&
+         (reinterpret_cast<uintptr_t>(A) & 15) == 0 && (reinterpret_cast<uintptr_t>(B) & 15) == 0;
+}
+
+static bool launch_tensor(DeviceCtx& ctx, const int8_t* A, const int8_t* B, int8_t* C, int M, int N,
+                          int K, const Quant& q) {
+  static bool configured[MAX_DEVICES] = {};
+  if (!configured[ctx.device]) {
+    cudaFuncSetAttribute(umma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    cudaFuncSetAttribute(umma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    configured[ctx.device] = true;
+  }
+  CUtensorMap map_a, map_b;
+  if (!make_tensor_map_2d(&map_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, A, M, K, K, BM, BK,
+                          CU_TENSOR_MAP_SWIZZLE_128B) ||
+      !make_tensor_map_2d(&map_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, B, K, N, N, BK, 128,
+                          CU_TENSOR_MAP_SWIZZLE_128B)) {
+    note_host_error(STATUS_TENSORMAP_FAILED);
+    return false;
+  }
+  const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
+  const int np = tiles_n * BN;
+  // Scratch: row_sum[M] | col_sum[np] (int32).
+  const size_t row_bytes = (size_t(M) * 4 + 255) & ~size_t(255);
+  int* row_sum = static_cast<int*>(device_scratch(ctx, row_bytes + size_t(np) * 4));
+  if (!row_sum) return false;
+  int* col_sum = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(row_sum) + row_bytes);
+  if (q.zb != 0) row_sums_kernel<<<(M + 7) / 8, 256>>>(A, row_sum, M, K);
+  if (q.za != 0) {
+    cudaMemsetAsync(col_sum, 0, size_t(np) * 4, 0);
+    col_sums_kernel<<<dim3((N + 255) / 256, (K + CS_ROWS - 1) / CS_ROWS), 256>>>(B, col_sum, K, N);
+  }
+  const int grid = std::min(tiles_m * tiles_n, ctx.sm_count);
+  const int c_vector_ok = (reinterpret_cast<uintptr_t>(C) & 15) == 0 && N % 16 == 0;
+  if (K <= 33025)
+    umma_kernel<false><<<grid, MMA_THREADS, SMEM_BYTES>>>(map_a, map_b, C, row_sum, col_sum, M, N,
+                                                         K, q, tiles_m, tiles_n, c_vector_ok,
+                                                         ctx.status);
+  else
+    umma_kernel<true><<<grid, MMA_THREADS, SMEM_BYTES>>>(map_a, map_b, C, row_sum, col_sum, M, N,
+                                                        K, q, tiles_m, tiles_n, c_vector_ok,
+                                                        ctx.status);
+  last_path() = PATH_TENSOR;
+  return true;
+}
+
+}  // namespace i8
+}  // namespace texo
+
+// A, B, C are device pointers: A [M,K], B [K,N], C [M,N], row-major int8.
+extern "C" void solve(const int8_t* A, const int8_t* B, int8_t* C, int M, int N, int K,
+                      float scale_A, float scale_B, float scale_C, int zero_point_A,
+                      int zero_point_B, int zero_point_C) {
+  using namespace texo;
+  using namespace texo::i8;
+  if (M <= 0 || N <= 0) return;
+  if (K < 0 || !C || (K > 0 && (!A || !B))) {
+    note_host_error(STATUS_BAD_ARGUMENT);
+    return;
+  }
+  DeviceCtx& ctx = device_ctx();
+  const Quant q = {scale_A, scale_B, scale_C, zero_point_A, zero_point_B, zero_point_C};
+  const int force = forced_path();
+  if (force != PATH_GENERIC && ctx.cc_major >= 10 && tensor_path_ok(A, B, M, N, K)) {
+    if (launch_tensor(ctx, A, B, C, M, N, K, q)) return;
+  }
+  launch_generic(A, B, C, M, N, K, q);
+}
+
+// Diagnostics (declared in include/texo_b200.h).
+extern "C" int texo_mm_int8_last_path(void) { return texo::i8::last_path(); }
+extern "C" void texo_mm_int8_force_path(int path) { texo::i8::forced_path() = path; }
+extern "C" int texo_mm_int8_status(void) { return texo::read_and_clear_status(); }

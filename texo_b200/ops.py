@@ -1,0 +1,143 @@
+"""Host-side mirror of the reference operator interface, on torch CUDA tensors.
+
+Each function keeps the name, argument order and meaning of the reference operator's
+`solve` (frezcirno/Texo src/mm_int8.cu:530-535, src/mm_int4.cu:386-390,
+src/dequantization.cu:40-43); torch only provides device memory and stream ordering.  The
+math always runs in the CUDA library; a missing library or a CPU tensor is an error.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+
+__all__ = ["mm_int8", "mm_int4", "dequantization", "mm_int8_host", "last_path", "status",
+           "force_path"]
+
+
+def _check_cuda(name: str, t: torch.Tensor, dtype: torch.dtype) -> None:
+    if not isinstance(t, torch.Tensor) or not t.is_cuda:
+        raise ValueError(f"{name} must be a CUDA tensor (there is no CPU path)")
+    if t.dtype != dtype:
+        raise ValueError(f"{name} must have dtype {dtype}, got {t.dtype}")
+    if not t.is_contiguous():
+        raise ValueError(f"{name} must be contiguous and row-major")
+
+
+class _DefaultStreamOrder:
+    """The library issues work on the legacy default stream (reference contract).  When the
+    caller's current torch stream is another one, order the two around the call."""
+
+    def __init__(self, device: torch.device):
+        self.device = device
+        self.cur = torch.cuda.current_stream(device)
+        self.default = torch.cuda.default_stream(device)
+        self.foreign = self.cur != self.default
+
+    def __enter__(self):
+        if self.foreign:
+            self.default.wait_stream(self.cur)
+        return self
+
+    def __exit__(self, *exc):
+        if self.foreign:
+            self.cur.wait_stream(self.default)
+        return False
+
+
+def mm_int8(A: torch.Tensor, B: torch.Tensor, scale_A: float, scale_B: float, scale_C: float,
+            zero_point_A: int, zero_point_B: int, zero_point_C: int,
+            out: torch.Tensor | None = None) -> torch.Tensor:
+    """C[M,N] int8 = requantised (A - zA) @ (B - zB); see include/texo_b200.h."""
+    _check_cuda("A", A, torch.int8)
+    _check_cuda("B", B, torch.int8)
+    if A.dim() != 2 or B.dim() != 2 or A.shape[1] != B.shape[0]:
+        raise ValueError(f"shape mismatch: A {tuple(A.shape)} B {tuple(B.shape)}")
+    M, K = A.shape
+    N = B.shape[1]
+    if M <= 0 or N <= 0:
+        raise ValueError("M and N must be positive")
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.int8, device=A.device)
+    else:
+        _check_cuda("out", out, torch.int8)
+        if tuple(out.shape) != (M, N):
+            raise ValueError("out has the wrong shape")
+    lib = _lib.load()
+    with torch.cuda.device(A.device), _DefaultStreamOrder(A.device):
+        lib.texo_mm_int8_solve(A.data_ptr() if K else None, B.data_ptr() if K else None,
+                               out.data_ptr(), M, N, K, scale_A, scale_B, scale_C,
+                               zero_point_A, zero_point_B, zero_point_C)
+    return out
+
+
+def mm_int4(x: torch.Tensor, w_q: torch.Tensor, scales: torch.Tensor, group_size: int,
+            out: torch.Tensor | None = None) -> torch.Tensor:
+    """y[M,N] fp16 = x[M,K] @ dequant(w_q[N,K/2], scales[N,K/G])^T (W4A16)."""
+    _check_cuda("x", x, torch.float16)
+    _check_cuda("w_q", w_q, torch.uint8)
+    _check_cuda("scales", scales, torch.float16)
+    M, K = x.shape
+    N = w_q.shape[0]
+    if K % 2 or w_q.shape[1] != K // 2:
+        raise ValueError("w_q must be [N, K/2] with even K")
+    if group_size <= 0 or K % group_size or tuple(scales.shape) != (N, K // group_size):
+        raise ValueError("scales must be [N, K/group_size]")
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.float16, device=x.device)
+    else:
+        _check_cuda("out", out, torch.float16)
+    lib = _lib.load()
+    with torch.cuda.device(x.device), _DefaultStreamOrder(x.device):
+        lib.texo_mm_int4_solve(x.data_ptr(), w_q.data_ptr(), scales.data_ptr(), out.data_ptr(),
+                               M, N, K, group_size)
+    return out
+
+
+def dequantization(X: torch.Tensor, S: torch.Tensor, T: int,
+                   out: torch.Tensor | None = None) -> torch.Tensor:
+    """Y[M,N] fp32 = X * S[m // T][n // T]."""
+    _check_cuda("X", X, torch.float32)
+    _check_cuda("S", S, torch.float32)
+    M, N = X.shape
+    if T <= 0 or tuple(S.shape) != ((M + T - 1) // T, (N + T - 1) // T):
+        raise ValueError("S must be [ceil(M/T), ceil(N/T)]")
+    if out is None:
+        out = torch.empty_like(X)
+    else:
+        _check_cuda("out", out, torch.float32)
+    lib = _lib.load()
+    with torch.cuda.device(X.device), _DefaultStreamOrder(X.device):
+        lib.texo_dequantization_solve(X.data_ptr(), S.data_ptr(), out.data_ptr(), M, N, T)
+    return out
+
+
+def mm_int8_host(A_host: torch.Tensor, B_host: torch.Tensor, C_host: torch.Tensor,
+                 staging: tuple[torch.Tensor, torch.Tensor, torch.Tensor],
+                 scale_A: float, scale_B: float, scale_C: float,
+                 zero_point_A: int, zero_point_B: int, zero_point_C: int) -> None:
+    """End-to-end call on HOST buffers, the sequence the reference harness performs around
+    `solve` (tests/mm_int8.cpp:56-79): upload A and B, run, download C.  `staging` holds the
+    device tensors (dA, dB, dC); host tensors should be pinned.  Asynchronous on the default
+    stream; synchronise before reading C_host."""
+    dA, dB, dC = staging
+    dA.copy_(A_host, non_blocking=True)
+    dB.copy_(B_host, non_blocking=True)
+    mm_int8(dA, dB, scale_A, scale_B, scale_C, zero_point_A, zero_point_B, zero_point_C, out=dC)
+    C_host.copy_(dC, non_blocking=True)
+
+
+def last_path(op: str = "mm_int8") -> int:
+    lib = _lib.load()
+    return lib.texo_mm_int8_last_path() if op == "mm_int8" else lib.texo_mm_int4_last_path()
+
+
+def force_path(path: int) -> None:
+    """Force the mm_int8 device path (0 auto, 1 generic, 2 tensor, 3 skinny); diagnostics."""
+    _lib.load().texo_mm_int8_force_path(int(path))
+
+
+def status(op: str = "mm_int8") -> int:
+    """Reads and clears the library's error state for the current device (0 = clean)."""
+    lib = _lib.load()
+    return lib.texo_mm_int8_status() if op == "mm_int8" else lib.texo_mm_int4_status()
