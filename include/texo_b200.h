@@ -69,6 +69,14 @@ int texo_mm_int8_status(void);
 int texo_mm_int4_last_path(void);
 int texo_mm_int4_status(void);
 
+/* Number of kernels the library has launched so far in this process. */
+long long texo_kernel_launches(void);
+/* CUDA-event bracket around the dominant kernel of each following call (for roofline
+ * reporting).  enable(1) resets the record; read() synchronises and returns the summed
+ * kernel time and the number of bracketed launches (0 on success). */
+void texo_profile_enable(int on);
+int texo_profile_read(float* total_ms, int* launches);
+
 #ifdef __cplusplus
 }
 #endif

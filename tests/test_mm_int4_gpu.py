@@ -1,0 +1,103 @@
+"""GPU parity tests for the W4A16 matmul through the C ABI.
+
+Floating point: accepted when |y - ref| <= 0.01 + 0.01 |ref| against the double-precision
+oracle - the tolerance of the reference harness (tests/mm_int4.cpp:10-11,94)."""
+import os
+import subprocess
+
+import numpy as np
+import pytest
+
+from tests import harness
+
+pytestmark = pytest.mark.gpu
+torch = pytest.importorskip("torch")
+
+ATOL = RTOL = 0.01
+MARKER = 0x7BCD
+
+
+@pytest.fixture(scope="module")
+def lib():
+    if not torch.cuda.is_available():
+        pytest.fail("no CUDA device: GPU tests need a B200")
+    from texo_b200 import _lib
+
+    return _lib.load()
+
+
+def run_case(lib, x, w, s, m, n, k, g, y_offset=0):
+    """Guard bands, optional odd output offset, two calls (NaN poison, then stale finite)."""
+    dx = torch.from_numpy(x.view(np.int16)).cuda()
+    dw = torch.from_numpy(w).cuda()
+    ds = torch.from_numpy(s.view(np.int16)).cuda()
+    prefix = 8 + y_offset
+    total = prefix + m * n + 8
+    out = None
+    for poison in (0x7E00, 0x4400):
+        init = np.full(total, MARKER, np.uint16)
+        init[prefix:prefix + m * n] = poison
+        dy = torch.from_numpy(init.view(np.int16)).cuda()
+        lib.texo_mm_int4_solve(dx.data_ptr(), dw.data_ptr(), ds.data_ptr(), dy.data_ptr() + 2 * prefix,
+                               m, n, k, g)
+        torch.cuda.synchronize()
+        got = dy.cpu().numpy().view(np.uint16)
+        assert np.all(got[:prefix] == MARKER) and np.all(got[prefix + m * n:] == MARKER), "guard overwritten"
+        out = got[prefix:prefix + m * n].reshape(m, n)
+    assert np.array_equal(dx.cpu().numpy().view(np.uint16), x) and np.array_equal(dw.cpu().numpy(), w)
+    return harness.half_bits_to_float(out)
+
+
+def test_pinned_example(lib):
+    data = np.load(os.path.join(harness.GOLDEN_DIR, "mm_int4_example.npz"))
+    got = run_case(lib, data["x"], data["w"], data["s"], 2, 4, 4, 2)
+    assert np.array_equal(got.astype(np.float64), data["y"])
+
+
+def test_harness_default_cases(lib, oracle):
+    cases, seed = harness.mm_int4_harness_shapes()
+    for m, n, k, g, sd, zero_x, off in cases:
+        x, w, s = oracle.int4_inputs(m, n, k, g, sd, zero_x)
+        got = run_case(lib, x, w, s, m, n, k, g, off)
+        want = oracle.mm_int4(x, w, s, m, n, k, g)
+        assert harness.int4_within_tolerance(got, want, ATOL, RTOL), (m, n, k, g)
+    # zero scales: first, middle, last group and an all-zero column (tests/mm_int4.cpp:166-175)
+    m, n, k, g = 70, 136, 512, 32
+    x, w, s = oracle.int4_inputs(m, n, k, g, seed)
+    s = s.copy()
+    groups = k // g
+    for col in range(n):
+        for gi in range(groups):
+            if col == 5 or (col % 3 == 0 and gi in (0, groups // 2, groups - 1)):
+                s[col, gi] = 0
+    got = run_case(lib, x, w, s, m, n, k, g)
+    assert harness.int4_within_tolerance(got, oracle.mm_int4(x, w, s, m, n, k, g), ATOL, RTOL)
+    assert lib.texo_mm_int4_status() == 0
+
+
+@pytest.mark.parametrize("shape", [(4096, 4096, 4096, 128, 0, 24), (8192, 520, 8192, 32, 5, 12),
+                                   (4096, 8192, 8192, 128, 11, 8)])
+def test_large_sampled_rows(lib, oracle, shape):
+    """tests/mm_int4.cpp:178-179 plus BASELINE config 4 (M=4096 K=8192 N=8192, G=128)."""
+    m, n, k, g, seed, nrows = shape
+    x, w, s = oracle.int4_inputs(m, n, k, g, seed)
+    dx = torch.from_numpy(x.view(np.int16)).cuda()
+    dw = torch.from_numpy(w).cuda()
+    ds = torch.from_numpy(s.view(np.int16)).cuda()
+    dy = torch.full((m, n), float("nan"), dtype=torch.float16, device="cuda")
+    lib.texo_mm_int4_solve(dx.data_ptr(), dw.data_ptr(), ds.data_ptr(), dy.data_ptr(), m, n, k, g)
+    torch.cuda.synchronize()
+    assert lib.texo_mm_int4_status() == 0
+    rows = [(m - 1) * i // max(1, nrows - 1) for i in range(nrows)]
+    for r in rows:
+        want = oracle.mm_int4(x, w, s, m, n, k, g, rows=(r, r + 1))
+        got = dy[r].float().cpu().numpy()[None, :]
+        assert harness.int4_within_tolerance(got, want, ATOL, RTOL), (shape, r)
+
+
+def test_unchanged_reference_harness_links_and_passes():
+    exe = os.path.join(harness.ORACLE_DIR, "_ref", "mm_int4_test")
+    if not os.path.exists(exe):
+        pytest.skip("oracle/_ref not built (reference checkout absent at build time)")
+    proc = subprocess.run([exe], capture_output=True, text=True, timeout=1800)
+    assert proc.returncode == 0 and "ALL PASSED" in proc.stdout, proc.stdout[-2000:] + proc.stderr[-2000:]

@@ -1,0 +1,83 @@
+"""CPU-only: column sharding + all-gather plumbing on world_size-2 gloo ranks.
+
+The CUDA operator is replaced by the oracle as the per-rank solver (test stand-in only), so
+what is checked here is the host logic: slab arithmetic, slab extraction, and that gathering
+every rank's slab reproduces the unsharded result bit for bit."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from tests import harness
+from texo_b200 import sharded
+
+
+def test_slab_arithmetic():
+    assert sharded.slab_width(8192, 8) == 1024
+    assert sharded.slab_width(10240, 8) == 1280
+    assert sharded.slab_width(57344, 8) == 7168
+    assert sharded.slab_width(28672, 8) == 3584
+    assert sharded.slab_width(1000, 3) == 384
+    # slabs tile [0, N) exactly, in order, also when N does not divide evenly
+    for N, world in [(8192, 8), (1000, 3), (100, 4), (130, 2), (16, 8)]:
+        edges = [sharded.column_slab(N, world, r) for r in range(world)]
+        assert edges[0][0] == 0 and edges[-1][1] == N
+        for (a0, a1), (b0, b1) in zip(edges, edges[1:]):
+            assert a1 == b0 and a0 <= a1
+    with pytest.raises(ValueError):
+        sharded.column_slab(10, 2, 2)
+
+
+def _oracle_solver(A, B, sa, sb, sc, za, zb, zc):
+    o = harness.load_oracle()
+    M, K = A.shape
+    N = B.shape[1]
+    out = o.mm_int8(A.numpy(), B.numpy(), M, N, K, (sa, sb, sc, za, zb, zc))
+    return torch.from_numpy(out)
+
+
+def _worker(rank, world, port, N, result_dir):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        M, K = 24, 96
+        rows, cols_k = np.arange(M), np.arange(K)
+        A = torch.from_numpy(harness.hashed_int8(1, 0, rows, cols_k))
+        # every rank materialises only its own slab of the logical B
+        n0, n1 = sharded.column_slab(N, world, rank)
+        B_slab = torch.from_numpy(harness.hashed_int8(1, 1, np.arange(K), np.arange(n0, n1)))
+        q = (0.02, 0.03, 4.0, 3, -5, 1)
+        C = sharded.mm_int8_sharded(A, B_slab, N, *q, gather=True, solver=_oracle_solver)
+        C_slab = sharded.mm_int8_sharded(A, B_slab, N, *q, gather=False, solver=_oracle_solver)
+        assert tuple(C_slab.shape) == (M, n1 - n0)
+        assert torch.equal(C[:, n0:n1], C_slab)
+        np.save(os.path.join(result_dir, f"c{rank}.npy"), C.numpy())
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("N", [256, 200])
+def test_two_rank_gather_equals_unsharded(tmp_path, oracle, N):
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    mp.spawn(_worker, args=(2, port, N, str(tmp_path)), nprocs=2, join=True)
+    M, K = 24, 96
+    A = harness.hashed_int8(1, 0, np.arange(M), np.arange(K))
+    B = harness.hashed_int8(1, 1, np.arange(K), np.arange(N))
+    want = oracle.mm_int8(A, B, M, N, K, (0.02, 0.03, 4.0, 3, -5, 1))
+    for r in range(2):
+        assert np.array_equal(np.load(tmp_path / f"c{r}.npy"), want)
+
+
+def test_operators_refuse_cpu_tensors():
+    from texo_b200 import ops
+
+    with pytest.raises(ValueError):
+        ops.mm_int8(torch.zeros((2, 2), dtype=torch.int8), torch.zeros((2, 2), dtype=torch.int8),
+                    1.0, 1.0, 1.0, 0, 0, 0)

@@ -27,6 +27,9 @@ _SIGNATURES = {
     "texo_mm_int8_status": (_c_int, []),
     "texo_mm_int4_last_path": (_c_int, []),
     "texo_mm_int4_status": (_c_int, []),
+    "texo_kernel_launches": (ctypes.c_longlong, []),
+    "texo_profile_enable": (None, [_c_int]),
+    "texo_profile_read": (_c_int, [ctypes.POINTER(_c_float), ctypes.POINTER(_c_int)]),
 }
 
 

@@ -68,7 +68,7 @@ def build(force: bool = False, verbose: bool = False) -> dict[str, str]:
             _run([nvcc, *NVCC_FLAGS, "-shared", "-o", target, src], verbose)
         out[op] = target
     combined = lib_path("texo_b200")
-    srcs = [os.path.join(CSRC, f"{op}.cu") for op in OPS]
+    srcs = [os.path.join(CSRC, f"{op}.cu") for op in OPS] + [os.path.join(CSRC, "capi.cu")]
     if force or _stale(combined, srcs + deps):
         objs = []
         for op in OPS:
@@ -76,6 +76,9 @@ def build(force: bool = False, verbose: bool = False) -> dict[str, str]:
             _run([nvcc, *NVCC_FLAGS, f"-Dsolve=texo_{op}_solve", "-c", "-o", obj,
                   os.path.join(CSRC, f"{op}.cu")], verbose)
             objs.append(obj)
+        obj = os.path.join(HERE, "_capi.o")
+        _run([nvcc, *NVCC_FLAGS, "-c", "-o", obj, os.path.join(CSRC, "capi.cu")], verbose)
+        objs.append(obj)
         _run([nvcc, *NVCC_FLAGS, "-shared", "-o", combined, *objs], verbose)
         for obj in objs:
             os.remove(obj)

@@ -9,6 +9,8 @@
 #include <cstdint>
 #include <cuda_runtime.h>
 
+#include "host_common.h"
+
 namespace texo {
 namespace dq {
 
@@ -60,13 +62,16 @@ __global__ void __launch_bounds__(THREADS)
 
 // X, S, Y are device pointers: X, Y [M,N]; S [ceil(M/T), ceil(N/T)], row-major FP32.
 extern "C" void solve(const float* X, const float* S, float* Y, int M, int N, int T) {
+  using namespace texo;
   using namespace texo::dq;
   if (M <= 0 || N <= 0 || T <= 0 || !X || !S || !Y) return;
   const int nt = (N + T - 1) / T;
   const bool vec = N % 4 == 0 && T % 4 == 0 &&
                    ((reinterpret_cast<uintptr_t>(X) | reinterpret_cast<uintptr_t>(Y)) & 15) == 0;
   // gridDim.y is limited to 65535 rows per launch.
+  const int slot = profile_start();
   for (int m0 = 0; m0 < M; m0 += 65535) {
+    ++launch_counter();
     const int rows = M - m0 < 65535 ? M - m0 : 65535;
     if (vec) {
       const int n4 = N / 4;
@@ -78,4 +83,5 @@ extern "C" void solve(const float* X, const float* S, float* Y, int M, int N, in
       rows_scalar_kernel<<<grid, THREADS>>>(X, S, Y, N, T, nt, m0);
     }
   }
+  profile_stop(slot);
 }

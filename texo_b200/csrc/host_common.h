@@ -86,6 +86,47 @@ inline int read_and_clear_status() {
   return code;
 }
 
+// ------------------------------------------------------------ instrumentation
+// Cumulative number of kernels this library has launched (all devices).
+inline long long& launch_counter() {
+  static long long count = 0;
+  return count;
+}
+
+// Optional CUDA-event bracket around the dominant kernel of each call, for roofline
+// reporting: while enabled, up to PROFILE_SLOTS launches are bracketed on the launching
+// stream; reading sums the elapsed times (and synchronises).
+constexpr int PROFILE_SLOTS = 4096;
+struct KernelProfile {
+  bool enabled = false;
+  int used = 0;
+  int created = 0;
+  cudaEvent_t start[PROFILE_SLOTS];
+  cudaEvent_t stop[PROFILE_SLOTS];
+};
+inline KernelProfile& kernel_profile() {
+  static KernelProfile profile;
+  return profile;
+}
+// Returns the slot to pass to profile_stop, or -1 when not profiling.
+inline int profile_start(cudaStream_t stream = 0) {
+  KernelProfile& p = kernel_profile();
+  if (!p.enabled || p.used >= PROFILE_SLOTS) return -1;
+  if (p.used >= p.created) {
+    if (cudaEventCreate(&p.start[p.created]) != cudaSuccess ||
+        cudaEventCreate(&p.stop[p.created]) != cudaSuccess) {
+      cudaGetLastError();
+      return -1;
+    }
+    ++p.created;
+  }
+  cudaEventRecord(p.start[p.used], stream);
+  return p.used++;
+}
+inline void profile_stop(int slot, cudaStream_t stream = 0) {
+  if (slot >= 0) cudaEventRecord(kernel_profile().stop[slot], stream);
+}
+
 using TensorMapEncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                        const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                        const cuuint32_t*, CUtensorMapInterleave,

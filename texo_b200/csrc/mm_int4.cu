@@ -111,7 +111,10 @@ extern "C" void solve(const __half* x, const uint8_t* w_q, const __half* scales,
     return;
   }
   dim3 grid((N + GT - 1) / GT, (M + GT - 1) / GT);
+  const int slot = profile_start();
   generic_kernel<<<grid, G_THREADS>>>(x, w_q, scales, y, M, N, K, group_size);
+  profile_stop(slot);
+  ++launch_counter();
   last_path() = 1;
 }
 

@@ -462,7 +462,10 @@ inline int& last_path() {
 static void launch_generic(const int8_t* A, const int8_t* B, int8_t* C, int M, int N, int K,
                            const Quant& q) {
   dim3 grid((N + GT - 1) / GT, (M + GT - 1) / GT);
+  const int slot = profile_start();
   generic_kernel<<<grid, G_THREADS>>>(A, B, C, M, N, K, q);
+  profile_stop(slot);
+  ++launch_counter();
   last_path() = PATH_GENERIC;
 }
 
@@ -495,13 +498,18 @@ static bool launch_tensor(DeviceCtx& ctx, const int8_t* A, const int8_t* B, int8
   int* row_sum = static_cast<int*>(device_scratch(ctx, row_bytes + size_t(np) * 4));
   if (!row_sum) return false;
   int* col_sum = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(row_sum) + row_bytes);
-  if (q.zb != 0) row_sums_kernel<<<(M + 7) / 8, 256>>>(A, row_sum, M, K);
+  if (q.zb != 0) {
+    row_sums_kernel<<<(M + 7) / 8, 256>>>(A, row_sum, M, K);
+    ++launch_counter();
+  }
   if (q.za != 0) {
     cudaMemsetAsync(col_sum, 0, size_t(np) * 4, 0);
     col_sums_kernel<<<dim3((N + 255) / 256, (K + CS_ROWS - 1) / CS_ROWS), 256>>>(B, col_sum, K, N);
+    ++launch_counter();
   }
   const int grid = std::min(tiles_m * tiles_n, ctx.sm_count);
   const int c_vector_ok = (reinterpret_cast<uintptr_t>(C) & 15) == 0 && N % 16 == 0;
+  const int slot = profile_start();
   if (K <= 33025)
     umma_kernel<false><<<grid, MMA_THREADS, SMEM_BYTES>>>(map_a, map_b, C, row_sum, col_sum, M, N,
                                                          K, q, tiles_m, tiles_n, c_vector_ok,
@@ -510,6 +518,8 @@ static bool launch_tensor(DeviceCtx& ctx, const int8_t* A, const int8_t* B, int8
     umma_kernel<true><<<grid, MMA_THREADS, SMEM_BYTES>>>(map_a, map_b, C, row_sum, col_sum, M, N,
                                                         K, q, tiles_m, tiles_n, c_vector_ok,
                                                         ctx.status);
+  profile_stop(slot);
+  ++launch_counter();
   last_path() = PATH_TENSOR;
   return true;
 }

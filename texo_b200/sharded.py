@@ -59,9 +59,9 @@ def all_gather_columns(C_slab: torch.Tensor, N: int, group=None) -> torch.Tensor
         padded = C_slab.new_zeros((M, w))
         padded[:, : C_slab.shape[1]] = C_slab
         C_slab = padded
-    gathered = C_slab.new_empty((world, M, w))
+    gathered = C_slab.new_empty((world * M, w))  # rank-major concatenation along dim 0
     dist.all_gather_into_tensor(gathered, C_slab.contiguous(), group=group)
-    return gathered.permute(1, 0, 2).reshape(M, world * w)[:, :N].contiguous()
+    return gathered.view(world, M, w).permute(1, 0, 2).reshape(M, world * w)[:, :N].contiguous()
 
 
 def mm_int8_sharded(A: torch.Tensor, B_slab: torch.Tensor, N: int, scale_A: float, scale_B: float,
