@@ -48,6 +48,19 @@ void texo_mm_int8_solve(const int8_t* A, const int8_t* B, int8_t* C, int M, int 
 void texo_mm_int4_solve(const void* x, const uint8_t* w_q, const void* scales, void* y, int M,
                         int N, int K, int group_size);
 
+/* Allocation-free form of texo_mm_int8_solve.  It has no counterpart in the reference (whose
+ * solve always goes through a cudaMalloc'd scratch, src/mm_int8.cu:500-509).  For callers
+ * that may not allocate device memory while running - HBM fully handed to their own pools,
+ * or a loop that cannot take the device-wide stall of cudaMalloc/cudaFree.  The scratch is
+ * a fixed 256 KiB array inside the library image on every GPU that loads it; limits
+ * M <= 32768 and N <= 32768.  Returns 0, or -1 bad arguments, -2 size beyond the limits,
+ * -3 device set-up failed.  Same results as texo_mm_int8_solve.  First call per device does
+ * a one-time set-up (make it outside stream capture); calls share the scratch, so calls
+ * that would overlap on the GPU race. */
+int texo_mm_int8_solve_noalloc(const int8_t* A, const int8_t* B, int8_t* C, int M, int N, int K,
+                               float scale_A, float scale_B, float scale_C, int zero_point_A,
+                               int zero_point_B, int zero_point_C);
+
 /* Tile-scale dequantization.  Replaces `solve` of the reference's
  * src/dequantization.cu:40-43 (tests/dequantization.cpp:4).  X, Y [M,N] fp32,
  * S [ceil(M/T), ceil(N/T)] fp32; Y = X * S[m/T][n/T]. */

@@ -551,3 +551,135 @@ extern "C" void solve(const int8_t* A, const int8_t* B, int8_t* C, int M, int N,
 extern "C" int texo_mm_int8_last_path(void) { return texo::i8::last_path(); }
 extern "C" void texo_mm_int8_force_path(int path) { texo::i8::forced_path() = path; }
 extern "C" int texo_mm_int8_status(void) { return texo::read_and_clear_status(); }
+
+// ------------------------------------------------------- allocation-free entry
+// Some callers must not trigger a device allocation once they are running: a serving
+// process that has already handed all of HBM to its own pools (a late cudaMalloc from a
+// library then simply fails), or a latency-critical loop that cannot accept the
+// device-wide synchronisation cudaMalloc / cudaFree imply.  For them the tensor path is
+// also offered with its scratch (row sums, column sums, status word) in a fixed array that
+// is part of the loaded module instead of the grow-only cudaMalloc'd buffer `solve` uses.
+// The price is a fixed ceiling on M and N and 256 KiB of device memory held by every GPU
+// that loads the library, until the process exits.
+namespace texo {
+namespace i8 {
+
+constexpr int NOALLOC_MAX_M = 32768;  // rows of A / C
+constexpr int NOALLOC_MAX_N = 32768;  // columns of B / C (a multiple of the 256-column tile)
+constexpr int NOALLOC_STATUS_WORDS = 64;
+// Layout: row_sum[NOALLOC_MAX_M] | col_sum[NOALLOC_MAX_N] | status[64].  262,400 bytes.
+static __device__ __align__(256) int noalloc_scratch[NOALLOC_MAX_M + NOALLOC_MAX_N +
+                                                     NOALLOC_STATUS_WORDS];
+
+struct NoAllocDevice {
+  bool ready = false;
+  int* scratch = nullptr;  // device address of noalloc_scratch on this device
+  int sm_count = 0;
+  int cc_major = 0;
+};
+
+// Once per device, with that device current: resolve the device address of the array (the
+// name `noalloc_scratch` in host code is only a handle, never a device pointer) and opt the
+// kernels into their shared-memory size.  Returns nullptr on a CUDA error.
+static NoAllocDevice* noalloc_device() {
+  static NoAllocDevice table[MAX_DEVICES];
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= MAX_DEVICES) return nullptr;
+  NoAllocDevice& d = table[device];
+  if (!d.ready) {
+    void* address = nullptr;
+    cudaError_t err = cudaGetSymbolAddress(&address, noalloc_scratch);
+    if (err != cudaSuccess || !address) {
+      std::fprintf(stderr, "texo_b200: cudaGetSymbolAddress(noalloc_scratch) failed: %s\n",
+                   cudaGetErrorString(err));
+      cudaGetLastError();
+      return nullptr;
+    }
+    d.scratch = static_cast<int*>(address);
+    if (cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess ||
+        cudaDeviceGetAttribute(&d.cc_major, cudaDevAttrComputeCapabilityMajor, device) != cudaSuccess ||
+        cudaFuncSetAttribute(umma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             SMEM_BYTES) != cudaSuccess ||
+        cudaFuncSetAttribute(umma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             SMEM_BYTES) != cudaSuccess) {
+      cudaGetLastError();
+      return nullptr;
+    }
+    d.ready = true;
+  }
+  return &d;
+}
+
+}  // namespace i8
+}  // namespace texo
+
+// Same operation and arguments as `solve`, but guaranteed to allocate nothing: no cudaMalloc,
+// cudaFree or allocating library routine is called, on any call.  Returns 0 on success,
+// -1 for invalid arguments, -2 when M or N exceeds the fixed scratch (M <= 32768,
+// N <= 32768), -3 when the one-time device set-up failed.  Output is bit-identical to
+// `solve`.  The first call on each device performs the set-up above, so make that call
+// outside of any stream capture.  All calls share the one scratch array, which still holds
+// the previous call's sums when the next one starts (the part that must start at zero is
+// cleared on the stream); two calls whose kernels overlap on the GPU (different host
+// threads or streams) would race on it - issue them one after another, as `solve` requires
+// anyway.
+extern "C" int texo_mm_int8_solve_noalloc(const int8_t* A, const int8_t* B, int8_t* C, int M, int N,
+                                          int K, float scale_A, float scale_B, float scale_C,
+                                          int zero_point_A, int zero_point_B, int zero_point_C) {
+  using namespace texo;
+  using namespace texo::i8;
+  if (M <= 0 || N <= 0 || K < 0 || !C || (K > 0 && (!A || !B))) {
+    std::fprintf(stderr, "texo_mm_int8_solve_noalloc: invalid arguments (M=%d N=%d K=%d)\n", M, N, K);
+    return -1;
+  }
+  if (M > NOALLOC_MAX_M || N > NOALLOC_MAX_N) {
+    std::fprintf(stderr,
+                 "texo_mm_int8_solve_noalloc: M=%d N=%d exceeds the fixed scratch (M <= %d, N <= %d); "
+                 "use solve() instead\n", M, N, NOALLOC_MAX_M, NOALLOC_MAX_N);
+    return -2;
+  }
+  NoAllocDevice* dev = noalloc_device();
+  if (!dev) return -3;
+  const Quant q = {scale_A, scale_B, scale_C, zero_point_A, zero_point_B, zero_point_C};
+  if (dev->cc_major >= 10 && tensor_path_ok(A, B, M, N, K)) {
+    CUtensorMap map_a, map_b;
+    if (make_tensor_map_2d(&map_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, A, M, K, K, BM, BK,
+                           CU_TENSOR_MAP_SWIZZLE_128B) &&
+        make_tensor_map_2d(&map_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, B, K, N, N, BK, 128,
+                           CU_TENSOR_MAP_SWIZZLE_128B)) {
+      const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
+      const int np = tiles_n * BN;  // <= NOALLOC_MAX_N because that is a multiple of BN
+      int* row_sum = dev->scratch;
+      int* col_sum = dev->scratch + NOALLOC_MAX_M;
+      int* status = dev->scratch + NOALLOC_MAX_M + NOALLOC_MAX_N;
+      if (q.zb != 0) {
+        row_sums_kernel<<<(M + 7) / 8, 256>>>(A, row_sum, M, K);
+        ++launch_counter();
+      }
+      if (q.za != 0) {
+        // col_sums_kernel accumulates with atomics: its part of the array must start at zero.
+        cudaMemsetAsync(col_sum, 0, size_t(np) * 4, 0);
+        col_sums_kernel<<<dim3((N + 255) / 256, (K + CS_ROWS - 1) / CS_ROWS), 256>>>(B, col_sum, K, N);
+        ++launch_counter();
+      }
+      const int grid = std::min(tiles_m * tiles_n, dev->sm_count);
+      const int c_vector_ok = (reinterpret_cast<uintptr_t>(C) & 15) == 0 && N % 16 == 0;
+      if (K <= 33025)
+        umma_kernel<false><<<grid, MMA_THREADS, SMEM_BYTES>>>(map_a, map_b, C, row_sum, col_sum, M,
+                                                             N, K, q, tiles_m, tiles_n,
+                                                             c_vector_ok, status);
+      else
+        umma_kernel<true><<<grid, MMA_THREADS, SMEM_BYTES>>>(map_a, map_b, C, row_sum, col_sum, M,
+                                                            N, K, q, tiles_m, tiles_n,
+                                                            c_vector_ok, status);
+      ++launch_counter();
+      last_path() = PATH_TENSOR;
+      return 0;
+    }
+  }
+  // Shapes the tensor path does not take need no scratch at all.
+  generic_kernel<<<dim3((N + GT - 1) / GT, (M + GT - 1) / GT), G_THREADS>>>(A, B, C, M, N, K, q);
+  ++launch_counter();
+  last_path() = PATH_GENERIC;
+  return 0;
+}
