@@ -90,6 +90,20 @@ long long texo_kernel_launches(void);
 void texo_profile_enable(int on);
 int texo_profile_read(float* total_ms, int* launches);
 
+/* Tensor-pipe ceiling probe (no counterpart in the reference): issues kind::i8 MMAs back to
+ * back on shared-memory-resident operands, `batches` x 64 instructions per SM (pairs = 0) or
+ * per SM pair (pairs = 1), and returns the achieved tera-ops per second, negative on error.
+ * Used by the benchmark as the box-measured INT8 denominator.  Synchronises. */
+double texo_int8_issue_ceiling_tops(int pairs, int batches);
+/* Same with `per_commit` MMAs between tcgen05.commit signals instead of 64. */
+double texo_int8_issue_rate_tops(int pairs, int batches, int per_commit);
+/* Operand-feed probe: streams the TMA boxes of an INT8 GEMM over A [M,K], B [K,N] (device
+ * pointers, 16-byte aligned rows) through a ring of `stages` (1..7) shared-memory stages
+ * without computing; returns TB/s of operand bytes delivered to the SMs.  mode bit 0 = A
+ * boxes, bit 1 = B boxes.  Synchronises. */
+double texo_int8_feed_rate_tbs(const void* A, const void* B, int M, int N, int K, int stages,
+                               int mode);
+
 #ifdef __cplusplus
 }
 #endif

@@ -108,12 +108,16 @@ def test_tensor_path_matches_oracle(lib, oracle, shape):
         q = list(_random_quant(rng, zero_a, zero_b))
         q[2] = float(np.float32(q[0] * q[1] * 128 * np.sqrt(k) * 127 / 100))
         q = tuple(q)
-        lib.texo_mm_int8_force_path(0)
-        got = run_case(lib, a, b, m, n, k, q)
-        assert lib.texo_mm_int8_last_path() in (2, 3), "aligned shape did not take a tensor-core path"
         want = oracle.mm_int8(a, b, m, n, k, q)
-        assert np.array_equal(got, want), (shape, q)
         assert np.count_nonzero(np.abs(want.astype(np.int32)) < 127) > want.size // 2
+        # automatic choice, then each tensor kernel on its own (2 = one CTA, 4 = CTA pair)
+        for force, allowed in ((0, (2, 3, 4)), (2, (2,)), (4, (4,))):
+            lib.texo_mm_int8_force_path(force)
+            got = run_case(lib, a, b, m, n, k, q)
+            path = lib.texo_mm_int8_last_path()
+            lib.texo_mm_int8_force_path(0)
+            assert path in allowed, f"forced {force}: took path {path}"
+            assert np.array_equal(got, want), (shape, q, force)
     assert lib.texo_mm_int8_status() == 0
 
 
@@ -144,14 +148,14 @@ def test_config1_full_matrix(lib, oracle):
 
 def test_wide_dot_on_tensor_path(lib, oracle):
     """K > 33025: |dot| can exceed int32, the epilogue must use 64-bit correction."""
-    m, n, k = 128, 256, 33040
-    a = np.full((m, k), 127, np.int8)
-    b = np.full((k, n), 127, np.int8)
-    a[::2] = -128
-    q = (1.0, 1.0, 33554432.0, -128, -128, 0)
-    got = run_case(lib, a, b, m, n, k, q)
-    assert lib.texo_mm_int8_last_path() == 2
-    assert np.array_equal(got, oracle.mm_int8(a, b, m, n, k, q))
+    for m, n, k, want_path in ((128, 256, 33040, 2), (384, 256, 33040, 4)):
+        a = np.full((m, k), 127, np.int8)
+        b = np.full((k, n), 127, np.int8)
+        a[::2] = -128
+        q = (1.0, 1.0, 33554432.0, -128, -128, 0)
+        got = run_case(lib, a, b, m, n, k, q)
+        assert lib.texo_mm_int8_last_path() == want_path
+        assert np.array_equal(got, oracle.mm_int8(a, b, m, n, k, q))
 
 
 def test_huge_k_takes_generic_path(lib, oracle):

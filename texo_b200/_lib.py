@@ -31,6 +31,9 @@ _SIGNATURES = {
     "texo_mm_int4_status": (_c_int, []),
     "texo_kernel_launches": (ctypes.c_longlong, []),
     "texo_profile_enable": (None, [_c_int]),
+    "texo_int8_issue_ceiling_tops": (ctypes.c_double, [_c_int, _c_int]),
+    "texo_int8_issue_rate_tops": (ctypes.c_double, [_c_int, _c_int, _c_int]),
+    "texo_int8_feed_rate_tbs": (ctypes.c_double, [_c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int]),
     "texo_profile_read": (_c_int, [ctypes.POINTER(_c_float), ctypes.POINTER(_c_int)]),
 }
 

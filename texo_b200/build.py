@@ -17,6 +17,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OPS = ("mm_int8", "mm_int4", "dequantization")
+EXTRA = ("capi", "peak_probe")  # only in the combined library
 HEADERS = ("ptx.cuh", "host_common.h")
 
 NVCC_FLAGS = [
@@ -68,7 +69,7 @@ def build(force: bool = False, verbose: bool = False) -> dict[str, str]:
             _run([nvcc, *NVCC_FLAGS, "-shared", "-o", target, src], verbose)
         out[op] = target
     combined = lib_path("texo_b200")
-    srcs = [os.path.join(CSRC, f"{op}.cu") for op in OPS] + [os.path.join(CSRC, "capi.cu")]
+    srcs = [os.path.join(CSRC, f"{name}.cu") for name in OPS + EXTRA]
     if force or _stale(combined, srcs + deps):
         objs = []
         for op in OPS:
@@ -76,9 +77,10 @@ def build(force: bool = False, verbose: bool = False) -> dict[str, str]:
             _run([nvcc, *NVCC_FLAGS, f"-Dsolve=texo_{op}_solve", "-c", "-o", obj,
                   os.path.join(CSRC, f"{op}.cu")], verbose)
             objs.append(obj)
-        obj = os.path.join(HERE, "_capi.o")
-        _run([nvcc, *NVCC_FLAGS, "-c", "-o", obj, os.path.join(CSRC, "capi.cu")], verbose)
-        objs.append(obj)
+        for extra in EXTRA:
+            obj = os.path.join(HERE, f"_{extra}.o")
+            _run([nvcc, *NVCC_FLAGS, "-c", "-o", obj, os.path.join(CSRC, f"{extra}.cu")], verbose)
+            objs.append(obj)
         _run([nvcc, *NVCC_FLAGS, "-shared", "-o", combined, *objs], verbose)
         for obj in objs:
             os.remove(obj)

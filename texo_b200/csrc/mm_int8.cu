@@ -443,8 +443,265 @@ __global__ void __launch_bounds__(MMA_THREADS, 1)
   }
 }
 
+// ---------------------------------------------------- tensor path, CTA pairs
+// Same pipeline with the MMA spanning two CTAs of a cluster (cta_group::2): pair tile
+// 256 x 256, each CTA stages only its own 128 rows of A and its own 128 columns of B per
+// k block (32 KiB instead of 48 KiB for the same 128 x 256 outputs per SM), which cuts the
+// L2 -> SM operand stream and the shared-memory operand reads by a third and leaves room for
+// a deeper ring.  The even CTA of the pair issues the MMAs; both CTAs drain their own 128
+// accumulator rows from their own TMEM.
+//
+// Stage release: a tcgen05.commit costs the tensor pipe about as much time as five MMAs of
+// this shape (measured: four MMAs per commit run at 80 % of the rate of eight per commit),
+// so stages are not released one by one.  K blocks are numbered globally across the tiles a
+// pair works through; one commit is issued after every even-numbered block and covers that
+// block and its predecessor.  Commit number c arrives on ring[c % 4]; the producer, before it
+// refills the stage of block g - P_STAGES, waits for the commit that covers that block.  The
+// consumer can never be four commits ahead of what the producer has observed (the ring is
+// seven blocks deep), so the phase parity of ring[c % 4] is unambiguous.
+constexpr int P_STAGES = 7;
+constexpr int P_RING = 4;
+constexpr int P_A_BYTES = BM * BK;   // 128 rows x 128 k-bytes
+constexpr int P_B_BYTES = BK * 128;  // 128 k-rows x 128 n-bytes (this CTA's half of the columns)
+constexpr int P_STAGE_BYTES = P_A_BYTES + P_B_BYTES;
+constexpr int P_SMEM_BYTES = P_STAGES * P_STAGE_BYTES + 1024 + 256;
+constexpr int P_GROUP_M = 8;  // pair-tile rows per raster group
+
+struct PairBarriers {
+  uint64_t full[P_STAGES];  // used in the even CTA: bytes of both CTAs' loads
+  uint64_t ring[P_RING];    // one set per CTA, signalled by the even CTA's MMA commits
+  uint64_t acc_full[2];     // one per CTA, signalled by the even CTA's MMA commits
+  uint64_t acc_empty[2];    // used in the even CTA: epilogue warps of both CTAs arrive
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+__device__ __forceinline__ void pair_tile_coords(int tile, int tiles_m, int tiles_n, int& tm,
+                                                 int& tn) {
+  const int group_tiles = P_GROUP_M * tiles_n;
+  const int first_m = tile / group_tiles * P_GROUP_M;
+  const int group_m = min(tiles_m - first_m, P_GROUP_M);
+  const int in_group = tile % group_tiles;
+  tm = first_m + in_group % group_m;
+  tn = in_group / group_m;
+}
+
+// Drains 128 columns [col0, col0+128) of one accumulator for this thread's row: zero-point
+// identity, FP32 requantisation, 32 int8 per 32-column chunk, vector stores when possible.
+template <bool WIDE>
+__device__ __forceinline__ void drain_half(uint32_t tmem_row_addr, int col0, int n_tile0, int m,
+                                           bool row_ok, int8_t* __restrict__ C,
+                                           const int* __restrict__ row_sum,
+                                           const int* __restrict__ col_sum, int N, int K,
+                                           const Quant& q, int c_vector_ok) {
+  using Wide = typename std::conditional<WIDE, long long, unsigned>::type;
+  using Signed = typename std::conditional<WIDE, long long, int>::type;
+  const float zc = float(q.zc);
+  Wide row_term = Wide(K) * Wide(q.za) * Wide(q.zb);
+  if (row_ok && q.zb != 0) row_term -= Wide(q.zb) * Wide(row_sum[m]);
+  int8_t* c_row = C + size_t(row_ok ? m : 0) * N;
+#pragma unroll 1
+  for (int chunk = 0; chunk < 4; ++chunk) {
+    const int col = col0 + chunk * 32;
+    const int n0 = n_tile0 + col;
+    uint32_t v[32];
+    tmem_ld_32x32(tmem_row_addr + col, v);
+    tmem_ld_wait();
+    if (n0 >= N) continue;  // warp-uniform
+    uint32_t packed[8];
+#pragma unroll
+    for (int g = 0; g < 8; ++g) {
+      int4 cs = make_int4(0, 0, 0, 0);
+      // col_sum is padded to a multiple of the tile width: never out of bounds.
+      if (q.za != 0) cs = __ldg(reinterpret_cast<const int4*>(col_sum + n0 + g * 4));
+      const int csv[4] = {cs.x, cs.y, cs.z, cs.w};
+      uint32_t word = 0;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const Wide dot = Wide(Signed(int(v[g * 4 + e]))) + row_term - Wide(q.za) * Wide(csv[e]);
+        const int r = requantize(float(Signed(dot)), q.sa, q.sb, q.sc, zc);
+        word |= uint32_t(r & 0xff) << (8 * e);
+      }
+      packed[g] = word;
+    }
+    if (row_ok) {
+      if (c_vector_ok && n0 + 32 <= N) {
+        int4* dst = reinterpret_cast<int4*>(c_row + n0);
+        dst[0] = make_int4(packed[0], packed[1], packed[2], packed[3]);
+        dst[1] = make_int4(packed[4], packed[5], packed[6], packed[7]);
+      } else {
+        for (int e = 0; e < 32 && n0 + e < N; ++e)
+          c_row[n0 + e] = int8_t((packed[e / 4] >> (8 * (e % 4))) & 0xff);
+      }
+    }
+  }
+}
+
+template <bool WIDE>
+__global__ void __launch_bounds__(MMA_THREADS, 1)
+    umma_pair_kernel(const __grid_constant__ CUtensorMap map_a,
+                     const __grid_constant__ CUtensorMap map_b, int8_t* __restrict__ C,
+                     const int* __restrict__ row_sum, const int* __restrict__ col_sum, int M, int N,
+                     int K, Quant q, int tiles_m, int tiles_n, int c_vector_ok, int* status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~uintptr_t(1023));
+  PairBarriers* bars = reinterpret_cast<PairBarriers*>(smem + P_STAGES * P_STAGE_BYTES);
+  volatile int* abort_flag = &bars->abort_flag;
+
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  const uint32_t rank = cluster_ctarank();  // 0 = even CTA (issues the MMAs)
+  const int cluster_id = blockIdx.x / 2, num_clusters = gridDim.x / 2;
+  const int num_tiles = tiles_m * tiles_n;
+  const int num_kb = (K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < P_STAGES; ++s) mbar_init(&bars->full[s], 1);
+    for (int r = 0; r < P_RING; ++r) mbar_init(&bars->ring[r], 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&bars->acc_full[b], 1);
+      mbar_init(&bars->acc_empty[b], 2 * EPI_WARPS);
+    }
+    bars->abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&map_a);
+    tma_prefetch_desc(&map_b);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(&bars->tmem_base, TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();  // the partner's barriers exist before anything signals them
+  tc_fence_after_sync();
+  const uint32_t tmem_base = bars->tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    int stage = 0;
+    int g = 0;          // global k-block number of the next load
+    int observed = -1;  // highest commit number seen complete
+    bool ok = true;
+    for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+      int tm, tn;
+      pair_tile_coords(tile, tiles_m, tiles_n, tm, tn);
+      const int m0 = tm * 256 + int(rank) * 128;
+      const int n0 = tn * 256 + int(rank) * 128;
+      for (int kb = 0; kb < num_kb && ok; ++kb, ++g) {
+        if (lane == 0) {
+          if (g >= P_STAGES) {
+            const int c = (g - P_STAGES + 1) >> 1;  // commit covering block g - P_STAGES
+            if (c > observed) {
+              ok = mbar_wait(&bars->ring[c & (P_RING - 1)], (c >> 2) & 1, abort_flag, status,
+                             STATUS_TIMEOUT_EMPTY);
+              observed = c;
+            }
+          }
+          if (ok) {
+            uint8_t* sa = smem + stage * P_STAGE_BYTES;
+            uint8_t* sb = sa + P_A_BYTES;
+            const uint32_t full_even = map_to_cta(smem_u32(&bars->full[stage]), 0);
+            if (rank == 0) mbar_arrive_expect_tx(&bars->full[stage], 2 * P_STAGE_BYTES);
+            tma_load_2d_pair(sa, &map_a, full_even, kb * BK, m0);
+            tma_load_2d_pair(sb, &map_b, full_even, n0, kb * BK);
+          }
+        }
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (++stage == P_STAGES) stage = 0;
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------- MMA issuer (even CTA only)
+    if (rank == 0) {
+      constexpr uint32_t IDESC = umma_idesc(/*D=s32*/ 2, /*A=s8*/ 1, /*B=s8*/ 1, /*A K-major*/ 0,
+                                            /*B N-major*/ 1, 256, 256);
+      int stage = 0;
+      uint32_t phase = 0;
+      int g = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+        if (lane == 0) {
+          ok = mbar_wait_cluster(&bars->acc_empty[acc], acc_phase ^ 1, abort_flag, status,
+                                 STATUS_TIMEOUT_TMEM_EMPTY);
+          tc_fence_after_sync();
+        }
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        const uint32_t tmem_d = tmem_base + acc * ACC_COLS;
+        for (int kb = 0; kb < num_kb && ok; ++kb, ++g) {
+          if (lane == 0) {
+            ok = mbar_wait(&bars->full[stage], phase, abort_flag, status, STATUS_TIMEOUT_FULL);
+            if (ok) {
+              tc_fence_after_sync();
+              const uint32_t sa = smem_u32(smem + stage * P_STAGE_BYTES);
+              const uint32_t sb = sa + P_A_BYTES;
+#pragma unroll
+              for (int j = 0; j < BK / UMMA_K; ++j) {
+                const uint64_t da = smem_desc(sa + j * UMMA_K, 16, 1024, SMEM_SWIZZLE_128B);
+                const uint64_t db = smem_desc(sb + j * UMMA_K * 128, 16, 1024, SMEM_SWIZZLE_128B);
+                umma_i8_pair(tmem_d, da, db, IDESC, (kb | j) != 0);
+              }
+              // releases this block's stage and its predecessor's, in both CTAs
+              if ((g & 1) == 0) umma_commit_pair(&bars->ring[(g >> 1) & (P_RING - 1)], 3);
+            }
+          }
+          ok = __shfl_sync(0xffffffffu, ok, 0);
+          if (++stage == P_STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (lane == 0 && ok) umma_commit_pair(&bars->acc_full[acc], 3);
+        __syncwarp();
+        if (++acc == 2) {
+          acc = 0;
+          acc_phase ^= 1;
+        }
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue
+    const int ew = warp - 2;
+    const int quarter = warp % 4;
+    const int half = ew / 4;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+      int tm, tn;
+      pair_tile_coords(tile, tiles_m, tiles_n, tm, tn);
+      ok = mbar_wait(&bars->acc_full[acc], acc_phase, abort_flag, status, STATUS_TIMEOUT_TMEM_FULL);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const int m = tm * 256 + int(rank) * 128 + quarter * 32 + lane;
+      drain_half<WIDE>(tmem_base + acc * ACC_COLS + (uint32_t(quarter * 32) << 16), half * 128,
+                       tn * 256, m, m < M, C, row_sum, col_sum, N, K, q, c_vector_ok);
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&bars->acc_empty[acc]), 0));
+      if (++acc == 2) {
+        acc = 0;
+        acc_phase ^= 1;
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();  // neither CTA leaves (or frees TMEM) while its partner may still signal it
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc_pair(tmem_base, TMEM_COLS);
+  }
+}
+
 // ------------------------------------------------------------------ dispatch
-enum Path { PATH_AUTO = 0, PATH_GENERIC = 1, PATH_TENSOR = 2, PATH_SKINNY = 3 };
+// PATH_TENSOR = one-CTA tensor kernel, PATH_TENSOR_PAIR = CTA-pair tensor kernel (the
+// automatic choice for M > 128).  Forcing PATH_TENSOR keeps the one-CTA kernel for any M.
+enum Path { PATH_AUTO = 0, PATH_GENERIC = 1, PATH_TENSOR = 2, PATH_SKINNY = 3, PATH_TENSOR_PAIR = 4 };
 
 inline int& forced_path() {
   static int path = [] {
@@ -475,14 +732,46 @@ static bool tensor_path_ok(const int8_t* A, const int8_t* B, int M, int N, int K
          (reinterpret_cast<uintptr_t>(A) & 15) == 0 && (reinterpret_cast<uintptr_t>(B) & 15) == 0;
 }
 
+// Largest number of CTA pairs that can be resident at once (0 if pairs cannot be launched).
+static int max_active_pairs(DeviceCtx& ctx) {
+  static int cached[MAX_DEVICES] = {};
+  static bool known[MAX_DEVICES] = {};
+  if (!known[ctx.device]) {
+    known[ctx.device] = true;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * ctx.sm_count);
+    cfg.blockDim = dim3(MMA_THREADS);
+    cfg.dynamicSmemBytes = P_SMEM_BYTES;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, umma_pair_kernel<false>, &cfg) != cudaSuccess) {
+      cudaGetLastError();
+      n = 0;
+    }
+    cached[ctx.device] = n;
+  }
+  return cached[ctx.device];
+}
+
 static bool launch_tensor(DeviceCtx& ctx, const int8_t* A, const int8_t* B, int8_t* C, int M, int N,
-                          int K, const Quant& q) {
+                          int K, const Quant& q, int force) {
   static bool configured[MAX_DEVICES] = {};
   if (!configured[ctx.device]) {
     cudaFuncSetAttribute(umma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     cudaFuncSetAttribute(umma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    cudaFuncSetAttribute(umma_pair_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         P_SMEM_BYTES);
+    cudaFuncSetAttribute(umma_pair_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         P_SMEM_BYTES);
     configured[ctx.device] = true;
   }
+  // One TMA box shape serves both kernels: A 128 rows x 128 k-bytes, B 128 k-rows x 128 columns.
   CUtensorMap map_a, map_b;
   if (!make_tensor_map_2d(&map_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, A, M, K, K, BM, BK,
                           CU_TENSOR_MAP_SWIZZLE_128B) ||
@@ -491,7 +780,7 @@ static bool launch_tensor(DeviceCtx& ctx, const int8_t* A, const int8_t* B, int8
     note_host_error(STATUS_TENSORMAP_FAILED);
     return false;
   }
-  const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
+  const int tiles_n = (N + BN - 1) / BN;
   const int np = tiles_n * BN;
   // Scratch: row_sum[M] | col_sum[np] (int32).
   const size_t row_bytes = (size_t(M) * 4 + 255) & ~size_t(255);
@@ -507,20 +796,48 @@ static bool launch_tensor(DeviceCtx& ctx, const int8_t* A, const int8_t* B, int8
     col_sums_kernel<<<dim3((N + 255) / 256, (K + CS_ROWS - 1) / CS_ROWS), 256>>>(B, col_sum, K, N);
     ++launch_counter();
   }
-  const int grid = std::min(tiles_m * tiles_n, ctx.sm_count);
   const int c_vector_ok = (reinterpret_cast<uintptr_t>(C) & 15) == 0 && N % 16 == 0;
+  const int pairs = (force == PATH_TENSOR || (force != PATH_TENSOR_PAIR && M <= BM))
+                        ? 0 : max_active_pairs(ctx);
   const int slot = profile_start();
-  if (K <= 33025)
-    umma_kernel<false><<<grid, MMA_THREADS, SMEM_BYTES>>>(map_a, map_b, C, row_sum, col_sum, M, N,
-                                                         K, q, tiles_m, tiles_n, c_vector_ok,
-                                                         ctx.status);
-  else
-    umma_kernel<true><<<grid, MMA_THREADS, SMEM_BYTES>>>(map_a, map_b, C, row_sum, col_sum, M, N,
-                                                        K, q, tiles_m, tiles_n, c_vector_ok,
-                                                        ctx.status);
+  if (pairs > 0) {
+    const int tiles_m = (M + 255) / 256;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * std::min(tiles_m * tiles_n, pairs));
+    cfg.blockDim = dim3(MMA_THREADS);
+    cfg.dynamicSmemBytes = P_SMEM_BYTES;
+    cfg.stream = 0;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    const int* rs = row_sum;
+    const int* cs = col_sum;
+    if (K <= 33025)
+      cudaLaunchKernelEx(&cfg, umma_pair_kernel<false>, map_a, map_b, C, rs, cs, M, N, K, q, tiles_m,
+                         tiles_n, c_vector_ok, ctx.status);
+    else
+      cudaLaunchKernelEx(&cfg, umma_pair_kernel<true>, map_a, map_b, C, rs, cs, M, N, K, q, tiles_m,
+                         tiles_n, c_vector_ok, ctx.status);
+    last_path() = PATH_TENSOR_PAIR;
+  } else {
+    const int tiles_m = (M + BM - 1) / BM;
+    const int grid = std::min(tiles_m * tiles_n, ctx.sm_count);
+    if (K <= 33025)
+      umma_kernel<false><<<grid, MMA_THREADS, SMEM_BYTES>>>(map_a, map_b, C, row_sum, col_sum, M, N,
+                                                           K, q, tiles_m, tiles_n, c_vector_ok,
+                                                           ctx.status);
+    else
+      umma_kernel<true><<<grid, MMA_THREADS, SMEM_BYTES>>>(map_a, map_b, C, row_sum, col_sum, M, N,
+                                                          K, q, tiles_m, tiles_n, c_vector_ok,
+                                                          ctx.status);
+    last_path() = PATH_TENSOR;
+  }
   profile_stop(slot);
   ++launch_counter();
-  last_path() = PATH_TENSOR;
   return true;
 }
 
@@ -542,7 +859,7 @@ extern "C" void solve(const int8_t* A, const int8_t* B, int8_t* C, int M, int N,
   const Quant q = {scale_A, scale_B, scale_C, zero_point_A, zero_point_B, zero_point_C};
   const int force = forced_path();
   if (force != PATH_GENERIC && ctx.cc_major >= 10 && tensor_path_ok(A, B, M, N, K)) {
-    if (launch_tensor(ctx, A, B, C, M, N, K, q)) return;
+    if (launch_tensor(ctx, A, B, C, M, N, K, q, force)) return;
   }
   launch_generic(A, B, C, M, N, K, q);
 }
