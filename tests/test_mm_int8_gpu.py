@@ -111,13 +111,38 @@ def test_tensor_path_matches_oracle(lib, oracle, shape):
         want = oracle.mm_int8(a, b, m, n, k, q)
         assert np.count_nonzero(np.abs(want.astype(np.int32)) < 127) > want.size // 2
         # automatic choice, then each tensor kernel on its own (2 = one CTA, 4 = CTA pair)
-        for force, allowed in ((0, (2, 3, 4)), (2, (2,)), (4, (4,))):
+        for force, allowed in ((0, (2, 3, 4)), (2, (2,)), (4, (4,)), (3, (3,) if m <= 32 else (2, 4))):
             lib.texo_mm_int8_force_path(force)
             got = run_case(lib, a, b, m, n, k, q)
             path = lib.texo_mm_int8_last_path()
             lib.texo_mm_int8_force_path(0)
             assert path in allowed, f"forced {force}: took path {path}"
             assert np.array_equal(got, want), (shape, q, force)
+    assert lib.texo_mm_int8_status() == 0
+
+
+SKINNY_SHAPES = [  # M <= 32 with aligned rows -> skinny (decode) path; whole and split tiles
+    (16, 256, 128), (16, 256, 1024), (1, 16, 16), (16, 512, 256), (7, 272, 144), (32, 1008, 1040),
+    (17, 4096, 4096), (3, 48, 2048), (32, 256, 19200), (16, 3584, 8192),
+]
+
+
+def test_skinny_path_matches_oracle(lib, oracle):
+    """Decode-shaped calls, back to back with changing shapes: the split-K workspace must be
+    left clean by every call (its layout depends on M and N), results bit-exact each time."""
+    rng = np.random.default_rng(11)
+    for rep in range(2):
+        for m, n, k in SKINNY_SHAPES:
+            a = np.clip(np.rint(rng.normal(0, 20, (m, k))), -128, 127).astype(np.int8)
+            b = rng.integers(-128, 128, (k, n), dtype=np.int8)
+            for zero_a, zero_b in ((None, None), (0, 0), (None, 0)):
+                q = list(_random_quant(rng, zero_a, zero_b))
+                q[2] = float(np.float32(q[0] * q[1] * 20 * 74 * np.sqrt(k) / 30))
+                q = tuple(q)
+                got = run_case(lib, a, b, m, n, k, q)
+                assert lib.texo_mm_int8_last_path() == 3, (m, n, k)
+                want = oracle.mm_int8(a, b, m, n, k, q)
+                assert np.array_equal(got, want), ((m, n, k), q, rep)
     assert lib.texo_mm_int8_status() == 0
 
 

@@ -26,6 +26,10 @@ struct DeviceCtx {
   void* scratch = nullptr;
   size_t scratch_bytes = 0;
   int* status = nullptr;  // 64 ints of device memory; word 0 = first error code
+  // Second scratch: split-K workspace of the skinny path.  It is all zero between calls
+  // (the kernel that consumes it cleans up after itself); zeroed when (re)allocated.
+  void* workspace = nullptr;
+  size_t workspace_bytes = 0;
 };
 
 inline int& host_status() {
@@ -72,6 +76,24 @@ inline void* device_scratch(DeviceCtx& ctx, size_t bytes) {
   return ctx.scratch;
 }
 
+// Grow-only, zero-initialised workspace (see DeviceCtx::workspace).
+inline void* device_workspace(DeviceCtx& ctx, size_t bytes) {
+  if (bytes > ctx.workspace_bytes) {
+    if (ctx.workspace) cudaFree(ctx.workspace);
+    ctx.workspace = nullptr;
+    ctx.workspace_bytes = 0;
+    size_t want = (bytes + (size_t(1) << 20) - 1) & ~((size_t(1) << 20) - 1);
+    if (cudaMalloc(&ctx.workspace, want) != cudaSuccess) {
+      cudaGetLastError();
+      std::fprintf(stderr, "texo_b200: workspace allocation of %zu bytes failed\n", want);
+      return nullptr;
+    }
+    cudaMemsetAsync(ctx.workspace, 0, want, 0);
+    ctx.workspace_bytes = want;
+  }
+  return ctx.workspace;
+}
+
 // Reads and clears the status: device word (blocking copy) or, if that is clean, the last
 // host-side error.  0 = no error.  Codes are listed in ptx.cuh.
 inline int read_and_clear_status() {
@@ -79,7 +101,11 @@ inline int read_and_clear_status() {
   int code = 0;
   if (ctx.status) {
     cudaMemcpy(&code, ctx.status, sizeof(int), cudaMemcpyDeviceToHost);
-    if (code != 0) cudaMemset(ctx.status, 0, sizeof(int));
+    if (code != 0) {
+      cudaMemset(ctx.status, 0, sizeof(int));
+      // a kernel that gave up may have left partial sums behind
+      if (ctx.workspace) cudaMemset(ctx.workspace, 0, ctx.workspace_bytes);
+    }
   }
   if (code == 0) code = host_status();
   host_status() = 0;

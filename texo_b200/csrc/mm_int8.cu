@@ -698,6 +698,362 @@ __global__ void __launch_bounds__(MMA_THREADS, 1)
   }
 }
 
+// --------------------------------------------------------------- skinny path
+// M <= 32 (decode): the job is to stream B [K,N] from HBM exactly once.  Operand roles are
+// swapped: a 128-column box of B is the 128-row MMA operand (N-major in memory = M-major
+// operand, again no transposed copy), the activations are the narrow operand.  The
+// activation tile carries one extra all-ones row (written once into every ring slot at
+// kernel start), so column R of the accumulator is colsum(B) for free and B is never read a
+// second time.
+//
+// Schedule (one CTA per SM, T = ceil(N/128) column tiles, G CTAs): every CTA owns
+// P = T / G whole tiles (tile p*G + c, so neighbouring CTAs stream neighbouring columns) and
+// the remaining S = T - P*G tiles are cut stream-K style into equal contiguous ranges of
+// (tile, k block) units, so every SM pulls the same number of bytes.  The shared ranges are
+// processed FIRST: a CTA adds its int32 partials into a zero-initialised workspace with
+// integer reductions (order-independent, hence still bit-exact); whoever arrives last at
+// the tile's counter reads the sums, requantises, and puts workspace and counter back to
+// zero - all while its producer and MMA warps are already streaming the next tile.  The
+// owned tiles come LAST and need no reduction, so the kernel's tail is a plain drain.
+// Nobody ever waits for another CTA.
+constexpr int S_STAGES = 8;
+constexpr int S_W_BYTES = 128 * 128;  // one 128 k-row x 128 column box of B
+constexpr int S_ACT_BYTES = 8192;     // up to 48 rows x 128 B, padded to the swizzle atom
+constexpr int S_STAGE_BYTES = S_W_BYTES + S_ACT_BYTES;
+constexpr int S_ACC_COLS = 64;  // TMEM columns per accumulator (M + ones + padding <= 48)
+constexpr int S_TMEM_COLS = 2 * S_ACC_COLS;  // double buffered
+constexpr int S_SMEM_BYTES = S_STAGES * S_STAGE_BYTES + 1024 + 512;
+constexpr int S_TILE_N = 128;
+constexpr int S_EPI_WARPS = 4;
+constexpr int S_THREADS = 64 + S_EPI_WARPS * 32;
+
+struct SkinnyBarriers {
+  uint64_t full[S_STAGES];
+  uint64_t empty[S_STAGES];
+  uint64_t acc_full[2];
+  uint64_t acc_empty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+  int last_flag;
+  int row_sum[32];
+};
+
+// First unit of CTA `c` when `units` are dealt to `ctas` CTAs as evenly as possible.
+__host__ __device__ __forceinline__ long long skinny_first_unit(long long units, int ctas, int c) {
+  const long long q = units / ctas, r = units % ctas;
+  return c * q + (c < r ? c : r);
+}
+// The CTA that owns unit `u` under the same deal.
+__device__ __forceinline__ int skinny_owner(long long units, int ctas, long long u) {
+  const long long q = units / ctas, r = units % ctas;
+  if (u < r * (q + 1)) return int(u / (q + 1));
+  return int(r + (u - r * (q + 1)) / q);
+}
+
+// The segments (tile, k-block range) of one CTA, in processing order; every warp role walks
+// an identical copy.
+struct SkinnySchedule {
+  int num_kb, ctas, owned, shared_tiles;
+  long long shared_units, su, su_end;
+  int next_owned, cta;
+  __device__ SkinnySchedule(int tiles, int num_kb_, int ctas_, int cta_)
+      : num_kb(num_kb_), ctas(ctas_), cta(cta_) {
+    owned = tiles / ctas;
+    shared_tiles = tiles - owned * ctas;
+    shared_units = (long long)shared_tiles * num_kb;
+    su = skinny_first_unit(shared_units, ctas, cta);
+    su_end = skinny_first_unit(shared_units, ctas, cta + 1);
+    next_owned = 0;
+  }
+  // Returns false when the CTA has no more work.  `shared_index` >= 0 marks a segment
+  // that covers only part of its tile's K range (index of the tile among the shared ones).
+  __device__ bool next(int& tile, int& kb0, int& kb1, int& shared_index) {
+    if (su < su_end) {
+      const int t = int(su / num_kb);
+      const long long seg_end = min(su_end, (long long)(t + 1) * num_kb);
+      kb0 = int(su - (long long)t * num_kb);
+      kb1 = int(seg_end - (long long)t * num_kb);
+      tile = owned * ctas + t;
+      shared_index = (kb0 == 0 && kb1 == num_kb) ? -1 : t;
+      su = seg_end;
+      return true;
+    }
+    if (next_owned < owned) {
+      tile = next_owned * ctas + cta;
+      kb0 = 0;
+      kb1 = num_kb;
+      shared_index = -1;
+      ++next_owned;
+      return true;
+    }
+    return false;
+  }
+  __device__ int contributors(int t) const {
+    return skinny_owner(shared_units, ctas, (long long)(t + 1) * num_kb - 1) -
+           skinny_owner(shared_units, ctas, (long long)t * num_kb) + 1;
+  }
+};
+
+__global__ void __launch_bounds__(S_THREADS, 1)
+    skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_act,
+                  const int8_t* __restrict__ A, int8_t* __restrict__ C, int* __restrict__ workspace,
+                  int* __restrict__ counters, int M, int N, int K, Quant q, int R, int* status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~uintptr_t(1023));
+  SkinnyBarriers* bars = reinterpret_cast<SkinnyBarriers*>(smem + S_STAGES * S_STAGE_BYTES);
+  volatile int* abort_flag = &bars->abort_flag;
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  const int num_kb = (K + BK - 1) / BK;
+  const int tiles = (N + S_TILE_N - 1) / S_TILE_N;
+  const int n_mma = R + 16;  // activation rows + the ones row + zero padding
+
+  // Producer state lives outside the role branch: the first ring fill is issued before the
+  // CTA-wide set-up barrier, so HBM latency overlaps TMEM allocation and the fills below.
+  SkinnySchedule prod_sched(tiles, num_kb, gridDim.x, blockIdx.x);
+  int p_stage = 0, p_tile = 0, p_kb = 0, p_kb1 = 0, p_shared = -1;
+  uint32_t p_phase = 0;
+  bool p_ok = true;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S_STAGES; ++s) {
+      mbar_init(&bars->full[s], 1);
+      mbar_init(&bars->empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&bars->acc_full[b], 1);
+      mbar_init(&bars->acc_empty[b], S_EPI_WARPS);
+    }
+    bars->abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 0) {
+    __syncwarp();
+    for (int i = 0; i < S_STAGES; ++i) {
+      if (p_kb == p_kb1 && !prod_sched.next(p_tile, p_kb, p_kb1, p_shared)) break;
+      if (lane == 0) {
+        uint8_t* sw = smem + p_stage * S_STAGE_BYTES;
+        mbar_arrive_expect_tx(&bars->full[p_stage], S_W_BYTES + R * 128);
+        tma_load_2d(sw, &map_w, &bars->full[p_stage], p_tile * S_TILE_N, p_kb * BK);
+        tma_load_2d(sw + S_W_BYTES, &map_act, &bars->full[p_stage], p_kb * BK, 0);
+      }
+      ++p_kb;
+      if (++p_stage == S_STAGES) {
+        p_stage = 0;
+        p_phase ^= 1;
+      }
+    }
+  } else {
+    // Rows R .. R+15 of every ring slot's activation tile are never touched by TMA (its box
+    // has R rows): row R is all ones when colsum(B) is needed, the rest zero.  A constant
+    // row is the same under any swizzle.
+    for (int i = threadIdx.x - 32; i < S_STAGES * 16 * 8; i += S_THREADS - 32) {
+      const int stage = i / (16 * 8), row = (i / 8) % 16, chunk = i % 8;
+      const uint32_t fill = (row == 0 && q.za != 0) ? 0x01010101u : 0u;
+      uint4* dst = reinterpret_cast<uint4*>(smem + stage * S_STAGE_BYTES + S_W_BYTES +
+                                            (R + row) * 128 + chunk * 16);
+      *dst = make_uint4(fill, fill, fill, fill);
+    }
+    if (threadIdx.x >= 32 && threadIdx.x < 64) bars->row_sum[threadIdx.x - 32] = 0;
+    fence_proxy_async_smem();
+    if (warp == 1) {
+      tmem_alloc(&bars->tmem_base, S_TMEM_COLS);
+      tmem_relinquish();
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = bars->tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------------------------------- TMA producer (rest)
+    while (p_ok) {
+      if (p_kb == p_kb1 && !prod_sched.next(p_tile, p_kb, p_kb1, p_shared)) break;
+      if (lane == 0) {
+        p_ok = mbar_wait(&bars->empty[p_stage], p_phase ^ 1, abort_flag, status, STATUS_TIMEOUT_EMPTY);
+        if (p_ok) {
+          uint8_t* sw = smem + p_stage * S_STAGE_BYTES;
+          mbar_arrive_expect_tx(&bars->full[p_stage], S_W_BYTES + R * 128);
+          tma_load_2d(sw, &map_w, &bars->full[p_stage], p_tile * S_TILE_N, p_kb * BK);
+          tma_load_2d(sw + S_W_BYTES, &map_act, &bars->full[p_stage], p_kb * BK, 0);
+        }
+      }
+      p_ok = __shfl_sync(0xffffffffu, p_ok, 0);
+      ++p_kb;
+      if (++p_stage == S_STAGES) {
+        p_stage = 0;
+        p_phase ^= 1;
+      }
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------------- MMA issuer
+    // D[n, m] += W[n, k] * act[m, k]: the W box is M-major (128 columns contiguous), the
+    // activations K-major.
+    const uint32_t idesc = umma_idesc(/*D=s32*/ 2, /*A=s8*/ 1, /*B=s8*/ 1, /*A M-major*/ 1,
+                                      /*B K-major*/ 0, 128, uint32_t(n_mma));
+    SkinnySchedule sched(tiles, num_kb, gridDim.x, blockIdx.x);
+    int stage = 0;
+    uint32_t phase = 0;
+    int buf = 0;
+    uint32_t buf_phase = 0;
+    bool ok = true;
+    int tile, kb0, kb1, shared_index;
+    while (ok && sched.next(tile, kb0, kb1, shared_index)) {
+      if (lane == 0) {
+        ok = mbar_wait(&bars->acc_empty[buf], buf_phase ^ 1, abort_flag, status,
+                       STATUS_TIMEOUT_TMEM_EMPTY);
+        tc_fence_after_sync();
+      }
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      const uint32_t tmem_d = tmem_base + buf * S_ACC_COLS;
+      for (int kb = kb0; kb < kb1 && ok; ++kb) {
+        if (lane == 0) {
+          ok = mbar_wait(&bars->full[stage], phase, abort_flag, status, STATUS_TIMEOUT_FULL);
+          if (ok) {
+            tc_fence_after_sync();
+            const uint32_t sw = smem_u32(smem + stage * S_STAGE_BYTES);
+            const uint32_t sact = sw + S_W_BYTES;
+#pragma unroll
+            for (int j = 0; j < BK / UMMA_K; ++j) {
+              const uint64_t da = smem_desc(sw + j * UMMA_K * 128, 16, 1024, SMEM_SWIZZLE_128B);
+              const uint64_t db = smem_desc(sact + j * UMMA_K, 16, 1024, SMEM_SWIZZLE_128B);
+              umma_i8(tmem_d, da, db, idesc, (kb == kb0 && j == 0) ? 0u : 1u);
+            }
+            umma_commit(&bars->empty[stage]);
+          }
+        }
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (++stage == S_STAGES) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+      if (lane == 0 && ok) umma_commit(&bars->acc_full[buf]);
+      __syncwarp();
+      if (++buf == 2) {
+        buf = 0;
+        buf_phase ^= 1;
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue
+    const int ew = warp - 2;
+    const int quarter = warp % 4;     // TMEM lanes 32*quarter .. +31
+    const int et = threadIdx.x - 64;  // 0..127 among the epilogue threads
+    // rowsum(A) for the zero-point identity: the activations are tiny, every CTA sums them.
+    if (q.zb != 0) {
+      for (int m = ew; m < M; m += S_EPI_WARPS) {
+        const int4* a = reinterpret_cast<const int4*>(A + size_t(m) * K);
+        int acc = 0;
+        for (int i = lane; i < K / 16; i += 32) {
+          const int4 v = __ldg(a + i);
+          acc = __dp4a(v.x, 0x01010101, acc);
+          acc = __dp4a(v.y, 0x01010101, acc);
+          acc = __dp4a(v.z, 0x01010101, acc);
+          acc = __dp4a(v.w, 0x01010101, acc);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        if (lane == 0) bars->row_sum[m] = acc;
+      }
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    const long long offset = (long long)K * q.za * q.zb;
+    const float zc = float(q.zc);
+    const int ws_rows = M + 1;  // workspace rows per shared tile: M dot rows + the colsum row
+    SkinnySchedule sched(tiles, num_kb, gridDim.x, blockIdx.x);
+    int buf = 0;
+    uint32_t buf_phase = 0;
+    bool ok = true;
+    int tile, kb0, kb1, shared_index;
+    while (sched.next(tile, kb0, kb1, shared_index)) {
+      ok = mbar_wait(&bars->acc_full[buf], buf_phase, abort_flag, status, STATUS_TIMEOUT_TMEM_FULL);
+      // All four epilogue warps go on or give up together (they meet at named barriers below).
+      {
+        uint32_t all_ok;
+        asm volatile(
+            "{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\t"
+            "bar.red.and.pred p, 1, 128, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(all_ok)
+            : "r"(uint32_t(ok))
+            : "memory");
+        ok = all_ok != 0;
+      }
+      if (!ok) break;
+      tc_fence_after_sync();
+      uint32_t v[32];   // accumulator columns 0..31: dot rows m (and colsum at column 16 when R = 16)
+      uint32_t cs_raw;  // colsum(B) for this thread's column
+      {
+        const uint32_t taddr = tmem_base + buf * S_ACC_COLS + (uint32_t(quarter * 32) << 16);
+        tmem_ld_32x32(taddr, v);
+        uint32_t hi[16];
+        if (R == 32) tmem_ld_32x16(taddr + 32, hi);
+        tmem_ld_wait();
+        cs_raw = (R == 32) ? hi[0] : v[16];
+      }
+      // the accumulator is in registers: hand the TMEM buffer back right away
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->acc_empty[buf]);
+      if (++buf == 2) {
+        buf = 0;
+        buf_phase ^= 1;
+      }
+      const int n_local = quarter * 32 + lane;  // column within the tile
+      const int n = tile * S_TILE_N + n_local;
+      bool finalize = shared_index < 0;
+      if (shared_index >= 0) {
+        int* ws = workspace + size_t(shared_index) * ws_rows * S_TILE_N;
+#pragma unroll
+        for (int m = 0; m < 32; ++m)
+          if (m < M) atomicAdd(ws + m * S_TILE_N + n_local, int(v[m]));
+        if (q.za != 0) atomicAdd(ws + M * S_TILE_N + n_local, int(cs_raw));
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (et == 0) {
+          const int contributors = sched.contributors(shared_index);
+          const int before = atomicAdd(&counters[shared_index], 1);
+          bars->last_flag = (before == contributors - 1);
+          if (before == contributors - 1) counters[shared_index] = 0;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        finalize = bars->last_flag != 0;
+        if (finalize) {
+          __threadfence();
+#pragma unroll
+          for (int m = 0; m < 32; ++m)
+            if (m < M) {
+              v[m] = uint32_t(__ldcg(ws + m * S_TILE_N + n_local));
+              __stcg(ws + m * S_TILE_N + n_local, 0);
+            }
+          if (q.za != 0) {
+            cs_raw = uint32_t(__ldcg(ws + M * S_TILE_N + n_local));
+            __stcg(ws + M * S_TILE_N + n_local, 0);
+          }
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");  // last_flag may be rewritten next segment
+      }
+      if (finalize && n < N) {
+        const long long col_term = (long long)q.za * int(cs_raw);
+#pragma unroll
+        for (int m = 0; m < 32; ++m)
+          if (m < M) {
+            const long long dot =
+                (long long)int(v[m]) - (long long)q.zb * bars->row_sum[m] - col_term + offset;
+            C[size_t(m) * N + n] = int8_t(requantize(float(dot), q.sa, q.sb, q.sc, zc));
+          }
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, S_TMEM_COLS);
+  }
+}
+
 // ------------------------------------------------------------------ dispatch
 // PATH_TENSOR = one-CTA tensor kernel, PATH_TENSOR_PAIR = CTA-pair tensor kernel (the
 // automatic choice for M > 128).  Forcing PATH_TENSOR keeps the one-CTA kernel for any M.
@@ -757,6 +1113,45 @@ static int max_active_pairs(DeviceCtx& ctx) {
     cached[ctx.device] = n;
   }
   return cached[ctx.device];
+}
+
+// Skinny (decode) path: M <= 32.
+static bool launch_skinny(DeviceCtx& ctx, const int8_t* A, const int8_t* B, int8_t* C, int M, int N,
+                          int K, const Quant& q) {
+  static bool configured[MAX_DEVICES] = {};
+  if (!configured[ctx.device]) {
+    cudaFuncSetAttribute(skinny_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S_SMEM_BYTES);
+    configured[ctx.device] = true;
+  }
+  const int R = M <= 16 ? 16 : 32;
+  CUtensorMap map_w, map_act;
+  if (!make_tensor_map_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, B, K, N, N, BK, 128,
+                          CU_TENSOR_MAP_SWIZZLE_128B) ||
+      !make_tensor_map_2d(&map_act, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, A, M, K, K, R, BK,
+                          CU_TENSOR_MAP_SWIZZLE_128B)) {
+    note_host_error(STATUS_TENSORMAP_FAILED);
+    return false;
+  }
+  const int tiles = (N + S_TILE_N - 1) / S_TILE_N;
+  const int num_kb = (K + BK - 1) / BK;
+  const long long units = (long long)tiles * num_kb;
+  const int grid = int(std::min<long long>(units, ctx.sm_count));
+  // Tiles that are split between CTAs (see the schedule above) need the workspace:
+  // counters[shared] (padded) | partial sums [shared][M+1][128] int32.
+  const int shared_tiles = tiles - tiles / grid * grid;
+  const size_t counter_bytes = (size_t(shared_tiles) * 4 + 255) & ~size_t(255);
+  const size_t ws_bytes = size_t(shared_tiles) * (M + 1) * S_TILE_N * 4;
+  uint8_t* base = static_cast<uint8_t*>(device_workspace(ctx, counter_bytes + ws_bytes + 256));
+  if (!base) return false;
+  const int slot = profile_start();
+  skinny_kernel<<<grid, S_THREADS, S_SMEM_BYTES>>>(map_w, map_act, A, C,
+                                                  reinterpret_cast<int*>(base + counter_bytes),
+                                                  reinterpret_cast<int*>(base), M, N, K, q, R,
+                                                  ctx.status);
+  profile_stop(slot);
+  ++launch_counter();
+  last_path() = PATH_SKINNY;
+  return true;
 }
 
 static bool launch_tensor(DeviceCtx& ctx, const int8_t* A, const int8_t* B, int8_t* C, int M, int N,
@@ -859,6 +1254,9 @@ extern "C" void solve(const int8_t* A, const int8_t* B, int8_t* C, int M, int N,
   const Quant q = {scale_A, scale_B, scale_C, zero_point_A, zero_point_B, zero_point_C};
   const int force = forced_path();
   if (force != PATH_GENERIC && ctx.cc_major >= 10 && tensor_path_ok(A, B, M, N, K)) {
+    if (M <= 32 && (force == PATH_AUTO || force == PATH_SKINNY) &&
+        launch_skinny(ctx, A, B, C, M, N, K, q))
+      return;
     if (launch_tensor(ctx, A, B, C, M, N, K, q, force)) return;
   }
   launch_generic(A, B, C, M, N, K, q);
