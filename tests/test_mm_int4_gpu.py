@@ -54,13 +54,22 @@ def test_pinned_example(lib):
     assert np.array_equal(got.astype(np.float64), data["y"])
 
 
+def _takes_tensor_path(k, g):
+    return k % 64 == 0 and g in (64, 128)
+
+
 def test_harness_default_cases(lib, oracle):
     cases, seed = harness.mm_int4_harness_shapes()
     for m, n, k, g, sd, zero_x, off in cases:
         x, w, s = oracle.int4_inputs(m, n, k, g, sd, zero_x)
-        got = run_case(lib, x, w, s, m, n, k, g, off)
         want = oracle.mm_int4(x, w, s, m, n, k, g)
-        assert harness.int4_within_tolerance(got, want, ATOL, RTOL), (m, n, k, g)
+        for force in (0, 1):  # automatic dispatch, then the generic kernel alone
+            lib.texo_mm_int4_force_path(force)
+            got = run_case(lib, x, w, s, m, n, k, g, off)
+            path = lib.texo_mm_int4_last_path()
+            lib.texo_mm_int4_force_path(0)
+            assert path == (2 if force == 0 and _takes_tensor_path(k, g) else 1), (m, n, k, g, force)
+            assert harness.int4_within_tolerance(got, want, ATOL, RTOL), (m, n, k, g, force)
     # zero scales: first, middle, last group and an all-zero column (tests/mm_int4.cpp:166-175)
     m, n, k, g = 70, 136, 512, 32
     x, w, s = oracle.int4_inputs(m, n, k, g, seed)
@@ -71,6 +80,20 @@ def test_harness_default_cases(lib, oracle):
             if col == 5 or (col % 3 == 0 and gi in (0, groups // 2, groups - 1)):
                 s[col, gi] = 0
     got = run_case(lib, x, w, s, m, n, k, g)
+    assert harness.int4_within_tolerance(got, oracle.mm_int4(x, w, s, m, n, k, g), ATOL, RTOL)
+    assert lib.texo_mm_int4_status() == 0
+
+
+@pytest.mark.parametrize("shape", [(128, 128, 64, 64), (256, 256, 128, 128), (300, 520, 1024, 64),
+                                   (512, 768, 2048, 128), (257, 255, 1984, 64), (1, 4096, 4096, 128),
+                                   (1000, 3, 192, 64)])
+def test_tensor_path_full_matrix(lib, oracle, shape):
+    """tcgen05 kind::f16 CTA-pair kernel: partial tiles in M and N, K not a multiple of the
+    group pair, both supported group sizes; every output within the reference tolerance."""
+    m, n, k, g = shape
+    x, w, s = oracle.int4_inputs(m, n, k, g, 100 + m)
+    got = run_case(lib, x, w, s, m, n, k, g)
+    assert lib.texo_mm_int4_last_path() == 2
     assert harness.int4_within_tolerance(got, oracle.mm_int4(x, w, s, m, n, k, g), ATOL, RTOL)
     assert lib.texo_mm_int4_status() == 0
 

@@ -28,6 +28,7 @@ _SIGNATURES = {
     "texo_mm_int8_force_path": (None, [_c_int]),
     "texo_mm_int8_status": (_c_int, []),
     "texo_mm_int4_last_path": (_c_int, []),
+    "texo_mm_int4_force_path": (None, [_c_int]),
     "texo_mm_int4_status": (_c_int, []),
     "texo_kernel_launches": (ctypes.c_longlong, []),
     "texo_profile_enable": (None, [_c_int]),

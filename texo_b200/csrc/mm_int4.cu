@@ -90,9 +90,347 @@ __global__ void __launch_bounds__(G_THREADS)
   }
 }
 
+// --------------------------------------------------------------- tensor path
+// CTA-pair tcgen05 kernel, kind::f16 with FP32 accumulation in TMEM.
+//
+// The product is computed transposed, D[n, m] = sum_k W[n,k] x[m,k]: the dequantised
+// weights are the 256-row operand (each CTA of the pair unpacks only its own 128 rows), x is
+// the 256-column operand (each CTA loads its own 128 rows of x by TMA).  With the weights on
+// the accumulator ROWS, the per-group scale s[n, g] is one scalar per TMEM lane, i.e. per
+// epilogue thread: every group's MMAs start a fresh accumulator (two 256-column buffers
+// alternate), the epilogue drains it with tcgen05.ld and does acc += s * partial in FP32
+// registers.  Weights enter the MMA as the exact integers q - 8 in FP16, so the only
+// roundings are the FP32 accumulations - the property the reference kernel relies on
+// (src/mm_int4.cu:31-38), without its s_g / s_{g+1} rescaling trick.
+//
+// Per CTA: warp 0 TMA (x tile + packed nibbles), warp 1 MMA issue (even CTA), warps 2-3
+// unpack nibbles -> FP16 into the swizzled operand tile, warps 4-11 epilogue.
+constexpr int T_BK = 64;  // k per stage: 64 halves = one 128-byte swizzle row
+constexpr int T_STAGES = 6;
+constexpr int T_X_BYTES = 128 * 128;   // this CTA's 128 rows of x, 64 halves each
+constexpr int T_W_BYTES = 128 * 128;   // this CTA's 128 weight rows, unpacked to FP16
+constexpr int T_RAW_BYTES = 128 * 32;  // the same rows as packed nibbles
+constexpr int T_STAGE_BYTES = T_X_BYTES + T_W_BYTES + T_RAW_BYTES;
+constexpr int T_RING = 8;  // group-completion barriers (see the commit numbering below)
+constexpr int T_CONV_WARPS = 2;
+constexpr int T_EPI_WARPS = 8;
+constexpr int T_THREADS = (2 + T_CONV_WARPS + T_EPI_WARPS) * 32;
+constexpr int T_SMEM_BYTES = T_STAGES * T_STAGE_BYTES + 1024 + 512;
+constexpr int T_GROUP_M = 8;
+
+struct TensorBarriers {
+  uint64_t x_full[T_STAGES];     // even CTA: bytes of both CTAs' x loads
+  uint64_t raw_full[T_STAGES];   // per CTA: packed nibbles landed
+  uint64_t conv_full[T_STAGES];  // even CTA: unpack warps of both CTAs arrived
+  uint64_t group_done[T_RING];   // per CTA: MMAs of a scale group complete
+  uint64_t acc_empty[2];         // even CTA: epilogue warps of both CTAs arrived
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+// Four packed bytes (eight nibbles, k ascending: high nibble first) -> eight FP16 values
+// q - 8.  0x6400 is 1024.0: OR-ing a nibble into mantissa bits 0-3 gives 1024 + v, into bits
+// 4-7 gives 1024 + 16 v; one HFMA2 per byte removes the offsets exactly.
+__device__ __forceinline__ uint4 unpack8(uint32_t word) {
+  const __half2 mul = __halves2half2(__float2half(0.0625f), __float2half(1.0f));
+  const __half2 add = __halves2half2(__float2half(-72.0f), __float2half(-1032.0f));
+  uint32_t out[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    // bytes [b, 0x64, b, 0x64]: low half 0x64:(b & 0xf0), high half 0x64:(b & 0x0f)
+    uint32_t pair = __byte_perm(word, 0x64646464u, 0x4040u + 0x0101u * i) & 0xff0ffff0u;
+    const __half2 v = __hfma2(*reinterpret_cast<const __half2*>(&pair), mul, add);
+    out[i] = *reinterpret_cast<const uint32_t*>(&v);
+  }
+  return make_uint4(out[0], out[1], out[2], out[3]);
+}
+
+__device__ __forceinline__ void w4_tile_coords(int tile, int tiles_n, int tiles_m, int& tn, int& tm) {
+  // groups of T_GROUP_M weight-row tiles walked along m, so that a wave shares x rows in L2
+  const int group_tiles = T_GROUP_M * tiles_m;
+  const int first_n = tile / group_tiles * T_GROUP_M;
+  const int group_n = min(tiles_n - first_n, T_GROUP_M);
+  const int in_group = tile % group_tiles;
+  tn = first_n + in_group % group_n;
+  tm = in_group / group_n;
+}
+
+__global__ void __launch_bounds__(T_THREADS, 1)
+    tensor_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_raw,
+                  const __half* __restrict__ scales, __half* __restrict__ y, int M, int N, int K,
+                  int G, int tiles_n, int tiles_m, int* status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~uintptr_t(1023));
+  TensorBarriers* bars = reinterpret_cast<TensorBarriers*>(smem + T_STAGES * T_STAGE_BYTES);
+  volatile int* abort_flag = &bars->abort_flag;
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  const uint32_t rank = cluster_ctarank();
+  const int cluster_id = blockIdx.x / 2, num_clusters = gridDim.x / 2;
+  const int num_tiles = tiles_n * tiles_m;
+  const int num_kb = K / T_BK;
+  const int kb_per_group = G / T_BK;  // 1 or 2
+  const int groups = K / G;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < T_STAGES; ++s) {
+      mbar_init(&bars->x_full[s], 1);
+      mbar_init(&bars->raw_full[s], 1);
+      mbar_init(&bars->conv_full[s], 2 * T_CONV_WARPS);
+    }
+    for (int r = 0; r < T_RING; ++r) mbar_init(&bars->group_done[r], 1);
+    for (int b = 0; b < 2; ++b) mbar_init(&bars->acc_empty[b], 2 * T_EPI_WARPS);
+    bars->abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&map_x);
+    tma_prefetch_desc(&map_raw);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(&bars->tmem_base, 512);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = bars->tmem_base;
+
+  // Commit numbering: scale groups are numbered globally over the tiles this pair processes;
+  // the MMA warp issues one tcgen05.commit per group, number c, onto group_done[c % T_RING].
+  // It tells the epilogue that accumulator c % 2 is complete and the producer that the
+  // group's stages may be refilled.  Nobody lags T_RING commits behind, so parities are safe.
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    int stage = 0;
+    int kbg = 0;        // global k-block number of the next load
+    int observed = -1;  // highest commit seen
+    bool ok = true;
+    for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+      int tn, tm;
+      w4_tile_coords(tile, tiles_n, tiles_m, tn, tm);
+      const int n0 = tn * 256 + int(rank) * 128;
+      const int m0 = tm * 256 + int(rank) * 128;
+      for (int kb = 0; kb < num_kb && ok; ++kb, ++kbg) {
+        if (lane == 0) {
+          if (kbg >= T_STAGES) {
+            const int c = (kbg - T_STAGES) / kb_per_group;
+            if (c > observed) {
+              ok = mbar_wait(&bars->group_done[c % T_RING], (c / T_RING) & 1, abort_flag, status,
+                             STATUS_TIMEOUT_EMPTY);
+              observed = c;
+            }
+          }
+          if (ok) {
+            uint8_t* sx = smem + stage * T_STAGE_BYTES;
+            uint8_t* sraw = sx + T_X_BYTES + T_W_BYTES;
+            const uint32_t x_full_even = map_to_cta(smem_u32(&bars->x_full[stage]), 0);
+            if (rank == 0) mbar_arrive_expect_tx(&bars->x_full[stage], 2 * T_X_BYTES);
+            tma_load_2d_pair(sx, &map_x, x_full_even, kb * T_BK, m0);
+            mbar_arrive_expect_tx(&bars->raw_full[stage], T_RAW_BYTES);
+            tma_load_2d(sraw, &map_raw, &bars->raw_full[stage], kb * (T_BK / 2), n0);
+          }
+        }
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (++stage == T_STAGES) stage = 0;
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------- MMA issuer (even CTA only)
+    if (rank == 0) {
+      constexpr uint32_t IDESC = umma_idesc(/*D=f32*/ 1, /*A=f16*/ 0, /*B=f16*/ 0, 0, 0, 256, 256);
+      int stage = 0;
+      uint32_t phase = 0;
+      int gc = 0;  // global group (= commit) number
+      bool ok = true;
+      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+        for (int g = 0; g < groups && ok; ++g, ++gc) {
+          const int buf = gc & 1;
+          if (lane == 0) {
+            ok = mbar_wait_cluster(&bars->acc_empty[buf], ((gc >> 1) & 1) ^ 1, abort_flag, status,
+                                   STATUS_TIMEOUT_TMEM_EMPTY);
+            tc_fence_after_sync();
+          }
+          ok = __shfl_sync(0xffffffffu, ok, 0);
+          const uint32_t tmem_d = tmem_base + buf * 256;
+          for (int kk = 0; kk < kb_per_group && ok; ++kk) {
+            if (lane == 0) {
+              ok = mbar_wait(&bars->x_full[stage], phase, abort_flag, status, STATUS_TIMEOUT_FULL) &&
+                   mbar_wait_cluster(&bars->conv_full[stage], phase, abort_flag, status,
+                                     STATUS_TIMEOUT_FULL);
+              if (ok) {
+                tc_fence_after_sync();
+                const uint32_t sx = smem_u32(smem + stage * T_STAGE_BYTES);
+                const uint32_t sw = sx + T_X_BYTES;
+#pragma unroll
+                for (int j = 0; j < T_BK / 16; ++j) {
+                  const uint64_t da = smem_desc(sw + j * 32, 16, 1024, SMEM_SWIZZLE_128B);
+                  const uint64_t db = smem_desc(sx + j * 32, 16, 1024, SMEM_SWIZZLE_128B);
+                  umma_f16_pair(tmem_d, da, db, IDESC, (kk | j) != 0);
+                }
+              }
+            }
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (++stage == T_STAGES) {
+              stage = 0;
+              phase ^= 1;
+            }
+          }
+          if (lane == 0 && ok) umma_commit_pair(&bars->group_done[gc % T_RING], 3);
+          __syncwarp();
+        }
+      }
+    }
+  } else if (warp < 2 + T_CONV_WARPS) {
+    // ------------------------------------------------------- nibble unpacking
+    const int cw = warp - 2;
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+      for (int kb = 0; kb < num_kb && ok; ++kb) {
+        ok = mbar_wait(&bars->raw_full[stage], phase, abort_flag, status, STATUS_TIMEOUT_FULL);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        uint8_t* sw = smem + stage * T_STAGE_BYTES + T_X_BYTES;
+        const uint8_t* sraw = sw + T_W_BYTES;
+#pragma unroll
+        for (int i = 0; i < 128 / (T_CONV_WARPS * 32); ++i) {
+          const int row = cw * (128 / T_CONV_WARPS) + i * 32 + lane;
+          const uint4 lo = *reinterpret_cast<const uint4*>(sraw + row * 32);
+          const uint4 hi = *reinterpret_cast<const uint4*>(sraw + row * 32 + 16);
+          const uint32_t words[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+#pragma unroll
+          for (int c = 0; c < 8; ++c)  // chunk c = k 8c .. 8c+7, stored 128-byte swizzled
+            *reinterpret_cast<uint4*>(sw + row * 128 + ((c ^ (row & 7)) << 4)) = unpack8(words[c]);
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&bars->conv_full[stage]), 0));
+        if (++stage == T_STAGES) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue
+    const int ew = warp - (2 + T_CONV_WARPS);
+    const int quarter = warp % 4;  // TMEM lanes 32*quarter .. +31
+    const int half = ew / 4;       // which 128 of the 256 accumulator columns (m)
+    int gc = 0;
+    bool ok = true;
+    for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+      int tn, tm;
+      w4_tile_coords(tile, tiles_n, tiles_m, tn, tm);
+      const int n = tn * 256 + int(rank) * 128 + quarter * 32 + lane;
+      const bool n_ok = n < N;
+      const __half* s_row = scales + size_t(n_ok ? n : 0) * groups;
+      float acc[128];
+#pragma unroll
+      for (int j = 0; j < 128; ++j) acc[j] = 0.f;
+      float s_next = n_ok ? __half2float(s_row[0]) : 0.f;
+      for (int g = 0; g < groups && ok; ++g, ++gc) {
+        const float s = s_next;
+        if (g + 1 < groups && n_ok) s_next = __half2float(s_row[g + 1]);
+        ok = mbar_wait(&bars->group_done[gc % T_RING], (gc / T_RING) & 1, abort_flag, status,
+                       STATUS_TIMEOUT_TMEM_FULL);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint32_t taddr = tmem_base + (gc & 1) * 256 + half * 128 + (uint32_t(quarter * 32) << 16);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32(taddr + c * 32, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) acc[c * 32 + j] = fmaf(s, __uint_as_float(v[j]), acc[c * 32 + j]);
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&bars->acc_empty[gc & 1]), 0));
+      }
+      if (ok && n_ok) {
+        const int m_base = tm * 256 + half * 128;
+#pragma unroll
+        for (int j = 0; j < 128; ++j) {
+          const int m = m_base + j;
+          if (m < M) y[size_t(m) * N + n] = __float2half_rn(acc[j]);
+        }
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc_pair(tmem_base, 512);
+  }
+}
+
 inline int& last_path() {
   static int path = 0;
   return path;
+}
+
+inline int& forced_path() {
+  static int path = 0;
+  return path;
+}
+
+// TMA needs 16-byte aligned rows: x rows of K halves, packed rows of K/2 bytes; the kernel
+// works in 64-wide k blocks and whole scale groups per accumulator.
+static bool tensor_path_ok(const __half* x, const uint8_t* w_q, int K, int G) {
+  return K > 0 && K % T_BK == 0 && (G == 64 || G == 128) &&
+         (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(w_q) & 15) == 0;
+}
+
+static bool launch_tensor(DeviceCtx& ctx, const __half* x, const uint8_t* w_q, const __half* scales,
+                          __half* y, int M, int N, int K, int G) {
+  static bool configured[MAX_DEVICES] = {};
+  static int pairs[MAX_DEVICES] = {};
+  cudaLaunchConfig_t cfg = {};
+  cfg.blockDim = dim3(T_THREADS);
+  cfg.dynamicSmemBytes = T_SMEM_BYTES;
+  cfg.stream = 0;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = 2;
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  if (!configured[ctx.device]) {
+    configured[ctx.device] = true;
+    cudaFuncSetAttribute(tensor_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T_SMEM_BYTES);
+    cfg.gridDim = dim3(2 * ctx.sm_count);
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, tensor_kernel, &cfg) != cudaSuccess) {
+      cudaGetLastError();
+      n = 0;
+    }
+    pairs[ctx.device] = n;
+  }
+  if (pairs[ctx.device] <= 0) return false;
+  CUtensorMap map_x, map_raw;
+  if (!make_tensor_map_2d(&map_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, x, M, K, size_t(K) * 2, 128,
+                          T_BK, CU_TENSOR_MAP_SWIZZLE_128B) ||
+      !make_tensor_map_2d(&map_raw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w_q, N, K / 2, K / 2, 128,
+                          T_BK / 2, CU_TENSOR_MAP_SWIZZLE_NONE)) {
+    note_host_error(STATUS_TENSORMAP_FAILED);
+    return false;
+  }
+  const int tiles_n = (N + 255) / 256, tiles_m = (M + 255) / 256;
+  cfg.gridDim = dim3(2 * std::min(tiles_n * tiles_m, pairs[ctx.device]));
+  const int slot = profile_start();
+  cudaLaunchKernelEx(&cfg, tensor_kernel, map_x, map_raw, scales, y, M, N, K, G, tiles_n, tiles_m,
+                     ctx.status);
+  profile_stop(slot);
+  ++launch_counter();
+  last_path() = 2;
+  return true;
 }
 
 }  // namespace w4
@@ -110,6 +448,10 @@ extern "C" void solve(const __half* x, const uint8_t* w_q, const __half* scales,
     note_host_error(STATUS_BAD_ARGUMENT);
     return;
   }
+  DeviceCtx& ctx = device_ctx();
+  if (forced_path() != 1 && ctx.cc_major >= 10 && tensor_path_ok(x, w_q, K, group_size) &&
+      launch_tensor(ctx, x, w_q, scales, y, M, N, K, group_size))
+    return;
   dim3 grid((N + GT - 1) / GT, (M + GT - 1) / GT);
   const int slot = profile_start();
   generic_kernel<<<grid, G_THREADS>>>(x, w_q, scales, y, M, N, K, group_size);
@@ -119,4 +461,5 @@ extern "C" void solve(const __half* x, const uint8_t* w_q, const __half* scales,
 }
 
 extern "C" int texo_mm_int4_last_path(void) { return texo::w4::last_path(); }
+extern "C" void texo_mm_int4_force_path(int path) { texo::w4::forced_path() = path; }
 extern "C" int texo_mm_int4_status(void) { return texo::read_and_clear_status(); }
