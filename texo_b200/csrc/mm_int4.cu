@@ -103,8 +103,8 @@ __global__ void __launch_bounds__(G_THREADS)
 // roundings are the FP32 accumulations - the property the reference kernel relies on
 // (src/mm_int4.cu:31-38), without its s_g / s_{g+1} rescaling trick.
 //
-// Per CTA: warp 0 TMA (x tile + packed nibbles), warp 1 MMA issue (even CTA), warps 2-3
-// unpack nibbles -> FP16 into the swizzled operand tile, warps 4-11 epilogue.
+// Per CTA: warp 0 TMA (x tile + packed nibbles), warp 1 MMA issue (even CTA), warps 4-7
+// unpack nibbles -> FP16 into the swizzled operand tile, warps 8-15 epilogue.
 constexpr int T_BK = 64;  // k per stage: 64 halves = one 128-byte swizzle row
 constexpr int T_STAGES = 6;
 constexpr int T_X_BYTES = 128 * 128;   // this CTA's 128 rows of x, 64 halves each
@@ -112,9 +112,15 @@ constexpr int T_W_BYTES = 128 * 128;   // this CTA's 128 weight rows, unpacked t
 constexpr int T_RAW_BYTES = 128 * 32;  // the same rows as packed nibbles
 constexpr int T_STAGE_BYTES = T_X_BYTES + T_W_BYTES + T_RAW_BYTES;
 constexpr int T_RING = 8;  // group-completion barriers (see the commit numbering below)
-constexpr int T_CONV_WARPS = 2;
+// 16 warps in four warpgroups: {TMA, MMA, 2 idle} | 4 unpack warps | 8 epilogue warps.  The
+// kernel starts with 128 registers per thread; the first two groups hand registers back
+// (setmaxnreg) so that each epilogue thread can keep its 128 FP32 accumulators live.
+constexpr int T_CONV_WARPS = 4;
+constexpr int T_CONV_WARP0 = 4;
 constexpr int T_EPI_WARPS = 8;
-constexpr int T_THREADS = (2 + T_CONV_WARPS + T_EPI_WARPS) * 32;
+constexpr int T_EPI_WARP0 = 8;
+constexpr int T_THREADS = 512;
+constexpr int T_REGS_CONTROL = 56, T_REGS_UNPACK = 72, T_REGS_EPILOGUE = 192;
 constexpr int T_SMEM_BYTES = T_STAGES * T_STAGE_BYTES + 1024 + 512;
 constexpr int T_GROUP_M = 8;
 
@@ -199,7 +205,9 @@ __global__ void __launch_bounds__(T_THREADS, 1)
   // the MMA warp issues one tcgen05.commit per group, number c, onto group_done[c % T_RING].
   // It tells the epilogue that accumulator c % 2 is complete and the producer that the
   // group's stages may be refilled.  Nobody lags T_RING commits behind, so parities are safe.
-  if (warp == 0) {
+  if (warp < T_CONV_WARP0) {
+   asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(T_REGS_CONTROL));
+   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     int stage = 0;
     int kbg = 0;        // global k-block number of the next load
@@ -280,9 +288,11 @@ __global__ void __launch_bounds__(T_THREADS, 1)
         }
       }
     }
-  } else if (warp < 2 + T_CONV_WARPS) {
+   }
+  } else if (warp < T_EPI_WARP0) {
     // ------------------------------------------------------- nibble unpacking
-    const int cw = warp - 2;
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(T_REGS_UNPACK));
+    const int cw = warp - T_CONV_WARP0;
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
@@ -305,7 +315,7 @@ __global__ void __launch_bounds__(T_THREADS, 1)
         }
         fence_proxy_async_smem();
         __syncwarp();
-        if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&bars->conv_full[stage]), 0));
+        if (lane == 0) mbar_arrive_remote(map_to_cta(smem_u32(&bars->conv_full[stage]), 0));
         if (++stage == T_STAGES) {
           stage = 0;
           phase ^= 1;
@@ -314,7 +324,8 @@ __global__ void __launch_bounds__(T_THREADS, 1)
     }
   } else {
     // ---------------------------------------------------------------- epilogue
-    const int ew = warp - (2 + T_CONV_WARPS);
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(T_REGS_EPILOGUE));
+    const int ew = warp - T_EPI_WARP0;
     const int quarter = warp % 4;  // TMEM lanes 32*quarter .. +31
     const int half = ew / 4;       // which 128 of the 256 accumulator columns (m)
     int gc = 0;
@@ -338,17 +349,27 @@ __global__ void __launch_bounds__(T_THREADS, 1)
         if (!ok) break;
         tc_fence_after_sync();
         const uint32_t taddr = tmem_base + (gc & 1) * 256 + half * 128 + (uint32_t(quarter * 32) << 16);
+        // Eight 16-column chunks, the load of chunk c+1 in flight while chunk c is folded in;
+        // the buffer goes back to the MMA warp as soon as the last chunk is in registers.
+        uint32_t va[16], vb[16];
+        tmem_ld_32x16(taddr, va);
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t v[32];
-          tmem_ld_32x32(taddr + c * 32, v);
+        for (int c = 0; c < 8; ++c) {
           tmem_ld_wait();
+          if (c + 1 < 8) {
+            if (c & 1)
+              tmem_ld_32x16(taddr + (c + 1) * 16, va);
+            else
+              tmem_ld_32x16(taddr + (c + 1) * 16, vb);
+          } else {
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_remote(map_to_cta(smem_u32(&bars->acc_empty[gc & 1]), 0));
+          }
 #pragma unroll
-          for (int j = 0; j < 32; ++j) acc[c * 32 + j] = fmaf(s, __uint_as_float(v[j]), acc[c * 32 + j]);
+          for (int j = 0; j < 16; ++j)
+            acc[c * 16 + j] = fmaf(s, __uint_as_float((c & 1) ? vb[j] : va[j]), acc[c * 16 + j]);
         }
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&bars->acc_empty[gc & 1]), 0));
       }
       if (ok && n_ok) {
         const int m_base = tm * 256 + half * 128;
@@ -379,6 +400,7 @@ inline int& forced_path() {
   static int path = 0;
   return path;
 }
+
 
 // TMA needs 16-byte aligned rows: x rows of K halves, packed rows of K/2 bytes; the kernel
 // works in 64-wide k blocks and whole scale groups per accumulator.
