@@ -159,58 +159,134 @@ __global__ void __launch_bounds__(G_THREADS)
 }
 
 // ------------------------------------------------------------ sums pre-pass
-// row_sum[m] = sum_k A[m,k]; one warp per row, 16-byte loads (A 16-byte aligned, K % 16 == 0).
-__global__ void __launch_bounds__(256)
-    row_sums_kernel(const int8_t* __restrict__ A, int* __restrict__ row_sum, int M, int K) {
-  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
-  const int m = blockIdx.x * 8 + warp;
-  if (m >= M) return;
-  const int4* a = reinterpret_cast<const int4*>(A + size_t(m) * K);
-  int acc = 0;
-  for (int i = lane; i < K / 16; i += 32) {
-    const int4 v = __ldg(a + i);
-    acc = __dp4a(v.x, 0x01010101, acc);
-    acc = __dp4a(v.y, 0x01010101, acc);
-    acc = __dp4a(v.z, 0x01010101, acc);
-    acc = __dp4a(v.w, 0x01010101, acc);
-  }
+// row_sum[m] = sum_k A[m,k] and col_sum[n] = sum_k B[k,n] for the zero-point identity, in ONE
+// launch with plain stores (no atomics, nothing to clear beforehand).  One persistent block
+// per SM walks a list of work items: first the column items (64 columns of B over the whole K
+// range: 4 threads across x 128 k lanes, eight independent 16-byte loads in flight per
+// thread, per-byte dp4a selectors, shuffles + a shared-memory tree over the k lanes), then the
+// row items (16 rows of A, one warp per row).  The block is small enough (512 threads, 4 KiB
+// of shared memory) to share an SM with a CTA of the tensor kernel: it signals
+// launch_dependents at once, so a tensor kernel launched behind it with programmatic stream
+// serialisation starts immediately and its first tile's MMAs run while the sums are still
+// being computed; the tensor kernel's epilogue waits (griddepcontrol.wait) for this grid
+// before it reads them.  Needs 16-byte aligned A / B and K % 16 == N % 16 == 0 (the tensor
+// path's own preconditions).
+constexpr int SUM_THREADS = 512;
+constexpr int SUM_COLS = 64;
+constexpr int SUM_TX = SUM_COLS / 16;             // threads across the columns
+constexpr int SUM_KLANES = SUM_THREADS / SUM_TX;  // k lanes per block
+constexpr int SUM_ROWS = SUM_THREADS / 32;        // rows per row item
+
+__device__ __forceinline__ void add_bytes(int (&acc)[16], const int4& v) {
+  const int w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-  if (lane == 0) row_sum[m] = acc;
+  for (int i = 0; i < 4; ++i) {
+    acc[i * 4 + 0] = __dp4a(w[i], 0x00000001, acc[i * 4 + 0]);
+    acc[i * 4 + 1] = __dp4a(w[i], 0x00000100, acc[i * 4 + 1]);
+    acc[i * 4 + 2] = __dp4a(w[i], 0x00010000, acc[i * 4 + 2]);
+    acc[i * 4 + 3] = __dp4a(w[i], 0x01000000, acc[i * 4 + 3]);
+  }
 }
 
-// col_sum[n] += sum over a 128-row K chunk of B[k,n]; 256 columns per block, 16 columns per
-// thread (B 16-byte aligned, N % 16 == 0).  col_sum must be zero on entry.
-constexpr int CS_ROWS = 128;
-__global__ void __launch_bounds__(256)
-    col_sums_kernel(const int8_t* __restrict__ B, int* __restrict__ col_sum, int K, int N) {
-  __shared__ int part[16][256 + 1];
-  const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
-  const int n = blockIdx.x * 256 + tx * 16;
-  const int k0 = blockIdx.y * CS_ROWS, k1 = min(K, k0 + CS_ROWS);
-  int acc[16] = {};
-  if (n < N) {
-    for (int k = k0 + ty; k < k1; k += 16) {
-      const int4 v = __ldg(reinterpret_cast<const int4*>(B + size_t(k) * N + n));
-      const int w[4] = {v.x, v.y, v.z, v.w};
+__global__ void __launch_bounds__(SUM_THREADS)
+    sums_kernel(const int8_t* __restrict__ A, const int8_t* __restrict__ B,
+                int* __restrict__ row_sum, int* __restrict__ col_sum, int M, int N, int K,
+                int col_items, int row_items) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  __shared__ int part[SUM_THREADS / 32][SUM_COLS + 1];
+  for (int item = blockIdx.x; item < col_items + row_items; item += gridDim.x) {
+    if (item < col_items) {
+      const int tx = threadIdx.x % SUM_TX, ty = threadIdx.x / SUM_TX;
+      const int n = item * SUM_COLS + tx * 16;
+      int acc[16] = {};
+      if (n < N) {
+        const int8_t* col = B + n;
+        int k = ty;
+        for (; k + 7 * SUM_KLANES < K; k += 8 * SUM_KLANES) {
+          int4 v[8];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        acc[i * 4 + 0] = __dp4a(w[i], 0x00000001, acc[i * 4 + 0]);
-        acc[i * 4 + 1] = __dp4a(w[i], 0x00000100, acc[i * 4 + 1]);
-        acc[i * 4 + 2] = __dp4a(w[i], 0x00010000, acc[i * 4 + 2]);
-        acc[i * 4 + 3] = __dp4a(w[i], 0x01000000, acc[i * 4 + 3]);
+          for (int u = 0; u < 8; ++u)
+            v[u] = __ldg(reinterpret_cast<const int4*>(col + size_t(k + u * SUM_KLANES) * N));
+#pragma unroll
+          for (int u = 0; u < 8; ++u) add_bytes(acc, v[u]);
+        }
+        for (; k < K; k += SUM_KLANES)
+          add_bytes(acc, __ldg(reinterpret_cast<const int4*>(col + size_t(k) * N)));
+      }
+      // a warp holds 32 / SUM_TX k lanes of the same column chunks: fold them with shuffles
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+#pragma unroll
+        for (int o = SUM_TX; o < 32; o <<= 1) acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], o);
+      }
+      __syncthreads();  // previous item's readers are done with `part`
+      if (threadIdx.x % 32 < SUM_TX) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) part[threadIdx.x / 32][tx * 16 + i] = acc[i];
+      }
+      __syncthreads();
+      if (threadIdx.x < SUM_COLS) {
+        int total = 0;
+#pragma unroll
+        for (int r = 0; r < SUM_THREADS / 32; ++r) total += part[r][threadIdx.x];
+        const int out = item * SUM_COLS + threadIdx.x;
+        if (out < N) col_sum[out] = total;
+      }
+    } else {
+      const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+      const int m = (item - col_items) * SUM_ROWS + warp;
+      if (m < M) {
+        const int4* a = reinterpret_cast<const int4*>(A + size_t(m) * K);
+        const int chunks = K / 16;
+        int acc = 0;
+        int i = lane;
+        for (; i + 7 * 32 < chunks; i += 8 * 32) {  // eight independent loads in flight
+          int4 v[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u) v[u] = __ldg(a + i + u * 32);
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            acc = __dp4a(v[u].x, 0x01010101, acc);
+            acc = __dp4a(v[u].y, 0x01010101, acc);
+            acc = __dp4a(v[u].z, 0x01010101, acc);
+            acc = __dp4a(v[u].w, 0x01010101, acc);
+          }
+        }
+        for (; i < chunks; i += 32) {
+          const int4 v = __ldg(a + i);
+          acc = __dp4a(v.x, 0x01010101, acc);
+          acc = __dp4a(v.y, 0x01010101, acc);
+          acc = __dp4a(v.z, 0x01010101, acc);
+          acc = __dp4a(v.w, 0x01010101, acc);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        if (lane == 0) row_sum[m] = acc;
       }
     }
   }
-#pragma unroll
-  for (int i = 0; i < 16; ++i) part[ty][tx * 16 + i] = acc[i];
-  __syncthreads();
-  const int c = threadIdx.x;
-  int sum = 0;
-#pragma unroll
-  for (int r = 0; r < 16; ++r) sum += part[r][c];
-  const int col = blockIdx.x * 256 + c;
-  if (col < N && sum != 0) atomicAdd(&col_sum[col], sum);
+}
+
+// Launches the pre-pass for whichever sums the zero points require; returns whether a kernel
+// was launched.  col_sum entries past N (the accumulator tile is 256 wide) are never written;
+// the epilogue may read them for columns it then discards.
+static bool launch_sums(const int8_t* A, const int8_t* B, int* row_sum, int* col_sum, int M, int N,
+                        int K, const Quant& q, int sm_count) {
+  const int col_items = q.za != 0 ? (N + SUM_COLS - 1) / SUM_COLS : 0;
+  const int row_items = q.zb != 0 ? (M + SUM_ROWS - 1) / SUM_ROWS : 0;
+  if (col_items + row_items == 0) return false;
+  // Ask for the largest shared-memory carve-out although the kernel needs little: an SM can
+  // only host a tensor-kernel CTA next to this block if it is already configured that way.
+  static bool configured = false;
+  if (!configured) {
+    cudaFuncSetAttribute(sums_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                         cudaSharedmemCarveoutMaxShared);
+    configured = true;
+  }
+  const int grid = std::min(col_items + row_items, sm_count);
+  sums_kernel<<<grid, SUM_THREADS>>>(A, B, row_sum, col_sum, M, N, K, col_items, row_items);
+  ++launch_counter();
+  return true;
 }
 
 // --------------------------------------------------------------- tensor path
@@ -458,8 +534,8 @@ __global__ void __launch_bounds__(MMA_THREADS, 1)
 // block and its predecessor.  Commit number c arrives on ring[c % 4]; the producer, before it
 // refills the stage of block g - P_STAGES, waits for the commit that covers that block.  The
 // consumer can never be four commits ahead of what the producer has observed (the ring is
-// seven blocks deep), so the phase parity of ring[c % 4] is unambiguous.
-constexpr int P_STAGES = 7;
+// six blocks deep), so the phase parity of ring[c % 4] is unambiguous.
+constexpr int P_STAGES = 6;
 constexpr int P_RING = 4;
 constexpr int P_A_BYTES = BM * BK;   // 128 rows x 128 k-bytes
 constexpr int P_B_BYTES = BK * 128;  // 128 k-rows x 128 n-bytes (this CTA's half of the columns)
@@ -498,7 +574,7 @@ __device__ __forceinline__ void drain_half(uint32_t tmem_row_addr, int col0, int
   using Signed = typename std::conditional<WIDE, long long, int>::type;
   const float zc = float(q.zc);
   Wide row_term = Wide(K) * Wide(q.za) * Wide(q.zb);
-  if (row_ok && q.zb != 0) row_term -= Wide(q.zb) * Wide(row_sum[m]);
+  if (row_ok && q.zb != 0) row_term -= Wide(q.zb) * Wide(__ldcg(row_sum + m));
   int8_t* c_row = C + size_t(row_ok ? m : 0) * N;
 #pragma unroll 1
   for (int chunk = 0; chunk < 4; ++chunk) {
@@ -512,8 +588,9 @@ __device__ __forceinline__ void drain_half(uint32_t tmem_row_addr, int col0, int
 #pragma unroll
     for (int g = 0; g < 8; ++g) {
       int4 cs = make_int4(0, 0, 0, 0);
-      // col_sum is padded to a multiple of the tile width: never out of bounds.
-      if (q.za != 0) cs = __ldg(reinterpret_cast<const int4*>(col_sum + n0 + g * 4));
+      // col_sum is padded to a multiple of the tile width: never out of bounds.  Read
+      // through L2: the values were written by another grid that overlapped this one.
+      if (q.za != 0) cs = __ldcg(reinterpret_cast<const int4*>(col_sum + n0 + g * 4));
       const int csv[4] = {cs.x, cs.y, cs.z, cs.w};
       uint32_t word = 0;
 #pragma unroll
@@ -669,6 +746,10 @@ __global__ void __launch_bounds__(MMA_THREADS, 1)
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
+    // The row / column sums come from the pre-pass grid, which may still be running when this
+    // kernel was launched behind it with programmatic stream serialisation.  (No effect when
+    // there is no such prerequisite.)
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
       int tm, tn;
       pair_tile_coords(tile, tiles_m, tiles_n, tm, tn);
@@ -1182,15 +1263,7 @@ static bool launch_tensor(DeviceCtx& ctx, const int8_t* A, const int8_t* B, int8
   int* row_sum = static_cast<int*>(device_scratch(ctx, row_bytes + size_t(np) * 4));
   if (!row_sum) return false;
   int* col_sum = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(row_sum) + row_bytes);
-  if (q.zb != 0) {
-    row_sums_kernel<<<(M + 7) / 8, 256>>>(A, row_sum, M, K);
-    ++launch_counter();
-  }
-  if (q.za != 0) {
-    cudaMemsetAsync(col_sum, 0, size_t(np) * 4, 0);
-    col_sums_kernel<<<dim3((N + 255) / 256, (K + CS_ROWS - 1) / CS_ROWS), 256>>>(B, col_sum, K, N);
-    ++launch_counter();
-  }
+  const bool sums_launched = launch_sums(A, B, row_sum, col_sum, M, N, K, q, ctx.sm_count);
   const int c_vector_ok = (reinterpret_cast<uintptr_t>(C) & 15) == 0 && N % 16 == 0;
   const int pairs = (force == PATH_TENSOR || (force != PATH_TENSOR_PAIR && M <= BM))
                         ? 0 : max_active_pairs(ctx);
@@ -1202,21 +1275,32 @@ static bool launch_tensor(DeviceCtx& ctx, const int8_t* A, const int8_t* B, int8
     cfg.blockDim = dim3(MMA_THREADS);
     cfg.dynamicSmemBytes = P_SMEM_BYTES;
     cfg.stream = 0;
-    cudaLaunchAttribute attr;
-    attr.id = cudaLaunchAttributeClusterDimension;
-    attr.val.clusterDim.x = 2;
-    attr.val.clusterDim.y = 1;
-    attr.val.clusterDim.z = 1;
-    cfg.attrs = &attr;
-    cfg.numAttrs = 1;
+    cudaLaunchAttribute attrs[2];
+    attrs[0].id = cudaLaunchAttributeClusterDimension;
+    attrs[0].val.clusterDim.x = 2;
+    attrs[0].val.clusterDim.y = 1;
+    attrs[0].val.clusterDim.z = 1;
+    // Start while the sums pre-pass is still running (the epilogue waits for it).
+    attrs[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attrs;
     const int* rs = row_sum;
     const int* cs = col_sum;
-    if (K <= 33025)
-      cudaLaunchKernelEx(&cfg, umma_pair_kernel<false>, map_a, map_b, C, rs, cs, M, N, K, q, tiles_m,
-                         tiles_n, c_vector_ok, ctx.status);
-    else
-      cudaLaunchKernelEx(&cfg, umma_pair_kernel<true>, map_a, map_b, C, rs, cs, M, N, K, q, tiles_m,
-                         tiles_n, c_vector_ok, ctx.status);
+    static bool overlap_supported[MAX_DEVICES] = {true, true, true, true, true, true, true, true,
+                                                  true, true, true, true, true, true, true, true};
+    for (int attempt = 0; attempt < 2; ++attempt) {
+      const bool overlap = sums_launched && attempt == 0 &&
+                           (ctx.device >= 16 || overlap_supported[ctx.device]);
+      cfg.numAttrs = overlap ? 2 : 1;
+      cudaError_t err =
+          K <= 33025 ? cudaLaunchKernelEx(&cfg, umma_pair_kernel<false>, map_a, map_b, C, rs, cs, M, N,
+                                          K, q, tiles_m, tiles_n, c_vector_ok, ctx.status)
+                     : cudaLaunchKernelEx(&cfg, umma_pair_kernel<true>, map_a, map_b, C, rs, cs, M, N,
+                                          K, q, tiles_m, tiles_n, c_vector_ok, ctx.status);
+      if (err == cudaSuccess || !overlap) break;
+      cudaGetLastError();  // the attribute was refused: launch again, fully serialised
+      if (ctx.device < 16) overlap_supported[ctx.device] = false;
+    }
     last_path() = PATH_TENSOR_PAIR;
   } else {
     const int tiles_m = (M + BM - 1) / BM;
@@ -1363,20 +1447,12 @@ extern "C" int texo_mm_int8_solve_noalloc(const int8_t* A, const int8_t* B, int8
         make_tensor_map_2d(&map_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, B, K, N, N, BK, 128,
                            CU_TENSOR_MAP_SWIZZLE_128B)) {
       const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
-      const int np = tiles_n * BN;  // <= NOALLOC_MAX_N because that is a multiple of BN
       int* row_sum = dev->scratch;
       int* col_sum = dev->scratch + NOALLOC_MAX_M;
       int* status = dev->scratch + NOALLOC_MAX_M + NOALLOC_MAX_N;
-      if (q.zb != 0) {
-        row_sums_kernel<<<(M + 7) / 8, 256>>>(A, row_sum, M, K);
-        ++launch_counter();
-      }
-      if (q.za != 0) {
-        // col_sums_kernel accumulates with atomics: its part of the array must start at zero.
-        cudaMemsetAsync(col_sum, 0, size_t(np) * 4, 0);
-        col_sums_kernel<<<dim3((N + 255) / 256, (K + CS_ROWS - 1) / CS_ROWS), 256>>>(B, col_sum, K, N);
-        ++launch_counter();
-      }
+      // Every entry the main kernel uses is rewritten by plain stores here, so nothing in the
+      // shared array has to be cleared first.
+      launch_sums(A, B, row_sum, col_sum, M, N, K, q, dev->sm_count);
       const int grid = std::min(tiles_m * tiles_n, dev->sm_count);
       const int c_vector_ok = (reinterpret_cast<uintptr_t>(C) & 15) == 0 && N % 16 == 0;
       if (K <= 33025)
