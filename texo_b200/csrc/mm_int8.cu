@@ -797,20 +797,25 @@ __global__ void __launch_bounds__(MMA_THREADS, 1)
 // zero - all while its producer and MMA warps are already streaming the next tile.  The
 // owned tiles come LAST and need no reduction, so the kernel's tail is a plain drain.
 // Nobody ever waits for another CTA.
-constexpr int S_STAGES = 8;
+// Shared memory is kept under half an SM (two CTAs fit side by side) so that the next call's
+// kernel, launched with programmatic stream serialisation, can already sit on the SM with its
+// set-up done while this one drains: back-to-back decode calls then lose neither the launch
+// gap nor the prologue.  M <= 16: 5 stages of 16 KiB weights + 4 KiB activations; M <= 32: 4
+// stages of 16 KiB + 8 KiB.
+constexpr int S_MAX_STAGES = 5;
 constexpr int S_W_BYTES = 128 * 128;  // one 128 k-row x 128 column box of B
-constexpr int S_ACT_BYTES = 8192;     // up to 48 rows x 128 B, padded to the swizzle atom
-constexpr int S_STAGE_BYTES = S_W_BYTES + S_ACT_BYTES;
 constexpr int S_ACC_COLS = 64;  // TMEM columns per accumulator (M + ones + padding <= 48)
 constexpr int S_TMEM_COLS = 2 * S_ACC_COLS;  // double buffered
-constexpr int S_SMEM_BYTES = S_STAGES * S_STAGE_BYTES + 1024 + 512;
+constexpr int S_SMEM_BYTES = 100 * 1024 + 1024 + 512;
+__host__ __device__ constexpr int skinny_act_bytes(int R) { return R == 16 ? 4096 : 8192; }
+__host__ __device__ constexpr int skinny_stages(int R) { return R == 16 ? 5 : 4; }
 constexpr int S_TILE_N = 128;
 constexpr int S_EPI_WARPS = 4;
 constexpr int S_THREADS = 64 + S_EPI_WARPS * 32;
 
 struct SkinnyBarriers {
-  uint64_t full[S_STAGES];
-  uint64_t empty[S_STAGES];
+  uint64_t full[S_MAX_STAGES];
+  uint64_t empty[S_MAX_STAGES];
   uint64_t acc_full[2];
   uint64_t acc_empty[2];
   uint32_t tmem_base;
@@ -882,7 +887,12 @@ __global__ void __launch_bounds__(S_THREADS, 1)
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~uintptr_t(1023));
-  SkinnyBarriers* bars = reinterpret_cast<SkinnyBarriers*>(smem + S_STAGES * S_STAGE_BYTES);
+  // A later call's kernel may start its set-up now (it waits for this grid before it touches
+  // global memory, see griddepcontrol.wait below).
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  const int S_STAGES = skinny_stages(R);
+  const int S_STAGE_BYTES = S_W_BYTES + skinny_act_bytes(R);
+  SkinnyBarriers* bars = reinterpret_cast<SkinnyBarriers*>(smem + 100 * 1024);
   volatile int* abort_flag = &bars->abort_flag;
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   const int num_kb = (K + BK - 1) / BK;
@@ -909,6 +919,9 @@ __global__ void __launch_bounds__(S_THREADS, 1)
   }
   if (warp == 0) {
     __syncwarp();
+    // Everything up to here touched only shared memory.  From here on global memory is read:
+    // wait for the grids ahead of this one in the stream (no-op without such a dependency).
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     for (int i = 0; i < S_STAGES; ++i) {
       if (p_kb == p_kb1 && !prod_sched.next(p_tile, p_kb, p_kb1, p_shared)) break;
       if (lane == 0) {
@@ -1021,6 +1034,7 @@ __global__ void __launch_bounds__(S_THREADS, 1)
     const int ew = warp - 2;
     const int quarter = warp % 4;     // TMEM lanes 32*quarter .. +31
     const int et = threadIdx.x - 64;  // 0..127 among the epilogue threads
+    asm volatile("griddepcontrol.wait;" ::: "memory");  // before reading A / touching C, workspace
     // rowsum(A) for the zero-point identity: the activations are tiny, every CTA sums them.
     if (q.zb != 0) {
       for (int m = ew; m < M; m += S_EPI_WARPS) {
@@ -1225,10 +1239,27 @@ static bool launch_skinny(DeviceCtx& ctx, const int8_t* A, const int8_t* B, int8
   uint8_t* base = static_cast<uint8_t*>(device_workspace(ctx, counter_bytes + ws_bytes + 256));
   if (!base) return false;
   const int slot = profile_start();
-  skinny_kernel<<<grid, S_THREADS, S_SMEM_BYTES>>>(map_w, map_act, A, C,
-                                                  reinterpret_cast<int*>(base + counter_bytes),
-                                                  reinterpret_cast<int*>(base), M, N, K, q, R,
-                                                  ctx.status);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(S_THREADS);
+  cfg.dynamicSmemBytes = S_SMEM_BYTES;
+  cfg.stream = 0;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &attr;
+  int* ws = reinterpret_cast<int*>(base + counter_bytes);
+  int* counters = reinterpret_cast<int*>(base);
+  static bool overlap_ok = true;
+  for (int attempt = 0; attempt < 2; ++attempt) {
+    cfg.numAttrs = (overlap_ok && attempt == 0) ? 1 : 0;
+    if (cudaLaunchKernelEx(&cfg, skinny_kernel, map_w, map_act, A, C, ws, counters, M, N, K, q, R,
+                           ctx.status) == cudaSuccess ||
+        cfg.numAttrs == 0)
+      break;
+    cudaGetLastError();  // attribute refused: launch again, fully serialised
+    overlap_ok = false;
+  }
   profile_stop(slot);
   ++launch_counter();
   last_path() = PATH_SKINNY;
