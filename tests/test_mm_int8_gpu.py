@@ -171,6 +171,26 @@ def test_config1_full_matrix(lib, oracle):
         assert np.array_equal(got, oracle.mm_int8(A, B, M, N, K, q))
 
 
+def test_tensor_path_output_zero_point_and_saturation(lib, oracle):
+    """The CTA-pair kernel requantises with an integer tail (round, saturating add of zC,
+    saturating pack); it must equal the FP32 tail of the oracle at the zC endpoints, when most
+    outputs saturate, when rint(acc) is far outside int8 and int32, and - through its FP32
+    fallback - for a zC outside the integer tail's proven range."""
+    m, n, k = 256, 512, 1024
+    rng = np.random.default_rng(21)
+    a = rng.integers(-128, 128, (m, k), dtype=np.int8)
+    b = rng.integers(-128, 128, (k, n), dtype=np.int8)
+    cases = [(0.02, 0.03, 50.0, 3, -5, -128), (0.02, 0.03, 50.0, 3, -5, 127),
+             (0.02, 0.03, 0.001, 0, 0, 5),            # almost everything saturates
+             (1.0e4, 1.0e4, 1.0e-3, 2, 1, -7),        # |acc| beyond int32
+             (0.02, 0.03, 50.0, 3, -5, (1 << 22) + 5),  # FP32 tail
+             (0.02, 0.03, 50.0, 3, -5, -(1 << 23))]
+    for q in cases:
+        got = run_case(lib, a, b, m, n, k, q)
+        assert lib.texo_mm_int8_last_path() == 4
+        assert np.array_equal(got, oracle.mm_int8(a, b, m, n, k, q)), q
+
+
 def test_wide_dot_on_tensor_path(lib, oracle):
     """K > 33025: |dot| can exceed int32, the epilogue must use 64-bit correction."""
     for m, n, k, want_path in ((128, 256, 33040, 2), (384, 256, 33040, 4)):

@@ -50,6 +50,25 @@ struct Quant {
   int za, zb, zc;
 };
 
+// The same requantisation for four outputs at once, with the tail done in integers:
+// cvt.rni.s32 (saturating) -> saturating add of zC -> saturating pack to int8.  Identical to
+// the FP32 tail whenever |zC| <= 2^22: if |rint(acc)| < 2^24 the float add is exact and the
+// two agree; beyond that both forms saturate to the same end of [-128, 127].  Callers check
+// the zC bound (the contract says [-128, 127]).
+__device__ __forceinline__ uint32_t requantize4(const float (&dot)[4], float sa, float sb, float sc,
+                                                int zc) {
+  int r[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float acc = __fdiv_rn(__fmul_rn(__fmul_rn(dot[i], sa), sb), sc);
+    asm("add.sat.s32 %0, %1, %2;" : "=r"(r[i]) : "r"(__float2int_rn(acc)), "r"(zc));
+  }
+  uint32_t hi, out;
+  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(r[3]), "r"(r[2]), "r"(0));
+  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(out) : "r"(r[1]), "r"(r[0]), "r"(hi));
+  return out;
+}
+
 // -------------------------------------------------------------- generic path
 constexpr int GT = 64;        // output tile edge
 constexpr int GK = 64;        // k bytes per smem tile
@@ -573,6 +592,7 @@ __device__ __forceinline__ void drain_half(uint32_t tmem_row_addr, int col0, int
   using Wide = typename std::conditional<WIDE, long long, unsigned>::type;
   using Signed = typename std::conditional<WIDE, long long, int>::type;
   const float zc = float(q.zc);
+  const bool int_tail = q.zc >= -(1 << 22) && q.zc <= (1 << 22);
   Wide row_term = Wide(K) * Wide(q.za) * Wide(q.zb);
   if (row_ok && q.zb != 0) row_term -= Wide(q.zb) * Wide(__ldcg(row_sum + m));
   int8_t* c_row = C + size_t(row_ok ? m : 0) * N;
@@ -592,14 +612,21 @@ __device__ __forceinline__ void drain_half(uint32_t tmem_row_addr, int col0, int
       // through L2: the values were written by another grid that overlapped this one.
       if (q.za != 0) cs = __ldcg(reinterpret_cast<const int4*>(col_sum + n0 + g * 4));
       const int csv[4] = {cs.x, cs.y, cs.z, cs.w};
-      uint32_t word = 0;
+      float dots[4];
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const Wide dot = Wide(Signed(int(v[g * 4 + e]))) + row_term - Wide(q.za) * Wide(csv[e]);
-        const int r = requantize(float(Signed(dot)), q.sa, q.sb, q.sc, zc);
-        word |= uint32_t(r & 0xff) << (8 * e);
+        dots[e] = float(Signed(dot));
       }
-      packed[g] = word;
+      if (int_tail) {
+        packed[g] = requantize4(dots, q.sa, q.sb, q.sc, q.zc);
+      } else {
+        uint32_t word = 0;
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          word |= uint32_t(requantize(dots[e], q.sa, q.sb, q.sc, zc) & 0xff) << (8 * e);
+        packed[g] = word;
+      }
     }
     if (row_ok) {
       if (c_vector_ok && n0 + 32 <= N) {
