@@ -100,6 +100,8 @@ int texo_profile_read(float* total_ms, int* launches);
 double texo_int8_issue_ceiling_tops(int pairs, int batches);
 /* Same with `per_commit` MMAs between tcgen05.commit signals instead of 64. */
 double texo_int8_issue_rate_tops(int pairs, int batches, int per_commit);
+/* The same probe with kind::f16 MMAs; tera-flops per second. */
+double texo_f16_issue_rate_tflops(int pairs, int batches, int per_commit);
 /* Operand-feed probe: streams the TMA boxes of an INT8 GEMM over A [M,K], B [K,N] (device
  * pointers, 16-byte aligned rows) through a ring of `stages` (1..7) shared-memory stages
  * without computing; returns TB/s of operand bytes delivered to the SMs.  mode bit 0 = A

@@ -34,6 +34,7 @@ _SIGNATURES = {
     "texo_profile_enable": (None, [_c_int]),
     "texo_int8_issue_ceiling_tops": (ctypes.c_double, [_c_int, _c_int]),
     "texo_int8_issue_rate_tops": (ctypes.c_double, [_c_int, _c_int, _c_int]),
+    "texo_f16_issue_rate_tflops": (ctypes.c_double, [_c_int, _c_int, _c_int]),
     "texo_int8_feed_rate_tbs": (ctypes.c_double, [_c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int]),
     "texo_profile_read": (_c_int, [ctypes.POINTER(_c_float), ctypes.POINTER(_c_int)]),
 }

@@ -26,7 +26,7 @@ struct ProbeBarriers {
   int abort_flag;
 };
 
-template <int CTAS>
+template <int CTAS, bool F16>
 __global__ void __launch_bounds__(THREADS, 1) issue_kernel(int batches, int per_commit, int* status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -69,7 +69,9 @@ __global__ void __launch_bounds__(THREADS, 1) issue_kernel(int batches, int per_
   const uint32_t tmem_base = bars->tmem_base;
 
   if (warp == 0 && rank == 0) {
-    constexpr uint32_t IDESC = umma_idesc(2, 1, 1, 0, 1, CTAS == 2 ? 256 : 128, 256);
+    // int8: A K-major, B N-major (as the INT8 kernels); f16: both K-major (as the W4A16 kernel)
+    constexpr uint32_t IDESC = F16 ? umma_idesc(1, 0, 0, 0, 0, CTAS == 2 ? 256 : 128, 256)
+                                   : umma_idesc(2, 1, 1, 0, 1, CTAS == 2 ? 256 : 128, 256);
     const uint32_t sa = smem_u32(smem), sb = sa + A_BYTES;
     bool ok = true;
     for (int b = 0; b < batches && ok; ++b) {
@@ -84,12 +86,19 @@ __global__ void __launch_bounds__(THREADS, 1) issue_kernel(int batches, int per_
           for (int i = 0; i < per_commit; ++i) {
             const int j = i & 3;
             const uint64_t da = smem_desc(sa + j * 32, 16, 1024, SMEM_SWIZZLE_128B);
-            const uint64_t db = smem_desc(sb + j * 32 * 128, 128 * 128, 1024, SMEM_SWIZZLE_128B);
+            const uint64_t db = F16 ? smem_desc(sb + j * 32, 16, 1024, SMEM_SWIZZLE_128B)
+                                    : smem_desc(sb + j * 32 * 128, 128 * 128, 1024, SMEM_SWIZZLE_128B);
             const uint32_t d = tmem_base + ((i >> 2) & 1) * 256;
-            if (CTAS == 2)
+            if (F16) {
+              if (CTAS == 2)
+                umma_f16_pair(d, da, db, IDESC, 1);
+              else
+                umma_f16(d, da, db, IDESC, 1);
+            } else if (CTAS == 2) {
               umma_i8_pair(d, da, db, IDESC, 1);
-            else
+            } else {
               umma_i8(d, da, db, IDESC, 1);
+            }
           }
           if (CTAS == 2)
             umma_commit_pair(&bars->done[b & 1], 1);
@@ -243,7 +252,15 @@ extern "C" double texo_int8_issue_ceiling_tops(int pairs, int batches) {
 // Same measurement with `per_commit` MMAs between completion signals.  On B200 the rate
 // falls off below eight MMAs per tcgen05.commit (four per commit: ~80 %), which is why the
 // tensor kernel releases its stages two k blocks at a time.
+static double issue_rate(int pairs, int batches, int per_commit, bool f16);
 extern "C" double texo_int8_issue_rate_tops(int pairs, int batches, int per_commit) {
+  return issue_rate(pairs, batches, per_commit, false);
+}
+// The same probe with kind::f16 MMAs (x16 k per instruction): tera-flops per second.
+extern "C" double texo_f16_issue_rate_tflops(int pairs, int batches, int per_commit) {
+  return issue_rate(pairs, batches, per_commit, true);
+}
+static double issue_rate(int pairs, int batches, int per_commit, bool f16) {
   using namespace texo;
   using namespace texo::probe;
   if (per_commit < 1 || per_commit > 1024 || batches < 1) return -1.0;
@@ -261,7 +278,8 @@ extern "C" double texo_int8_issue_rate_tops(int pairs, int batches, int per_comm
   cudaError_t err;
   int grid = sms;
   if (pairs) {
-    cudaFuncSetAttribute(issue_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaFuncSetAttribute(issue_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaFuncSetAttribute(issue_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     cudaLaunchConfig_t cfg = {};
     grid = sms / 2 * 2;
     cfg.gridDim = dim3(grid);
@@ -275,11 +293,16 @@ extern "C" double texo_int8_issue_rate_tops(int pairs, int batches, int per_comm
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
     cudaEventRecord(e0, 0);
-    err = cudaLaunchKernelEx(&cfg, issue_kernel<2>, batches, per_commit, status);
+    err = f16 ? cudaLaunchKernelEx(&cfg, issue_kernel<2, true>, batches, per_commit, status)
+              : cudaLaunchKernelEx(&cfg, issue_kernel<2, false>, batches, per_commit, status);
   } else {
-    cudaFuncSetAttribute(issue_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaFuncSetAttribute(issue_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaFuncSetAttribute(issue_kernel<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     cudaEventRecord(e0, 0);
-    issue_kernel<1><<<grid, THREADS, smem>>>(batches, per_commit, status);
+    if (f16)
+      issue_kernel<1, true><<<grid, THREADS, smem>>>(batches, per_commit, status);
+    else
+      issue_kernel<1, false><<<grid, THREADS, smem>>>(batches, per_commit, status);
     err = cudaGetLastError();
   }
   cudaEventRecord(e1, 0);
@@ -290,9 +313,9 @@ extern "C" double texo_int8_issue_rate_tops(int pairs, int batches, int per_comm
     cudaEventElapsedTime(&ms, e0, e1);
     cudaMemcpy(&code, status, sizeof(int), cudaMemcpyDeviceToHost);
     if (code == 0 && ms > 0.f) {
-      // every SM retires 128 x 256 x 32 MACs per instruction in both modes
+      // every SM retires 128 x 256 x 32 (int8) or x 16 (f16) MACs per instruction in both modes
       const double macs = double(sms / (pairs ? 2 : 1) * (pairs ? 2 : 1)) * batches * double(per_commit) * 128.0 *
-                          256.0 * 32.0;
+                          256.0 * (f16 ? 16.0 : 32.0);
       result = 2.0 * macs / (ms * 1e-3) / 1e12;
     } else if (code != 0) {
       result = -double(code);
