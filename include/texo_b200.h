@@ -61,6 +61,15 @@ int texo_mm_int8_solve_noalloc(const int8_t* A, const int8_t* B, int8_t* C, int 
                                float scale_A, float scale_B, float scale_C, int zero_point_A,
                                int zero_point_B, int zero_point_C);
 
+/* Host-buffer form of texo_mm_int8_solve: A, B, C are HOST pointers (pinned for full speed).
+ * Does what the reference harness does around `solve` (upload, run, download:
+ * tests/mm_int8.cpp:56-79) as a pipeline of row chunks on internal streams, so uploads,
+ * compute and downloads overlap.  Asynchronous; C_host is valid after
+ * cudaDeviceSynchronize().  Returns 0, -1 bad arguments, -3 CUDA failure. */
+int texo_mm_int8_solve_host(const int8_t* A_host, const int8_t* B_host, int8_t* C_host, int M, int N,
+                            int K, float scale_A, float scale_B, float scale_C, int zero_point_A,
+                            int zero_point_B, int zero_point_C);
+
 /* Tile-scale dequantization.  Replaces `solve` of the reference's
  * src/dequantization.cu:40-43 (tests/dequantization.cpp:4).  X, Y [M,N] fp32,
  * S [ceil(M/T), ceil(N/T)] fp32; Y = X * S[m/T][n/T]. */

@@ -191,6 +191,28 @@ def test_tensor_path_output_zero_point_and_saturation(lib, oracle):
         assert np.array_equal(got, oracle.mm_int8(a, b, m, n, k, q)), q
 
 
+@pytest.mark.parametrize("shape", [(1000, 768, 512), (2304, 512, 1024), (65, 67, 31), (17, 19, 0)])
+def test_host_buffer_entry_point(lib, oracle, shape):
+    """texo_mm_int8_solve_host: pinned host operands, chunked upload / compute / download
+    pipeline inside the library; two calls in a row on the same buffers; bit-exact."""
+    m, n, k = shape
+    rng = np.random.default_rng(5 + m)
+    q = (0.02, 0.03, float(np.float32(0.02 * 0.03 * 160 * np.sqrt(max(k, 1)))), 3, -5, 1)
+    C = torch.empty((m, n), dtype=torch.int8).pin_memory()
+    for call in range(2):
+        a = rng.integers(-128, 128, (m, k), dtype=np.int8)
+        b = rng.integers(-128, 128, (k, n), dtype=np.int8)
+        A = torch.from_numpy(a).pin_memory() if k else torch.empty((m, 0), dtype=torch.int8)
+        B = torch.from_numpy(b).pin_memory() if k else torch.empty((0, n), dtype=torch.int8)
+        C.fill_(99)
+        rc = lib.texo_mm_int8_solve_host(A.data_ptr() if k else None, B.data_ptr() if k else None,
+                                         C.data_ptr(), m, n, k, *q)
+        assert rc == 0
+        torch.cuda.synchronize()
+        assert np.array_equal(C.numpy(), oracle.mm_int8(a, b, m, n, k, q)), (shape, call)
+    assert lib.texo_mm_int8_status() == 0
+
+
 def test_wide_dot_on_tensor_path(lib, oracle):
     """K > 33025: |dot| can exceed int32, the epilogue must use 64-bit correction."""
     for m, n, k, want_path in ((128, 256, 33040, 2), (384, 256, 33040, 4)):

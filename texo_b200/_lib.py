@@ -22,6 +22,8 @@ _SIGNATURES = {
                                   _c_float, _c_float, _c_float, _c_int, _c_int, _c_int]),
     "texo_mm_int8_solve_noalloc": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int,
                                             _c_float, _c_float, _c_float, _c_int, _c_int, _c_int]),
+    "texo_mm_int8_solve_host": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int,
+                                         _c_float, _c_float, _c_float, _c_int, _c_int, _c_int]),
     "texo_mm_int4_solve": (None, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int]),
     "texo_dequantization_solve": (None, [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int]),
     "texo_mm_int8_last_path": (_c_int, []),

@@ -17,7 +17,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OPS = ("mm_int8", "mm_int4", "dequantization")
-EXTRA = ("capi", "peak_probe")  # only in the combined library
+EXTRA = ("capi", "peak_probe", "host_api")  # only in the combined library
 HEADERS = ("ptx.cuh", "host_common.h")
 
 NVCC_FLAGS = [

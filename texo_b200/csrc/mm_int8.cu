@@ -289,8 +289,10 @@ __global__ void __launch_bounds__(SUM_THREADS)
 // Launches the pre-pass for whichever sums the zero points require; returns whether a kernel
 // was launched.  col_sum entries past N (the accumulator tile is 256 wide) are never written;
 // the epilogue may read them for columns it then discards.
+// `max_blocks` = number of SMs when the tensor kernel is going to run beside it (one
+// persistent block per SM), 0 for one block per work item when it runs on its own.
 static bool launch_sums(const int8_t* A, const int8_t* B, int* row_sum, int* col_sum, int M, int N,
-                        int K, const Quant& q, int sm_count) {
+                        int K, const Quant& q, int max_blocks) {
   const int col_items = q.za != 0 ? (N + SUM_COLS - 1) / SUM_COLS : 0;
   const int row_items = q.zb != 0 ? (M + SUM_ROWS - 1) / SUM_ROWS : 0;
   if (col_items + row_items == 0) return false;
@@ -302,7 +304,7 @@ static bool launch_sums(const int8_t* A, const int8_t* B, int* row_sum, int* col
                          cudaSharedmemCarveoutMaxShared);
     configured = true;
   }
-  const int grid = std::min(col_items + row_items, sm_count);
+  const int grid = max_blocks > 0 ? std::min(col_items + row_items, max_blocks) : col_items + row_items;
   sums_kernel<<<grid, SUM_THREADS>>>(A, B, row_sum, col_sum, M, N, K, col_items, row_items);
   ++launch_counter();
   return true;
@@ -1321,10 +1323,11 @@ static bool launch_tensor(DeviceCtx& ctx, const int8_t* A, const int8_t* B, int8
   int* row_sum = static_cast<int*>(device_scratch(ctx, row_bytes + size_t(np) * 4));
   if (!row_sum) return false;
   int* col_sum = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(row_sum) + row_bytes);
-  const bool sums_launched = launch_sums(A, B, row_sum, col_sum, M, N, K, q, ctx.sm_count);
   const int c_vector_ok = (reinterpret_cast<uintptr_t>(C) & 15) == 0 && N % 16 == 0;
   const int pairs = (force == PATH_TENSOR || (force != PATH_TENSOR_PAIR && M <= BM))
                         ? 0 : max_active_pairs(ctx);
+  const bool sums_launched =
+      launch_sums(A, B, row_sum, col_sum, M, N, K, q, pairs > 0 ? ctx.sm_count : 0);
   const int slot = profile_start();
   if (pairs > 0) {
     const int tiles_m = (M + 255) / 256;
@@ -1510,7 +1513,7 @@ extern "C" int texo_mm_int8_solve_noalloc(const int8_t* A, const int8_t* B, int8
       int* status = dev->scratch + NOALLOC_MAX_M + NOALLOC_MAX_N;
       // Every entry the main kernel uses is rewritten by plain stores here, so nothing in the
       // shared array has to be cleared first.
-      launch_sums(A, B, row_sum, col_sum, M, N, K, q, dev->sm_count);
+      launch_sums(A, B, row_sum, col_sum, M, N, K, q, 0);
       const int grid = std::min(tiles_m * tiles_n, dev->sm_count);
       const int c_vector_ok = (reinterpret_cast<uintptr_t>(C) & 15) == 0 && N % 16 == 0;
       if (K <= 33025)

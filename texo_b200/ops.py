@@ -113,18 +113,24 @@ def dequantization(X: torch.Tensor, S: torch.Tensor, T: int,
 
 
 def mm_int8_host(A_host: torch.Tensor, B_host: torch.Tensor, C_host: torch.Tensor,
-                 staging: tuple[torch.Tensor, torch.Tensor, torch.Tensor],
                  scale_A: float, scale_B: float, scale_C: float,
                  zero_point_A: int, zero_point_B: int, zero_point_C: int) -> None:
-    """End-to-end call on HOST buffers, the sequence the reference harness performs around
-    `solve` (tests/mm_int8.cpp:56-79): upload A and B, run, download C.  `staging` holds the
-    device tensors (dA, dB, dC); host tensors should be pinned.  Asynchronous on the default
-    stream; synchronise before reading C_host."""
-    dA, dB, dC = staging
-    dA.copy_(A_host, non_blocking=True)
-    dB.copy_(B_host, non_blocking=True)
-    mm_int8(dA, dB, scale_A, scale_B, scale_C, zero_point_A, zero_point_B, zero_point_C, out=dC)
-    C_host.copy_(dC, non_blocking=True)
+    """mm_int8 on HOST tensors (pin them for full speed): what the reference harness does around
+    `solve` (upload A and B, run, download C; tests/mm_int8.cpp:56-79), pipelined in row chunks
+    by the library so that uploads, compute and downloads overlap.  Asynchronous: synchronise
+    the device before reading C_host."""
+    for name, t in (("A_host", A_host), ("B_host", B_host), ("C_host", C_host)):
+        if not isinstance(t, torch.Tensor) or t.is_cuda or t.dtype != torch.int8 or not t.is_contiguous():
+            raise ValueError(f"{name} must be a contiguous CPU int8 tensor")
+    M, K = A_host.shape
+    N = B_host.shape[1]
+    if B_host.shape[0] != K or tuple(C_host.shape) != (M, N):
+        raise ValueError("shape mismatch")
+    rc = _lib.load().texo_mm_int8_solve_host(A_host.data_ptr(), B_host.data_ptr(), C_host.data_ptr(),
+                                             M, N, K, scale_A, scale_B, scale_C, zero_point_A,
+                                             zero_point_B, zero_point_C)
+    if rc != 0:
+        raise RuntimeError(f"texo_mm_int8_solve_host failed with code {rc}")
 
 
 def last_path(op: str = "mm_int8") -> int:
