@@ -2,7 +2,7 @@
 """Benchmark of the quantized-matmul hot path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload int8_8192|int8_decode|int4_w4a16|dequant]
+                    [--workload int8_8192|int8_decode|int4_w4a16|dequant|layer_sweep]
 
 One "step" is one `solve` call over one batch of synthetic input.  The default workload is
 the INT8 quantized matmul M=N=K=8192 (uniform int8 inputs, per-tensor scales and non-zero
@@ -455,6 +455,89 @@ def run_ours(args, spec, workload):
         dist.destroy_process_group()
 
 
+def run_layer_sweep(args):
+    """BASELINE config 5: the four INT8 projections of a transformer layer at M = 8192, weight
+    columns sharded over the ranks (strong scaling: the layer is fixed, each GPU owns N/g
+    columns), with and without the all-gather of C.  Prints one JSON line with one entry per
+    projection; `value` is the aggregate TOPS of the four GEMMs without the gather."""
+    import torch
+    import torch.distributed as dist
+
+    from texo_b200 import _lib, sharded
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    lib = _lib.load()
+    q = quant_params()
+    M = 8192
+    layers = [("qkv", 8192, 10240), ("o_proj", 8192, 8192), ("gate_up", 8192, 57344),
+              ("down", 28672, 8192)]
+    steps = args.steps or 50
+    g = torch.Generator(device=dev).manual_seed(SEED + rank)
+    results, total_ops, total_ms = [], 0.0, 0.0
+
+    def sync():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn):
+        for _ in range(max(3, args.warmup)):
+            fn()
+        sync()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        sync()
+        t = torch.tensor([e0.elapsed_time(e1) / steps], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    for name, K, N in layers:
+        n0, n1 = sharded.column_slab(N, world, rank)
+        A = torch.randint(-128, 128, (M, K), generator=torch.Generator(device=dev).manual_seed(SEED),
+                          device=dev, dtype=torch.int8)
+        B = torch.randint(-128, 128, (K, n1 - n0), generator=g, device=dev, dtype=torch.int8)
+        C = torch.empty((M, n1 - n0), device=dev, dtype=torch.int8)
+
+        def gemm():
+            lib.texo_mm_int8_solve(A.data_ptr(), B.data_ptr(), C.data_ptr(), M, n1 - n0, K, *q)
+
+        def gemm_gather():
+            gemm()
+            if world > 1:
+                sharded.all_gather_columns(C, N)
+
+        ms = timed(gemm)
+        ms_g = timed(gemm_gather) if world > 1 else ms
+        ops = 2.0 * M * N * K
+        results.append({"layer": name, "K": K, "N": N, "slab": n1 - n0, "gemm_ms": ms,
+                        "gemm_plus_gather_ms": ms_g, "tops": ops / (ms * 1e-3) / 1e12})
+        total_ops += ops
+        total_ms += ms
+        del A, B, C
+    if rank == 0:
+        print(json.dumps({
+            "metric": METRIC, "value": total_ops / (total_ms * 1e-3) / 1e12, "unit": UNIT,
+            "n_gpus": world, "steps": steps, "warmup": max(3, args.warmup), "ms_per_step": total_ms,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int8",
+            "data": "synthetic",
+            "config": {"workload": "layer_sweep",
+                       "description": "INT8 QKV / O / gate-up / down projections at M=8192, N sharded",
+                       "quant": q},
+            "layers": results}), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -465,6 +548,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup)
+    if args.workload == "layer_sweep":
+        run_layer_sweep(args)
+        return
     spec = workload_spec(args.workload)
     if args.steps is None:
         # about a second of GPU work, so that clocks under load are actually sampled
