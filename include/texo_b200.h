@@ -94,6 +94,11 @@ int texo_mm_int4_last_path(void);
 void texo_mm_int4_force_path(int path);
 int texo_mm_int4_status(void);
 
+/* Failure-path self-test: makes one device-side bounded wait run out of its budget (about a
+ * second) on a barrier nothing completes, and returns the status code the kernel recorded
+ * (5), or a negative value if the kernel did not return normally.  Nothing faults or hangs. */
+int texo_selftest_wait_timeout(void);
+
 /* Number of kernels the library has launched so far in this process. */
 long long texo_kernel_launches(void);
 /* CUDA-event bracket around the dominant kernel of each following call (for roofline

@@ -213,6 +213,20 @@ def test_host_buffer_entry_point(lib, oracle, shape):
     assert lib.texo_mm_int8_status() == 0
 
 
+def test_bounded_wait_reports_instead_of_hanging(lib, oracle):
+    """Failure path without a fault: a device-side wait on a barrier that nothing completes
+    runs out of its clock budget, the kernel returns normally with a status code, and the
+    very next call on the same context still gives the right answer."""
+    assert lib.texo_selftest_wait_timeout() == 5
+    assert lib.texo_mm_int8_status() == 0  # reading the code cleared it
+    m, n, k = 256, 256, 256
+    rng = np.random.default_rng(2)
+    a = rng.integers(-128, 128, (m, k), dtype=np.int8)
+    b = rng.integers(-128, 128, (k, n), dtype=np.int8)
+    q = (0.02, 0.03, 4.0, 3, -5, 1)
+    assert np.array_equal(run_case(lib, a, b, m, n, k, q), oracle.mm_int8(a, b, m, n, k, q))
+
+
 def test_wide_dot_on_tensor_path(lib, oracle):
     """K > 33025: |dot| can exceed int32, the epilogue must use 64-bit correction."""
     for m, n, k, want_path in ((128, 256, 33040, 2), (384, 256, 33040, 4)):

@@ -75,6 +75,39 @@ def test_two_rank_gather_equals_unsharded(tmp_path, oracle, N):
         assert np.array_equal(np.load(tmp_path / f"c{r}.npy"), want)
 
 
+def _failing_worker(rank, world, port, result_dir):
+    import datetime
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world,
+                            timeout=datetime.timedelta(seconds=10))
+    M, K, N = 8, 32, 256
+    A = torch.zeros((M, K), dtype=torch.int8)
+    n0, n1 = sharded.column_slab(N, world, rank)
+    B_slab = torch.zeros((K, n1 - n0), dtype=torch.int8)
+    if rank == 1:
+        os._exit(0)  # this rank disappears between steps, before the collective
+    try:
+        sharded.mm_int8_sharded(A, B_slab, N, 1.0, 1.0, 1.0, 0, 0, 0, gather=True, solver=_oracle_solver)
+        outcome = "completed"
+    except Exception as exc:  # the surviving rank must get an error, not hang
+        outcome = "error:" + type(exc).__name__
+    with open(os.path.join(result_dir, "outcome.txt"), "w") as fh:
+        fh.write(outcome)
+    os._exit(0)
+
+
+def test_lost_rank_surfaces_as_an_error_on_the_survivor(tmp_path):
+    """Host-side failure injection: one of two gloo ranks exits before the all-gather; the
+    other one's collective must end with an error within the process-group timeout."""
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    mp.spawn(_failing_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    assert (tmp_path / "outcome.txt").read_text().startswith("error:")
+
+
 def test_operators_refuse_cpu_tensors():
     from texo_b200 import ops
 

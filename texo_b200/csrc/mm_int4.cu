@@ -125,9 +125,8 @@ constexpr int T_SMEM_BYTES = T_STAGES * T_STAGE_BYTES + 1024 + 512;
 constexpr int T_GROUP_M = 8;
 
 struct TensorBarriers {
-  uint64_t x_full[T_STAGES];     // even CTA: bytes of both CTAs' x loads
-  uint64_t raw_full[T_STAGES];   // per CTA: packed nibbles landed
-  uint64_t conv_full[T_STAGES];  // even CTA: unpack warps of both CTAs arrived
+  uint64_t ready[T_STAGES];     // even CTA: x bytes of both CTAs landed AND all unpack warps arrived
+  uint64_t raw_full[T_STAGES];  // per CTA: packed nibbles landed
   uint64_t group_done[T_RING];   // per CTA: MMAs of a scale group complete
   uint64_t acc_empty[2];         // even CTA: epilogue warps of both CTAs arrived
   uint32_t tmem_base;
@@ -180,9 +179,8 @@ __global__ void __launch_bounds__(T_THREADS, 1)
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < T_STAGES; ++s) {
-      mbar_init(&bars->x_full[s], 1);
+      mbar_init(&bars->ready[s], 1 + 2 * T_CONV_WARPS);  // producer's expect_tx + unpack warps
       mbar_init(&bars->raw_full[s], 1);
-      mbar_init(&bars->conv_full[s], 2 * T_CONV_WARPS);
     }
     for (int r = 0; r < T_RING; ++r) mbar_init(&bars->group_done[r], 1);
     for (int b = 0; b < 2; ++b) mbar_init(&bars->acc_empty[b], 2 * T_EPI_WARPS);
@@ -231,9 +229,9 @@ __global__ void __launch_bounds__(T_THREADS, 1)
           if (ok) {
             uint8_t* sx = smem + stage * T_STAGE_BYTES;
             uint8_t* sraw = sx + T_X_BYTES + T_W_BYTES;
-            const uint32_t x_full_even = map_to_cta(smem_u32(&bars->x_full[stage]), 0);
-            if (rank == 0) mbar_arrive_expect_tx(&bars->x_full[stage], 2 * T_X_BYTES);
-            tma_load_2d_pair(sx, &map_x, x_full_even, kb * T_BK, m0);
+            const uint32_t ready_even = map_to_cta(smem_u32(&bars->ready[stage]), 0);
+            if (rank == 0) mbar_arrive_expect_tx(&bars->ready[stage], 2 * T_X_BYTES);
+            tma_load_2d_pair(sx, &map_x, ready_even, kb * T_BK, m0);
             mbar_arrive_expect_tx(&bars->raw_full[stage], T_RAW_BYTES);
             tma_load_2d(sraw, &map_raw, &bars->raw_full[stage], kb * (T_BK / 2), n0);
           }
@@ -254,17 +252,15 @@ __global__ void __launch_bounds__(T_THREADS, 1)
         for (int g = 0; g < groups && ok; ++g, ++gc) {
           const int buf = gc & 1;
           if (lane == 0) {
-            ok = mbar_wait_cluster(&bars->acc_empty[buf], ((gc >> 1) & 1) ^ 1, abort_flag, status,
-                                   STATUS_TIMEOUT_TMEM_EMPTY);
+            ok = mbar_wait(&bars->acc_empty[buf], ((gc >> 1) & 1) ^ 1, abort_flag, status,
+                           STATUS_TIMEOUT_TMEM_EMPTY);
             tc_fence_after_sync();
           }
           ok = __shfl_sync(0xffffffffu, ok, 0);
           const uint32_t tmem_d = tmem_base + buf * 256;
           for (int kk = 0; kk < kb_per_group && ok; ++kk) {
             if (lane == 0) {
-              ok = mbar_wait(&bars->x_full[stage], phase, abort_flag, status, STATUS_TIMEOUT_FULL) &&
-                   mbar_wait_cluster(&bars->conv_full[stage], phase, abort_flag, status,
-                                     STATUS_TIMEOUT_FULL);
+              ok = mbar_wait(&bars->ready[stage], phase, abort_flag, status, STATUS_TIMEOUT_FULL);
               if (ok) {
                 tc_fence_after_sync();
                 const uint32_t sx = smem_u32(smem + stage * T_STAGE_BYTES);
@@ -315,7 +311,7 @@ __global__ void __launch_bounds__(T_THREADS, 1)
         }
         fence_proxy_async_smem();
         __syncwarp();
-        if (lane == 0) mbar_arrive_remote(map_to_cta(smem_u32(&bars->conv_full[stage]), 0));
+        if (lane == 0) mbar_arrive_remote(map_to_cta(smem_u32(&bars->ready[stage]), 0));
         if (++stage == T_STAGES) {
           stage = 0;
           phase ^= 1;
