@@ -70,6 +70,19 @@ int texo_mm_int8_solve_host(const int8_t* A_host, const int8_t* B_host, int8_t* 
                             int K, float scale_A, float scale_B, float scale_C, int zero_point_A,
                             int zero_point_B, int zero_point_C);
 
+/* Prepared weights for mm_int8 (no counterpart in the reference, which recomputes colsum(B)
+ * and a transposed copy of B on every call, src/mm_int8.cu:559-561).  prepare() computes
+ * colsum(B) once for a device-resident B [K,N] (asynchronously, default stream) and returns
+ * a handle; solve_prepared() is texo_mm_int8_solve with B, K, N taken from the handle and
+ * only the row sums of the new activations left to compute; results are bit-identical.  B
+ * must stay alive and unchanged until release().  prepare() returns NULL on bad arguments. */
+typedef struct texo_int8_weights texo_int8_weights;
+texo_int8_weights* texo_mm_int8_prepare_weights(const int8_t* B, int K, int N);
+void texo_mm_int8_release_weights(texo_int8_weights* weights);
+void texo_mm_int8_solve_prepared(const int8_t* A, const texo_int8_weights* weights, int8_t* C, int M,
+                                 float scale_A, float scale_B, float scale_C, int zero_point_A,
+                                 int zero_point_B, int zero_point_C);
+
 /* Tile-scale dequantization.  Replaces `solve` of the reference's
  * src/dequantization.cu:40-43 (tests/dequantization.cpp:4).  X, Y [M,N] fp32,
  * S [ceil(M/T), ceil(N/T)] fp32; Y = X * S[m/T][n/T]. */

@@ -227,6 +227,31 @@ def test_bounded_wait_reports_instead_of_hanging(lib, oracle):
     assert np.array_equal(run_case(lib, a, b, m, n, k, q), oracle.mm_int8(a, b, m, n, k, q))
 
 
+@pytest.mark.parametrize("kn", [(1024, 768), (2048, 1008), (100, 67)])
+def test_prepared_weights_match_the_stateless_call(lib, oracle, kn):
+    """colsum(B) cached with the weight handle: same bytes as `solve` for tensor-path,
+    decode-shaped and generic-path calls, across several activations and zero points."""
+    k, n = kn
+    rng = np.random.default_rng(31 + k)
+    b = rng.integers(-128, 128, (k, n), dtype=np.int8)
+    B = _dev(b)
+    handle = lib.texo_mm_int8_prepare_weights(B.data_ptr(), k, n)
+    assert handle
+    try:
+        for m in (300, 16, 129):
+            a = rng.integers(-128, 128, (m, k), dtype=np.int8)
+            A = _dev(a)
+            for q in ((0.02, 0.03, float(np.float32(0.02 * 0.03 * 160 * np.sqrt(k))), 3, -5, 1),
+                      (0.02, 0.03, float(np.float32(0.02 * 0.03 * 160 * np.sqrt(k))), 0, 4, -2)):
+                C = torch.full((m, n), 44, dtype=torch.int8, device="cuda")
+                lib.texo_mm_int8_solve_prepared(A.data_ptr(), handle, C.data_ptr(), m, *q)
+                torch.cuda.synchronize()
+                assert np.array_equal(C.cpu().numpy(), oracle.mm_int8(a, b, m, n, k, q)), (kn, m, q)
+    finally:
+        lib.texo_mm_int8_release_weights(handle)
+    assert lib.texo_mm_int8_status() == 0
+
+
 def test_wide_dot_on_tensor_path(lib, oracle):
     """K > 33025: |dot| can exceed int32, the epilogue must use 64-bit correction."""
     for m, n, k, want_path in ((128, 256, 33040, 2), (384, 256, 33040, 4)):

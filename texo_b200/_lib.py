@@ -24,6 +24,10 @@ _SIGNATURES = {
                                             _c_float, _c_float, _c_float, _c_int, _c_int, _c_int]),
     "texo_mm_int8_solve_host": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int,
                                          _c_float, _c_float, _c_float, _c_int, _c_int, _c_int]),
+    "texo_mm_int8_prepare_weights": (_c_ptr, [_c_ptr, _c_int, _c_int]),
+    "texo_mm_int8_release_weights": (None, [_c_ptr]),
+    "texo_mm_int8_solve_prepared": (None, [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_float, _c_float, _c_float,
+                                           _c_int, _c_int, _c_int]),
     "texo_mm_int4_solve": (None, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int]),
     "texo_dequantization_solve": (None, [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int]),
     "texo_mm_int8_last_path": (_c_int, []),

@@ -1295,8 +1295,10 @@ static bool launch_skinny(DeviceCtx& ctx, const int8_t* A, const int8_t* B, int8
   return true;
 }
 
+// `cached_col_sum` (may be null): colsum(B) computed earlier for these weights, padded to a
+// multiple of the 256-column tile; the pre-pass then only sums the rows of A.
 static bool launch_tensor(DeviceCtx& ctx, const int8_t* A, const int8_t* B, int8_t* C, int M, int N,
-                          int K, const Quant& q, int force) {
+                          int K, const Quant& q, int force, const int* cached_col_sum = nullptr) {
   static bool configured[MAX_DEVICES] = {};
   if (!configured[ctx.device]) {
     cudaFuncSetAttribute(umma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
@@ -1326,8 +1328,13 @@ static bool launch_tensor(DeviceCtx& ctx, const int8_t* A, const int8_t* B, int8
   const int c_vector_ok = (reinterpret_cast<uintptr_t>(C) & 15) == 0 && N % 16 == 0;
   const int pairs = (force == PATH_TENSOR || (force != PATH_TENSOR_PAIR && M <= BM))
                         ? 0 : max_active_pairs(ctx);
+  Quant sums_q = q;
+  if (cached_col_sum) {
+    sums_q.za = 0;  // nothing to do for the columns
+    col_sum = const_cast<int*>(cached_col_sum);
+  }
   const bool sums_launched =
-      launch_sums(A, B, row_sum, col_sum, M, N, K, q, pairs > 0 ? ctx.sm_count : 0);
+      launch_sums(A, B, row_sum, col_sum, M, N, K, sums_q, pairs > 0 ? ctx.sm_count : 0);
   const int slot = profile_start();
   if (pairs > 0) {
     const int tiles_m = (M + 255) / 256;
@@ -1405,6 +1412,72 @@ extern "C" void solve(const int8_t* A, const int8_t* B, int8_t* C, int M, int N,
     if (launch_tensor(ctx, A, B, C, M, N, K, q, force)) return;
   }
   launch_generic(A, B, C, M, N, K, q);
+}
+
+// ------------------------------------------------------------ prepared weights
+// Inference calls the same weights with new activations again and again; colsum(B) depends
+// on the weights only.  The reference recomputes it (together with a transposed copy of B)
+// on every call (src/mm_int8.cu:559-561 of frezcirno/Texo).  These entry points compute it
+// once per weight matrix and keep it with the handle, so a call only has to sum the rows of
+// the new activations.  B must stay alive and unchanged while the handle is in use.
+struct texo_int8_weights {
+  const int8_t* B;
+  int K, N, device;
+  int* col_sum;  // [ceil(N/256)*256] on `device`, or null when the tensor path cannot take B
+};
+
+extern "C" texo_int8_weights* texo_mm_int8_prepare_weights(const int8_t* B, int K, int N) {
+  using namespace texo;
+  using namespace texo::i8;
+  if (!B || K <= 0 || N <= 0) return nullptr;
+  DeviceCtx& ctx = device_ctx();
+  texo_int8_weights* w = new texo_int8_weights{B, K, N, ctx.device, nullptr};
+  const bool aligned = K < (1 << 17) && K % 16 == 0 && N % 16 == 0 &&
+                       (reinterpret_cast<uintptr_t>(B) & 15) == 0;
+  if (ctx.cc_major >= 10 && aligned) {
+    const size_t np = size_t((N + BN - 1) / BN) * BN;
+    if (cudaMalloc(&w->col_sum, np * sizeof(int)) != cudaSuccess) {
+      cudaGetLastError();
+      w->col_sum = nullptr;
+      return w;  // still usable: calls fall back to the stateless path
+    }
+    cudaMemsetAsync(w->col_sum, 0, np * sizeof(int), 0);
+    Quant only_cols = {1.f, 1.f, 1.f, 1, 0, 0};
+    launch_sums(nullptr, B, nullptr, w->col_sum, 0, N, K, only_cols, 0);
+  }
+  return w;
+}
+
+extern "C" void texo_mm_int8_release_weights(texo_int8_weights* w) {
+  if (!w) return;
+  if (w->col_sum) {
+    cudaDeviceSynchronize();  // calls that still read the sums must finish first
+    cudaFree(w->col_sum);
+  }
+  delete w;
+}
+
+// Same operation as `solve` with B, K, N taken from the handle.
+extern "C" void texo_mm_int8_solve_prepared(const int8_t* A, const texo_int8_weights* w, int8_t* C,
+                                            int M, float scale_A, float scale_B, float scale_C,
+                                            int zero_point_A, int zero_point_B, int zero_point_C) {
+  using namespace texo;
+  using namespace texo::i8;
+  if (!w || M <= 0) {
+    if (!w) note_host_error(STATUS_BAD_ARGUMENT);
+    return;
+  }
+  DeviceCtx& ctx = device_ctx();
+  const Quant q = {scale_A, scale_B, scale_C, zero_point_A, zero_point_B, zero_point_C};
+  const int force = forced_path();
+  if (w->col_sum && ctx.device == w->device && A && C && M > 32 && force != PATH_GENERIC &&
+      force != PATH_SKINNY && tensor_path_ok(A, w->B, M, w->N, w->K)) {
+    if (launch_tensor(ctx, A, w->B, C, M, w->N, w->K, q, force, w->col_sum)) return;
+  }
+  // decode shapes get colsum(B) for free inside the skinny kernel; everything else is the
+  // stateless path
+  solve(A, w->B, C, M, w->N, w->K, scale_A, scale_B, scale_C, zero_point_A, zero_point_B,
+        zero_point_C);
 }
 
 // Diagnostics (declared in include/texo_b200.h).

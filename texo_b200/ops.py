@@ -11,8 +11,8 @@ import torch
 
 from . import _lib
 
-__all__ = ["mm_int8", "mm_int4", "dequantization", "mm_int8_host", "last_path", "status",
-           "force_path"]
+__all__ = ["mm_int8", "mm_int4", "dequantization", "mm_int8_host", "Int8Weights", "last_path",
+           "status", "force_path"]
 
 
 def _check_cuda(name: str, t: torch.Tensor, dtype: torch.dtype) -> None:
@@ -131,6 +131,52 @@ def mm_int8_host(A_host: torch.Tensor, B_host: torch.Tensor, C_host: torch.Tenso
                                              zero_point_B, zero_point_C)
     if rc != 0:
         raise RuntimeError(f"texo_mm_int8_solve_host failed with code {rc}")
+
+
+class Int8Weights:
+    """A device-resident weight matrix B [K,N] prepared once for repeated mm_int8 calls: the
+    library computes colsum(B) at construction and reuses it, so each call only sums the rows
+    of its activations.  Results are bit-identical to `mm_int8`.  Keep B unchanged."""
+
+    def __init__(self, B: torch.Tensor):
+        _check_cuda("B", B, torch.int8)
+        if B.dim() != 2 or B.shape[0] <= 0 or B.shape[1] <= 0:
+            raise ValueError("B must be a non-empty [K, N] matrix")
+        self.B = B  # keeps the storage alive
+        self.K, self.N = B.shape
+        self._lib = _lib.load()
+        with torch.cuda.device(B.device), _DefaultStreamOrder(B.device):
+            self._handle = self._lib.texo_mm_int8_prepare_weights(B.data_ptr(), self.K, self.N)
+        if not self._handle:
+            raise RuntimeError("texo_mm_int8_prepare_weights failed")
+
+    def matmul(self, A: torch.Tensor, scale_A: float, scale_B: float, scale_C: float,
+               zero_point_A: int, zero_point_B: int, zero_point_C: int,
+               out: torch.Tensor | None = None) -> torch.Tensor:
+        _check_cuda("A", A, torch.int8)
+        if A.dim() != 2 or A.shape[1] != self.K:
+            raise ValueError(f"A must be [M, {self.K}]")
+        M = A.shape[0]
+        if out is None:
+            out = torch.empty((M, self.N), dtype=torch.int8, device=A.device)
+        else:
+            _check_cuda("out", out, torch.int8)
+        with torch.cuda.device(A.device), _DefaultStreamOrder(A.device):
+            self._lib.texo_mm_int8_solve_prepared(A.data_ptr(), self._handle, out.data_ptr(), M,
+                                                  scale_A, scale_B, scale_C, zero_point_A,
+                                                  zero_point_B, zero_point_C)
+        return out
+
+    def close(self) -> None:
+        if getattr(self, "_handle", None):
+            self._lib.texo_mm_int8_release_weights(self._handle)
+            self._handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
 
 
 def last_path(op: str = "mm_int8") -> int:
