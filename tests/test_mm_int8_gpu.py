@@ -191,6 +191,41 @@ def test_tensor_path_output_zero_point_and_saturation(lib, oracle):
         assert np.array_equal(got, oracle.mm_int8(a, b, m, n, k, q)), q
 
 
+def test_division_forms_agree_with_ieee_division(lib, oracle):
+    """The tensor kernels divide by scale_C with a branch-free Newton sequence when the scales
+    bound every numerator into its safe range, and with the IEEE division otherwise.  Both
+    must give the oracle's bits: awkward divisors (all-ones mantissa, powers of two, negative),
+    scales at the edges of the admitted range, and scales just outside it."""
+    rng = np.random.default_rng(77)
+    ones = float(np.nextafter(np.float32(2.0), np.float32(0.0)))  # mantissa all ones
+    quants = [
+        (0.02, 0.03, ones, 3, -5, 1), (0.02, 0.03, ones * 64, 3, -5, 1), (0.02, 0.03, -1.7, 3, -5, 1),
+        (-0.02, 0.03, 2.0, 0, 4, -3), (0.02, -0.03, 1.0, 5, 0, 0), (0.02, 0.03, float(np.float32(1 / 3)), 1, 1, 1),
+        (2.0 ** -30, 32.0, None, 3, -5, 1), (32.0, 2.0 ** -30, None, 3, -5, 1),  # edges, inside
+        (2.0 ** -31, 32.0, None, 3, -5, 1), (33.0, 0.03, None, 3, -5, 1),        # just outside
+        (0.02, 0.03, 2.0 ** -61, 3, -5, 1), (0.02, 0.03, 2.0 ** 61, 3, -5, 1),
+        (1.0e-20, 1.0e-20, 1.0e-38, 2, 2, 2),                                                # denormal numerators
+        (0.02, 0.03, None, 40000, -5, 1),                                                     # zero point beyond 2^15
+    ]
+    for (m, n, k), paths in (((256, 512, 1024), (2, 4)), ((16, 512, 1024), (3,)), ((32, 272, 2048), (3,))):
+        a = rng.integers(-128, 128, (m, k), dtype=np.int8)
+        b = rng.integers(-128, 128, (k, n), dtype=np.int8)
+        for q in quants:
+            if q[2] is None:  # a scale_C that leaves most outputs unsaturated
+                spread = 74.0 * (128 + abs(q[3])) * np.sqrt(k)
+                q = q[:2] + (abs(q[0] * q[1]) * spread / 40 * 1.37,) + q[3:]
+            q = tuple(float(np.float32(v)) for v in q[:3]) + q[3:]
+            want = oracle.mm_int8(a, b, m, n, k, q)
+            for force in paths:
+                lib.texo_mm_int8_force_path(force)
+                got = run_case(lib, a, b, m, n, k, q)
+                path = lib.texo_mm_int8_last_path()
+                lib.texo_mm_int8_force_path(0)
+                assert path == force
+                assert np.array_equal(got, want), ((m, n, k), q, force)
+    assert lib.texo_mm_int8_status() == 0
+
+
 @pytest.mark.parametrize("shape", [(1000, 768, 512), (2304, 512, 1024), (65, 67, 31), (17, 19, 0)])
 def test_host_buffer_entry_point(lib, oracle, shape):
     """texo_mm_int8_solve_host: pinned host operands, chunked upload / compute / download

@@ -48,25 +48,87 @@ __device__ __forceinline__ int requantize(float dot, float sa, float sb, float s
 struct Quant {
   float sa, sb, sc;
   int za, zb, zc;
+  float rsc;     // RN(1 / sc), for the branch-free division below
+  int fast_div;  // 1 when every quotient of this call is inside that division's safe range
 };
 
-// The same requantisation for four outputs at once, with the tail done in integers:
-// cvt.rni.s32 (saturating) -> saturating add of zC -> saturating pack to int8.  Identical to
-// the FP32 tail whenever |zC| <= 2^22: if |rint(acc)| < 2^24 the float add is exact and the
-// two agree; beyond that both forms saturate to the same end of [-128, 127].  Callers check
-// the zC bound (the contract says [-128, 127]).
-__device__ __forceinline__ uint32_t requantize4(const float (&dot)[4], float sa, float sb, float sc,
-                                                int zc) {
-  int r[4];
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const float acc = __fdiv_rn(__fmul_rn(__fmul_rn(dot[i], sa), sb), sc);
-    asm("add.sat.s32 %0, %1, %2;" : "=r"(r[i]) : "r"(__float2int_rn(acc)), "r"(zc));
+// Host side: fills the derived fields.  The branch-free division is exact only while no
+// intermediate leaves the normal range, so it is enabled when the scales bound every
+// possible numerator: a non-zero |dot| lies in [1, 2^49] (K < 2^17 terms of at most 2^32
+// with |zA|, |zB| <= 2^15), hence |dot * sA * sB| in [2^-60, 2^59] for |sA|, |sB| in
+// [2^-30, 2^5]; and |sC| in [2^-60, 2^60] keeps quotient and residuals normal.  |zC| <= 2^22
+// lets the tail run in integers (see requantize_fast).  Anything else (including NaN or
+// infinite scales) takes the plain IEEE division, element by element.
+inline Quant make_quant(float sa, float sb, float sc, int za, int zb, int zc, int K) {
+  Quant q = {sa, sb, sc, za, zb, zc, 0.f, 0};
+  auto within = [](float v, float lo, float hi) {
+    const float a = v < 0 ? -v : v;
+    return a >= lo && a <= hi;  // false for NaN
+  };
+  const bool ok = within(sa, 0x1p-30f, 0x1p5f) && within(sb, 0x1p-30f, 0x1p5f) &&
+                  within(sc, 0x1p-60f, 0x1p60f) && za >= -32768 && za <= 32768 && zb >= -32768 &&
+                  zb <= 32768 && zc >= -(1 << 22) && zc <= (1 << 22) && K < (1 << 17);
+  if (ok) {
+    q.rsc = 1.0f / sc;  // correctly rounded on the host
+    q.fast_div = 1;
   }
+  return q;
+}
+
+// x / sc, correctly rounded (identical to __fdiv_rn), for x and sc in the range make_quant
+// admits: two Newton corrections of x * RN(1/sc) with exact FMA residuals.  Unlike the IEEE
+// division sequence it has no slow-path branch, so the divisions of neighbouring outputs
+// interleave instead of running one dependent chain after the other.
+__device__ __forceinline__ float div_rn_inrange(float x, float sc, float rsc) {
+  const float q0 = __fmul_rn(x, rsc);
+  const float r0 = __fmaf_rn(-sc, q0, x);
+  const float q1 = __fmaf_rn(r0, rsc, q0);
+  const float r1 = __fmaf_rn(-sc, q1, x);
+  return __fmaf_rn(r1, rsc, q1);
+}
+
+// Requantisation with that division and the tail done in integers: cvt.rni.s32
+// (saturating) -> saturating add of zC; the caller saturates to int8.  Identical to the FP32
+// tail whenever |zC| <= 2^22: if |rint(acc)| < 2^24 the float add is exact and the two
+// agree; beyond that both forms saturate to the same end of [-128, 127].
+__device__ __forceinline__ int requantize_fast(float dot, const Quant& q) {
+  const float acc = div_rn_inrange(__fmul_rn(__fmul_rn(dot, q.sa), q.sb), q.sc, q.rsc);
+  int r;
+  asm("add.sat.s32 %0, %1, %2;" : "=r"(r) : "r"(__float2int_rn(acc)), "r"(q.zc));
+  return r;
+}
+__device__ __forceinline__ uint32_t pack_sat_s8(int r0, int r1, int r2, int r3) {
   uint32_t hi, out;
-  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(r[3]), "r"(r[2]), "r"(0));
-  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(out) : "r"(r[1]), "r"(r[0]), "r"(hi));
+  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(r3), "r"(r2), "r"(0));
+  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(out) : "r"(r1), "r"(r0), "r"(hi));
   return out;
+}
+
+// One thread's 32 consecutive accumulator columns -> 32 int8 in eight words: zero-point
+// identity, then requantisation.  `col_sum_at` points at colsum(B) of the first column
+// (read through L2: another grid may have produced it while this one was running).
+template <bool WIDE, bool FAST>
+__device__ __forceinline__ void requantize_chunk(
+    const uint32_t (&v)[32], const int* __restrict__ col_sum_at,
+    typename std::conditional<WIDE, long long, unsigned>::type row_term, const Quant& q,
+    uint32_t (&packed)[8]) {
+  using Wide = typename std::conditional<WIDE, long long, unsigned>::type;
+  using Signed = typename std::conditional<WIDE, long long, int>::type;
+  const float zc = float(q.zc);
+#pragma unroll
+  for (int g = 0; g < 8; ++g) {
+    int4 cs = make_int4(0, 0, 0, 0);
+    if (q.za != 0) cs = __ldcg(reinterpret_cast<const int4*>(col_sum_at + g * 4));
+    const int csv[4] = {cs.x, cs.y, cs.z, cs.w};
+    int r[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const Wide dot = Wide(Signed(int(v[g * 4 + e]))) + row_term - Wide(q.za) * Wide(csv[e]);
+      const float x = float(Signed(dot));
+      r[e] = FAST ? requantize_fast(x, q) : requantize(x, q.sa, q.sb, q.sc, zc);
+    }
+    packed[g] = pack_sat_s8(r[0], r[1], r[2], r[3]);
+  }
 }
 
 // -------------------------------------------------------------- generic path
@@ -468,9 +530,7 @@ __global__ void __launch_bounds__(MMA_THREADS, 1)
     const int quarter = warp % 4;  // TMEM lanes this warp may read: 32*quarter .. +31
     const int half = ew / 4;       // which 128 of the 256 accumulator columns
     using Wide = typename std::conditional<WIDE, long long, unsigned>::type;
-    using Signed = typename std::conditional<WIDE, long long, int>::type;
     const Wide offset = Wide(K) * Wide(q.za) * Wide(q.zb);
-    const float zc = float(q.zc);
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
@@ -496,21 +556,11 @@ __global__ void __launch_bounds__(MMA_THREADS, 1)
         tmem_ld_wait();
         if (n0 >= N) continue;  // warp-uniform
         uint32_t packed[8];
-#pragma unroll
-        for (int g = 0; g < 8; ++g) {
-          int4 cs = make_int4(0, 0, 0, 0);
-          // col_sum is padded to a multiple of BN, so this never reads out of bounds.
-          if (q.za != 0) cs = __ldg(reinterpret_cast<const int4*>(col_sum + n0 + g * 4));
-          const int csv[4] = {cs.x, cs.y, cs.z, cs.w};
-          uint32_t word = 0;
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const Wide dot = Wide(Signed(int(v[g * 4 + e]))) + row_term - Wide(q.za) * Wide(csv[e]);
-            const int r = requantize(float(Signed(dot)), q.sa, q.sb, q.sc, zc);
-            word |= uint32_t(r & 0xff) << (8 * e);
-          }
-          packed[g] = word;
-        }
+        // col_sum is padded to a multiple of BN, so this never reads out of bounds.
+        if (q.fast_div)
+          requantize_chunk<WIDE, true>(v, col_sum + n0, row_term, q, packed);
+        else
+          requantize_chunk<WIDE, false>(v, col_sum + n0, row_term, q, packed);
         if (row_ok) {
           if (c_vector_ok && n0 + 32 <= N) {
             int4* dst = reinterpret_cast<int4*>(c_row + n0);
@@ -592,9 +642,6 @@ __device__ __forceinline__ void drain_half(uint32_t tmem_row_addr, int col0, int
                                            const int* __restrict__ col_sum, int N, int K,
                                            const Quant& q, int c_vector_ok) {
   using Wide = typename std::conditional<WIDE, long long, unsigned>::type;
-  using Signed = typename std::conditional<WIDE, long long, int>::type;
-  const float zc = float(q.zc);
-  const bool int_tail = q.zc >= -(1 << 22) && q.zc <= (1 << 22);
   Wide row_term = Wide(K) * Wide(q.za) * Wide(q.zb);
   if (row_ok && q.zb != 0) row_term -= Wide(q.zb) * Wide(__ldcg(row_sum + m));
   int8_t* c_row = C + size_t(row_ok ? m : 0) * N;
@@ -607,29 +654,11 @@ __device__ __forceinline__ void drain_half(uint32_t tmem_row_addr, int col0, int
     tmem_ld_wait();
     if (n0 >= N) continue;  // warp-uniform
     uint32_t packed[8];
-#pragma unroll
-    for (int g = 0; g < 8; ++g) {
-      int4 cs = make_int4(0, 0, 0, 0);
-      // col_sum is padded to a multiple of the tile width: never out of bounds.  Read
-      // through L2: the values were written by another grid that overlapped this one.
-      if (q.za != 0) cs = __ldcg(reinterpret_cast<const int4*>(col_sum + n0 + g * 4));
-      const int csv[4] = {cs.x, cs.y, cs.z, cs.w};
-      float dots[4];
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const Wide dot = Wide(Signed(int(v[g * 4 + e]))) + row_term - Wide(q.za) * Wide(csv[e]);
-        dots[e] = float(Signed(dot));
-      }
-      if (int_tail) {
-        packed[g] = requantize4(dots, q.sa, q.sb, q.sc, q.zc);
-      } else {
-        uint32_t word = 0;
-#pragma unroll
-        for (int e = 0; e < 4; ++e)
-          word |= uint32_t(requantize(dots[e], q.sa, q.sb, q.sc, zc) & 0xff) << (8 * e);
-        packed[g] = word;
-      }
-    }
+    // col_sum is padded to a multiple of the tile width: never out of bounds.
+    if (q.fast_div)
+      requantize_chunk<WIDE, true>(v, col_sum + n0, row_term, q, packed);
+    else
+      requantize_chunk<WIDE, false>(v, col_sum + n0, row_term, q, packed);
     if (row_ok) {
       if (c_vector_ok && n0 + 32 <= N) {
         int4* dst = reinterpret_cast<int4*>(c_row + n0);
@@ -816,29 +845,42 @@ __global__ void __launch_bounds__(MMA_THREADS, 1)
 // kernel start), so column R of the accumulator is colsum(B) for free and B is never read a
 // second time.
 //
-// Schedule (one CTA per SM, T = ceil(N/128) column tiles, G CTAs): every CTA owns
+// A column tile is 256 columns = two 128-column boxes side by side, loaded back to back for
+// the same 128 k rows (ring slot i takes the left box, slot i+1 the right one, each with its
+// own accumulator half): HBM then sees 256 contiguous bytes per row instead of 128, which
+// measured 6.0 TB/s against 4.3 TB/s for the same bytes fetched as lone 128-byte rows.
+//
+// Schedule (one CTA per SM, T = ceil(N/256) column tiles, G CTAs): every CTA owns
 // P = T / G whole tiles (tile p*G + c, so neighbouring CTAs stream neighbouring columns) and
 // the remaining S = T - P*G tiles are cut stream-K style into equal contiguous ranges of
 // (tile, k block) units, so every SM pulls the same number of bytes.  The shared ranges are
 // processed FIRST: a CTA adds its int32 partials into a zero-initialised workspace with
 // integer reductions (order-independent, hence still bit-exact); whoever arrives last at
-// the tile's counter reads the sums, requantises, and puts workspace and counter back to
+// the half tile's counter reads the sums, requantises, and puts workspace and counter back to
 // zero - all while its producer and MMA warps are already streaming the next tile.  The
 // owned tiles come LAST and need no reduction, so the kernel's tail is a plain drain.
 // Nobody ever waits for another CTA.
-// Shared memory is kept under half an SM (two CTAs fit side by side) so that the next call's
-// kernel, launched with programmatic stream serialisation, can already sit on the SM with its
-// set-up done while this one drains: back-to-back decode calls then lose neither the launch
-// gap nor the prologue.  M <= 16: 5 stages of 16 KiB weights + 4 KiB activations; M <= 32: 4
-// stages of 16 KiB + 8 KiB.
-constexpr int S_MAX_STAGES = 5;
-constexpr int S_W_BYTES = 128 * 128;  // one 128 k-row x 128 column box of B
+// Nearly all of an SM's shared memory goes to the ring (M <= 16: 6 stages of 32 KiB weights +
+// 4 KiB activations; 16 < M <= 32: 5 stages of 32 KiB + 6 KiB): each SM has to keep about
+// 100 KiB in flight to cover HBM latency at its share of the bandwidth, and a ring that deep
+// measured faster than a shallow one that would let two CTAs share an SM.  The kernel is
+// launched with programmatic stream serialisation all the same: the next call's CTA starts on
+// an SM as soon as this call's CTA there has exited (at once on SMs the grid left idle) and
+// does its set-up while the slowest CTAs of this call finish.
+// When the tiles divide evenly over at least three quarters of the SMs the grid is shrunk to
+// that count, so nothing is shared and no reduction runs at all: 112 CTAs streaming one
+// 256-column tile each reach the same HBM rate as 148 and finish without a flush.
+constexpr int S_MAX_STAGES = 6;
+constexpr int S_BOX_BYTES = 128 * 128;     // one 128 k-row x 128 column box of B
+constexpr int S_W_BYTES = 2 * S_BOX_BYTES;  // the two boxes of a 256-column tile
 constexpr int S_ACC_COLS = 64;  // TMEM columns per accumulator (M + ones + padding <= 48)
-constexpr int S_TMEM_COLS = 2 * S_ACC_COLS;  // double buffered
-constexpr int S_SMEM_BYTES = 100 * 1024 + 1024 + 512;
-__host__ __device__ constexpr int skinny_act_bytes(int R) { return R == 16 ? 4096 : 8192; }
-__host__ __device__ constexpr int skinny_stages(int R) { return R == 16 ? 5 : 4; }
-constexpr int S_TILE_N = 128;
+constexpr int S_TMEM_COLS = 4 * S_ACC_COLS;  // two halves per tile, double buffered
+__host__ __device__ constexpr int skinny_act_bytes(int R) { return (R + 16) * 128; }
+__host__ __device__ constexpr int skinny_stages(int R) { return R == 16 ? 6 : 5; }
+__host__ __device__ constexpr int skinny_smem_bytes(int R) {
+  return skinny_stages(R) * (S_W_BYTES + skinny_act_bytes(R)) + 1024 + 512;
+}
+constexpr int S_TILE_N = 256;  // two 128-column boxes side by side, see above
 constexpr int S_EPI_WARPS = 4;
 constexpr int S_THREADS = 64 + S_EPI_WARPS * 32;
 
@@ -909,6 +951,26 @@ struct SkinnySchedule {
   }
 };
 
+// Requantises ROWS accumulator rows of one output column and stores the first M of them.  All
+// rows are computed without a branch (rows past M hold zeros), so their dependent chains
+// (64-bit correction, int-to-float, two multiplies, an IEEE division, round, saturate)
+// interleave; with one warp per scheduler a per-row branch would run them back to back.
+template <int ROWS, bool FAST>
+__device__ __forceinline__ void skinny_store_rows(const uint32_t (&v)[32], const int* row_sum,
+                                                  long long base, const Quant& q, float zc, int M,
+                                                  int8_t* out, size_t stride) {
+  int r[ROWS];
+#pragma unroll
+  for (int m = 0; m < ROWS; ++m) {
+    const long long dot = (long long)int(v[m]) - (long long)q.zb * row_sum[m] + base;
+    r[m] = FAST ? min(max(requantize_fast(float(dot), q), -128), 127)
+                : requantize(float(dot), q.sa, q.sb, q.sc, zc);
+  }
+#pragma unroll
+  for (int m = 0; m < ROWS; ++m)
+    if (m < M) out[m * stride] = int8_t(r[m]);
+}
+
 __global__ void __launch_bounds__(S_THREADS, 1)
     skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_act,
                   const int8_t* __restrict__ A, int8_t* __restrict__ C, int* __restrict__ workspace,
@@ -921,7 +983,7 @@ __global__ void __launch_bounds__(S_THREADS, 1)
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int S_STAGES = skinny_stages(R);
   const int S_STAGE_BYTES = S_W_BYTES + skinny_act_bytes(R);
-  SkinnyBarriers* bars = reinterpret_cast<SkinnyBarriers*>(smem + 100 * 1024);
+  SkinnyBarriers* bars = reinterpret_cast<SkinnyBarriers*>(smem + S_STAGES * S_STAGE_BYTES);
   volatile int* abort_flag = &bars->abort_flag;
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   const int num_kb = (K + BK - 1) / BK;
@@ -949,7 +1011,7 @@ __global__ void __launch_bounds__(S_THREADS, 1)
   if (warp == 0) {
     __syncwarp();
     // Everything up to here touched only shared memory.  From here on global memory is read:
-    // wait for the grids ahead of this one in the stream (no-op without such a dependency).
+    // wait for the grids ahead of this one (no-op without such a dependency).
     asm volatile("griddepcontrol.wait;" ::: "memory");
     for (int i = 0; i < S_STAGES; ++i) {
       if (p_kb == p_kb1 && !prod_sched.next(p_tile, p_kb, p_kb1, p_shared)) break;
@@ -957,6 +1019,7 @@ __global__ void __launch_bounds__(S_THREADS, 1)
         uint8_t* sw = smem + p_stage * S_STAGE_BYTES;
         mbar_arrive_expect_tx(&bars->full[p_stage], S_W_BYTES + R * 128);
         tma_load_2d(sw, &map_w, &bars->full[p_stage], p_tile * S_TILE_N, p_kb * BK);
+        tma_load_2d(sw + S_BOX_BYTES, &map_w, &bars->full[p_stage], p_tile * S_TILE_N + 128, p_kb * BK);
         tma_load_2d(sw + S_W_BYTES, &map_act, &bars->full[p_stage], p_kb * BK, 0);
       }
       ++p_kb;
@@ -998,6 +1061,7 @@ __global__ void __launch_bounds__(S_THREADS, 1)
           uint8_t* sw = smem + p_stage * S_STAGE_BYTES;
           mbar_arrive_expect_tx(&bars->full[p_stage], S_W_BYTES + R * 128);
           tma_load_2d(sw, &map_w, &bars->full[p_stage], p_tile * S_TILE_N, p_kb * BK);
+          tma_load_2d(sw + S_BOX_BYTES, &map_w, &bars->full[p_stage], p_tile * S_TILE_N + 128, p_kb * BK);
           tma_load_2d(sw + S_W_BYTES, &map_act, &bars->full[p_stage], p_kb * BK, 0);
         }
       }
@@ -1028,7 +1092,6 @@ __global__ void __launch_bounds__(S_THREADS, 1)
         tc_fence_after_sync();
       }
       ok = __shfl_sync(0xffffffffu, ok, 0);
-      const uint32_t tmem_d = tmem_base + buf * S_ACC_COLS;
       for (int kb = kb0; kb < kb1 && ok; ++kb) {
         if (lane == 0) {
           ok = mbar_wait(&bars->full[stage], phase, abort_flag, status, STATUS_TIMEOUT_FULL);
@@ -1037,10 +1100,15 @@ __global__ void __launch_bounds__(S_THREADS, 1)
             const uint32_t sw = smem_u32(smem + stage * S_STAGE_BYTES);
             const uint32_t sact = sw + S_W_BYTES;
 #pragma unroll
-            for (int j = 0; j < BK / UMMA_K; ++j) {
-              const uint64_t da = smem_desc(sw + j * UMMA_K * 128, 16, 1024, SMEM_SWIZZLE_128B);
-              const uint64_t db = smem_desc(sact + j * UMMA_K, 16, 1024, SMEM_SWIZZLE_128B);
-              umma_i8(tmem_d, da, db, idesc, (kb == kb0 && j == 0) ? 0u : 1u);
+            for (int half = 0; half < 2; ++half) {
+              const uint32_t tmem_d = tmem_base + (buf * 2 + half) * S_ACC_COLS;
+#pragma unroll
+              for (int j = 0; j < BK / UMMA_K; ++j) {
+                const uint64_t da = smem_desc(sw + half * S_BOX_BYTES + j * UMMA_K * 128, 16, 1024,
+                                              SMEM_SWIZZLE_128B);
+                const uint64_t db = smem_desc(sact + j * UMMA_K, 16, 1024, SMEM_SWIZZLE_128B);
+                umma_i8(tmem_d, da, db, idesc, (kb == kb0 && j == 0) ? 0u : 1u);
+              }
             }
             umma_commit(&bars->empty[stage]);
           }
@@ -1105,67 +1173,79 @@ __global__ void __launch_bounds__(S_THREADS, 1)
       }
       if (!ok) break;
       tc_fence_after_sync();
-      uint32_t v[32];   // accumulator columns 0..31: dot rows m (and colsum at column 16 when R = 16)
-      uint32_t cs_raw;  // colsum(B) for this thread's column
-      {
-        const uint32_t taddr = tmem_base + buf * S_ACC_COLS + (uint32_t(quarter * 32) << 16);
-        tmem_ld_32x32(taddr, v);
-        uint32_t hi[16];
-        if (R == 32) tmem_ld_32x16(taddr + 32, hi);
-        tmem_ld_wait();
-        cs_raw = (R == 32) ? hi[0] : v[16];
-      }
-      // the accumulator is in registers: hand the TMEM buffer back right away
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bars->acc_empty[buf]);
+      const int cur = buf;
       if (++buf == 2) {
         buf = 0;
         buf_phase ^= 1;
       }
-      const int n_local = quarter * 32 + lane;  // column within the tile
-      const int n = tile * S_TILE_N + n_local;
-      bool finalize = shared_index < 0;
-      if (shared_index >= 0) {
-        int* ws = workspace + size_t(shared_index) * ws_rows * S_TILE_N;
-#pragma unroll
-        for (int m = 0; m < 32; ++m)
-          if (m < M) atomicAdd(ws + m * S_TILE_N + n_local, int(v[m]));
-        if (q.za != 0) atomicAdd(ws + M * S_TILE_N + n_local, int(cs_raw));
-        __threadfence();
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (et == 0) {
-          const int contributors = sched.contributors(shared_index);
-          const int before = atomicAdd(&counters[shared_index], 1);
-          bars->last_flag = (before == contributors - 1);
-          if (before == contributors - 1) counters[shared_index] = 0;
+#pragma unroll 1
+      for (int half = 0; half < 2; ++half) {
+        uint32_t v[32];   // accumulator columns 0..31: dot rows m (and colsum at column 16 when R = 16)
+        uint32_t cs_raw;  // colsum(B) for this thread's column
+        {
+          const uint32_t taddr =
+              tmem_base + (cur * 2 + half) * S_ACC_COLS + (uint32_t(quarter * 32) << 16);
+          tmem_ld_32x32(taddr, v);
+          uint32_t hi[16];
+          if (R == 32) tmem_ld_32x16(taddr + 32, hi);
+          tmem_ld_wait();
+          cs_raw = (R == 32) ? hi[0] : v[16];
         }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        finalize = bars->last_flag != 0;
-        if (finalize) {
-          __threadfence();
+        if (half == 1) {
+          // both halves are in registers or already flushed: hand the TMEM buffer back
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bars->acc_empty[cur]);
+        }
+        const int n_local = quarter * 32 + lane;  // column within the 128-column half
+        const int n = tile * S_TILE_N + half * 128 + n_local;
+        bool finalize = shared_index < 0;
+        if (shared_index >= 0) {
+          const int slot = shared_index * 2 + half;
+          int* ws = workspace + size_t(slot) * ws_rows * 128;
 #pragma unroll
           for (int m = 0; m < 32; ++m)
-            if (m < M) {
-              v[m] = uint32_t(__ldcg(ws + m * S_TILE_N + n_local));
-              __stcg(ws + m * S_TILE_N + n_local, 0);
+            if (m < M) atomicAdd(ws + m * 128 + n_local, int(v[m]));
+          if (q.za != 0) atomicAdd(ws + M * 128 + n_local, int(cs_raw));
+          __threadfence();
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (et == 0) {
+            const int contributors = sched.contributors(shared_index);
+            const int before = atomicAdd(&counters[slot], 1);
+            bars->last_flag = (before == contributors - 1);
+            if (before == contributors - 1) counters[slot] = 0;
+          }
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          finalize = bars->last_flag != 0;
+          if (finalize) {
+            __threadfence();
+#pragma unroll
+            for (int m = 0; m < 32; ++m)
+              if (m < M) {
+                v[m] = uint32_t(__ldcg(ws + m * 128 + n_local));
+                __stcg(ws + m * 128 + n_local, 0);
+              }
+            if (q.za != 0) {
+              cs_raw = uint32_t(__ldcg(ws + M * 128 + n_local));
+              __stcg(ws + M * 128 + n_local, 0);
             }
-          if (q.za != 0) {
-            cs_raw = uint32_t(__ldcg(ws + M * S_TILE_N + n_local));
-            __stcg(ws + M * S_TILE_N + n_local, 0);
+          }
+          asm volatile("bar.sync 1, 128;" ::: "memory");  // last_flag is rewritten by the next half
+        }
+        if (finalize && n < N) {
+          const long long base = offset - (long long)q.za * int(cs_raw);
+          if (R == 16) {
+            if (q.fast_div)
+              skinny_store_rows<16, true>(v, bars->row_sum, base, q, zc, M, C + n, size_t(N));
+            else
+              skinny_store_rows<16, false>(v, bars->row_sum, base, q, zc, M, C + n, size_t(N));
+          } else {
+            if (q.fast_div)
+              skinny_store_rows<32, true>(v, bars->row_sum, base, q, zc, M, C + n, size_t(N));
+            else
+              skinny_store_rows<32, false>(v, bars->row_sum, base, q, zc, M, C + n, size_t(N));
           }
         }
-        asm volatile("bar.sync 1, 128;" ::: "memory");  // last_flag may be rewritten next segment
-      }
-      if (finalize && n < N) {
-        const long long col_term = (long long)q.za * int(cs_raw);
-#pragma unroll
-        for (int m = 0; m < 32; ++m)
-          if (m < M) {
-            const long long dot =
-                (long long)int(v[m]) - (long long)q.zb * bars->row_sum[m] - col_term + offset;
-            C[size_t(m) * N + n] = int8_t(requantize(float(dot), q.sa, q.sb, q.sc, zc));
-          }
       }
     }
   }
@@ -1244,7 +1324,8 @@ static bool launch_skinny(DeviceCtx& ctx, const int8_t* A, const int8_t* B, int8
                           int K, const Quant& q) {
   static bool configured[MAX_DEVICES] = {};
   if (!configured[ctx.device]) {
-    cudaFuncSetAttribute(skinny_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S_SMEM_BYTES);
+    cudaFuncSetAttribute(skinny_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         skinny_smem_bytes(16));
     configured[ctx.device] = true;
   }
   const int R = M <= 16 ? 16 : 32;
@@ -1259,19 +1340,25 @@ static bool launch_skinny(DeviceCtx& ctx, const int8_t* A, const int8_t* B, int8
   const int tiles = (N + S_TILE_N - 1) / S_TILE_N;
   const int num_kb = (K + BK - 1) / BK;
   const long long units = (long long)tiles * num_kb;
-  const int grid = int(std::min<long long>(units, ctx.sm_count));
+  int grid = int(std::min<long long>(units, ctx.sm_count));
+  {
+    // p whole tiles per CTA and nothing shared, if that keeps >= 3/4 of the SMs streaming.
+    const int per_cta = (tiles + ctx.sm_count - 1) / ctx.sm_count;
+    if (tiles % per_cta == 0 && (tiles / per_cta) * 4 >= ctx.sm_count * 3) grid = tiles / per_cta;
+  }
   // Tiles that are split between CTAs (see the schedule above) need the workspace:
-  // counters[shared] (padded) | partial sums [shared][M+1][128] int32.
+  // counters[shared][2] (padded) | partial sums [shared][2][M+1][128] int32, one slot per
+  // 128-column half.
   const int shared_tiles = tiles - tiles / grid * grid;
-  const size_t counter_bytes = (size_t(shared_tiles) * 4 + 255) & ~size_t(255);
-  const size_t ws_bytes = size_t(shared_tiles) * (M + 1) * S_TILE_N * 4;
+  const size_t counter_bytes = (size_t(shared_tiles) * 2 * 4 + 255) & ~size_t(255);
+  const size_t ws_bytes = size_t(shared_tiles) * 2 * (M + 1) * 128 * 4;
   uint8_t* base = static_cast<uint8_t*>(device_workspace(ctx, counter_bytes + ws_bytes + 256));
   if (!base) return false;
   const int slot = profile_start();
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
   cfg.blockDim = dim3(S_THREADS);
-  cfg.dynamicSmemBytes = S_SMEM_BYTES;
+  cfg.dynamicSmemBytes = skinny_smem_bytes(R);
   cfg.stream = 0;
   cudaLaunchAttribute attr;
   attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -1403,7 +1490,7 @@ extern "C" void solve(const int8_t* A, const int8_t* B, int8_t* C, int M, int N,
     return;
   }
   DeviceCtx& ctx = device_ctx();
-  const Quant q = {scale_A, scale_B, scale_C, zero_point_A, zero_point_B, zero_point_C};
+  const Quant q = make_quant(scale_A, scale_B, scale_C, zero_point_A, zero_point_B, zero_point_C, K);
   const int force = forced_path();
   if (force != PATH_GENERIC && ctx.cc_major >= 10 && tensor_path_ok(A, B, M, N, K)) {
     if (M <= 32 && (force == PATH_AUTO || force == PATH_SKINNY) &&
@@ -1468,7 +1555,8 @@ extern "C" void texo_mm_int8_solve_prepared(const int8_t* A, const texo_int8_wei
     return;
   }
   DeviceCtx& ctx = device_ctx();
-  const Quant q = {scale_A, scale_B, scale_C, zero_point_A, zero_point_B, zero_point_C};
+  const Quant q =
+      make_quant(scale_A, scale_B, scale_C, zero_point_A, zero_point_B, zero_point_C, w->K);
   const int force = forced_path();
   if (w->col_sum && ctx.device == w->device && A && C && M > 32 && force != PATH_GENERIC &&
       force != PATH_SKINNY && tensor_path_ok(A, w->B, M, w->N, w->K)) {
@@ -1573,7 +1661,7 @@ extern "C" int texo_mm_int8_solve_noalloc(const int8_t* A, const int8_t* B, int8
   }
   NoAllocDevice* dev = noalloc_device();
   if (!dev) return -3;
-  const Quant q = {scale_A, scale_B, scale_C, zero_point_A, zero_point_B, zero_point_C};
+  const Quant q = make_quant(scale_A, scale_B, scale_C, zero_point_A, zero_point_B, zero_point_C, K);
   if (dev->cc_major >= 10 && tensor_path_ok(A, B, M, N, K)) {
     CUtensorMap map_a, map_b;
     if (make_tensor_map_2d(&map_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, A, M, K, K, BM, BK,
