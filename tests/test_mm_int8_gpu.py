@@ -287,6 +287,36 @@ def test_prepared_weights_match_the_stateless_call(lib, oracle, kn):
     assert lib.texo_mm_int8_status() == 0
 
 
+def test_prepared_decode_calls_chained_without_sync(lib, oracle):
+    """Decode calls through a weight handle load their first weights before the previous call
+    on the stream has completed; activations and outputs must still be ordered.  A chain of
+    calls with no synchronisation in between, each with activations written on the stream
+    just before it (a device copy) and its own output, is checked call by call."""
+    rng = np.random.default_rng(5)
+    for m, n, k in ((16, 7168, 2048), (32, 3584, 1024), (5, 1008, 4096)):
+        b = rng.integers(-128, 128, (k, n), dtype=np.int8)
+        B = _dev(b)
+        handle = lib.texo_mm_int8_prepare_weights(B.data_ptr(), k, n)
+        assert handle
+        try:
+            acts = [rng.integers(-128, 128, (m, k), dtype=np.int8) for _ in range(6)]
+            staged = [_dev(a) for a in acts]
+            A = torch.zeros((m, k), dtype=torch.int8, device="cuda")
+            outs = [torch.full((m, n), 44, dtype=torch.int8, device="cuda") for _ in acts]
+            q = (0.02, 0.03, float(np.float32(0.02 * 0.03 * 160 * np.sqrt(k))), 3, -5, 1)
+            torch.cuda.synchronize()
+            for src, C in zip(staged, outs):
+                A.copy_(src)  # same activation buffer every call, rewritten on the stream
+                lib.texo_mm_int8_solve_prepared(A.data_ptr(), handle, C.data_ptr(), m, *q)
+                assert lib.texo_mm_int8_last_path() == 3
+            torch.cuda.synchronize()
+            for a, C in zip(acts, outs):
+                assert np.array_equal(C.cpu().numpy(), oracle.mm_int8(a, b, m, n, k, q)), (m, n, k)
+        finally:
+            lib.texo_mm_int8_release_weights(handle)
+    assert lib.texo_mm_int8_status() == 0
+
+
 def test_wide_dot_on_tensor_path(lib, oracle):
     """K > 33025: |dot| can exceed int32, the epilogue must use 64-bit correction."""
     for m, n, k, want_path in ((128, 256, 33040, 2), (384, 256, 33040, 4)):

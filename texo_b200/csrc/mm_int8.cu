@@ -974,7 +974,8 @@ __device__ __forceinline__ void skinny_store_rows(const uint32_t (&v)[32], const
 __global__ void __launch_bounds__(S_THREADS, 1)
     skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_act,
                   const int8_t* __restrict__ A, int8_t* __restrict__ C, int* __restrict__ workspace,
-                  int* __restrict__ counters, int M, int N, int K, Quant q, int R, int* status) {
+                  int* __restrict__ counters, int M, int N, int K, Quant q, int R,
+                  int weights_stable, int* status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~uintptr_t(1023));
@@ -1010,16 +1011,45 @@ __global__ void __launch_bounds__(S_THREADS, 1)
   }
   if (warp == 0) {
     __syncwarp();
-    // Everything up to here touched only shared memory.  From here on global memory is read:
-    // wait for the grids ahead of this one (no-op without such a dependency).
+    // The grid ahead of this one in the stream is still finishing (its slowest SMs end several
+    // microseconds after its fastest, and its completion takes a couple more to reach this
+    // grid).  Use that time for the first ring fill of weights.  With prepared weights the
+    // caller has promised that B does not change, so the boxes are loaded into shared memory
+    // right away and only the activations wait.  Otherwise B might be the output of that
+    // grid, and all that is safe is a hint: an L2 prefetch brings nothing into the SM, and L2
+    // is the point of coherence for every SM's global accesses, so it is harmless even if B
+    // were still being written; the loads proper then start after griddepcontrol.wait and
+    // find their data in L2.
+    if (lane == 0) {
+      SkinnySchedule early(tiles, num_kb, gridDim.x, blockIdx.x);
+      int e_tile = 0, e_kb = 0, e_kb1 = 0, e_shared = -1;
+      for (int i = 0; i < S_STAGES; ++i) {
+        if (e_kb == e_kb1 && !early.next(e_tile, e_kb, e_kb1, e_shared)) break;
+        if (weights_stable) {
+          uint8_t* sw = smem + i * S_STAGE_BYTES;
+          mbar_arrive_expect_tx(&bars->full[i], S_W_BYTES + R * 128);
+          tma_load_2d(sw, &map_w, &bars->full[i], e_tile * S_TILE_N, e_kb * BK);
+          tma_load_2d(sw + S_BOX_BYTES, &map_w, &bars->full[i], e_tile * S_TILE_N + 128, e_kb * BK);
+        } else {
+          tma_prefetch_l2_2d(&map_w, e_tile * S_TILE_N, e_kb * BK);
+          tma_prefetch_l2_2d(&map_w, e_tile * S_TILE_N + 128, e_kb * BK);
+        }
+        ++e_kb;
+      }
+    }
+    __syncwarp();
+    // From here on memory that the grids ahead may have written is read: wait for them (no-op
+    // without such a dependency).
     asm volatile("griddepcontrol.wait;" ::: "memory");
     for (int i = 0; i < S_STAGES; ++i) {
       if (p_kb == p_kb1 && !prod_sched.next(p_tile, p_kb, p_kb1, p_shared)) break;
       if (lane == 0) {
         uint8_t* sw = smem + p_stage * S_STAGE_BYTES;
-        mbar_arrive_expect_tx(&bars->full[p_stage], S_W_BYTES + R * 128);
-        tma_load_2d(sw, &map_w, &bars->full[p_stage], p_tile * S_TILE_N, p_kb * BK);
-        tma_load_2d(sw + S_BOX_BYTES, &map_w, &bars->full[p_stage], p_tile * S_TILE_N + 128, p_kb * BK);
+        if (!weights_stable) {
+          mbar_arrive_expect_tx(&bars->full[p_stage], S_W_BYTES + R * 128);
+          tma_load_2d(sw, &map_w, &bars->full[p_stage], p_tile * S_TILE_N, p_kb * BK);
+          tma_load_2d(sw + S_BOX_BYTES, &map_w, &bars->full[p_stage], p_tile * S_TILE_N + 128, p_kb * BK);
+        }
         tma_load_2d(sw + S_W_BYTES, &map_act, &bars->full[p_stage], p_kb * BK, 0);
       }
       ++p_kb;
@@ -1320,8 +1350,10 @@ static int max_active_pairs(DeviceCtx& ctx) {
 }
 
 // Skinny (decode) path: M <= 32.
+// `weights_stable`: the caller guarantees that B has not been written since before the
+// previous call on this stream started (prepared weights), see the kernel's first ring fill.
 static bool launch_skinny(DeviceCtx& ctx, const int8_t* A, const int8_t* B, int8_t* C, int M, int N,
-                          int K, const Quant& q) {
+                          int K, const Quant& q, int weights_stable = 0) {
   static bool configured[MAX_DEVICES] = {};
   if (!configured[ctx.device]) {
     cudaFuncSetAttribute(skinny_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -1370,7 +1402,7 @@ static bool launch_skinny(DeviceCtx& ctx, const int8_t* A, const int8_t* B, int8
   for (int attempt = 0; attempt < 2; ++attempt) {
     cfg.numAttrs = (overlap_ok && attempt == 0) ? 1 : 0;
     if (cudaLaunchKernelEx(&cfg, skinny_kernel, map_w, map_act, A, C, ws, counters, M, N, K, q, R,
-                           ctx.status) == cudaSuccess ||
+                           weights_stable, ctx.status) == cudaSuccess ||
         cfg.numAttrs == 0)
       break;
     cudaGetLastError();  // attribute refused: launch again, fully serialised
@@ -1562,8 +1594,14 @@ extern "C" void texo_mm_int8_solve_prepared(const int8_t* A, const texo_int8_wei
       force != PATH_SKINNY && tensor_path_ok(A, w->B, M, w->N, w->K)) {
     if (launch_tensor(ctx, A, w->B, C, M, w->N, w->K, q, force, w->col_sum)) return;
   }
-  // decode shapes get colsum(B) for free inside the skinny kernel; everything else is the
-  // stateless path
+  // Decode shapes get colsum(B) for free inside the skinny kernel; what the handle adds
+  // there is the promise that B is unchanged, so the kernel may load weights before the
+  // previous call on the stream has completed.
+  if (ctx.device == w->device && A && C && M <= 32 && ctx.cc_major >= 10 &&
+      (force == PATH_AUTO || force == PATH_SKINNY) && tensor_path_ok(A, w->B, M, w->N, w->K) &&
+      launch_skinny(ctx, A, w->B, C, M, w->N, w->K, q, /*weights_stable=*/1))
+    return;
+  // everything else is the stateless path
   solve(A, w->B, C, M, w->N, w->K, scale_A, scale_B, scale_C, zero_point_A, zero_point_B,
         zero_point_C);
 }
