@@ -2,7 +2,7 @@
 """Benchmark of the quantized-matmul hot path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload int8_8192|int8_decode|int4_w4a16|dequant|layer_sweep]
+                    [--workload int8_8192|int8_decode|int4_w4a16|int4_w4a8|dequant|layer_sweep]
 
 One "step" is one `solve` call over one batch of synthetic input.  The default workload is
 the INT8 quantized matmul M=N=K=8192 (uniform int8 inputs, per-tensor scales and non-zero
@@ -51,6 +51,10 @@ def workload_spec(name: str):
     if name == "int4_w4a16":
         return dict(op="mm_int4", M=4096, N=8192, K=8192, G=128, dtype="f16",
                     desc="W4A16 matmul M=4096 K=8192 N=8192 G=128 (BASELINE config 4)")
+    if name == "int4_w4a8":
+        return dict(op="mm_int4a8", M=4096, N=8192, K=8192, dtype="int8",
+                    desc="W4A8 matmul M=4096 K=8192 N=8192: packed INT4 weights, INT8 activations, "
+                         "per-tensor scales and zero points (BASELINE config 4, literal reading)")
     if name == "dequant":
         return dict(op="dequantization", M=8192, N=8192, T=128, dtype="f32",
                     desc="tile-scale dequantization 8192x8192 T=128")
@@ -73,6 +77,9 @@ def algorithmic_work(spec):
     if spec["op"] == "mm_int4":
         M, N, K, G = spec["M"], spec["N"], spec["K"], spec["G"]
         return 2.0 * M * N * K, float(2 * M * K + N * K // 2 + 2 * N * (K // G) + 2 * M * N)
+    if spec["op"] == "mm_int4a8":
+        M, N, K = spec["M"], spec["N"], spec["K"]
+        return 2.0 * M * N * K, float(M * K + N * K // 2 + M * N)
     M, N, T = spec["M"], spec["N"], spec["T"]
     return float(M * N), float(8 * M * N + 4 * (-(-M // T)) * (-(-N // T)))
 
@@ -151,6 +158,10 @@ def cpu_inputs(spec, harness):
             A = rng.integers(-128, 128, (M, K), dtype=np.int8)
         B = rng.integers(-128, 128, (K, N), dtype=np.int8)
         return A, B
+    if spec["op"] == "mm_int4a8":
+        M, N, K = spec["M"], spec["N"], spec["K"]
+        return (rng.integers(-128, 128, (M, K), dtype=np.int8),
+                rng.integers(0, 256, (N, K // 2), dtype=np.uint8))
     if spec["op"] == "mm_int4":
         M, N, K, G = spec["M"], spec["N"], spec["K"], spec["G"]
         x = harness.float_to_half_bits(rng.normal(0, 1, (M, K)))
@@ -167,6 +178,9 @@ def cpu_run_rows(oracle, spec, inputs, q, r0, r1):
     if spec["op"] == "mm_int8":
         A, B = inputs
         oracle.mm_int8(A, B, spec["M"], spec["N"], spec["K"], q, mode=1, rows=(r0, r1))
+    elif spec["op"] == "mm_int4a8":
+        A, w = inputs
+        oracle.mm_int4a8(A, w, spec["M"], spec["N"], spec["K"], q, rows=(r0, r1))
     elif spec["op"] == "mm_int4":
         x, w, s = inputs
         oracle.mm_int4(x, w, s, spec["M"], spec["N"], spec["K"], spec["G"], rows=(r0, r1))
@@ -281,6 +295,32 @@ def run_ours(args, spec, workload):
         h2d, d2h = M * K + K * N, M * N
         flush_note = (f"{nsets} weight/output sets rotated; working set per step "
                       f"{(M * K + K * N + M * N) / 2**20:.0f} MiB exceeds the 126 MB L2")
+    elif spec["op"] == "mm_int4a8":
+        M, N, K = spec["M"], spec["N"], spec["K"]
+        A = torch.randint(-128, 128, (M, K), generator=g_a, device=dev, dtype=torch.int8)
+        nsets = 3
+        Ws = [torch.randint(0, 256, (N, K // 2), generator=g_b, device=dev, dtype=torch.uint8)
+              for _ in range(nsets)]
+        Cs = [torch.empty((M, N), device=dev, dtype=torch.int8) for _ in range(nsets)]
+
+        def step(i):
+            j = i % nsets
+            lib.texo_mm_int4a8_solve(A.data_ptr(), Ws[j].data_ptr(), Cs[j].data_ptr(), M, N, K, *q)
+
+        hA, hW = A.cpu().pin_memory(), Ws[0].cpu().pin_memory()
+        hC = torch.empty((M, N), dtype=torch.int8).pin_memory()
+        dA, dW, dC = torch.empty_like(A), torch.empty_like(Ws[0]), torch.empty_like(Cs[0])
+
+        def e2e_step(i):
+            dA.copy_(hA, non_blocking=True)
+            dW.copy_(hW, non_blocking=True)
+            ops.mm_int4a8(dA, dW, *q, out=dC)
+            hC.copy_(dC, non_blocking=True)
+
+        h2d, d2h = M * K + N * K // 2, M * N
+        flush_note = (f"{nsets} weight/output sets rotated; working set per step "
+                      f"{(M * K + N * K // 2 + M * N) / 2**20:.0f} MiB (A stays in L2, weights and "
+                      f"outputs do not)")
     elif spec["op"] == "mm_int4":
         M, N, K, G = spec["M"], spec["N"], spec["K"], spec["G"]
         x = torch.randn((M, K), generator=g_a, device=dev).to(torch.float16)
@@ -420,7 +460,7 @@ def run_ours(args, spec, workload):
     else:
         # No INT8 figure is measured on this pool; kind::i8 issues at twice the bf16 rate, so
         # the denominator is 2x the measured cuBLAS bf16 throughput (W4A16 runs kind::f16: 1x).
-        factor = 2.0 if spec["op"] == "mm_int8" else 1.0
+        factor = 2.0 if spec["op"] in ("mm_int8", "mm_int4a8") else 1.0
         key = "bf16_tflops_sustained" if long_run else "bf16_tflops"
         base = peaks.get(key, 1400.0 if long_run else 1590.0)
         peak = factor * base
@@ -566,7 +606,8 @@ def main():
     spec = workload_spec(args.workload)
     if args.steps is None:
         # about a second of GPU work, so that clocks under load are actually sampled
-        args.steps = {"int8_8192": 2000, "int8_decode": 10000, "int4_w4a16": 1500, "dequant": 5000}[args.workload]
+        args.steps = {"int8_8192": 2000, "int8_decode": 10000, "int4_w4a16": 1500, "int4_w4a8": 3000,
+                      "dequant": 5000}[args.workload]
         if args.impl == "reference":
             args.steps = 5
     if args.impl == "reference":

@@ -91,6 +91,23 @@ void texo_dequantization_solve(const float* X, const float* S, float* Y, int M, 
 /* ---- diagnostics (no counterpart in the reference, whose operators return void and keep no
  * error state; see reference tests/test_utils.h:11-17 for its only error handling) ------- */
 
+/* W4A8: packed-INT4 weights against INT8 activations, INT8 output.  No counterpart in the
+ * reference (its mm_int4 takes FP16 activations, src/mm_int4.cu:386-390); it combines the
+ * reference's weight format - w_q [N,K/2] uint8, high nibble = even k, value = nibble - 8
+ * (src/mm_int4.cu:5-6,25-26) - with the arithmetic and argument meaning of its INT8 operator
+ * (src/mm_int8.cu:12-25,530-535):
+ *   C[m,n] = clamp(rint(float(sum_k (A[m,k]-zA)(q[n,k]-zB)) * sA * sB / sC) + zC, -128, 127)
+ * A [M,K] int8, C [M,N] int8, device pointers, legacy default stream, asynchronous.  K even,
+ * K >= 0 (K == 0: A and w_q may be null); any byte alignment (the tensor-core path needs
+ * 16-byte aligned A / w_q and K % 32 == 0, other calls take a SIMT kernel). */
+void texo_mm_int4a8_solve(const int8_t* A, const uint8_t* w_q, int8_t* C, int M, int N, int K,
+                          float scale_A, float scale_B, float scale_C, int zero_point_A,
+                          int zero_point_B, int zero_point_C);
+/* mm_int4a8 diagnostics: path 1 = generic SIMT kernel, 2 = tcgen05 kind::i8 CTA-pair kernel. */
+int texo_mm_int4a8_last_path(void);
+void texo_mm_int4a8_force_path(int path);
+int texo_mm_int4a8_status(void);
+
 /* Which device path the last mm_int8 call took: 1 generic, 2 tensor (tcgen05), 3 skinny. */
 int texo_mm_int8_last_path(void);
 /* Force a path for the following calls (0 = automatic).  A forced path is still skipped

@@ -7,6 +7,8 @@
  *   - mm_int4 (W4A16) (src/mm_int4.cu:5-6,9-29 nibble order and naive kernel,
  *                     tests/mm_int4.cpp:35-45 double reference)
  *   - dequantization  (src/dequantization.cu:40-51, tests/dequantization.cpp:20-25)
+ *   - mm_int4a8 (W4A8): no reference operator; composed from the two pinned pieces above
+ *                     (nibble format of mm_int4, integer dot + FP32 epilogue of mm_int8)
  *
  * Only tests, the smoke check and the benchmark's cpu_baseline / reference arm may
  * link or call this file.  The shipped library never does.
@@ -193,6 +195,35 @@ int oracle_mm_int4_rows(const uint16_t *x, const uint8_t *w_q, const uint16_t *s
       }
       Y_rows[(size_t)(m - row0) * N + n] = dot;
     }
+  return 0;
+}
+
+/* ------------------------------------------------------- W4A8 (mm_int4a8) */
+
+/* Packed-INT4 weights against INT8 activations with the INT8 operator's requantisation.
+ * The reference has no such operator ("parity unpinned"): this composes two pieces that
+ * ARE pinned above - the nibble order and the -8 offset of src/mm_int4.cu:5-6,25-26
+ * (q = nibble - 8, high nibble = even k), and the exact integer dot + FP32 epilogue of
+ * src/mm_int8.cu:12-25.  Rows [row0,row1) of C; w_q is [N, K/2]. */
+int oracle_mm_int4a8_rows(const int8_t *A, const uint8_t *w_q, int8_t *C_rows, int M, int N,
+                          int K, float sa, float sb, float sc, int za, int zb, int zc,
+                          int row0, int row1) {
+  if (M <= 0 || N <= 0 || K < 0 || (K & 1) || row0 < 0 || row1 > M || row0 > row1) return -1;
+  int8_t *q = (int8_t *)malloc((size_t)(K > 0 ? K : 1) * N);
+  if (!q) return -1;
+#pragma omp parallel for schedule(static)
+  for (int n = 0; n < N; ++n)
+    for (int k = 0; k < K; ++k) {
+      int byte = w_q[(size_t)n * (K / 2) + k / 2];
+      q[(size_t)n * K + k] = (int8_t)(((k & 1) == 0 ? byte >> 4 : byte & 15) - 8);
+    }
+#pragma omp parallel for schedule(dynamic, 1)
+  for (int m = row0; m < row1; ++m)
+    for (int n = 0; n < N; ++n) {
+      int64_t dot = K > 0 ? dot_zp(A + (size_t)m * K, q + (size_t)n * K, K, za, zb) : 0;
+      C_rows[(size_t)(m - row0) * N + n] = requantize_f32(dot, sa, sb, sc, zc);
+    }
+  free(q);
   return 0;
 }
 

@@ -69,6 +69,18 @@ class Oracle:
         assert rc == 0
         return out
 
+    # -------------------------------------------------------------- mm_int4a8
+    def mm_int4a8(self, A, w, M, N, K, q, rows: tuple[int, int] | None = None):
+        """W4A8: A [M,K] int8, w [N,K/2] packed nibbles, q = (sA, sB, sC, zA, zB, zC)."""
+        r0, r1 = rows if rows else (0, M)
+        A = np.ascontiguousarray(A, dtype=np.int8) if K else None
+        w = np.ascontiguousarray(w, dtype=np.uint8) if K else None
+        out = np.empty((r1 - r0, N), dtype=np.int8)
+        rc = self.lib.oracle_mm_int4a8_rows(_p(A), _p(w), _p(out), M, N, K, _f(q[0]), _f(q[1]),
+                                            _f(q[2]), q[3], q[4], q[5], r0, r1)
+        assert rc == 0
+        return out
+
     # --------------------------------------------------------- dequantization
     def dequantization(self, X, S, M, N, T):
         out = np.empty((M, N), dtype=np.float64)

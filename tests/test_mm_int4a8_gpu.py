@@ -1,0 +1,219 @@
+"""GPU parity tests for mm_int4a8 (W4A8), through the C ABI of libtexo_b200.so.
+
+The reference has no W4A8 operator, so parity against it is unpinned; the bar here is
+bit-exactness against the oracle composed of the reference's pinned INT4 weight format and
+its pinned INT8 arithmetic (oracle/qmm_oracle.c), on both device paths.
+"""
+import numpy as np
+import pytest
+
+from tests import harness
+
+pytestmark = pytest.mark.gpu
+torch = pytest.importorskip("torch")
+
+GUARD = 16
+MARKER = 91
+
+
+@pytest.fixture(scope="module")
+def lib():
+    if not torch.cuda.is_available():
+        pytest.fail("no CUDA device: GPU tests need a B200")
+    from texo_b200 import _lib
+
+    return _lib.load()
+
+
+def _dev(a: np.ndarray):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def run_case(lib, a, w, m, n, k, q, offsets=(0, 0, 0), force=0):
+    """Guard bands around C, pointer offsets, two calls with opposite poison, inputs unchanged."""
+    ao, wo, co = offsets
+    a_h = np.concatenate([np.full(ao, MARKER, np.int8), a.reshape(-1), np.full(1, MARKER, np.int8)])
+    w_h = np.concatenate([np.full(wo, MARKER, np.uint8), w.reshape(-1), np.full(1, MARKER, np.uint8)])
+    dA, dW = _dev(a_h), _dev(w_h)
+    prefix = GUARD + co
+    total = prefix + m * n + GUARD
+    out = None
+    lib.texo_mm_int4a8_force_path(force)
+    try:
+        for call in range(2):
+            init = np.full(total, MARKER, np.int8)
+            init[prefix:prefix + m * n] = 127 if call == 0 else -128
+            dC = _dev(init)
+            lib.texo_mm_int4a8_solve(dA.data_ptr() + ao if k else None, dW.data_ptr() + wo if k else None,
+                                     dC.data_ptr() + prefix, m, n, k, *q)
+            torch.cuda.synchronize()
+            host = dC.cpu().numpy()
+            assert np.all(host[:prefix] == MARKER) and np.all(host[prefix + m * n:] == MARKER), "guard band"
+            result = host[prefix:prefix + m * n].reshape(m, n)
+            if out is not None:
+                assert np.array_equal(out, result), "result depends on the previous content of C"
+            out = result
+    finally:
+        lib.texo_mm_int4a8_force_path(0)
+    assert np.array_equal(dA.cpu().numpy(), a_h) and np.array_equal(dW.cpu().numpy(), w_h), "inputs changed"
+    return out
+
+
+def _quant(rng, k, zero_a=None, zero_b=None):
+    sa, sb = rng.uniform(0.005, 0.05, 2).astype(np.float32)
+    za = int(rng.integers(-8, 9)) if zero_a is None else zero_a
+    zb = int(rng.integers(-8, 8)) if zero_b is None else zero_b
+    # most outputs unsaturated, so that the comparison has teeth: noise plus the mean term
+    spread = 74 * 4.6 * np.sqrt(max(k, 1)) + max(k, 1) * (abs(za) + 0.5) * (abs(zb) + 0.5)
+    sc = np.float32(sa * sb * spread / 60)
+    return (float(sa), float(sb), float(sc), za, zb, int(rng.integers(-8, 9)))
+
+
+SHAPES = [  # (M, N, K); K % 32 == 0 and aligned rows -> tensor path; partial tiles included
+    (256, 256, 128), (256, 256, 32), (256, 512, 1024), (130, 272, 160), (1, 16, 32),
+    (300, 1008, 1056), (512, 768, 2048), (16, 4096, 512), (2000, 48, 4096),
+]
+
+
+@pytest.mark.parametrize("shape", SHAPES)
+def test_tensor_and_generic_paths_match_oracle(lib, oracle, shape):
+    m, n, k = shape
+    rng = np.random.default_rng(hash(shape) % (2 ** 32))
+    a = rng.integers(-128, 128, (m, k), dtype=np.int8)
+    w = rng.integers(0, 256, (n, k // 2), dtype=np.uint8)
+    for zero_a, zero_b in ((None, None), (0, -8), (0, None), (None, -8)):
+        q = _quant(rng, k, zero_a, zero_b)
+        want = oracle.mm_int4a8(a, w, m, n, k, q)
+        if m >= 16:  # (a single activation row can push every output the same way)
+            assert np.count_nonzero(np.abs(want.astype(np.int32)) < 127) > want.size // 3
+        for force, expect in ((0, 2), (1, 1)):
+            got = run_case(lib, a, w, m, n, k, q, force=force)
+            assert lib.texo_mm_int4a8_last_path() == expect, (shape, force)
+            assert np.array_equal(got, want), (shape, q, force)
+    assert lib.texo_mm_int4a8_status() == 0
+
+
+@pytest.mark.parametrize("shape", [(65, 67, 30), (7, 19, 2), (33, 40, 34), (17, 19, 0), (64, 64, 4098)])
+def test_shapes_only_the_generic_path_takes(lib, oracle, shape):
+    m, n, k = shape
+    rng = np.random.default_rng(3 + k)
+    a = rng.integers(-128, 128, (m, k), dtype=np.int8)
+    w = rng.integers(0, 256, (n, k // 2), dtype=np.uint8)
+    q = _quant(rng, k)
+    got = run_case(lib, a, w, m, n, k, q)
+    assert lib.texo_mm_int4a8_last_path() == 1
+    assert np.array_equal(got, oracle.mm_int4a8(a, w, m, n, k, q))
+    if k == 0:
+        assert np.all(got == np.clip(q[5], -128, 127))
+
+
+def test_unaligned_pointers_fall_back_and_stay_exact(lib, oracle):
+    m, n, k = 130, 144, 256
+    rng = np.random.default_rng(9)
+    a = rng.integers(-128, 128, (m, k), dtype=np.int8)
+    w = rng.integers(0, 256, (n, k // 2), dtype=np.uint8)
+    q = _quant(rng, k)
+    want = oracle.mm_int4a8(a, w, m, n, k, q)
+    for offsets, path in (((1, 0, 0), 1), ((0, 3, 0), 1), ((0, 0, 7), 2), ((16, 16, 1), 2)):
+        got = run_case(lib, a, w, m, n, k, q, offsets=offsets)
+        assert lib.texo_mm_int4a8_last_path() == path, offsets
+        assert np.array_equal(got, want), offsets
+
+
+def test_pinned_nibble_order_example(lib):
+    """The byte values of the reference's pinned mm_int4 example (tests/mm_int4.cpp:110-117):
+    153 -> (1,1), 170 -> (2,2), 119 -> (-1,-1), 136 -> (0,0).  With identity-like activations
+    the output reads the unpacked weights back directly."""
+    k = 32
+    n = 16
+    w = np.zeros((n, k // 2), dtype=np.uint8)
+    w[0, :] = 153
+    w[1, :] = 170
+    w[2, :] = 119
+    w[3, :] = 136
+    w[4, 0] = 0x7F  # k0 = -1, k1 = 7
+    w[5, 0] = 0xF0  # k0 = 7, k1 = -8
+    a = np.zeros((k, k), dtype=np.int8)
+    np.fill_diagonal(a, 1)  # row m picks weight k = m
+    q = (1.0, 1.0, 1.0, 0, 0, 0)
+    for force in (0, 1):
+        got = run_case(lib, a, w, k, n, k, q, force=force)
+        assert np.all(got[:, 0] == 1) and np.all(got[:, 1] == 2) and np.all(got[:, 2] == -1)
+        assert np.all(got[:, 3] == 0)
+        assert got[0, 4] == -1 and got[1, 4] == 7 and np.all(got[2:, 4] == -8)
+        assert got[0, 5] == 7 and got[1, 5] == -8
+
+
+def test_wide_correction_and_both_division_forms(lib, oracle):
+    """Zero points large enough that |dot| exceeds int32 (64-bit correction in the drain), and
+    scales outside the range of the branch-free division (IEEE division fallback)."""
+    m, n, k = 256, 256, 4096
+    rng = np.random.default_rng(13)
+    a = rng.integers(-128, 128, (m, k), dtype=np.int8)
+    w = rng.integers(0, 256, (n, k // 2), dtype=np.uint8)
+    cases = [
+        (1.0e-6, 1.0e-3, 1.0, 30000, 30000, 3),      # wide
+        (1.0e-6, 1.0e-3, 1.0, -30000, 29000, -3),
+        (1.0e4, 1.0e4, 2.0e13, 3, -5, 1),             # scales beyond the fast range
+        (0.02, 0.03, 40.0, 3, -5, (1 << 22) + 1),     # zC beyond the integer tail
+        (0.02, 0.03, 0.001, 3, -5, 1),                # everything saturates
+    ]
+    for q in cases:
+        q = tuple(float(np.float32(v)) for v in q[:3]) + q[3:]
+        want = oracle.mm_int4a8(a, w, m, n, k, q)
+        got = run_case(lib, a, w, m, n, k, q)
+        assert lib.texo_mm_int4a8_last_path() == 2
+        assert np.array_equal(got, want), q
+    assert lib.texo_mm_int4a8_status() == 0
+
+
+def test_config4_size_sampled_rows_and_linearity(lib, oracle):
+    """M=4096, K=8192, N=8192 (the INT4 configuration): 48 sampled rows against the oracle, and
+    a size-independent property on the whole output - with unit scales, zero zero points and
+    weights restricted so that nothing saturates, C(A1) + C(A2) == C(A1 + A2) exactly."""
+    m, n, k = 4096, 8192, 8192
+    a = harness.hashed_int8(2024, 1, np.arange(m), np.arange(k))
+    w = harness.hashed_int8(2024, 2, np.arange(n), np.arange(k // 2)).view(np.uint8)
+    A, W = _dev(a), _dev(w)
+    C = torch.empty((m, n), dtype=torch.int8, device="cuda")
+    q = (0.02, 0.03, float(np.float32(0.02 * 0.03 * 74 * 9.6 * np.sqrt(k) / 40)), 3, -5, 1)
+    lib.texo_mm_int4a8_solve(A.data_ptr(), W.data_ptr(), C.data_ptr(), m, n, k, *q)
+    torch.cuda.synchronize()
+    assert lib.texo_mm_int4a8_last_path() == 2 and lib.texo_mm_int4a8_status() == 0
+    got = C.cpu().numpy()
+    rows = np.unique(np.concatenate([[0, 127, 128, 255, 256, m - 1], np.random.default_rng(1).integers(0, m, 42)]))
+    for r in rows:
+        want = oracle.mm_int4a8(a, w, m, n, k, q, rows=(int(r), int(r) + 1))
+        assert np.array_equal(got[r:r + 1], want), f"row {r}"
+    # linearity: one-hot-ish sparse activations keep |dot| below 127
+    rng = np.random.default_rng(2)
+    a1 = np.zeros((m, k), dtype=np.int8)
+    a2 = np.zeros((m, k), dtype=np.int8)
+    cols = rng.integers(0, k, (m, 4))
+    for j in range(2):
+        a1[np.arange(m), cols[:, j]] = rng.integers(1, 4, m)
+        a2[np.arange(m), cols[:, 2 + j]] = -rng.integers(1, 4, m)
+    unit = (1.0, 1.0, 1.0, 0, 0, 0)
+    outs = []
+    for act in (a1, a2, (a1.astype(np.int16) + a2).astype(np.int8)):
+        lib.texo_mm_int4a8_solve(_dev(act).data_ptr(), W.data_ptr(), C.data_ptr(), m, n, k, *unit)
+        torch.cuda.synchronize()
+        outs.append(C.cpu().numpy().astype(np.int16))
+    assert np.abs(outs[0]).max() < 64 and np.abs(outs[1]).max() < 64
+    assert np.array_equal(outs[0] + outs[1], outs[2])
+    assert lib.texo_mm_int4a8_status() == 0
+
+
+def test_python_operator(lib, oracle):
+    from texo_b200 import ops
+
+    m, n, k = 384, 512, 1024
+    rng = np.random.default_rng(4)
+    a = rng.integers(-128, 128, (m, k), dtype=np.int8)
+    w = rng.integers(0, 256, (n, k // 2), dtype=np.uint8)
+    q = _quant(rng, k)
+    got = ops.mm_int4a8(_dev(a), _dev(w), *q).cpu().numpy()
+    assert ops.last_path("mm_int4a8") == 2 and ops.status("mm_int4a8") == 0
+    assert np.array_equal(got, oracle.mm_int4a8(a, w, m, n, k, q))
+    with pytest.raises(ValueError):
+        ops.mm_int4a8(torch.zeros((4, 6), dtype=torch.int8), torch.zeros((4, 3), dtype=torch.uint8), *q)

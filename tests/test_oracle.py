@@ -133,3 +133,23 @@ def test_dequantization_closed_form(oracle, name, rows, cols, tile):
     got = oracle.dequantization(x, s, rows, cols, tile)
     want = x.astype(np.float64) * np.repeat(np.repeat(s, tile, 0), tile, 1)[:rows, :cols]
     assert np.array_equal(got, want)
+
+
+def test_mm_int4a8_is_the_pinned_pieces_composed(oracle):
+    """W4A8 has no reference operator; its oracle must equal the pinned INT8 oracle applied to
+    weights unpacked in the pinned INT4 nibble order (high nibble = even k, value - 8), and
+    must read the reference's example bytes as (1,1), (2,2), (-1,-1), (0,0)."""
+    rng = np.random.default_rng(8)
+    for m, n, k in ((5, 7, 2), (33, 20, 64), (16, 48, 130), (3, 4, 0)):
+        a = rng.integers(-128, 128, (m, k), dtype=np.int8)
+        w = rng.integers(0, 256, (n, k // 2), dtype=np.uint8)
+        unpacked = np.empty((n, k), dtype=np.int8)
+        unpacked[:, 0::2] = (w >> 4).astype(np.int8) - 8
+        unpacked[:, 1::2] = (w & 15).astype(np.int8) - 8
+        for q in ((0.02, 0.03, 0.05, 3, -5, 1), (0.5, 0.25, 1.0, 0, 0, 0), (0.02, 0.03, 0.05, -7, 7, -128)):
+            want = oracle.mm_int8(a, np.ascontiguousarray(unpacked.T), m, n, k, q)
+            assert np.array_equal(oracle.mm_int4a8(a, w, m, n, k, q), want)
+    w = np.array([[153], [170], [119], [136]], dtype=np.uint8)
+    a = np.array([[1, 0], [0, 1]], dtype=np.int8)
+    got = oracle.mm_int4a8(a, w, 2, 4, 2, (1.0, 1.0, 1.0, 0, 0, 0))
+    assert np.array_equal(got, np.array([[1, 2, -1, 0], [1, 2, -1, 0]], dtype=np.int8))

@@ -30,6 +30,11 @@ _SIGNATURES = {
                                            _c_int, _c_int, _c_int]),
     "texo_mm_int4_solve": (None, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int]),
     "texo_dequantization_solve": (None, [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int]),
+    "texo_mm_int4a8_solve": (None, [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int,
+                                    _c_float, _c_float, _c_float, _c_int, _c_int, _c_int]),
+    "texo_mm_int4a8_last_path": (_c_int, []),
+    "texo_mm_int4a8_force_path": (None, [_c_int]),
+    "texo_mm_int4a8_status": (_c_int, []),
     "texo_mm_int8_last_path": (_c_int, []),
     "texo_mm_int8_force_path": (None, [_c_int]),
     "texo_mm_int8_status": (_c_int, []),

@@ -2,7 +2,9 @@
 
 Produces, next to this file:
   libmm_int8.so, libmm_int4.so, libdequantization.so   one `solve` each (reference ABI)
-  libtexo_b200.so                                      all three, `texo_<op>_solve` names
+  libmm_int4a8.so                                      `solve` of the W4A8 operator (no
+                                                       reference counterpart, same convention)
+  libtexo_b200.so                                      all of them, `texo_<op>_solve` names
 
 Mirrors the reference build rule (its Makefile:4-5,233-234: one operator source per binary,
 `nvcc -O3 -arch=$(NVCC_ARCH)`), with the architecture fixed to sm_100a.
@@ -16,9 +18,9 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
-OPS = ("mm_int8", "mm_int4", "dequantization")
+OPS = ("mm_int8", "mm_int4", "dequantization", "mm_int4a8")
 EXTRA = ("capi", "peak_probe", "host_api")  # only in the combined library
-HEADERS = ("ptx.cuh", "host_common.h")
+HEADERS = ("ptx.cuh", "host_common.h", "requant.cuh")
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

@@ -1,0 +1,538 @@
+// Packed-INT4-weight x INT8-activation quantized matmul (W4A8) for B200 (sm_100a).
+//
+//   C[m,n] = clamp(rint(float(sum_k (A[m,k]-zA)(q[n,k]-zB)) * sA * sB / sC) + zC, -128, 127)
+//   q[n,k] = (k even ? w_q[n,k/2] >> 4 : w_q[n,k/2] & 15) - 8
+//
+// A [M,K] int8 row-major, w_q [N,K/2] bytes in the nibble order of frezcirno/Texo
+// src/mm_int4.cu:5-6,25-26 (high nibble = even k), C [M,N] int8 row-major; scales and zero
+// points, rounding and clamping exactly as the INT8 operator (src/mm_int8.cu:12-25).  The
+// reference has no such operator (its mm_int4 takes FP16 activations): this one combines
+// the reference's INT4 weight format with its INT8 arithmetic, and is checked against an
+// oracle built from those two pinned pieces.
+//
+// Tensor path: CTA pairs, 256 x 256 output tile, 128 k per stage.  Per stage and CTA: TMA
+// brings 128 rows of A (16 KiB, K-major, 128-byte swizzle) and this CTA's 128 weight rows as
+// packed nibbles (8 KiB); four unpack warps expand the nibbles to bytes 0..15 directly into
+// a K-major, 128-byte-swizzled operand tile (16 KiB); the even CTA issues
+// tcgen05.mma.cta_group::2.kind::i8 with A signed and B UNSIGNED, accumulating int32 in TMEM.
+// Keeping the nibbles unsigned makes the unpack five integer instructions per eight
+// weights; the offset moves into the zero point:
+//   sum (a-zA)(q-zB) = sum a*u - (zB+8)*rowsum(A) - zA*rowsum(u) + K*zA*(zB+8),   u = q + 8.
+// The epilogue is the INT8 operator's TMEM drain (zero-point identity, requantisation,
+// 32-byte row stores).  rowsum(A) and the nibble sums come from a small pre-pass that the
+// pair kernel overlaps by programmatic dependent launch.
+//
+// Generic path: any shape with even K, any alignment, K = 0: SIMT tiles with int64 totals.
+#include <algorithm>
+#include <cmath>
+#include <cstdint>
+#include <cstdlib>
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include "host_common.h"
+#include "ptx.cuh"
+#include "requant.cuh"
+
+namespace texo {
+namespace w4a8 {
+
+using i8::Quant;
+
+// -------------------------------------------------------------- generic path
+constexpr int GT = 16;   // output tile edge, one output per thread
+constexpr int GKB = 32;  // packed bytes (64 k) per shared-memory tile
+
+__global__ void __launch_bounds__(GT * GT)
+    generic_kernel(const int8_t* __restrict__ A, const uint8_t* __restrict__ W,
+                   int8_t* __restrict__ C, int M, int N, int K, Quant q) {
+  __shared__ int8_t As[GT][2 * GKB + 4];
+  __shared__ uint8_t Ws[GT][GKB + 4];
+  const int tx = threadIdx.x % GT, ty = threadIdx.x / GT;
+  const int m = blockIdx.y * GT + ty, n = blockIdx.x * GT + tx;
+  const int kbytes = K / 2;
+  long long raw = 0, sum_a = 0, sum_u = 0;
+  for (int j0 = 0; j0 < kbytes; j0 += GKB) {
+    for (int i = threadIdx.x; i < GT * 2 * GKB; i += GT * GT) {
+      const int r = i / (2 * GKB), c = i % (2 * GKB);
+      const int mm = blockIdx.y * GT + r, k = 2 * j0 + c;
+      As[r][c] = (mm < M && k < K) ? A[size_t(mm) * K + k] : int8_t(0);
+    }
+    for (int i = threadIdx.x; i < GT * GKB; i += GT * GT) {
+      const int r = i / GKB, c = i % GKB;
+      const int nn = blockIdx.x * GT + r, j = j0 + c;
+      Ws[r][c] = (nn < N && j < kbytes) ? W[size_t(nn) * kbytes + j] : uint8_t(0);
+    }
+    __syncthreads();
+    int acc = 0, sa = 0, su = 0;
+#pragma unroll 8
+    for (int c = 0; c < GKB; ++c) {
+      const int hi = Ws[tx][c] >> 4, lo = Ws[tx][c] & 15;
+      const int a0 = As[ty][2 * c], a1 = As[ty][2 * c + 1];
+      acc += a0 * hi + a1 * lo;
+      sa += a0 + a1;
+      su += hi + lo;
+    }
+    // beyond K both tiles hold zeros except that a zero byte still counts as u = 0: fine
+    raw += acc;
+    sum_a += sa;
+    sum_u += su;
+    __syncthreads();
+  }
+  if (m < M && n < N) {
+    const long long dot = raw - (long long)q.zb * sum_a - (long long)q.za * sum_u +
+                          (long long)K * q.za * q.zb;
+    C[size_t(m) * N + n] = int8_t(i8::requantize(float(dot), q.sa, q.sb, q.sc, float(q.zc)));
+  }
+}
+
+// ------------------------------------------------------------ sums pre-pass
+// One warp per row: rows 0..M-1 are rows of A (signed byte sums), rows M..M+N-1 are weight
+// rows (sums of the unsigned nibbles).  16-byte loads; the tensor path guarantees alignment.
+constexpr int SUM_WARPS = 8;
+
+__global__ void __launch_bounds__(SUM_WARPS * 32)
+    sums_kernel(const int8_t* __restrict__ A, const uint8_t* __restrict__ W, int* __restrict__ row_sum,
+                int* __restrict__ w_sum, int M, int N, int K, int first_row, int rows) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  const int r = first_row + blockIdx.x * SUM_WARPS + threadIdx.x / 32;
+  const int lane = threadIdx.x % 32;
+  if (r >= first_row + rows) return;
+  int acc = 0;
+  if (r < M) {
+    const int4* src = reinterpret_cast<const int4*>(A + size_t(r) * K);
+    for (int i = lane; i < K / 16; i += 32) {
+      const int4 v = __ldg(src + i);
+      acc = __dp4a(v.x, 0x01010101, acc);
+      acc = __dp4a(v.y, 0x01010101, acc);
+      acc = __dp4a(v.z, 0x01010101, acc);
+      acc = __dp4a(v.w, 0x01010101, acc);
+    }
+  } else {
+    const uint4* src = reinterpret_cast<const uint4*>(W + size_t(r - M) * (K / 2));
+    for (int i = lane; i < K / 32; i += 32) {
+      const uint4 v = __ldg(src + i);
+      const uint32_t words[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        const uint32_t both = (words[w] & 0x0f0f0f0fu) + ((words[w] >> 4) & 0x0f0f0f0fu);
+        acc = int(__dp4a(both, 0x01010101u, unsigned(acc)));  // bytes <= 30, unsigned
+      }
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if (lane == 0) {
+    if (r < M)
+      row_sum[r] = acc;
+    else
+      w_sum[r - M] = acc;
+  }
+}
+
+// --------------------------------------------------------------- tensor path
+constexpr int BK = 128;    // k per stage = one 128-byte swizzle row of int8
+constexpr int UMMA_K = 32;  // k per kind::i8 instruction
+constexpr int Q_STAGES = 5;
+constexpr int Q_RING = 4;
+constexpr int Q_A_BYTES = 128 * BK;          // this CTA's 128 rows of A
+constexpr int Q_B_BYTES = 128 * BK;          // this CTA's 128 weight rows as bytes 0..15
+constexpr int Q_RAW_BYTES = 128 * (BK / 2);  // the same rows as packed nibbles
+constexpr int Q_STAGE_BYTES = Q_A_BYTES + Q_B_BYTES + Q_RAW_BYTES;
+constexpr int Q_SMEM_BYTES = Q_STAGES * Q_STAGE_BYTES + 1024 + 256;
+constexpr int Q_UNPACK_WARPS = 4, Q_UNPACK_WARP0 = 2;
+constexpr int Q_EPI_WARPS = 8, Q_EPI_WARP0 = 6;
+constexpr int Q_THREADS = (Q_EPI_WARP0 + Q_EPI_WARPS) * 32;
+constexpr int Q_ACC_COLS = 256, Q_TMEM_COLS = 512;
+
+struct PairBarriers {
+  uint64_t ready[Q_STAGES];     // even CTA: A bytes of both CTAs landed AND all unpack warps arrived
+  uint64_t raw_full[Q_STAGES];  // per CTA: packed nibbles landed
+  uint64_t ring[Q_RING];        // per CTA: MMA commits that free stages (see the producer)
+  uint64_t acc_full[2];         // per CTA
+  uint64_t acc_empty[2];        // even CTA: epilogue warps of both CTAs arrive
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+// Sixteen packed bytes (32 weights, k ascending, high nibble first) -> 32 bytes 0..15.
+__device__ __forceinline__ void unpack32(const uint4& packed, uint4& first, uint4& second) {
+  const uint32_t words[4] = {packed.x, packed.y, packed.z, packed.w};
+  uint32_t out[8];
+#pragma unroll
+  for (int w = 0; w < 4; ++w) {
+    const uint32_t hi = (words[w] >> 4) & 0x0f0f0f0fu, lo = words[w] & 0x0f0f0f0fu;
+    out[2 * w] = __byte_perm(hi, lo, 0x5140);      // hi.b0 lo.b0 hi.b1 lo.b1
+    out[2 * w + 1] = __byte_perm(hi, lo, 0x7362);  // hi.b2 lo.b2 hi.b3 lo.b3
+  }
+  first = make_uint4(out[0], out[1], out[2], out[3]);
+  second = make_uint4(out[4], out[5], out[6], out[7]);
+}
+
+template <bool WIDE>
+__global__ void __launch_bounds__(Q_THREADS, 1)
+    pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_raw,
+                int8_t* __restrict__ C, const int* __restrict__ row_sum,
+                const int* __restrict__ w_sum, int M, int N, int K, Quant q, int tiles_m, int tiles_n,
+                int c_vector_ok, int* status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~uintptr_t(1023));
+  PairBarriers* bars = reinterpret_cast<PairBarriers*>(smem + Q_STAGES * Q_STAGE_BYTES);
+  volatile int* abort_flag = &bars->abort_flag;
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  const uint32_t rank = cluster_ctarank();  // 0 = even CTA (issues the MMAs)
+  const int cluster_id = blockIdx.x / 2, num_clusters = gridDim.x / 2;
+  const int num_tiles = tiles_m * tiles_n;
+  const int num_kb = (K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < Q_STAGES; ++s) {
+      mbar_init(&bars->ready[s], 1 + 2 * Q_UNPACK_WARPS);  // producer's expect_tx + unpack warps
+      mbar_init(&bars->raw_full[s], 1);
+    }
+    for (int r = 0; r < Q_RING; ++r) mbar_init(&bars->ring[r], 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&bars->acc_full[b], 1);
+      mbar_init(&bars->acc_empty[b], 2 * Q_EPI_WARPS);
+    }
+    bars->abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&map_a);
+    tma_prefetch_desc(&map_raw);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(&bars->tmem_base, Q_TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();  // the partner's barriers exist before anything signals them
+  tc_fence_after_sync();
+  const uint32_t tmem_base = bars->tmem_base;
+
+  // Stage release: k blocks are numbered globally over the tiles a pair works through; the
+  // MMA warp commits after every even-numbered block (a commit costs the tensor pipe about
+  // as much as five MMAs of this shape), covering that block and its predecessor.  Commit c
+  // arrives on ring[c % 4] of both CTAs.
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    int stage = 0;
+    int g = 0;          // global k-block number of the next load
+    int observed = -1;  // highest commit number seen complete
+    bool ok = true;
+    for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+      int tm, tn;
+      i8::pair_tile_coords(tile, tiles_m, tiles_n, tm, tn);
+      const int m0 = tm * 256 + int(rank) * 128;
+      const int n0 = tn * 256 + int(rank) * 128;
+      for (int kb = 0; kb < num_kb && ok; ++kb, ++g) {
+        if (lane == 0) {
+          if (g >= Q_STAGES) {
+            const int c = (g - Q_STAGES + 1) >> 1;  // commit covering block g - Q_STAGES
+            if (c > observed) {
+              ok = mbar_wait(&bars->ring[c & (Q_RING - 1)], (c >> 2) & 1, abort_flag, status,
+                             STATUS_TIMEOUT_EMPTY);
+              observed = c;
+            }
+          }
+          if (ok) {
+            uint8_t* sa = smem + stage * Q_STAGE_BYTES;
+            uint8_t* sraw = sa + Q_A_BYTES + Q_B_BYTES;
+            const uint32_t ready_even = map_to_cta(smem_u32(&bars->ready[stage]), 0);
+            if (rank == 0) mbar_arrive_expect_tx(&bars->ready[stage], 2 * Q_A_BYTES);
+            tma_load_2d_pair(sa, &map_a, ready_even, kb * BK, m0);
+            mbar_arrive_expect_tx(&bars->raw_full[stage], Q_RAW_BYTES);
+            tma_load_2d(sraw, &map_raw, &bars->raw_full[stage], kb * (BK / 2), n0);
+          }
+        }
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (++stage == Q_STAGES) stage = 0;
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------- MMA issuer (even CTA only)
+    if (rank == 0) {
+      constexpr uint32_t IDESC = umma_idesc(/*D=s32*/ 2, /*A=s8*/ 1, /*B=u8*/ 0, /*A K-major*/ 0,
+                                            /*B K-major*/ 0, 256, 256);
+      int stage = 0;
+      uint32_t phase = 0;
+      int g = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+        if (lane == 0) {
+          ok = mbar_wait_cluster(&bars->acc_empty[acc], acc_phase ^ 1, abort_flag, status,
+                                 STATUS_TIMEOUT_TMEM_EMPTY);
+          tc_fence_after_sync();
+        }
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        const uint32_t tmem_d = tmem_base + acc * Q_ACC_COLS;
+        for (int kb = 0; kb < num_kb && ok; ++kb, ++g) {
+          if (lane == 0) {
+            ok = mbar_wait(&bars->ready[stage], phase, abort_flag, status, STATUS_TIMEOUT_FULL);
+            if (ok) {
+              tc_fence_after_sync();
+              const uint32_t sa = smem_u32(smem + stage * Q_STAGE_BYTES);
+              const uint32_t sb = sa + Q_A_BYTES;
+#pragma unroll
+              for (int j = 0; j < BK / UMMA_K; ++j) {
+                const uint64_t da = smem_desc(sa + j * UMMA_K, 16, 1024, SMEM_SWIZZLE_128B);
+                const uint64_t db = smem_desc(sb + j * UMMA_K, 16, 1024, SMEM_SWIZZLE_128B);
+                umma_i8_pair(tmem_d, da, db, IDESC, (kb | j) != 0);
+              }
+              // releases this block's stage and its predecessor's, in both CTAs
+              if ((g & 1) == 0) umma_commit_pair(&bars->ring[(g >> 1) & (Q_RING - 1)], 3);
+            }
+          }
+          ok = __shfl_sync(0xffffffffu, ok, 0);
+          if (++stage == Q_STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (lane == 0 && ok) umma_commit_pair(&bars->acc_full[acc], 3);
+        __syncwarp();
+        if (++acc == 2) {
+          acc = 0;
+          acc_phase ^= 1;
+        }
+      }
+    }
+  } else if (warp < Q_EPI_WARP0) {
+    // ------------------------------------------------------- nibble unpacking
+    const int t = (warp - Q_UNPACK_WARP0) * 32 + lane;  // 0..127
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+      for (int kb = 0; kb < num_kb && ok; ++kb) {
+        ok = mbar_wait(&bars->raw_full[stage], phase, abort_flag, status, STATUS_TIMEOUT_FULL);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        uint8_t* sb = smem + stage * Q_STAGE_BYTES + Q_A_BYTES;
+        const uint8_t* sraw = sb + Q_B_BYTES;
+        // 512 sixteen-byte pieces (128 rows x 4): consecutive threads take consecutive pieces,
+        // so loads are contiguous; the two 16-byte chunks a piece expands to go to the
+        // 128-byte-swizzled positions 2p and 2p+1 of its row (bank-conflict free: the eight
+        // threads of a store phase cover two rows of opposite parity).
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int piece = t + 128 * i;
+          const int row = piece >> 2, p = piece & 3;
+          const uint4 packed = *reinterpret_cast<const uint4*>(sraw + piece * 16);
+          uint4 first, second;
+          unpack32(packed, first, second);
+          uint8_t* dst = sb + row * 128;
+          *reinterpret_cast<uint4*>(dst + (((2 * p) ^ (row & 7)) << 4)) = first;
+          *reinterpret_cast<uint4*>(dst + (((2 * p + 1) ^ (row & 7)) << 4)) = second;
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_remote(map_to_cta(smem_u32(&bars->ready[stage]), 0));
+        if (++stage == Q_STAGES) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue
+    const int ew = warp - Q_EPI_WARP0;
+    const int quarter = warp % 4;  // TMEM lanes this warp may read: 32*quarter .. +31
+    const int half = ew / 4;       // which 128 of the 256 accumulator columns
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    // The sums come from the pre-pass grid, which may still be running when this kernel was
+    // launched behind it with programmatic stream serialisation.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+      int tm, tn;
+      i8::pair_tile_coords(tile, tiles_m, tiles_n, tm, tn);
+      ok = mbar_wait(&bars->acc_full[acc], acc_phase, abort_flag, status, STATUS_TIMEOUT_TMEM_FULL);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const int m = tm * 256 + int(rank) * 128 + quarter * 32 + lane;
+      i8::drain_half<WIDE>(tmem_base + acc * Q_ACC_COLS + (uint32_t(quarter * 32) << 16), half * 128,
+                           tn * 256, m, m < M, C, row_sum, w_sum, N, K, q, c_vector_ok);
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&bars->acc_empty[acc]), 0));
+      if (++acc == 2) {
+        acc = 0;
+        acc_phase ^= 1;
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();  // neither CTA leaves (or frees TMEM) while its partner may still signal it
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc_pair(tmem_base, Q_TMEM_COLS);
+  }
+}
+
+// ------------------------------------------------------------------ dispatch
+enum Path { PATH_AUTO = 0, PATH_GENERIC = 1, PATH_TENSOR = 2 };
+
+inline int& forced_path() {
+  static int path = [] {
+    const char* env = std::getenv("TEXO_MM_INT4A8_PATH");
+    return env ? std::atoi(env) : 0;
+  }();
+  return path;
+}
+
+inline int& last_path() {
+  static int path = 0;
+  return path;
+}
+
+static bool tensor_path_ok(const int8_t* A, const uint8_t* W, int K) {
+  return K > 0 && K < (1 << 17) && K % 32 == 0 && (reinterpret_cast<uintptr_t>(A) & 15) == 0 &&
+         (reinterpret_cast<uintptr_t>(W) & 15) == 0;
+}
+
+// Largest number of CTA pairs that can be resident at once (0 if pairs cannot be launched).
+static int max_active_pairs(DeviceCtx& ctx) {
+  static int cached[MAX_DEVICES] = {};
+  static bool known[MAX_DEVICES] = {};
+  if (!known[ctx.device]) {
+    known[ctx.device] = true;
+    cudaFuncSetAttribute(pair_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Q_SMEM_BYTES);
+    cudaFuncSetAttribute(pair_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Q_SMEM_BYTES);
+    cudaFuncSetAttribute(sums_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                         cudaSharedmemCarveoutMaxShared);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * ctx.sm_count);
+    cfg.blockDim = dim3(Q_THREADS);
+    cfg.dynamicSmemBytes = Q_SMEM_BYTES;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, pair_kernel<false>, &cfg) != cudaSuccess) n = 0;
+    cudaGetLastError();
+    cached[ctx.device] = n;
+  }
+  return cached[ctx.device];
+}
+
+static bool launch_tensor(DeviceCtx& ctx, const int8_t* A, const uint8_t* W, int8_t* C, int M, int N,
+                          int K, const Quant& q, bool wide) {
+  const int pairs = max_active_pairs(ctx);
+  if (pairs <= 0) return false;
+  CUtensorMap map_a, map_raw;
+  if (!make_tensor_map_2d(&map_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, A, M, K, K, 128, BK,
+                          CU_TENSOR_MAP_SWIZZLE_128B) ||
+      !make_tensor_map_2d(&map_raw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, W, N, K / 2, K / 2, 128, BK / 2,
+                          CU_TENSOR_MAP_SWIZZLE_NONE)) {
+    note_host_error(STATUS_TENSORMAP_FAILED);
+    return false;
+  }
+  const int tiles_m = (M + 255) / 256, tiles_n = (N + 255) / 256;
+  // scratch: rowsum(A) [M] | nibble sums [tiles_n * 256] (padded: the drain reads whole tiles)
+  const size_t m_pad = (size_t(M) + 63) & ~size_t(63);
+  int* scratch = static_cast<int*>(device_scratch(ctx, (m_pad + size_t(tiles_n) * 256) * sizeof(int)));
+  if (!scratch) return false;
+  int* row_sum = scratch;
+  int* w_sum = scratch + m_pad;
+  // rows of A are needed when the effective weight zero point (zB + 8) is non-zero, the
+  // nibble sums when zA is
+  const int first = q.zb != 0 ? 0 : M;
+  const int rows = (q.zb != 0 ? M : 0) + (q.za != 0 ? N : 0);
+  bool sums_launched = false;
+  if (rows > 0) {
+    sums_kernel<<<(rows + SUM_WARPS - 1) / SUM_WARPS, SUM_WARPS * 32>>>(A, W, row_sum, w_sum, M, N, K,
+                                                                         first, rows);
+    ++launch_counter();
+    sums_launched = true;
+  }
+  const int slot = profile_start();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * std::min(tiles_m * tiles_n, pairs));
+  cfg.blockDim = dim3(Q_THREADS);
+  cfg.dynamicSmemBytes = Q_SMEM_BYTES;
+  cfg.stream = 0;
+  cudaLaunchAttribute attrs[2];
+  attrs[0].id = cudaLaunchAttributeClusterDimension;
+  attrs[0].val.clusterDim.x = 2;
+  attrs[0].val.clusterDim.y = 1;
+  attrs[0].val.clusterDim.z = 1;
+  // Start while the sums pre-pass is still running (the epilogue waits for it).
+  attrs[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attrs[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attrs;
+  const int c_vector_ok = (reinterpret_cast<uintptr_t>(C) & 15) == 0 && N % 16 == 0;
+  const int* rs = row_sum;
+  const int* ws = w_sum;
+  static bool overlap_ok = true;
+  for (int attempt = 0; attempt < 2; ++attempt) {
+    const bool overlap = sums_launched && overlap_ok && attempt == 0;
+    cfg.numAttrs = overlap ? 2 : 1;
+    const cudaError_t err =
+        wide ? cudaLaunchKernelEx(&cfg, pair_kernel<true>, map_a, map_raw, C, rs, ws, M, N, K, q,
+                                  tiles_m, tiles_n, c_vector_ok, ctx.status)
+             : cudaLaunchKernelEx(&cfg, pair_kernel<false>, map_a, map_raw, C, rs, ws, M, N, K, q,
+                                  tiles_m, tiles_n, c_vector_ok, ctx.status);
+    if (err == cudaSuccess || !overlap) break;
+    cudaGetLastError();  // the attribute was refused: launch again, fully serialised
+    overlap_ok = false;
+  }
+  profile_stop(slot);
+  ++launch_counter();
+  last_path() = PATH_TENSOR;
+  return true;
+}
+
+}  // namespace w4a8
+}  // namespace texo
+
+// A [M,K] int8, w_q [N,K/2] packed nibbles, C [M,N] int8: device pointers.  K must be even.
+extern "C" void solve(const int8_t* A, const uint8_t* w_q, int8_t* C, int M, int N, int K,
+                      float scale_A, float scale_B, float scale_C, int zero_point_A,
+                      int zero_point_B, int zero_point_C) {
+  using namespace texo;
+  using namespace texo::w4a8;
+  if (M <= 0 || N <= 0) return;
+  if (K < 0 || K % 2 != 0 || !C || (K > 0 && (!A || !w_q))) {
+    note_host_error(STATUS_BAD_ARGUMENT);
+    return;
+  }
+  DeviceCtx& ctx = device_ctx();
+  // unsigned nibbles u = q + 8 against the zero point zB + 8
+  const long long zb_eff = (long long)zero_point_B + 8;
+  const int force = forced_path();
+  if (force != PATH_GENERIC && ctx.cc_major >= 10 && tensor_path_ok(A, w_q, K) &&
+      zb_eff <= 0x7fffffffLL) {
+    const i8::Quant q =
+        i8::make_quant(scale_A, scale_B, scale_C, zero_point_A, int(zb_eff), zero_point_C, K);
+    // the 32-bit (mod 2^32) correction is exact while |dot| < 2^31
+    const double bound = double(K) * (128.0 + std::abs(double(zero_point_A))) *
+                         (15.0 + std::abs(double(zb_eff)));
+    if (launch_tensor(ctx, A, w_q, C, M, N, K, q, bound >= 2147483648.0)) return;
+  }
+  i8::Quant q = i8::make_quant(scale_A, scale_B, scale_C, zero_point_A, 0, zero_point_C, K);
+  // the generic kernel works on the unsigned nibbles too
+  if (zb_eff > 0x7fffffffLL) {
+    note_host_error(STATUS_BAD_ARGUMENT);
+    return;
+  }
+  q.zb = int(zb_eff);
+  generic_kernel<<<dim3((N + GT - 1) / GT, (M + GT - 1) / GT), GT * GT>>>(A, w_q, C, M, N, K, q);
+  ++launch_counter();
+  last_path() = PATH_GENERIC;
+}
+
+extern "C" int texo_mm_int4a8_last_path() { return texo::w4a8::last_path(); }
+extern "C" void texo_mm_int4a8_force_path(int path) { texo::w4a8::forced_path() = path; }
+extern "C" int texo_mm_int4a8_status() { return texo::read_and_clear_status(); }

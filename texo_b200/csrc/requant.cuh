@@ -1,0 +1,163 @@
+// INT8 requantisation shared by the tensor-core kernels that end in an int8 output (the
+// INT8 operator and the packed-INT4-weight x INT8-activation operator): the FP32 epilogue of
+// frezcirno/Texo src/mm_int8.cu:12-25 and the zero-point identity of :127-129, as a TMEM
+// drain.
+#pragma once
+#include <cstdint>
+#include <type_traits>
+#include <cuda_runtime.h>
+
+#include "ptx.cuh"
+
+namespace texo {
+namespace i8 {
+
+// ------------------------------------------------------------------ epilogue
+// FP32 requantisation; the operation order is contractual (no reassociation, no
+// reciprocal, IEEE division, ties-to-even rounding).
+__device__ __forceinline__ int requantize(float dot, float sa, float sb, float sc, float zc) {
+  float acc = __fdiv_rn(__fmul_rn(__fmul_rn(dot, sa), sb), sc);
+  acc = __fadd_rn(rintf(acc), zc);
+  acc = fminf(fmaxf(acc, -128.f), 127.f);
+  return __float2int_rn(acc);
+}
+
+struct Quant {
+  float sa, sb, sc;
+  int za, zb, zc;
+  float rsc;     // RN(1 / sc), for the branch-free division below
+  int fast_div;  // 1 when every quotient of this call is inside that division's safe range
+};
+
+// Host side: fills the derived fields.  The branch-free division is exact only while no
+// intermediate leaves the normal range, so it is enabled when the scales bound every
+// possible numerator: a non-zero |dot| lies in [1, 2^49] (K < 2^17 terms of at most 2^32
+// with |zA|, |zB| <= 2^15), hence |dot * sA * sB| in [2^-60, 2^59] for |sA|, |sB| in
+// [2^-30, 2^5]; and |sC| in [2^-60, 2^60] keeps quotient and residuals normal.  |zC| <= 2^22
+// lets the tail run in integers (see requantize_fast).  Anything else (including NaN or
+// infinite scales) takes the plain IEEE division, element by element.
+inline Quant make_quant(float sa, float sb, float sc, int za, int zb, int zc, int K) {
+  Quant q = {sa, sb, sc, za, zb, zc, 0.f, 0};
+  auto within = [](float v, float lo, float hi) {
+    const float a = v < 0 ? -v : v;
+    return a >= lo && a <= hi;  // false for NaN
+  };
+  const bool ok = within(sa, 0x1p-30f, 0x1p5f) && within(sb, 0x1p-30f, 0x1p5f) &&
+                  within(sc, 0x1p-60f, 0x1p60f) && za >= -32768 && za <= 32768 && zb >= -32768 &&
+                  zb <= 32768 && zc >= -(1 << 22) && zc <= (1 << 22) && K < (1 << 17);
+  if (ok) {
+    q.rsc = 1.0f / sc;  // correctly rounded on the host
+    q.fast_div = 1;
+  }
+  return q;
+}
+
+// x / sc, correctly rounded (identical to __fdiv_rn), for x and sc in the range make_quant
+// admits: two Newton corrections of x * RN(1/sc) with exact FMA residuals.  Unlike the IEEE
+// division sequence it has no slow-path branch, so the divisions of neighbouring outputs
+// interleave instead of running one dependent chain after the other.
+__device__ __forceinline__ float div_rn_inrange(float x, float sc, float rsc) {
+  const float q0 = __fmul_rn(x, rsc);
+  const float r0 = __fmaf_rn(-sc, q0, x);
+  const float q1 = __fmaf_rn(r0, rsc, q0);
+  const float r1 = __fmaf_rn(-sc, q1, x);
+  return __fmaf_rn(r1, rsc, q1);
+}
+
+// Requantisation with that division and the tail done in integers: cvt.rni.s32
+// (saturating) -> saturating add of zC; the caller saturates to int8.  Identical to the FP32
+// tail whenever |zC| <= 2^22: if |rint(acc)| < 2^24 the float add is exact and the two
+// agree; beyond that both forms saturate to the same end of [-128, 127].
+__device__ __forceinline__ int requantize_fast(float dot, const Quant& q) {
+  const float acc = div_rn_inrange(__fmul_rn(__fmul_rn(dot, q.sa), q.sb), q.sc, q.rsc);
+  int r;
+  asm("add.sat.s32 %0, %1, %2;" : "=r"(r) : "r"(__float2int_rn(acc)), "r"(q.zc));
+  return r;
+}
+__device__ __forceinline__ uint32_t pack_sat_s8(int r0, int r1, int r2, int r3) {
+  uint32_t hi, out;
+  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(r3), "r"(r2), "r"(0));
+  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(out) : "r"(r1), "r"(r0), "r"(hi));
+  return out;
+}
+
+// One thread's 32 consecutive accumulator columns -> 32 int8 in eight words: zero-point
+// identity, then requantisation.  `col_sum_at` points at colsum(B) of the first column
+// (read through L2: another grid may have produced it while this one was running).
+template <bool WIDE, bool FAST>
+__device__ __forceinline__ void requantize_chunk(
+    const uint32_t (&v)[32], const int* __restrict__ col_sum_at,
+    typename std::conditional<WIDE, long long, unsigned>::type row_term, const Quant& q,
+    uint32_t (&packed)[8]) {
+  using Wide = typename std::conditional<WIDE, long long, unsigned>::type;
+  using Signed = typename std::conditional<WIDE, long long, int>::type;
+  const float zc = float(q.zc);
+#pragma unroll
+  for (int g = 0; g < 8; ++g) {
+    int4 cs = make_int4(0, 0, 0, 0);
+    if (q.za != 0) cs = __ldcg(reinterpret_cast<const int4*>(col_sum_at + g * 4));
+    const int csv[4] = {cs.x, cs.y, cs.z, cs.w};
+    int r[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const Wide dot = Wide(Signed(int(v[g * 4 + e]))) + row_term - Wide(q.za) * Wide(csv[e]);
+      const float x = float(Signed(dot));
+      r[e] = FAST ? requantize_fast(x, q) : requantize(x, q.sa, q.sb, q.sc, zc);
+    }
+    packed[g] = pack_sat_s8(r[0], r[1], r[2], r[3]);
+  }
+}
+
+constexpr int P_GROUP_M = 8;  // pair-tile rows per raster group
+
+__device__ __forceinline__ void pair_tile_coords(int tile, int tiles_m, int tiles_n, int& tm,
+                                                 int& tn) {
+  const int group_tiles = P_GROUP_M * tiles_n;
+  const int first_m = tile / group_tiles * P_GROUP_M;
+  const int group_m = min(tiles_m - first_m, P_GROUP_M);
+  const int in_group = tile % group_tiles;
+  tm = first_m + in_group % group_m;
+  tn = in_group / group_m;
+}
+
+// Drains 128 columns [col0, col0+128) of one accumulator for this thread's row: zero-point
+// identity, FP32 requantisation, 32 int8 per 32-column chunk, vector stores when possible.
+template <bool WIDE>
+__device__ __forceinline__ void drain_half(uint32_t tmem_row_addr, int col0, int n_tile0, int m,
+                                           bool row_ok, int8_t* __restrict__ C,
+                                           const int* __restrict__ row_sum,
+                                           const int* __restrict__ col_sum, int N, int K,
+                                           const Quant& q, int c_vector_ok) {
+  using Wide = typename std::conditional<WIDE, long long, unsigned>::type;
+  Wide row_term = Wide(K) * Wide(q.za) * Wide(q.zb);
+  if (row_ok && q.zb != 0) row_term -= Wide(q.zb) * Wide(__ldcg(row_sum + m));
+  int8_t* c_row = C + size_t(row_ok ? m : 0) * N;
+#pragma unroll 1
+  for (int chunk = 0; chunk < 4; ++chunk) {
+    const int col = col0 + chunk * 32;
+    const int n0 = n_tile0 + col;
+    uint32_t v[32];
+    tmem_ld_32x32(tmem_row_addr + col, v);
+    tmem_ld_wait();
+    if (n0 >= N) continue;  // warp-uniform
+    uint32_t packed[8];
+    // col_sum is padded to a multiple of the tile width: never out of bounds.
+    if (q.fast_div)
+      requantize_chunk<WIDE, true>(v, col_sum + n0, row_term, q, packed);
+    else
+      requantize_chunk<WIDE, false>(v, col_sum + n0, row_term, q, packed);
+    if (row_ok) {
+      if (c_vector_ok && n0 + 32 <= N) {
+        int4* dst = reinterpret_cast<int4*>(c_row + n0);
+        dst[0] = make_int4(packed[0], packed[1], packed[2], packed[3]);
+        dst[1] = make_int4(packed[4], packed[5], packed[6], packed[7]);
+      } else {
+        for (int e = 0; e < 32 && n0 + e < N; ++e)
+          c_row[n0 + e] = int8_t((packed[e / 4] >> (8 * (e % 4))) & 0xff);
+      }
+    }
+  }
+}
+
+}  // namespace i8
+}  // namespace texo

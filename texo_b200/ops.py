@@ -11,8 +11,8 @@ import torch
 
 from . import _lib
 
-__all__ = ["mm_int8", "mm_int4", "dequantization", "mm_int8_host", "Int8Weights", "last_path",
-           "status", "force_path"]
+__all__ = ["mm_int8", "mm_int4", "mm_int4a8", "dequantization", "mm_int8_host", "Int8Weights",
+           "last_path", "status", "force_path"]
 
 
 def _check_cuda(name: str, t: torch.Tensor, dtype: torch.dtype) -> None:
@@ -91,6 +91,35 @@ def mm_int4(x: torch.Tensor, w_q: torch.Tensor, scales: torch.Tensor, group_size
     with torch.cuda.device(x.device), _DefaultStreamOrder(x.device):
         lib.texo_mm_int4_solve(x.data_ptr(), w_q.data_ptr(), scales.data_ptr(), out.data_ptr(),
                                M, N, K, group_size)
+    return out
+
+
+def mm_int4a8(A: torch.Tensor, w_q: torch.Tensor, scale_A: float, scale_B: float, scale_C: float,
+              zero_point_A: int, zero_point_B: int, zero_point_C: int,
+              out: torch.Tensor | None = None) -> torch.Tensor:
+    """C[M,N] int8 = requantised (A - zA) @ (unpack(w_q) - zB)^T with w_q [N,K/2] packed
+    nibbles in the mm_int4 format (W4A8); see include/texo_b200.h."""
+    _check_cuda("A", A, torch.int8)
+    _check_cuda("w_q", w_q, torch.uint8)
+    if A.dim() != 2 or w_q.dim() != 2:
+        raise ValueError("A and w_q must be matrices")
+    M, K = A.shape
+    N = w_q.shape[0]
+    if K % 2 or w_q.shape[1] != K // 2:
+        raise ValueError("w_q must be [N, K/2] with even K")
+    if M <= 0 or N <= 0:
+        raise ValueError("M and N must be positive")
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.int8, device=A.device)
+    else:
+        _check_cuda("out", out, torch.int8)
+        if tuple(out.shape) != (M, N):
+            raise ValueError("out has the wrong shape")
+    lib = _lib.load()
+    with torch.cuda.device(A.device), _DefaultStreamOrder(A.device):
+        lib.texo_mm_int4a8_solve(A.data_ptr() if K else None, w_q.data_ptr() if K else None,
+                                 out.data_ptr(), M, N, K, scale_A, scale_B, scale_C,
+                                 zero_point_A, zero_point_B, zero_point_C)
     return out
 
 
@@ -180,8 +209,7 @@ class Int8Weights:
 
 
 def last_path(op: str = "mm_int8") -> int:
-    lib = _lib.load()
-    return lib.texo_mm_int8_last_path() if op == "mm_int8" else lib.texo_mm_int4_last_path()
+    return getattr(_lib.load(), f"texo_{op}_last_path")()
 
 
 def force_path(path: int) -> None:
@@ -191,5 +219,4 @@ def force_path(path: int) -> None:
 
 def status(op: str = "mm_int8") -> int:
     """Reads and clears the library's error state for the current device (0 = clean)."""
-    lib = _lib.load()
-    return lib.texo_mm_int8_status() if op == "mm_int8" else lib.texo_mm_int4_status()
+    return getattr(_lib.load(), f"texo_{op}_status")()
