@@ -2,7 +2,7 @@
 """Benchmark of the quantized-matmul hot path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload int8_8192|int8_decode|int4_w4a16|int4_w4a8|dequant|layer_sweep]
+                    [--workload int8_8192|int8_decode|int4_w4a16|int4_w4a8|dequant|rmsnorm_quant|layer_sweep]
 
 One "step" is one `solve` call over one batch of synthetic input.  The default workload is
 the INT8 quantized matmul M=N=K=8192 (uniform int8 inputs, per-tensor scales and non-zero
@@ -58,6 +58,10 @@ def workload_spec(name: str):
     if name == "dequant":
         return dict(op="dequantization", M=8192, N=8192, T=128, dtype="f32",
                     desc="tile-scale dequantization 8192x8192 T=128")
+    if name == "rmsnorm_quant":
+        return dict(op="rms_norm_quant", M=8192, N=8192, dtype="f32",
+                    desc="RMSNorm(x + residual) * weight quantised to int8 (+ residual stream out), "
+                         "8192 rows x 8192 features: the producer of the INT8 matmul's activations")
     raise SystemExit(f"unknown workload {name}")
 
 
@@ -80,6 +84,9 @@ def algorithmic_work(spec):
     if spec["op"] == "mm_int4a8":
         M, N, K = spec["M"], spec["N"], spec["K"]
         return 2.0 * M * N * K, float(M * K + N * K // 2 + M * N)
+    if spec["op"] == "rms_norm_quant":
+        M, N = spec["M"], spec["N"]  # rows x features; reads x, residual (+weight), writes q and z
+        return float(M * N), float(13 * M * N + 4 * N)
     M, N, T = spec["M"], spec["N"], spec["T"]
     return float(M * N), float(8 * M * N + 4 * (-(-M // T)) * (-(-N // T)))
 
@@ -168,6 +175,10 @@ def cpu_inputs(spec, harness):
         w = rng.integers(0, 256, (N, K // 2), dtype=np.uint8)
         s = harness.float_to_half_bits(rng.uniform(0.01, 0.11, (N, K // G)))
         return x, w, s
+    if spec["op"] == "rms_norm_quant":
+        M, N = spec["M"], spec["N"]
+        return (rng.normal(0, 1.5, (M, N)).astype(np.float32), rng.normal(0, 0.7, (M, N)).astype(np.float32),
+                rng.uniform(0.5, 1.5, N).astype(np.float32))
     M, N, T = spec["M"], spec["N"], spec["T"]
     X = rng.uniform(-8, 8, (M, N)).astype(np.float32)
     S = rng.uniform(0.5, 2.0, (-(-M // T), -(-N // T))).astype(np.float32)
@@ -184,6 +195,10 @@ def cpu_run_rows(oracle, spec, inputs, q, r0, r1):
     elif spec["op"] == "mm_int4":
         x, w, s = inputs
         oracle.mm_int4(x, w, s, spec["M"], spec["N"], spec["K"], spec["G"], rows=(r0, r1))
+    elif spec["op"] == "rms_norm_quant":
+        x, r, w = inputs
+        y, _ = oracle.rms_norm_w_residual(x[r0:r1], r[r0:r1], w, 1e-5)
+        np.clip(np.rint(y / 0.03) + 3, -128, 127).astype(np.int8)
     else:
         X, S = inputs
         oracle.dequantization(X, S, spec["M"], spec["N"], spec["T"])
@@ -350,6 +365,35 @@ def run_ours(args, spec, workload):
         h2d = 2 * M * K + N * K // 2 + 2 * N * (K // G)
         d2h = 2 * M * N
         flush_note = f"{nsets} weight/output sets rotated; working set per step exceeds L2"
+    elif spec["op"] == "rms_norm_quant":
+        M, N = spec["M"], spec["N"]
+        nsets = 2
+        Xs = [torch.randn((M, N), generator=g_b, device=dev) * 1.5 for _ in range(nsets)]
+        Rs = [torch.randn((M, N), generator=g_b, device=dev) * 0.7 for _ in range(nsets)]
+        Wt = torch.rand((N,), generator=g_a, device=dev) + 0.5
+        Qs = [torch.empty((M, N), device=dev, dtype=torch.int8) for _ in range(nsets)]
+        Zs = [torch.empty((M, N), device=dev) for _ in range(nsets)]
+
+        def step(i):
+            j = i % nsets
+            lib.texo_rms_norm_quant_solve(Xs[j].data_ptr(), Rs[j].data_ptr(), Wt.data_ptr(),
+                                          Qs[j].data_ptr(), Zs[j].data_ptr(), M, N, 1e-5, 0.03, 3)
+
+        hX, hR = Xs[0].cpu().pin_memory(), Rs[0].cpu().pin_memory()
+        hQ = torch.empty((M, N), dtype=torch.int8).pin_memory()
+        hZ = torch.empty((M, N)).pin_memory()
+        dX, dR = torch.empty_like(Xs[0]), torch.empty_like(Rs[0])
+        dQ, dZ = torch.empty_like(Qs[0]), torch.empty_like(Zs[0])
+
+        def e2e_step(i):
+            dX.copy_(hX, non_blocking=True)
+            dR.copy_(hR, non_blocking=True)
+            ops.rms_norm_quant(dX, dR, Wt, 1e-5, 0.03, 3, out=dQ, z_out=dZ)
+            hQ.copy_(dQ, non_blocking=True)
+            hZ.copy_(dZ, non_blocking=True)
+
+        h2d, d2h = 8 * M * N, 5 * M * N
+        flush_note = f"{nsets} input/output sets rotated; 832 MiB per step exceeds L2"
     else:
         M, N, T = spec["M"], spec["N"], spec["T"]
         nsets = 2
@@ -451,7 +495,7 @@ def run_ours(args, spec, workload):
     single_launch_steps = launches == args.steps
     kernel_avg_ms = ms_per_step if single_launch_steps else bracketed_ms
     long_run = total_ms > 300.0  # long enough for the power cap to pull the clocks down
-    if spec["op"] == "dequantization" or (spec["op"] == "mm_int8" and spec["M"] <= 32):
+    if spec["op"] in ("dequantization", "rms_norm_quant") or (spec["op"] == "mm_int8" and spec["M"] <= 32):
         peak = peaks.get("hbm_gbs", 6650.0)
         achieved = bytes_per_step / (kernel_avg_ms * 1e-3) / 1e9
         roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
@@ -473,8 +517,7 @@ def run_ours(args, spec, workload):
     if single_launch_steps:
         roofline["kernel_launches_timed"] = launches
         roofline["kernel_timing"] = ("one launch per step: CUDA events around the timed region / "
-                                     "launches (consecutive launches overlap their set-up with "
-                                     "the previous one's tail by programmatic dependent launch)")
+                                     "launches (back to back, as a caller issues them)")
         roofline["kernel_ms_isolated"] = bracketed_ms
     else:
         roofline["kernel_launches_timed"] = kernel_n.value
@@ -607,7 +650,7 @@ def main():
     if args.steps is None:
         # about a second of GPU work, so that clocks under load are actually sampled
         args.steps = {"int8_8192": 2000, "int8_decode": 10000, "int4_w4a16": 1500, "int4_w4a8": 3000,
-                      "dequant": 5000}[args.workload]
+                      "dequant": 5000, "rmsnorm_quant": 4000}[args.workload]
         if args.impl == "reference":
             args.steps = 5
     if args.impl == "reference":

@@ -108,6 +108,24 @@ int texo_mm_int4a8_last_path(void);
 void texo_mm_int4a8_force_path(int path);
 int texo_mm_int4a8_status(void);
 
+/* RMSNorm with residual add, FP32.  Replaces `solve` of the reference's
+ * src/rms_norm_w_residual.cu:66-75: x, residual, out [N,C], weight [C], device pointers,
+ *   out = (x + residual) * rsqrt(mean_j((x + residual)^2) + eps) * weight.
+ * The sum of squares is reduced in FP32 in this library's own (fixed) order, as the
+ * reference reduces it in its own: results agree to FP32 reduction error. */
+void texo_rms_norm_w_residual_solve(const float* x, const float* residual, const float* weight,
+                                    float* out, int N, int C, float eps);
+/* The same, fused with INT8 activation quantisation - the producer of mm_int8's A.  No
+ * counterpart in the reference.  q [N,C] int8 = clamp(rint(out / scale) + zero_point, -128,
+ * 127) with `out` as above (never written to memory); z_out [N,C] FP32, if not null, receives
+ * x + residual (the updated residual stream).  scale finite and non-zero. */
+void texo_rms_norm_quant_solve(const float* x, const float* residual, const float* weight,
+                               int8_t* q, float* z_out, int N, int C, float eps, float scale,
+                               int zero_point);
+/* 1 = two-pass kernel (any C, any alignment), 2 = row-in-registers kernel (C % 4 == 0,
+ * C <= 16384, 16-byte aligned pointers). */
+int texo_rms_norm_last_path(void);
+
 /* Which device path the last mm_int8 call took: 1 generic, 2 tensor (tcgen05), 3 skinny. */
 int texo_mm_int8_last_path(void);
 /* Force a path for the following calls (0 = automatic).  A forced path is still skipped

@@ -227,6 +227,34 @@ int oracle_mm_int4a8_rows(const int8_t *A, const uint8_t *w_q, int8_t *C_rows, i
   return 0;
 }
 
+/* ------------------------------------------- rms_norm_w_residual (+ quantiser) */
+
+/* src/rms_norm_w_residual.cu:40-64: z = x + residual (FP32 add), y = z * rsqrt(mean(z^2) +
+ * eps) * weight.  The reference reduces in FP32 in a tree order of its own, so its result is
+ * defined up to FP32 reduction error; this restatement keeps the FP32 add (bit-defined) and
+ * does everything after it in double.  Y (double) and Z (float, may be NULL) are [N,C].
+ * The reference has no test or golden vector for this operator: parity unpinned, the formula
+ * is taken from its source alone. */
+int oracle_rms_norm_w_residual(const float *x, const float *residual, const float *weight,
+                               double *Y, float *Z, int N, int C, float eps) {
+  if (N <= 0 || C <= 0) return -1;
+#pragma omp parallel for schedule(static)
+  for (int n = 0; n < N; ++n) {
+    double sum = 0;
+    for (int j = 0; j < C; ++j) {
+      float z = x[(size_t)n * C + j] + residual[(size_t)n * C + j];
+      sum += (double)z * (double)z;
+      if (Z) Z[(size_t)n * C + j] = z;
+    }
+    double inv_rms = 1.0 / sqrt(sum / C + (double)eps);
+    for (int j = 0; j < C; ++j) {
+      float z = x[(size_t)n * C + j] + residual[(size_t)n * C + j];
+      Y[(size_t)n * C + j] = (double)z * inv_rms * (double)weight[j];
+    }
+  }
+  return 0;
+}
+
 /* ----------------------------------------------------------- dequantization */
 
 /* Y[m,n] = X[m,n] * S[m/T][n/T] in double (tests/dequantization.cpp:20-25). */

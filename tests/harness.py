@@ -81,6 +81,19 @@ class Oracle:
         assert rc == 0
         return out
 
+    # ---------------------------------------------------- rms_norm_w_residual
+    def rms_norm_w_residual(self, x, residual, weight, eps):
+        """Returns (y [N,C] float64, z [N,C] float32 = x + residual)."""
+        N, C = x.shape
+        y = np.empty((N, C), dtype=np.float64)
+        z = np.empty((N, C), dtype=np.float32)
+        rc = self.lib.oracle_rms_norm_w_residual(_p(np.ascontiguousarray(x, dtype=np.float32)),
+                                                 _p(np.ascontiguousarray(residual, dtype=np.float32)),
+                                                 _p(np.ascontiguousarray(weight, dtype=np.float32)),
+                                                 _p(y), _p(z), N, C, _f(eps))
+        assert rc == 0
+        return y, z
+
     # --------------------------------------------------------- dequantization
     def dequantization(self, X, S, M, N, T):
         out = np.empty((M, N), dtype=np.float64)

@@ -153,3 +153,15 @@ def test_mm_int4a8_is_the_pinned_pieces_composed(oracle):
     a = np.array([[1, 0], [0, 1]], dtype=np.int8)
     got = oracle.mm_int4a8(a, w, 2, 4, 2, (1.0, 1.0, 1.0, 0, 0, 0))
     assert np.array_equal(got, np.array([[1, 2, -1, 0], [1, 2, -1, 0]], dtype=np.int8))
+
+
+def test_rms_norm_w_residual_against_numpy(oracle):
+    rng = np.random.default_rng(12)
+    x = rng.normal(0, 2, (5, 37)).astype(np.float32)
+    r = rng.normal(0, 1, (5, 37)).astype(np.float32)
+    w = rng.uniform(0.5, 1.5, 37).astype(np.float32)
+    y, z = oracle.rms_norm_w_residual(x, r, w, 1e-5)
+    zz = (x + r).astype(np.float32)
+    assert np.array_equal(z, zz)
+    want = zz.astype(np.float64) / np.sqrt((zz.astype(np.float64) ** 2).mean(axis=1, keepdims=True) + np.float64(np.float32(1e-5))) * w
+    assert np.allclose(y, want, rtol=1e-12, atol=0)

@@ -4,6 +4,8 @@ Produces, next to this file:
   libmm_int8.so, libmm_int4.so, libdequantization.so   one `solve` each (reference ABI)
   libmm_int4a8.so                                      `solve` of the W4A8 operator (no
                                                        reference counterpart, same convention)
+  librms_norm_w_residual.so                            `solve` of the reference's
+                                                       rms_norm_w_residual + the quantising form
   libtexo_b200.so                                      all of them, `texo_<op>_solve` names
 
 Mirrors the reference build rule (its Makefile:4-5,233-234: one operator source per binary,
@@ -18,7 +20,7 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
-OPS = ("mm_int8", "mm_int4", "dequantization", "mm_int4a8")
+OPS = ("mm_int8", "mm_int4", "dequantization", "mm_int4a8", "rms_norm_w_residual")
 EXTRA = ("capi", "peak_probe", "host_api")  # only in the combined library
 HEADERS = ("ptx.cuh", "host_common.h", "requant.cuh")
 

@@ -11,8 +11,8 @@ import torch
 
 from . import _lib
 
-__all__ = ["mm_int8", "mm_int4", "mm_int4a8", "dequantization", "mm_int8_host", "Int8Weights",
-           "last_path", "status", "force_path"]
+__all__ = ["mm_int8", "mm_int4", "mm_int4a8", "dequantization", "rms_norm_w_residual",
+           "rms_norm_quant", "mm_int8_host", "Int8Weights", "last_path", "status", "force_path"]
 
 
 def _check_cuda(name: str, t: torch.Tensor, dtype: torch.dtype) -> None:
@@ -138,6 +138,59 @@ def dequantization(X: torch.Tensor, S: torch.Tensor, T: int,
     lib = _lib.load()
     with torch.cuda.device(X.device), _DefaultStreamOrder(X.device):
         lib.texo_dequantization_solve(X.data_ptr(), S.data_ptr(), out.data_ptr(), M, N, T)
+    return out
+
+
+def _check_norm_inputs(x, residual, weight):
+    _check_cuda("x", x, torch.float32)
+    _check_cuda("residual", residual, torch.float32)
+    _check_cuda("weight", weight, torch.float32)
+    if x.dim() != 2 or residual.shape != x.shape or tuple(weight.shape) != (x.shape[1],):
+        raise ValueError("x, residual must be [N, C] and weight [C]")
+    if x.shape[0] <= 0 or x.shape[1] <= 0:
+        raise ValueError("N and C must be positive")
+
+
+def rms_norm_w_residual(x: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, eps: float,
+                        out: torch.Tensor | None = None) -> torch.Tensor:
+    """out[N,C] fp32 = (x + residual) * rsqrt(mean((x + residual)^2) + eps) * weight."""
+    _check_norm_inputs(x, residual, weight)
+    if out is None:
+        out = torch.empty_like(x)
+    else:
+        _check_cuda("out", out, torch.float32)
+        if out.shape != x.shape:
+            raise ValueError("out has the wrong shape")
+    lib = _lib.load()
+    with torch.cuda.device(x.device), _DefaultStreamOrder(x.device):
+        lib.texo_rms_norm_w_residual_solve(x.data_ptr(), residual.data_ptr(), weight.data_ptr(),
+                                           out.data_ptr(), x.shape[0], x.shape[1], eps)
+    return out
+
+
+def rms_norm_quant(x: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, eps: float,
+                   scale: float, zero_point: int, out: torch.Tensor | None = None,
+                   z_out: torch.Tensor | None = None) -> torch.Tensor:
+    """q[N,C] int8 = clamp(rint(rms_norm_w_residual(...) / scale) + zero_point); z_out, if
+    given, receives x + residual.  The int8 activations feed mm_int8 / mm_int4a8 as A."""
+    _check_norm_inputs(x, residual, weight)
+    if not (scale == scale) or scale == 0.0:
+        raise ValueError("scale must be finite and non-zero")
+    if out is None:
+        out = torch.empty(x.shape, dtype=torch.int8, device=x.device)
+    else:
+        _check_cuda("out", out, torch.int8)
+        if out.shape != x.shape:
+            raise ValueError("out has the wrong shape")
+    if z_out is not None:
+        _check_cuda("z_out", z_out, torch.float32)
+        if z_out.shape != x.shape:
+            raise ValueError("z_out has the wrong shape")
+    lib = _lib.load()
+    with torch.cuda.device(x.device), _DefaultStreamOrder(x.device):
+        lib.texo_rms_norm_quant_solve(x.data_ptr(), residual.data_ptr(), weight.data_ptr(),
+                                      out.data_ptr(), z_out.data_ptr() if z_out is not None else None,
+                                      x.shape[0], x.shape[1], eps, scale, zero_point)
     return out
 
 
