@@ -91,6 +91,16 @@ void texo_dequantization_solve(const float* X, const float* S, float* Y, int M, 
 /* ---- diagnostics (no counterpart in the reference, whose operators return void and keep no
  * error state; see reference tests/test_utils.h:11-17 for its only error handling) ------- */
 
+/* mm_int8 with per-output-channel weight quantisation (no counterpart in the reference, which
+ * is per-tensor only, src/mm_int8.cu:533-535): scale_B [N] FP32 and zero_point_B [N] int32 are
+ * DEVICE arrays, zero_point_B may be null (all zero).  Column n:
+ *   C[m,n] = clamp(rint(float(sum_k (A-zA)(B-zB[n])) * scale_A * scale_B[n] / scale_C) + zC)
+ * in the FP32 operation order of texo_mm_int8_solve.  Arrays 16-byte aligned for the
+ * tensor-core paths (otherwise the generic kernel runs). */
+void texo_mm_int8_solve_per_channel(const int8_t* A, const int8_t* B, int8_t* C, int M, int N, int K,
+                                    float scale_A, const float* scale_B, float scale_C,
+                                    int zero_point_A, const int* zero_point_B, int zero_point_C);
+
 /* W4A8: packed-INT4 weights against INT8 activations, INT8 output.  No counterpart in the
  * reference (its mm_int4 takes FP16 activations, src/mm_int4.cu:386-390); it combines the
  * reference's weight format - w_q [N,K/2] uint8, high nibble = even k, value = nibble - 8

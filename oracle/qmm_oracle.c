@@ -121,6 +121,30 @@ int oracle_mm_int8_double(const int8_t *A, const int8_t *B, int8_t *C, int M, in
   return oracle_mm_int8_rows(A, B, C, M, N, K, sa, sb, sc, za, zb, zc, 0, M, 1);
 }
 
+/* Per-output-channel weight quantisation: sb[N] scales and zb[N] zero points (zb may be
+ * NULL = all zero) in place of the scalars; everything else as the normative mm_int8
+ * (exact integer dot, FP32 epilogue of src/mm_int8.cu:12-25 with sB[n] in the place of sB).
+ * The reference is per-tensor only: this generalisation has no reference counterpart. */
+int oracle_mm_int8_per_channel_rows(const int8_t *A, const int8_t *B, int8_t *C_rows, int M,
+                                    int N, int K, float sa, const float *sb, float sc, int za,
+                                    const int *zb, int zc, int row0, int row1) {
+  if (M <= 0 || N <= 0 || K < 0 || !sb || row0 < 0 || row1 > M || row0 > row1) return -1;
+  int8_t *bt = NULL;
+  if (K > 0) {
+    bt = transpose_b(B, K, N);
+    if (!bt) return -1;
+  }
+#pragma omp parallel for schedule(dynamic, 1)
+  for (int m = row0; m < row1; ++m)
+    for (int n = 0; n < N; ++n) {
+      int z = zb ? zb[n] : 0;
+      int64_t dot = K > 0 ? dot_zp(A + (size_t)m * K, bt + (size_t)n * K, K, za, z) : 0;
+      C_rows[(size_t)(m - row0) * N + n] = requantize_f32(dot, sa, sb[n], sc, zc);
+    }
+  free(bt);
+  return 0;
+}
+
 /* Verbatim-structure single-thread version of tests/mm_int8.cpp:39-48 (B walked with
  * stride N, double scaling): the reference's own CPU cost model for the timing arm. */
 int oracle_mm_int8_harness_loop(const int8_t *A, const int8_t *B, int8_t *C_rows, int M,

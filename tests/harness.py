@@ -46,6 +46,19 @@ class Oracle:
         assert rc == 0
         return out
 
+    def mm_int8_per_channel(self, A, B, M, N, K, sa, sb, sc, za, zb, zc, rows=None):
+        """sb: float32 [N]; zb: int32 [N] or None."""
+        r0, r1 = rows if rows else (0, M)
+        A = np.ascontiguousarray(A, dtype=np.int8) if K else None
+        B = np.ascontiguousarray(B, dtype=np.int8) if K else None
+        sb = np.ascontiguousarray(sb, dtype=np.float32)
+        zb = None if zb is None else np.ascontiguousarray(zb, dtype=np.int32)
+        out = np.empty((r1 - r0, N), dtype=np.int8)
+        rc = self.lib.oracle_mm_int8_per_channel_rows(_p(A), _p(B), _p(out), M, N, K, _f(sa), _p(sb),
+                                                      _f(sc), za, _p(zb), zc, r0, r1)
+        assert rc == 0
+        return out
+
     def mm_int8_harness_loop(self, A, B, M, N, K, q, rows):
         r0, r1 = rows
         out = np.empty((r1 - r0, N), dtype=np.int8)

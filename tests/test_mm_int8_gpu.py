@@ -428,3 +428,48 @@ def test_unchanged_reference_harness_links_and_passes(args):
         pytest.skip("oracle/_ref not built (reference checkout absent at build time)")
     proc = subprocess.run([exe, *args], capture_output=True, text=True, timeout=900)
     assert proc.returncode == 0 and "ALL PASSED" in proc.stdout, proc.stdout[-2000:] + proc.stderr[-2000:]
+
+
+@pytest.mark.parametrize("shape,paths", [((300, 1008, 1040), (0, 2, 4, 1)), ((128, 256, 512), (0, 2, 1)),
+                                         ((16, 1024, 2048), (0, 3, 1)), ((32, 272, 4096), (3,)),
+                                         ((65, 67, 31), (0,)), ((2000, 48, 4096), (0,))])
+def test_per_channel_weight_quantisation(lib, oracle, shape, paths):
+    """One weight scale and zero point per output column, on every device path: bit-exact
+    against the per-channel oracle; with constant vectors it must equal the per-tensor call."""
+    m, n, k = shape
+    rng = np.random.default_rng(n + k)
+    a = rng.integers(-128, 128, (m, k), dtype=np.int8)
+    b = rng.integers(-128, 128, (k, n), dtype=np.int8)
+    sa, za, zc = 0.021, 3, -2
+    sb = rng.uniform(0.005, 0.05, n).astype(np.float32)
+    sb[::7] *= np.float32(1e-9)  # some columns outside the range of the branch-free division
+    zb = rng.integers(-8, 9, n).astype(np.int32)
+    sc = float(np.float32(sa * 0.0275 * 128 * 74 * np.sqrt(k) / 60))
+    A, B = _dev(a), _dev(b)
+    SB, ZB = torch.from_numpy(sb).cuda(), torch.from_numpy(zb).cuda()
+    for zvec, zdev in ((zb, ZB), (None, None)):
+        want = oracle.mm_int8_per_channel(a, b, m, n, k, sa, sb, sc, za, zvec, zc)
+        for force in paths:
+            lib.texo_mm_int8_force_path(force)
+            C = torch.full((m, n), 77, dtype=torch.int8, device="cuda")
+            lib.texo_mm_int8_solve_per_channel(A.data_ptr(), B.data_ptr(), C.data_ptr(), m, n, k, sa,
+                                               SB.data_ptr(), sc, za,
+                                               zdev.data_ptr() if zdev is not None else None, zc)
+            torch.cuda.synchronize()
+            path = lib.texo_mm_int8_last_path()
+            lib.texo_mm_int8_force_path(0)
+            if force:
+                assert path == force, (shape, force, path)
+            assert np.array_equal(C.cpu().numpy(), want), (shape, force, zvec is None)
+    # constant vectors == per-tensor call
+    const_s = torch.full((n,), 0.03, device="cuda")
+    const_z = torch.full((n,), -5, dtype=torch.int32, device="cuda")
+    q = (sa, float(np.float32(0.03)), sc, za, -5, zc)
+    C1 = torch.empty((m, n), dtype=torch.int8, device="cuda")
+    C2 = torch.empty((m, n), dtype=torch.int8, device="cuda")
+    lib.texo_mm_int8_solve_per_channel(A.data_ptr(), B.data_ptr(), C1.data_ptr(), m, n, k, q[0],
+                                       const_s.data_ptr(), q[2], q[3], const_z.data_ptr(), q[5])
+    lib.texo_mm_int8_solve(A.data_ptr(), B.data_ptr(), C2.data_ptr(), m, n, k, *q)
+    torch.cuda.synchronize()
+    assert torch.equal(C1, C2)
+    assert lib.texo_mm_int8_status() == 0

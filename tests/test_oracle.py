@@ -165,3 +165,22 @@ def test_rms_norm_w_residual_against_numpy(oracle):
     assert np.array_equal(z, zz)
     want = zz.astype(np.float64) / np.sqrt((zz.astype(np.float64) ** 2).mean(axis=1, keepdims=True) + np.float64(np.float32(1e-5))) * w
     assert np.allclose(y, want, rtol=1e-12, atol=0)
+
+
+def test_per_channel_oracle_reduces_to_per_tensor(oracle):
+    rng = np.random.default_rng(3)
+    m, n, k = 9, 21, 50
+    a = rng.integers(-128, 128, (m, k), dtype=np.int8)
+    b = rng.integers(-128, 128, (k, n), dtype=np.int8)
+    q = (0.02, 0.03, 0.6, 3, -5, 1)
+    sb = np.full(n, q[1], dtype=np.float32)
+    zb = np.full(n, q[4], dtype=np.int32)
+    assert np.array_equal(oracle.mm_int8_per_channel(a, b, m, n, k, q[0], sb, q[2], q[3], zb, q[5]),
+                          oracle.mm_int8(a, b, m, n, k, q))
+    # column by column against the per-tensor oracle with that column's parameters
+    sb = rng.uniform(0.005, 0.05, n).astype(np.float32)
+    zb = rng.integers(-8, 9, n).astype(np.int32)
+    got = oracle.mm_int8_per_channel(a, b, m, n, k, q[0], sb, q[2], q[3], zb, q[5])
+    for col in range(n):
+        want = oracle.mm_int8(a, b[:, col:col + 1], m, 1, k, (q[0], float(sb[col]), q[2], q[3], int(zb[col]), q[5]))
+        assert np.array_equal(got[:, col:col + 1], want)

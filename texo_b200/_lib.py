@@ -20,6 +20,8 @@ _SIGNATURES = {
     # name: (restype, argtypes)
     "texo_mm_int8_solve": (None, [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int,
                                   _c_float, _c_float, _c_float, _c_int, _c_int, _c_int]),
+    "texo_mm_int8_solve_per_channel": (None, [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int,
+                                              _c_float, _c_ptr, _c_float, _c_int, _c_ptr, _c_int]),
     "texo_mm_int8_solve_noalloc": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int,
                                             _c_float, _c_float, _c_float, _c_int, _c_int, _c_int]),
     "texo_mm_int8_solve_host": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int,

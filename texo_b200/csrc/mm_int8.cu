@@ -128,7 +128,7 @@ __global__ void __launch_bounds__(G_THREADS)
     }
   }
 
-  const long long offset = (long long)K * q.za * q.zb;
+  const long long kza = (long long)K * q.za;
   const float zc = float(q.zc);
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
@@ -138,8 +138,10 @@ __global__ void __launch_bounds__(G_THREADS)
     for (int j = 0; j < 4; ++j) {
       const int n = col0 + tx * 4 + j;
       if (n >= N) continue;
-      const long long dot = tot[i][j] - (long long)q.zb * tra[i] - (long long)q.za * tcb[j] + offset;
-      C[size_t(m) * N + n] = int8_t(requantize(float(dot), q.sa, q.sb, q.sc, zc));
+      const float sb = q.sb_vec ? q.sb_vec[n] : q.sb;
+      const long long zb = q.sb_vec ? (q.zb_vec ? q.zb_vec[n] : 0) : q.zb;
+      const long long dot = tot[i][j] - zb * tra[i] - (long long)q.za * tcb[j] + kza * zb;
+      C[size_t(m) * N + n] = int8_t(requantize(float(dot), q.sa, sb, q.sc, zc));
     }
   }
 }
@@ -434,8 +436,6 @@ __global__ void __launch_bounds__(MMA_THREADS, 1)
     const int ew = warp - 2;
     const int quarter = warp % 4;  // TMEM lanes this warp may read: 32*quarter .. +31
     const int half = ew / 4;       // which 128 of the 256 accumulator columns
-    using Wide = typename std::conditional<WIDE, long long, unsigned>::type;
-    const Wide offset = Wide(K) * Wide(q.za) * Wide(q.zb);
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
@@ -448,35 +448,8 @@ __global__ void __launch_bounds__(MMA_THREADS, 1)
       if (!ok) break;
       tc_fence_after_sync();
       const int m = tm * BM + quarter * 32 + lane;
-      const bool row_ok = m < M;
-      Wide row_term = offset;
-      if (row_ok && q.zb != 0) row_term -= Wide(q.zb) * Wide(row_sum[m]);
-      int8_t* c_row = C + size_t(row_ok ? m : 0) * N;
-#pragma unroll 1
-      for (int chunk = 0; chunk < 4; ++chunk) {
-        const int col = half * 128 + chunk * 32;
-        const int n0 = tn * BN + col;
-        uint32_t v[32];
-        tmem_ld_32x32(tmem_base + acc * ACC_COLS + col + (uint32_t(quarter * 32) << 16), v);
-        tmem_ld_wait();
-        if (n0 >= N) continue;  // warp-uniform
-        uint32_t packed[8];
-        // col_sum is padded to a multiple of BN, so this never reads out of bounds.
-        if (q.fast_div)
-          requantize_chunk<WIDE, true>(v, col_sum + n0, row_term, q, packed);
-        else
-          requantize_chunk<WIDE, false>(v, col_sum + n0, row_term, q, packed);
-        if (row_ok) {
-          if (c_vector_ok && n0 + 32 <= N) {
-            int4* dst = reinterpret_cast<int4*>(c_row + n0);
-            dst[0] = make_int4(packed[0], packed[1], packed[2], packed[3]);
-            dst[1] = make_int4(packed[4], packed[5], packed[6], packed[7]);
-          } else {
-            for (int e = 0; e < 32 && n0 + e < N; ++e)
-              c_row[n0 + e] = int8_t((packed[e / 4] >> (8 * (e % 4))) & 0xff);
-          }
-        }
-      }
+      drain_half<WIDE>(tmem_base + acc * ACC_COLS + (uint32_t(quarter * 32) << 16), half * 128,
+                       tn * BN, m, m < M, C, row_sum, col_sum, N, K, q, c_vector_ok);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->acc_empty[acc]);
@@ -810,16 +783,25 @@ struct SkinnySchedule {
 // rows are computed without a branch (rows past M hold zeros), so their dependent chains
 // (64-bit correction, int-to-float, two multiplies, an IEEE division, round, saturate)
 // interleave; with one warp per scheduler a per-row branch would run them back to back.
+// `kza` = K * zA, `col_term` = zA * colsum(B)[n], `sb_n` / `zb_n` the weight scale and zero
+// point of this thread's column: dot = raw + zB * (K*zA - rowsum(A)[m]) - zA * colsum(B)[n].
 template <int ROWS, bool FAST>
 __device__ __forceinline__ void skinny_store_rows(const uint32_t (&v)[32], const int* row_sum,
-                                                  long long base, const Quant& q, float zc, int M,
+                                                  long long kza, long long col_term, float sb_n,
+                                                  int zb_n, const Quant& q, float zc, int M,
                                                   int8_t* out, size_t stride) {
   int r[ROWS];
 #pragma unroll
   for (int m = 0; m < ROWS; ++m) {
-    const long long dot = (long long)int(v[m]) - (long long)q.zb * row_sum[m] + base;
-    r[m] = FAST ? min(max(requantize_fast(float(dot), q), -128), 127)
-                : requantize(float(dot), q.sa, q.sb, q.sc, zc);
+    const long long dot = (long long)int(v[m]) + (long long)zb_n * (kza - row_sum[m]) - col_term;
+    if (FAST) {
+      const float acc = div_rn_inrange(__fmul_rn(__fmul_rn(float(dot), q.sa), sb_n), q.sc, q.rsc);
+      int t;
+      asm("add.sat.s32 %0, %1, %2;" : "=r"(t) : "r"(__float2int_rn(acc)), "r"(q.zc));
+      r[m] = min(max(t, -128), 127);
+    } else {
+      r[m] = requantize(float(dot), q.sa, sb_n, q.sc, zc);
+    }
   }
 #pragma unroll
   for (int m = 0; m < ROWS; ++m)
@@ -1018,7 +1000,7 @@ __global__ void __launch_bounds__(S_THREADS, 1)
     const int et = threadIdx.x - 64;  // 0..127 among the epilogue threads
     asm volatile("griddepcontrol.wait;" ::: "memory");  // before reading A / touching C, workspace
     // rowsum(A) for the zero-point identity: the activations are tiny, every CTA sums them.
-    if (q.zb != 0) {
+    if (q.zb != 0 || q.zb_vec != nullptr) {
       for (int m = ew; m < M; m += S_EPI_WARPS) {
         const int4* a = reinterpret_cast<const int4*>(A + size_t(m) * K);
         int acc = 0;
@@ -1035,7 +1017,7 @@ __global__ void __launch_bounds__(S_THREADS, 1)
       }
     }
     asm volatile("bar.sync 1, 128;" ::: "memory");
-    const long long offset = (long long)K * q.za * q.zb;
+    const long long kza = (long long)K * q.za;
     const float zc = float(q.zc);
     const int ws_rows = M + 1;  // workspace rows per shared tile: M dot rows + the colsum row
     SkinnySchedule sched(tiles, num_kb, gridDim.x, blockIdx.x);
@@ -1118,17 +1100,24 @@ __global__ void __launch_bounds__(S_THREADS, 1)
           asm volatile("bar.sync 1, 128;" ::: "memory");  // last_flag is rewritten by the next half
         }
         if (finalize && n < N) {
-          const long long base = offset - (long long)q.za * int(cs_raw);
+          const long long col_term = (long long)q.za * int(cs_raw);
+          const float sb_n = q.sb_vec ? __ldg(q.sb_vec + n) : q.sb;
+          const int zb_n = q.sb_vec ? (q.zb_vec ? __ldg(q.zb_vec + n) : 0) : q.zb;
+          const bool fast = q.fast_div && (!q.sb_vec || channel_in_fast_range(sb_n, zb_n));
           if (R == 16) {
-            if (q.fast_div)
-              skinny_store_rows<16, true>(v, bars->row_sum, base, q, zc, M, C + n, size_t(N));
+            if (fast)
+              skinny_store_rows<16, true>(v, bars->row_sum, kza, col_term, sb_n, zb_n, q, zc, M,
+                                          C + n, size_t(N));
             else
-              skinny_store_rows<16, false>(v, bars->row_sum, base, q, zc, M, C + n, size_t(N));
+              skinny_store_rows<16, false>(v, bars->row_sum, kza, col_term, sb_n, zb_n, q, zc, M,
+                                           C + n, size_t(N));
           } else {
-            if (q.fast_div)
-              skinny_store_rows<32, true>(v, bars->row_sum, base, q, zc, M, C + n, size_t(N));
+            if (fast)
+              skinny_store_rows<32, true>(v, bars->row_sum, kza, col_term, sb_n, zb_n, q, zc, M,
+                                          C + n, size_t(N));
             else
-              skinny_store_rows<32, false>(v, bars->row_sum, base, q, zc, M, C + n, size_t(N));
+              skinny_store_rows<32, false>(v, bars->row_sum, kza, col_term, sb_n, zb_n, q, zc, M,
+                                           C + n, size_t(N));
           }
         }
       }
@@ -1303,6 +1292,7 @@ static bool launch_tensor(DeviceCtx& ctx, const int8_t* A, const int8_t* B, int8
   const int pairs = (force == PATH_TENSOR || (force != PATH_TENSOR_PAIR && M <= BM))
                         ? 0 : max_active_pairs(ctx);
   Quant sums_q = q;
+  if (q.zb_vec) sums_q.zb = 1;  // per-channel zero points: the row sums are needed
   if (cached_col_sum) {
     sums_q.za = 0;  // nothing to do for the columns
     col_sum = const_cast<int*>(cached_col_sum);
@@ -1365,27 +1355,61 @@ static bool launch_tensor(DeviceCtx& ctx, const int8_t* A, const int8_t* B, int8
 }  // namespace i8
 }  // namespace texo
 
-// A, B, C are device pointers: A [M,K], B [K,N], C [M,N], row-major int8.
-extern "C" void solve(const int8_t* A, const int8_t* B, int8_t* C, int M, int N, int K,
-                      float scale_A, float scale_B, float scale_C, int zero_point_A,
-                      int zero_point_B, int zero_point_C) {
-  using namespace texo;
-  using namespace texo::i8;
+namespace texo {
+namespace i8 {
+// Dispatch shared by the per-tensor and the per-channel entry points.
+static void solve_with(const int8_t* A, const int8_t* B, int8_t* C, int M, int N, int K,
+                       const Quant& q) {
   if (M <= 0 || N <= 0) return;
   if (K < 0 || !C || (K > 0 && (!A || !B))) {
     note_host_error(STATUS_BAD_ARGUMENT);
     return;
   }
   DeviceCtx& ctx = device_ctx();
-  const Quant q = make_quant(scale_A, scale_B, scale_C, zero_point_A, zero_point_B, zero_point_C, K);
   const int force = forced_path();
-  if (force != PATH_GENERIC && ctx.cc_major >= 10 && tensor_path_ok(A, B, M, N, K)) {
+  const bool vectors_ok = (reinterpret_cast<uintptr_t>(q.sb_vec) & 15) == 0 &&
+                          (reinterpret_cast<uintptr_t>(q.zb_vec) & 15) == 0;
+  if (force != PATH_GENERIC && ctx.cc_major >= 10 && vectors_ok && tensor_path_ok(A, B, M, N, K)) {
     if (M <= 32 && (force == PATH_AUTO || force == PATH_SKINNY) &&
         launch_skinny(ctx, A, B, C, M, N, K, q))
       return;
     if (launch_tensor(ctx, A, B, C, M, N, K, q, force)) return;
   }
   launch_generic(A, B, C, M, N, K, q);
+}
+}  // namespace i8
+}  // namespace texo
+
+// A, B, C are device pointers: A [M,K], B [K,N], C [M,N], row-major int8.
+extern "C" void solve(const int8_t* A, const int8_t* B, int8_t* C, int M, int N, int K,
+                      float scale_A, float scale_B, float scale_C, int zero_point_A,
+                      int zero_point_B, int zero_point_C) {
+  using namespace texo::i8;
+  solve_with(A, B, C, M, N, K,
+             make_quant(scale_A, scale_B, scale_C, zero_point_A, zero_point_B, zero_point_C, K));
+}
+
+// The same operator with one weight scale (and optionally one weight zero point) per output
+// column: scale_B [N] FP32 and zero_point_B [N] int32 are DEVICE arrays; zero_point_B may be
+// null (all zero).  Column n is requantised as float(dot) * scale_A * scale_B[n] / scale_C
+// with dot = sum_k (A[m,k] - zA)(B[k,n] - zero_point_B[n]), in the same FP32 operation order.
+extern "C" void texo_mm_int8_solve_per_channel(const int8_t* A, const int8_t* B, int8_t* C, int M,
+                                               int N, int K, float scale_A, const float* scale_B,
+                                               float scale_C, int zero_point_A,
+                                               const int* zero_point_B, int zero_point_C) {
+  using namespace texo;
+  using namespace texo::i8;
+  if (M <= 0 || N <= 0) return;
+  if (!scale_B) {
+    note_host_error(STATUS_BAD_ARGUMENT);
+    return;
+  }
+  // The scalar fields stand for "a column inside the fast range"; the kernels check every
+  // column's own scale and zero point before they take the branch-free division.
+  Quant q = make_quant(scale_A, 1.0f, scale_C, zero_point_A, 0, zero_point_C, K);
+  q.sb_vec = scale_B;
+  q.zb_vec = zero_point_B;
+  solve_with(A, B, C, M, N, K, q);
 }
 
 // ------------------------------------------------------------ prepared weights

@@ -27,6 +27,11 @@ struct Quant {
   int za, zb, zc;
   float rsc;     // RN(1 / sc), for the branch-free division below
   int fast_div;  // 1 when every quotient of this call is inside that division's safe range
+  // Per-output-channel weight quantisation (both null for per-tensor): device arrays [N],
+  // 16-byte aligned; column n then uses sb_vec[n] instead of sb and, if zb_vec is not null,
+  // zb_vec[n] instead of zb (zb_vec null with sb_vec set means zero point 0 everywhere).
+  const float* sb_vec;
+  const int* zb_vec;
 };
 
 // Host side: fills the derived fields.  The branch-free division is exact only while no
@@ -37,7 +42,7 @@ struct Quant {
 // lets the tail run in integers (see requantize_fast).  Anything else (including NaN or
 // infinite scales) takes the plain IEEE division, element by element.
 inline Quant make_quant(float sa, float sb, float sc, int za, int zb, int zc, int K) {
-  Quant q = {sa, sb, sc, za, zb, zc, 0.f, 0};
+  Quant q = {sa, sb, sc, za, zb, zc, 0.f, 0, nullptr, nullptr};
   auto within = [](float v, float lo, float hi) {
     const float a = v < 0 ? -v : v;
     return a >= lo && a <= hi;  // false for NaN
@@ -81,31 +86,106 @@ __device__ __forceinline__ uint32_t pack_sat_s8(int r0, int r1, int r2, int r3) 
   return out;
 }
 
+// The scalar checks of make_quant applied to one column's weight scale and zero point.
+__device__ __forceinline__ bool channel_in_fast_range(float sb, int zb) {
+  const float a = fabsf(sb);
+  return a >= 0x1p-30f && a <= 0x1p5f && zb >= -32768 && zb <= 32768;
+}
+
 // One thread's 32 consecutive accumulator columns -> 32 int8 in eight words: zero-point
 // identity, then requantisation.  `col_sum_at` points at colsum(B) of the first column
-// (read through L2: another grid may have produced it while this one was running).
-template <bool WIDE, bool FAST>
+// (read through L2: another grid may have produced it while this one was running), `rt_row`
+// is K*zA - rowsum(A)[m] for this thread's row, so that
+//   dot = raw + zB * rt_row - zA * colsum(B)[n].
+// PC: per-channel weight scale / zero point, read from q.sb_vec / q.zb_vec at column n0 + ...
+// (N is a multiple of 4 on the tensor paths, so a group of four columns is inside or outside
+// the matrix as a whole).
+template <bool WIDE, bool FAST, bool PC>
 __device__ __forceinline__ void requantize_chunk(
     const uint32_t (&v)[32], const int* __restrict__ col_sum_at,
-    typename std::conditional<WIDE, long long, unsigned>::type row_term, const Quant& q,
+    typename std::conditional<WIDE, long long, unsigned>::type rt_row, const Quant& q, int n0, int N,
     uint32_t (&packed)[8]) {
   using Wide = typename std::conditional<WIDE, long long, unsigned>::type;
   using Signed = typename std::conditional<WIDE, long long, int>::type;
   const float zc = float(q.zc);
+  const Wide tensor_term = Wide(Signed(q.zb)) * rt_row;
 #pragma unroll
   for (int g = 0; g < 8; ++g) {
     int4 cs = make_int4(0, 0, 0, 0);
     if (q.za != 0) cs = __ldcg(reinterpret_cast<const int4*>(col_sum_at + g * 4));
     const int csv[4] = {cs.x, cs.y, cs.z, cs.w};
+    float sbv[4] = {q.sb, q.sb, q.sb, q.sb};
+    int zbv[4] = {0, 0, 0, 0};
+    if (PC && n0 + g * 4 < N) {
+      const float4 s4 = __ldg(reinterpret_cast<const float4*>(q.sb_vec + n0 + g * 4));
+      sbv[0] = s4.x, sbv[1] = s4.y, sbv[2] = s4.z, sbv[3] = s4.w;
+      if (q.zb_vec) {
+        const int4 z4 = __ldg(reinterpret_cast<const int4*>(q.zb_vec + n0 + g * 4));
+        zbv[0] = z4.x, zbv[1] = z4.y, zbv[2] = z4.z, zbv[3] = z4.w;
+      }
+    }
     int r[4];
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
-      const Wide dot = Wide(Signed(int(v[g * 4 + e]))) + row_term - Wide(q.za) * Wide(csv[e]);
+      const Wide zb_term = PC ? Wide(Signed(zbv[e])) * rt_row : tensor_term;
+      const Wide dot = Wide(Signed(int(v[g * 4 + e]))) + zb_term - Wide(Signed(q.za)) * Wide(Signed(csv[e]));
       const float x = float(Signed(dot));
-      r[e] = FAST ? requantize_fast(x, q) : requantize(x, q.sa, q.sb, q.sc, zc);
+      if (FAST) {
+        const float acc = div_rn_inrange(__fmul_rn(__fmul_rn(x, q.sa), sbv[e]), q.sc, q.rsc);
+        asm("add.sat.s32 %0, %1, %2;" : "=r"(r[e]) : "r"(__float2int_rn(acc)), "r"(q.zc));
+      } else {
+        r[e] = requantize(x, q.sa, sbv[e], q.sc, zc);
+      }
     }
     packed[g] = pack_sat_s8(r[0], r[1], r[2], r[3]);
   }
+}
+
+// Whether all per-channel parameters of the 32 columns starting at n0 allow the branch-free
+// division (warp-uniform: every lane of an epilogue warp looks at the same columns).
+__device__ __forceinline__ bool chunk_channels_fast(const Quant& q, int n0, int N) {
+  bool ok = true;
+#pragma unroll
+  for (int g = 0; g < 8; ++g) {
+    if (n0 + g * 4 >= N) continue;
+    const float4 s4 = __ldg(reinterpret_cast<const float4*>(q.sb_vec + n0 + g * 4));
+    int4 z4 = make_int4(0, 0, 0, 0);
+    if (q.zb_vec) z4 = __ldg(reinterpret_cast<const int4*>(q.zb_vec + n0 + g * 4));
+    ok = ok && channel_in_fast_range(s4.x, z4.x) && channel_in_fast_range(s4.y, z4.y) &&
+         channel_in_fast_range(s4.z, z4.z) && channel_in_fast_range(s4.w, z4.w);
+  }
+  return ok;
+}
+
+// Picks the form of requantize_chunk for one chunk.
+template <bool WIDE>
+__device__ __forceinline__ void requantize_chunk_auto(
+    const uint32_t (&v)[32], const int* __restrict__ col_sum_at,
+    typename std::conditional<WIDE, long long, unsigned>::type rt_row, const Quant& q, int n0, int N,
+    uint32_t (&packed)[8]) {
+  if (q.sb_vec == nullptr) {
+    if (q.fast_div)
+      requantize_chunk<WIDE, true, false>(v, col_sum_at, rt_row, q, n0, N, packed);
+    else
+      requantize_chunk<WIDE, false, false>(v, col_sum_at, rt_row, q, n0, N, packed);
+  } else {
+    if (q.fast_div && chunk_channels_fast(q, n0, N))
+      requantize_chunk<WIDE, true, true>(v, col_sum_at, rt_row, q, n0, N, packed);
+    else
+      requantize_chunk<WIDE, false, true>(v, col_sum_at, rt_row, q, n0, N, packed);
+  }
+}
+
+// K*zA - rowsum(A)[m]: the per-row factor of the zero-point identity.  The row sums exist
+// only when some weight zero point can be non-zero.
+template <bool WIDE>
+__device__ __forceinline__ typename std::conditional<WIDE, long long, unsigned>::type row_factor(
+    const int* __restrict__ row_sum, int m, bool row_ok, int K, const Quant& q) {
+  using Wide = typename std::conditional<WIDE, long long, unsigned>::type;
+  using Signed = typename std::conditional<WIDE, long long, int>::type;
+  Wide rt = Wide(Signed(K)) * Wide(Signed(q.za));
+  if (row_ok && (q.zb != 0 || q.zb_vec != nullptr)) rt -= Wide(Signed(__ldcg(row_sum + m)));
+  return rt;
 }
 
 constexpr int P_GROUP_M = 8;  // pair-tile rows per raster group
@@ -128,9 +208,7 @@ __device__ __forceinline__ void drain_half(uint32_t tmem_row_addr, int col0, int
                                            const int* __restrict__ row_sum,
                                            const int* __restrict__ col_sum, int N, int K,
                                            const Quant& q, int c_vector_ok) {
-  using Wide = typename std::conditional<WIDE, long long, unsigned>::type;
-  Wide row_term = Wide(K) * Wide(q.za) * Wide(q.zb);
-  if (row_ok && q.zb != 0) row_term -= Wide(q.zb) * Wide(__ldcg(row_sum + m));
+  const auto rt_row = row_factor<WIDE>(row_sum, m, row_ok, K, q);
   int8_t* c_row = C + size_t(row_ok ? m : 0) * N;
 #pragma unroll 1
   for (int chunk = 0; chunk < 4; ++chunk) {
@@ -142,10 +220,7 @@ __device__ __forceinline__ void drain_half(uint32_t tmem_row_addr, int col0, int
     if (n0 >= N) continue;  // warp-uniform
     uint32_t packed[8];
     // col_sum is padded to a multiple of the tile width: never out of bounds.
-    if (q.fast_div)
-      requantize_chunk<WIDE, true>(v, col_sum + n0, row_term, q, packed);
-    else
-      requantize_chunk<WIDE, false>(v, col_sum + n0, row_term, q, packed);
+    requantize_chunk_auto<WIDE>(v, col_sum + n0, rt_row, q, n0, N, packed);
     if (row_ok) {
       if (c_vector_ok && n0 + 32 <= N) {
         int4* dst = reinterpret_cast<int4*>(c_row + n0);

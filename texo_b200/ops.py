@@ -11,7 +11,7 @@ import torch
 
 from . import _lib
 
-__all__ = ["mm_int8", "mm_int4", "mm_int4a8", "dequantization", "rms_norm_w_residual",
+__all__ = ["mm_int8", "mm_int8_per_channel", "mm_int4", "mm_int4a8", "dequantization", "rms_norm_w_residual",
            "rms_norm_quant", "mm_int8_host", "Int8Weights", "last_path", "status", "force_path"]
 
 
@@ -68,6 +68,39 @@ def mm_int8(A: torch.Tensor, B: torch.Tensor, scale_A: float, scale_B: float, sc
         lib.texo_mm_int8_solve(A.data_ptr() if K else None, B.data_ptr() if K else None,
                                out.data_ptr(), M, N, K, scale_A, scale_B, scale_C,
                                zero_point_A, zero_point_B, zero_point_C)
+    return out
+
+
+def mm_int8_per_channel(A: torch.Tensor, B: torch.Tensor, scale_A: float, scale_B: torch.Tensor,
+                        scale_C: float, zero_point_A: int, zero_point_B: torch.Tensor | None,
+                        zero_point_C: int, out: torch.Tensor | None = None) -> torch.Tensor:
+    """mm_int8 with one weight scale (fp32 [N]) and optionally one weight zero point (int32 [N])
+    per output column, both CUDA tensors; see include/texo_b200.h."""
+    _check_cuda("A", A, torch.int8)
+    _check_cuda("B", B, torch.int8)
+    _check_cuda("scale_B", scale_B, torch.float32)
+    if A.dim() != 2 or B.dim() != 2 or A.shape[1] != B.shape[0]:
+        raise ValueError(f"shape mismatch: A {tuple(A.shape)} B {tuple(B.shape)}")
+    M, K = A.shape
+    N = B.shape[1]
+    if M <= 0 or N <= 0 or tuple(scale_B.shape) != (N,):
+        raise ValueError("M, N must be positive and scale_B must be [N]")
+    if zero_point_B is not None:
+        _check_cuda("zero_point_B", zero_point_B, torch.int32)
+        if tuple(zero_point_B.shape) != (N,):
+            raise ValueError("zero_point_B must be [N]")
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.int8, device=A.device)
+    else:
+        _check_cuda("out", out, torch.int8)
+        if tuple(out.shape) != (M, N):
+            raise ValueError("out has the wrong shape")
+    lib = _lib.load()
+    with torch.cuda.device(A.device), _DefaultStreamOrder(A.device):
+        lib.texo_mm_int8_solve_per_channel(
+            A.data_ptr() if K else None, B.data_ptr() if K else None, out.data_ptr(), M, N, K,
+            scale_A, scale_B.data_ptr(), scale_C, zero_point_A,
+            zero_point_B.data_ptr() if zero_point_B is not None else None, zero_point_C)
     return out
 
 
