@@ -2,7 +2,7 @@
 """Benchmark of the quantized-matmul hot path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload int8_8192|int8_decode|int4_w4a16|int4_w4a8|dequant|rmsnorm_quant|layer_sweep]
+                    [--workload int8_8192|int8_decode|int4_w4a16|int4_w4a8|int8_swiglu|dequant|rmsnorm_quant|layer_sweep]
 
 One "step" is one `solve` call over one batch of synthetic input.  The default workload is
 the INT8 quantized matmul M=N=K=8192 (uniform int8 inputs, per-tensor scales and non-zero
@@ -58,6 +58,11 @@ def workload_spec(name: str):
     if name == "dequant":
         return dict(op="dequantization", M=8192, N=8192, T=128, dtype="f32",
                     desc="tile-scale dequantization 8192x8192 T=128")
+    if name == "int8_swiglu":
+        return dict(op="mm_int8_swiglu", M=8192, N=3584, K=8192, dtype="int8",
+                    desc="INT8 gate/up projection with fused SwiGLU + requantisation: M=8192 K=8192, "
+                         "2x3584 interleaved weight columns -> H [8192, 3584] (one GPU's share of the "
+                         "BASELINE config 5 gate/up layer)")
     if name == "rmsnorm_quant":
         return dict(op="rms_norm_quant", M=8192, N=8192, dtype="f32",
                     desc="RMSNorm(x + residual) * weight quantised to int8 (+ residual stream out), "
@@ -73,6 +78,13 @@ def quant_params():
     return (sa, sb, sc, za or 3, zb or -5, zc)
 
 
+def swiglu_scales(spec):
+    """Weight scales that put gate and up values at a few units, and the output scale."""
+    q = quant_params()
+    spread = q[0] * 128 * 74 * np.sqrt(spec["K"])
+    return float(np.float32(1.5 / spread)), float(np.float32(2.0 / spread)), float(np.float32(0.03))
+
+
 def algorithmic_work(spec):
     """(ops per step, minimum bytes per step)."""
     if spec["op"] == "mm_int8":
@@ -84,6 +96,9 @@ def algorithmic_work(spec):
     if spec["op"] == "mm_int4a8":
         M, N, K = spec["M"], spec["N"], spec["K"]
         return 2.0 * M * N * K, float(M * K + N * K // 2 + M * N)
+    if spec["op"] == "mm_int8_swiglu":
+        M, F, K = spec["M"], spec["N"], spec["K"]  # N holds F, the number of output columns
+        return 2.0 * M * 2 * F * K, float(M * K + K * 2 * F + M * F)
     if spec["op"] == "rms_norm_quant":
         M, N = spec["M"], spec["N"]  # rows x features; reads x, residual (+weight), writes q and z
         return float(M * N), float(13 * M * N + 4 * N)
@@ -169,6 +184,10 @@ def cpu_inputs(spec, harness):
         M, N, K = spec["M"], spec["N"], spec["K"]
         return (rng.integers(-128, 128, (M, K), dtype=np.int8),
                 rng.integers(0, 256, (N, K // 2), dtype=np.uint8))
+    if spec["op"] == "mm_int8_swiglu":
+        M, F, K = spec["M"], spec["N"], spec["K"]
+        return (rng.integers(-128, 128, (M, K), dtype=np.int8),
+                rng.integers(-128, 128, (K, 2 * F), dtype=np.int8))
     if spec["op"] == "mm_int4":
         M, N, K, G = spec["M"], spec["N"], spec["K"], spec["G"]
         x = harness.float_to_half_bits(rng.normal(0, 1, (M, K)))
@@ -192,6 +211,11 @@ def cpu_run_rows(oracle, spec, inputs, q, r0, r1):
     elif spec["op"] == "mm_int4a8":
         A, w = inputs
         oracle.mm_int4a8(A, w, spec["M"], spec["N"], spec["K"], q, rows=(r0, r1))
+    elif spec["op"] == "mm_int8_swiglu":
+        A, B = inputs
+        sg, su, sh = swiglu_scales(spec)
+        oracle.mm_int8_swiglu(A, B, spec["M"], spec["N"], spec["K"], q[0], sg, su, sh, q[3], q[4], -q[4],
+                              rows=(r0, r1))
     elif spec["op"] == "mm_int4":
         x, w, s = inputs
         oracle.mm_int4(x, w, s, spec["M"], spec["N"], spec["K"], spec["G"], rows=(r0, r1))
@@ -310,6 +334,33 @@ def run_ours(args, spec, workload):
         h2d, d2h = M * K + K * N, M * N
         flush_note = (f"{nsets} weight/output sets rotated; working set per step "
                       f"{(M * K + K * N + M * N) / 2**20:.0f} MiB exceeds the 126 MB L2")
+    elif spec["op"] == "mm_int8_swiglu":
+        M, F, K = spec["M"], spec["N"], spec["K"]
+        sg, su, sh = swiglu_scales(spec)
+        A = torch.randint(-128, 128, (M, K), generator=g_a, device=dev, dtype=torch.int8)
+        nsets = 3
+        Bs = [torch.randint(-128, 128, (K, 2 * F), generator=g_b, device=dev, dtype=torch.int8)
+              for _ in range(nsets)]
+        Hs = [torch.empty((M, F), device=dev, dtype=torch.int8) for _ in range(nsets)]
+
+        def step(i):
+            j = i % nsets
+            lib.texo_mm_int8_swiglu_solve(A.data_ptr(), Bs[j].data_ptr(), Hs[j].data_ptr(), M, F, K,
+                                          q[0], sg, su, sh, q[3], q[4], -q[4], q[5])
+
+        hA, hB = A.cpu().pin_memory(), Bs[0].cpu().pin_memory()
+        hH = torch.empty((M, F), dtype=torch.int8).pin_memory()
+        dA, dB, dH = torch.empty_like(A), torch.empty_like(Bs[0]), torch.empty_like(Hs[0])
+
+        def e2e_step(i):
+            dA.copy_(hA, non_blocking=True)
+            dB.copy_(hB, non_blocking=True)
+            ops.mm_int8_swiglu(dA, dB, q[0], sg, su, sh, q[3], q[4], -q[4], q[5], out=dH)
+            hH.copy_(dH, non_blocking=True)
+
+        h2d, d2h = M * K + K * 2 * F, M * F
+        flush_note = (f"{nsets} weight/output sets rotated; working set per step "
+                      f"{(M * K + K * 2 * F + M * F) / 2**20:.0f} MiB")
     elif spec["op"] == "mm_int4a8":
         M, N, K = spec["M"], spec["N"], spec["K"]
         A = torch.randint(-128, 128, (M, K), generator=g_a, device=dev, dtype=torch.int8)
@@ -504,7 +555,7 @@ def run_ours(args, spec, workload):
     else:
         # No INT8 figure is measured on this pool; kind::i8 issues at twice the bf16 rate, so
         # the denominator is 2x the measured cuBLAS bf16 throughput (W4A16 runs kind::f16: 1x).
-        factor = 2.0 if spec["op"] in ("mm_int8", "mm_int4a8") else 1.0
+        factor = 2.0 if spec["op"] in ("mm_int8", "mm_int4a8", "mm_int8_swiglu") else 1.0
         key = "bf16_tflops_sustained" if long_run else "bf16_tflops"
         base = peaks.get(key, 1400.0 if long_run else 1590.0)
         peak = factor * base
@@ -650,7 +701,7 @@ def main():
     if args.steps is None:
         # about a second of GPU work, so that clocks under load are actually sampled
         args.steps = {"int8_8192": 2000, "int8_decode": 10000, "int4_w4a16": 1500, "int4_w4a8": 3000,
-                      "dequant": 5000, "rmsnorm_quant": 4000}[args.workload]
+                      "dequant": 5000, "rmsnorm_quant": 4000, "int8_swiglu": 2500}[args.workload]
         if args.impl == "reference":
             args.steps = 5
     if args.impl == "reference":

@@ -101,6 +101,19 @@ void texo_mm_int8_solve_per_channel(const int8_t* A, const int8_t* B, int8_t* C,
                                     float scale_A, const float* scale_B, float scale_C,
                                     int zero_point_A, const int* zero_point_B, int zero_point_C);
 
+/* Gate/up projection with the SwiGLU consumer fused into the epilogue (no counterpart in the
+ * reference as one operator; it fuses its INT8 matmul, src/mm_int8.cu, with the formula of its
+ * src/swiglu.cu:15-18).  B_gu [K, 2F] int8 holds gate and up weight columns interleaved
+ * (column 2j = gate j, 2j+1 = up j); H [M, F] int8:
+ *   gate = float(dot_gate) * scale_A * scale_gate,  up = float(dot_up) * scale_A * scale_up,
+ *   H = clamp(rint(up * gate / (1 + exp(-gate)) / scale_H) + zero_point_H, -128, 127)
+ * with the dots as in texo_mm_int8_solve (zero points zero_point_gate / zero_point_up for the
+ * two kinds of column).  exp is the GPU's approximate __expf, as in the reference operator. */
+void texo_mm_int8_swiglu_solve(const int8_t* A, const int8_t* B_gu, int8_t* H, int M, int F, int K,
+                               float scale_A, float scale_gate, float scale_up, float scale_H,
+                               int zero_point_A, int zero_point_gate, int zero_point_up,
+                               int zero_point_H);
+
 /* W4A8: packed-INT4 weights against INT8 activations, INT8 output.  No counterpart in the
  * reference (its mm_int4 takes FP16 activations, src/mm_int4.cu:386-390); it combines the
  * reference's weight format - w_q [N,K/2] uint8, high nibble = even k, value = nibble - 8

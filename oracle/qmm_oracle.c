@@ -145,6 +145,44 @@ int oracle_mm_int8_per_channel_rows(const int8_t *A, const int8_t *B, int8_t *C_
   return 0;
 }
 
+/* Gate/up projection with fused SwiGLU (no reference counterpart; composed from the pinned
+ * integer dot of mm_int8 and the formula of src/swiglu.cu:15-18, x2 * x1 / (1 + exp(-x1))).
+ * B is [K, 2F] with column 2j = gate j and 2j+1 = up j.  gate and up are dequantised in FP32
+ * in the order float(dot) * sA * s (bit-defined); everything after that is done in double
+ * here (the device uses the approximate __expf, as the reference does).  T_rows (double)
+ * receives h / s_out BEFORE rounding for rows [row0,row1): the caller rounds, adds the zero
+ * point, clamps, and knows how close each value was to a tie. */
+int oracle_mm_int8_swiglu_rows(const int8_t *A, const int8_t *B, double *T_rows, int M, int F,
+                               int K, float sa, float s_gate, float s_up, float s_out, int za,
+                               int z_gate, int z_up, int row0, int row1) {
+  if (M <= 0 || F <= 0 || K < 0 || row0 < 0 || row1 > M || row0 > row1) return -1;
+  const int N = 2 * F;
+  int8_t *bt = NULL;
+  if (K > 0) {
+    bt = transpose_b(B, K, N);
+    if (!bt) return -1;
+  }
+#pragma omp parallel for schedule(dynamic, 1)
+  for (int m = row0; m < row1; ++m)
+    for (int f = 0; f < F; ++f) {
+      int64_t dg = 0, du = 0;
+      if (K > 0) {
+        dg = dot_zp(A + (size_t)m * K, bt + (size_t)(2 * f) * K, K, za, z_gate);
+        du = dot_zp(A + (size_t)m * K, bt + (size_t)(2 * f + 1) * K, K, za, z_up);
+      }
+      float gate = (float)dg;
+      gate = gate * sa;
+      gate = gate * s_gate;
+      float up = (float)du;
+      up = up * sa;
+      up = up * s_up;
+      double h = (double)up * (double)gate / (1.0 + exp(-(double)gate));
+      T_rows[(size_t)(m - row0) * F + f] = h / (double)s_out;
+    }
+  free(bt);
+  return 0;
+}
+
 /* Verbatim-structure single-thread version of tests/mm_int8.cpp:39-48 (B walked with
  * stride N, double scaling): the reference's own CPU cost model for the timing arm. */
 int oracle_mm_int8_harness_loop(const int8_t *A, const int8_t *B, int8_t *C_rows, int M,

@@ -59,6 +59,17 @@ class Oracle:
         assert rc == 0
         return out
 
+    def mm_int8_swiglu(self, A, B, M, F, K, sa, s_gate, s_up, s_out, za, z_gate, z_up, rows=None):
+        """Returns h / s_out before rounding, float64 [rows, F]."""
+        r0, r1 = rows if rows else (0, M)
+        A = np.ascontiguousarray(A, dtype=np.int8) if K else None
+        B = np.ascontiguousarray(B, dtype=np.int8) if K else None
+        out = np.empty((r1 - r0, F), dtype=np.float64)
+        rc = self.lib.oracle_mm_int8_swiglu_rows(_p(A), _p(B), _p(out), M, F, K, _f(sa), _f(s_gate),
+                                                 _f(s_up), _f(s_out), za, z_gate, z_up, r0, r1)
+        assert rc == 0
+        return out
+
     def mm_int8_harness_loop(self, A, B, M, N, K, q, rows):
         r0, r1 = rows
         out = np.empty((r1 - r0, N), dtype=np.int8)

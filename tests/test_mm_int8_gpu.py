@@ -473,3 +473,43 @@ def test_per_channel_weight_quantisation(lib, oracle, shape, paths):
     torch.cuda.synchronize()
     assert torch.equal(C1, C2)
     assert lib.texo_mm_int8_status() == 0
+
+
+@pytest.mark.parametrize("shape,paths", [((300, 504, 1040), (0, 2, 4, 1)), ((128, 256, 512), (0, 2, 1)),
+                                         ((16, 512, 2048), (0,)), ((65, 33, 31), (0,)),
+                                         ((1024, 1024, 4096), (0,))])
+def test_fused_swiglu_epilogue(lib, oracle, shape, paths):
+    """Gate/up projection with up * silu(gate) and requantisation fused into the drain.  The
+    dequantised gate and up values are bit-defined; the activation uses the GPU's approximate
+    exponential (as the reference's swiglu operator does), so the int8 result may differ from
+    the double-precision oracle by one step, and only next to a rounding tie."""
+    m, f, k = shape
+    rng = np.random.default_rng(f + k)
+    a = rng.integers(-128, 128, (m, k), dtype=np.int8)
+    b = rng.integers(-128, 128, (k, 2 * f), dtype=np.int8)
+    sa, za = 0.02, 3
+    spread = 128 * 74 * np.sqrt(k)
+    for s_gate, s_up, z_gate, z_up, z_h in ((1.5 / (sa * spread), 2.0 / (sa * spread), -5, 4, 1),
+                                            (0.8 / (sa * spread), 1.0 / (sa * spread), 0, 0, -3)):
+        s_gate, s_up = float(np.float32(s_gate)), float(np.float32(s_up))
+        s_h = float(np.float32(0.03))
+        t = oracle.mm_int8_swiglu(a, b, m, f, k, sa, s_gate, s_up, s_h, za, z_gate, z_up)
+        want = np.clip(np.rint(t) + z_h, -128, 127)
+        assert np.count_nonzero(np.abs(want) < 127) > want.size // 2
+        A, B = _dev(a), _dev(b)
+        for force in paths:
+            lib.texo_mm_int8_force_path(force)
+            H = torch.full((m, f), 77, dtype=torch.int8, device="cuda")
+            lib.texo_mm_int8_swiglu_solve(A.data_ptr(), B.data_ptr(), H.data_ptr(), m, f, k, sa, s_gate,
+                                          s_up, s_h, za, z_gate, z_up, z_h)
+            torch.cuda.synchronize()
+            path = lib.texo_mm_int8_last_path()
+            lib.texo_mm_int8_force_path(0)
+            if force:
+                assert path == force, (shape, force, path)
+            got = H.cpu().numpy().astype(np.float64)
+            differ = got != want
+            near_tie = np.abs(np.abs(t - np.floor(t)) - 0.5) < 1e-4 * np.maximum(1.0, np.abs(t))
+            assert np.all(np.abs(got - want)[differ] <= 1) and np.all(near_tie[differ]), (shape, force)
+            assert differ.mean() < 2e-3, (shape, force, differ.mean())
+    assert lib.texo_mm_int8_status() == 0

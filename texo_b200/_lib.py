@@ -22,6 +22,9 @@ _SIGNATURES = {
                                   _c_float, _c_float, _c_float, _c_int, _c_int, _c_int]),
     "texo_mm_int8_solve_per_channel": (None, [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int,
                                               _c_float, _c_ptr, _c_float, _c_int, _c_ptr, _c_int]),
+    "texo_mm_int8_swiglu_solve": (None, [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int,
+                                         _c_float, _c_float, _c_float, _c_float,
+                                         _c_int, _c_int, _c_int, _c_int]),
     "texo_mm_int8_solve_noalloc": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int,
                                             _c_float, _c_float, _c_float, _c_int, _c_int, _c_int]),
     "texo_mm_int8_solve_host": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int,

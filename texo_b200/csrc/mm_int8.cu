@@ -1288,11 +1288,13 @@ static bool launch_tensor(DeviceCtx& ctx, const int8_t* A, const int8_t* B, int8
   int* row_sum = static_cast<int*>(device_scratch(ctx, row_bytes + size_t(np) * 4));
   if (!row_sum) return false;
   int* col_sum = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(row_sum) + row_bytes);
-  const int c_vector_ok = (reinterpret_cast<uintptr_t>(C) & 15) == 0 && N % 16 == 0;
+  // 16-byte row stores need aligned rows of the output (H [M, N/2] in the SwiGLU form)
+  const int c_vector_ok =
+      (reinterpret_cast<uintptr_t>(C) & 15) == 0 && (q.swiglu ? (N / 2) % 16 == 0 : N % 16 == 0);
   const int pairs = (force == PATH_TENSOR || (force != PATH_TENSOR_PAIR && M <= BM))
                         ? 0 : max_active_pairs(ctx);
   Quant sums_q = q;
-  if (q.zb_vec) sums_q.zb = 1;  // per-channel zero points: the row sums are needed
+  if (q.zb_vec || (q.swiglu && q.z_up != 0)) sums_q.zb = 1;  // the row sums are needed
   if (cached_col_sum) {
     sums_q.za = 0;  // nothing to do for the columns
     col_sum = const_cast<int*>(cached_col_sum);
@@ -1387,6 +1389,62 @@ extern "C" void solve(const int8_t* A, const int8_t* B, int8_t* C, int M, int N,
   using namespace texo::i8;
   solve_with(A, B, C, M, N, K,
              make_quant(scale_A, scale_B, scale_C, zero_point_A, zero_point_B, zero_point_C, K));
+}
+
+namespace texo {
+namespace i8 {
+// Any shape / alignment for the fused SwiGLU form: one output per thread, int64 dots.
+__global__ void __launch_bounds__(256)
+    swiglu_generic_kernel(const int8_t* __restrict__ A, const int8_t* __restrict__ B,
+                          int8_t* __restrict__ H, int M, int F, int K, Quant q) {
+  const int f = blockIdx.x * 16 + threadIdx.x % 16, m = blockIdx.y * 16 + threadIdx.x / 16;
+  if (m >= M || f >= F) return;
+  const int N = 2 * F;
+  long long dg = 0, du = 0;
+  for (int k = 0; k < K; ++k) {
+    const int a = int(A[size_t(m) * K + k]) - q.za;
+    dg += (long long)a * (int(B[size_t(k) * N + 2 * f]) - q.zb);
+    du += (long long)a * (int(B[size_t(k) * N + 2 * f + 1]) - q.z_up);
+  }
+  const float gate = __fmul_rn(__fmul_rn(float(dg), q.sa), q.sb);
+  const float up = __fmul_rn(__fmul_rn(float(du), q.sa), q.s_up);
+  H[size_t(m) * F + f] = int8_t(swiglu_requantize(gate, up, q));
+}
+}  // namespace i8
+}  // namespace texo
+
+// Gate/up projection with the SwiGLU consumer fused into the TMEM drain.  B_gu [K, 2F] holds
+// the gate and up weight columns interleaved (column 2j = gate j, column 2j+1 = up j), each
+// with its own per-tensor scale and zero point; H [M, F] int8 =
+//   clamp(rint(up * gate / (1 + exp(-gate)) / scale_H) + zero_point_H, -128, 127),
+//   gate = float(dot_gate) * scale_A * scale_gate,  up = float(dot_up) * scale_A * scale_up.
+// The [M, 2F] intermediate never exists in memory.
+extern "C" void texo_mm_int8_swiglu_solve(const int8_t* A, const int8_t* B_gu, int8_t* H, int M, int F,
+                                          int K, float scale_A, float scale_gate, float scale_up,
+                                          float scale_H, int zero_point_A, int zero_point_gate,
+                                          int zero_point_up, int zero_point_H) {
+  using namespace texo;
+  using namespace texo::i8;
+  if (M <= 0 || F <= 0) return;
+  if (K < 0 || F > (1 << 30) || !H || (K > 0 && (!A || !B_gu))) {
+    note_host_error(STATUS_BAD_ARGUMENT);
+    return;
+  }
+  Quant q = make_quant(scale_A, scale_gate, 1.0f, zero_point_A, zero_point_gate, 0, K);
+  q.swiglu = 1;
+  q.s_up = scale_up;
+  q.s_out = scale_H;
+  q.z_up = zero_point_up;
+  q.z_out = zero_point_H;
+  DeviceCtx& ctx = device_ctx();
+  const int force = forced_path();
+  const int N = 2 * F;
+  if (force != PATH_GENERIC && ctx.cc_major >= 10 && tensor_path_ok(A, B_gu, M, N, K) &&
+      launch_tensor(ctx, A, B_gu, H, M, N, K, q, force == PATH_SKINNY ? PATH_AUTO : force))
+    return;
+  swiglu_generic_kernel<<<dim3((F + 15) / 16, (M + 15) / 16), 256>>>(A, B_gu, H, M, F, K, q);
+  ++launch_counter();
+  last_path() = PATH_GENERIC;
 }
 
 // The same operator with one weight scale (and optionally one weight zero point) per output

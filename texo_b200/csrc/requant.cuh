@@ -32,6 +32,12 @@ struct Quant {
   // zb_vec[n] instead of zb (zb_vec null with sb_vec set means zero point 0 everywhere).
   const float* sb_vec;
   const int* zb_vec;
+  // Fused SwiGLU consumer (swiglu != 0): B holds gate and up columns interleaved (column 2j =
+  // gate j, 2j+1 = up j); sb / zb describe the gate columns, s_up / z_up the up columns, and
+  // the output is H [M, N/2] = requantised up * silu(gate) with scale s_out, zero point z_out.
+  int swiglu;
+  float s_up, s_out;
+  int z_up, z_out;
 };
 
 // Host side: fills the derived fields.  The branch-free division is exact only while no
@@ -42,7 +48,7 @@ struct Quant {
 // lets the tail run in integers (see requantize_fast).  Anything else (including NaN or
 // infinite scales) takes the plain IEEE division, element by element.
 inline Quant make_quant(float sa, float sb, float sc, int za, int zb, int zc, int K) {
-  Quant q = {sa, sb, sc, za, zb, zc, 0.f, 0, nullptr, nullptr};
+  Quant q = {sa, sb, sc, za, zb, zc, 0.f, 0, nullptr, nullptr, 0, 0.f, 0.f, 0, 0};
   auto within = [](float v, float lo, float hi) {
     const float a = v < 0 ? -v : v;
     return a >= lo && a <= hi;  // false for NaN
@@ -184,7 +190,8 @@ __device__ __forceinline__ typename std::conditional<WIDE, long long, unsigned>:
   using Wide = typename std::conditional<WIDE, long long, unsigned>::type;
   using Signed = typename std::conditional<WIDE, long long, int>::type;
   Wide rt = Wide(Signed(K)) * Wide(Signed(q.za));
-  if (row_ok && (q.zb != 0 || q.zb_vec != nullptr)) rt -= Wide(Signed(__ldcg(row_sum + m)));
+  if (row_ok && (q.zb != 0 || q.zb_vec != nullptr || (q.swiglu && q.z_up != 0)))
+    rt -= Wide(Signed(__ldcg(row_sum + m)));
   return rt;
 }
 
@@ -200,6 +207,72 @@ __device__ __forceinline__ void pair_tile_coords(int tile, int tiles_m, int tile
   tn = in_group / group_m;
 }
 
+// up * silu(gate), requantised: the arithmetic of the reference's src/swiglu.cu:15-18
+// (x2 * x1 / (1 + __expf(-x1)), FP32, same operation order) on the dequantised gate and up
+// values, then clamp(rint(h / s_out) + z_out).
+__device__ __forceinline__ int swiglu_requantize(float gate, float up, const Quant& q) {
+  const float h = __fdiv_rn(__fmul_rn(up, gate), __fadd_rn(1.f, __expf(-gate)));
+  float r = __fadd_rn(rintf(__fdiv_rn(h, q.s_out)), float(q.z_out));
+  r = fminf(fmaxf(r, -128.f), 127.f);
+  return __float2int_rn(r);
+}
+
+// The SwiGLU form of drain_half (below): this thread's row, 128 accumulator columns = 64
+// (gate, up) pairs -> 64 int8 of H, sixteen per 32-column chunk.  N counts accumulator
+// columns (2F); H has row stride N / 2.
+template <bool WIDE>
+__device__ __forceinline__ void drain_half_swiglu(uint32_t tmem_row_addr, int col0, int n_tile0,
+                                                  int m, bool row_ok, int8_t* __restrict__ H,
+                                                  const int* __restrict__ row_sum,
+                                                  const int* __restrict__ col_sum, int N, int K,
+                                                  const Quant& q, int h_vector_ok) {
+  using Wide = typename std::conditional<WIDE, long long, unsigned>::type;
+  using Signed = typename std::conditional<WIDE, long long, int>::type;
+  const Wide rt_row = row_factor<WIDE>(row_sum, m, row_ok, K, q);
+  const Wide gate_term = Wide(Signed(q.zb)) * rt_row, up_term = Wide(Signed(q.z_up)) * rt_row;
+  int8_t* h_row = H + size_t(row_ok ? m : 0) * (N / 2);
+#pragma unroll 1
+  for (int chunk = 0; chunk < 4; ++chunk) {
+    const int col = col0 + chunk * 32;
+    const int n0 = n_tile0 + col;
+    uint32_t v[32];
+    tmem_ld_32x32(tmem_row_addr + col, v);
+    tmem_ld_wait();
+    if (n0 >= N) continue;  // warp-uniform
+    uint32_t packed[4];
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {  // eight accumulator columns -> four outputs
+      int4 c0 = make_int4(0, 0, 0, 0), c1 = c0;
+      if (q.za != 0) {
+        c0 = __ldcg(reinterpret_cast<const int4*>(col_sum + n0 + g * 8));
+        c1 = __ldcg(reinterpret_cast<const int4*>(col_sum + n0 + g * 8 + 4));
+      }
+      const int csv[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+      int r[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const Wide dg = Wide(Signed(int(v[g * 8 + 2 * e]))) + gate_term -
+                        Wide(Signed(q.za)) * Wide(Signed(csv[2 * e]));
+        const Wide du = Wide(Signed(int(v[g * 8 + 2 * e + 1]))) + up_term -
+                        Wide(Signed(q.za)) * Wide(Signed(csv[2 * e + 1]));
+        const float gate = __fmul_rn(__fmul_rn(float(Signed(dg)), q.sa), q.sb);
+        const float up = __fmul_rn(__fmul_rn(float(Signed(du)), q.sa), q.s_up);
+        r[e] = swiglu_requantize(gate, up, q);
+      }
+      packed[g] = pack_sat_s8(r[0], r[1], r[2], r[3]);
+    }
+    if (row_ok) {
+      const int f0 = n0 / 2;  // first output column of this chunk
+      if (h_vector_ok && f0 + 16 <= N / 2) {
+        *reinterpret_cast<int4*>(h_row + f0) = make_int4(packed[0], packed[1], packed[2], packed[3]);
+      } else {
+        for (int e = 0; e < 16 && f0 + e < N / 2; ++e)
+          h_row[f0 + e] = int8_t((packed[e / 4] >> (8 * (e % 4))) & 0xff);
+      }
+    }
+  }
+}
+
 // Drains 128 columns [col0, col0+128) of one accumulator for this thread's row: zero-point
 // identity, FP32 requantisation, 32 int8 per 32-column chunk, vector stores when possible.
 template <bool WIDE>
@@ -208,6 +281,11 @@ __device__ __forceinline__ void drain_half(uint32_t tmem_row_addr, int col0, int
                                            const int* __restrict__ row_sum,
                                            const int* __restrict__ col_sum, int N, int K,
                                            const Quant& q, int c_vector_ok) {
+  if (q.swiglu) {
+    drain_half_swiglu<WIDE>(tmem_row_addr, col0, n_tile0, m, row_ok, C, row_sum, col_sum, N, K, q,
+                            c_vector_ok);
+    return;
+  }
   const auto rt_row = row_factor<WIDE>(row_sum, m, row_ok, K, q);
   int8_t* c_row = C + size_t(row_ok ? m : 0) * N;
 #pragma unroll 1

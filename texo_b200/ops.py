@@ -11,7 +11,7 @@ import torch
 
 from . import _lib
 
-__all__ = ["mm_int8", "mm_int8_per_channel", "mm_int4", "mm_int4a8", "dequantization", "rms_norm_w_residual",
+__all__ = ["mm_int8", "mm_int8_per_channel", "mm_int8_swiglu", "mm_int4", "mm_int4a8", "dequantization", "rms_norm_w_residual",
            "rms_norm_quant", "mm_int8_host", "Int8Weights", "last_path", "status", "force_path"]
 
 
@@ -101,6 +101,34 @@ def mm_int8_per_channel(A: torch.Tensor, B: torch.Tensor, scale_A: float, scale_
             A.data_ptr() if K else None, B.data_ptr() if K else None, out.data_ptr(), M, N, K,
             scale_A, scale_B.data_ptr(), scale_C, zero_point_A,
             zero_point_B.data_ptr() if zero_point_B is not None else None, zero_point_C)
+    return out
+
+
+def mm_int8_swiglu(A: torch.Tensor, B_gu: torch.Tensor, scale_A: float, scale_gate: float,
+                   scale_up: float, scale_H: float, zero_point_A: int, zero_point_gate: int,
+                   zero_point_up: int, zero_point_H: int,
+                   out: torch.Tensor | None = None) -> torch.Tensor:
+    """H[M,F] int8 = requantised up * silu(gate), with gate / up the interleaved columns of
+    A @ B_gu (B_gu [K, 2F]); see include/texo_b200.h."""
+    _check_cuda("A", A, torch.int8)
+    _check_cuda("B_gu", B_gu, torch.int8)
+    if A.dim() != 2 or B_gu.dim() != 2 or A.shape[1] != B_gu.shape[0] or B_gu.shape[1] % 2:
+        raise ValueError(f"shape mismatch: A {tuple(A.shape)} B_gu {tuple(B_gu.shape)}")
+    M, K = A.shape
+    F = B_gu.shape[1] // 2
+    if M <= 0 or F <= 0:
+        raise ValueError("M and F must be positive")
+    if out is None:
+        out = torch.empty((M, F), dtype=torch.int8, device=A.device)
+    else:
+        _check_cuda("out", out, torch.int8)
+        if tuple(out.shape) != (M, F):
+            raise ValueError("out has the wrong shape")
+    lib = _lib.load()
+    with torch.cuda.device(A.device), _DefaultStreamOrder(A.device):
+        lib.texo_mm_int8_swiglu_solve(A.data_ptr() if K else None, B_gu.data_ptr() if K else None,
+                                      out.data_ptr(), M, F, K, scale_A, scale_gate, scale_up, scale_H,
+                                      zero_point_A, zero_point_gate, zero_point_up, zero_point_H)
     return out
 
 
