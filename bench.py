@@ -2,7 +2,7 @@
 """Benchmark of the quantized-matmul hot path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload int8_8192|int8_decode|int4_w4a16|int4_w4a8|int8_swiglu|dequant|rmsnorm_quant|layer_sweep]
+                    [--workload int8_8192|int8_8192_presummed|int8_decode|int4_w4a16|int4_w4a8|int8_swiglu|dequant|rmsnorm_quant|layer_sweep]
 
 One "step" is one `solve` call over one batch of synthetic input.  The default workload is
 the INT8 quantized matmul M=N=K=8192 (uniform int8 inputs, per-tensor scales and non-zero
@@ -45,6 +45,11 @@ def workload_spec(name: str):
     if name == "int8_8192":
         return dict(op="mm_int8", M=8192, N=8192, K=8192, dtype="int8",
                     desc="INT8 zero-point/scale matmul M=N=K=8192 (BASELINE config 2)")
+    if name == "int8_8192_presummed":
+        return dict(op="mm_int8", M=8192, N=8192, K=8192, dtype="int8", presummed=True,
+                    desc="INT8 matmul M=N=K=8192 as an inference engine would issue it: colsum(B) "
+                         "cached with the weight handle, rowsum(A) delivered by the activation "
+                         "producer - the tensor kernel alone, no pre-pass")
     if name == "int8_decode":
         return dict(op="mm_int8", M=16, N=28672, K=8192, dtype="int8",
                     desc="INT8 decode-shaped matmul M=16 K=8192 N=28672 (BASELINE config 3)")
@@ -318,9 +323,19 @@ def run_ours(args, spec, workload):
               for _ in range(nsets)]
         Cs = [torch.empty((M, N), device=dev, dtype=torch.int8) for _ in range(nsets)]
 
-        def step(i):
-            j = i % nsets
-            lib.texo_mm_int8_solve(A.data_ptr(), Bs[j].data_ptr(), Cs[j].data_ptr(), M, N, K, *q)
+        if spec.get("presummed"):
+            handles = [lib.texo_mm_int8_prepare_weights(b.data_ptr(), K, N) for b in Bs]
+            row_sums = A.to(torch.int32).sum(dim=1, dtype=torch.int32).contiguous()
+            torch.cuda.synchronize()
+
+            def step(i):
+                j = i % nsets
+                lib.texo_mm_int8_solve_presummed(A.data_ptr(), row_sums.data_ptr(), handles[j],
+                                                 Cs[j].data_ptr(), M, *q)
+        else:
+            def step(i):
+                j = i % nsets
+                lib.texo_mm_int8_solve(A.data_ptr(), Bs[j].data_ptr(), Cs[j].data_ptr(), M, N, K, *q)
 
         host_in = [torch.empty((M, K), dtype=torch.int8).pin_memory(),
                    torch.empty((K, N), dtype=torch.int8).pin_memory()]
@@ -424,11 +439,13 @@ def run_ours(args, spec, workload):
         Wt = torch.rand((N,), generator=g_a, device=dev) + 0.5
         Qs = [torch.empty((M, N), device=dev, dtype=torch.int8) for _ in range(nsets)]
         Zs = [torch.empty((M, N), device=dev) for _ in range(nsets)]
+        RS = torch.empty((M,), device=dev, dtype=torch.int32)
 
         def step(i):
             j = i % nsets
             lib.texo_rms_norm_quant_solve(Xs[j].data_ptr(), Rs[j].data_ptr(), Wt.data_ptr(),
-                                          Qs[j].data_ptr(), Zs[j].data_ptr(), M, N, 1e-5, 0.03, 3)
+                                          Qs[j].data_ptr(), Zs[j].data_ptr(), RS.data_ptr(), M, N, 1e-5,
+                                          0.03, 3)
 
         hX, hR = Xs[0].cpu().pin_memory(), Rs[0].cpu().pin_memory()
         hQ = torch.empty((M, N), dtype=torch.int8).pin_memory()
@@ -700,7 +717,7 @@ def main():
     spec = workload_spec(args.workload)
     if args.steps is None:
         # about a second of GPU work, so that clocks under load are actually sampled
-        args.steps = {"int8_8192": 2000, "int8_decode": 10000, "int4_w4a16": 1500, "int4_w4a8": 3000,
+        args.steps = {"int8_8192": 2000, "int8_8192_presummed": 2000, "int8_decode": 10000, "int4_w4a16": 1500, "int4_w4a8": 3000,
                       "dequant": 5000, "rmsnorm_quant": 4000, "int8_swiglu": 2500}[args.workload]
         if args.impl == "reference":
             args.steps = 5

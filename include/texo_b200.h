@@ -82,6 +82,13 @@ void texo_mm_int8_release_weights(texo_int8_weights* weights);
 void texo_mm_int8_solve_prepared(const int8_t* A, const texo_int8_weights* weights, int8_t* C, int M,
                                  float scale_A, float scale_B, float scale_C, int zero_point_A,
                                  int zero_point_B, int zero_point_C);
+/* texo_mm_int8_solve_prepared with rowsum(A) supplied as well: row_sum_A [M] int32 (device),
+ * row m = sum_k A[m,k], e.g. as written by texo_rms_norm_quant_solve.  With the column sums
+ * in the handle and the row sums from the producer, a call launches the tensor kernel alone.
+ * row_sum_A null = texo_mm_int8_solve_prepared. */
+void texo_mm_int8_solve_presummed(const int8_t* A, const int* row_sum_A, const texo_int8_weights* w,
+                                  int8_t* C, int M, float scale_A, float scale_B, float scale_C,
+                                  int zero_point_A, int zero_point_B, int zero_point_C);
 
 /* Tile-scale dequantization.  Replaces `solve` of the reference's
  * src/dequantization.cu:40-43 (tests/dequantization.cpp:4).  X, Y [M,N] fp32,
@@ -141,10 +148,11 @@ void texo_rms_norm_w_residual_solve(const float* x, const float* residual, const
 /* The same, fused with INT8 activation quantisation - the producer of mm_int8's A.  No
  * counterpart in the reference.  q [N,C] int8 = clamp(rint(out / scale) + zero_point, -128,
  * 127) with `out` as above (never written to memory); z_out [N,C] FP32, if not null, receives
- * x + residual (the updated residual stream).  scale finite and non-zero. */
+ * x + residual (the updated residual stream); q_row_sum [N] int32, if not null, receives
+ * sum_j q[n,j] for texo_mm_int8_solve_presummed.  scale finite and non-zero. */
 void texo_rms_norm_quant_solve(const float* x, const float* residual, const float* weight,
-                               int8_t* q, float* z_out, int N, int C, float eps, float scale,
-                               int zero_point);
+                               int8_t* q, float* z_out, int* q_row_sum, int N, int C, float eps,
+                               float scale, int zero_point);
 /* 1 = two-pass kernel (any C, any alignment), 2 = row-in-registers kernel (C % 4 == 0,
  * C <= 16384, 16-byte aligned pointers). */
 int texo_rms_norm_last_path(void);

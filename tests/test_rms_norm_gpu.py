@@ -70,9 +70,11 @@ def test_quantised_matches_oracle(lib, oracle, shape):
         scale = float(np.float32(scale))
         q = torch.full((n, c), 99, dtype=torch.int8, device="cuda")
         zo = torch.full((n, c), 5.0, device="cuda") if with_z else None
+        rs = torch.full((n,), 12345, dtype=torch.int32, device="cuda")
         lib.texo_rms_norm_quant_solve(X.data_ptr(), R.data_ptr(), W.data_ptr(), q.data_ptr(),
-                                      zo.data_ptr() if with_z else None, n, c, EPS, scale, zp)
+                                      zo.data_ptr() if with_z else None, rs.data_ptr(), n, c, EPS, scale, zp)
         torch.cuda.synchronize()
+        assert np.array_equal(rs.cpu().numpy(), q.cpu().numpy().astype(np.int64).sum(axis=1))
         t = y / np.float64(scale)
         want = np.clip(np.rint(t) + zp, -128, 127)
         got = q.cpu().numpy().astype(np.float64)
@@ -119,18 +121,31 @@ def test_against_the_reference_kernel(lib):
         assert np.all(np.abs(a - b) <= 2e-6 * np.abs(b).max(axis=1, keepdims=True) + 1e-7)
 
 
-def test_producer_feeds_the_matmul(lib, oracle):
-    """norm+quantise -> mm_int8 on the device equals the oracle chain on the same int8 bytes."""
+@pytest.mark.parametrize("n", [64, 300])
+def test_producer_feeds_the_matmul(lib, oracle, n):
+    """norm+quantise -> mm_int8 on the device equals the oracle chain on the same int8 bytes;
+    with the producer's row sums and prepared weights (no pre-pass at all) the bytes are the
+    same again."""
     from texo_b200 import ops
 
-    n, c, cols = 64, 2048, 512
+    c, cols = 2048, 512
     x, r, w = _inputs(n, c, 21)
     rng = np.random.default_rng(5)
     b = rng.integers(-128, 128, (c, cols), dtype=np.int8)
     X, R, W, B = (torch.from_numpy(t).cuda() for t in (x, r, w, b))
     scale_a, zp_a = 0.03, 2
-    A = ops.rms_norm_quant(X, R, W, EPS, scale_a, zp_a)
+    rs = torch.empty((n,), dtype=torch.int32, device="cuda")
+    A = ops.rms_norm_quant(X, R, W, EPS, scale_a, zp_a, row_sum_out=rs)
     q = (scale_a, 0.02, float(np.float32(scale_a * 0.02 * 40 * 74 * np.sqrt(c) / 40)), zp_a, -3, 1)
     C = ops.mm_int8(A, B, *q)
     torch.cuda.synchronize()
-    assert np.array_equal(C.cpu().numpy(), oracle.mm_int8(A.cpu().numpy(), b, n, cols, c, q))
+    want = oracle.mm_int8(A.cpu().numpy(), b, n, cols, c, q)
+    assert np.array_equal(C.cpu().numpy(), want)
+    weights = ops.Int8Weights(B)
+    launches = lib.texo_kernel_launches()
+    C2 = weights.matmul(A, *q, row_sum=rs)
+    torch.cuda.synchronize()
+    assert np.array_equal(C2.cpu().numpy(), want)
+    if n > 32:
+        assert lib.texo_kernel_launches() - launches == 1  # the tensor kernel alone
+    weights.close()

@@ -38,8 +38,10 @@ _SIGNATURES = {
     "texo_mm_int4a8_solve": (None, [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int,
                                     _c_float, _c_float, _c_float, _c_int, _c_int, _c_int]),
     "texo_rms_norm_w_residual_solve": (None, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_float]),
-    "texo_rms_norm_quant_solve": (None, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int,
+    "texo_rms_norm_quant_solve": (None, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int,
                                          _c_float, _c_float, _c_int]),
+    "texo_mm_int8_solve_presummed": (None, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_float, _c_float,
+                                            _c_float, _c_int, _c_int, _c_int]),
     "texo_rms_norm_last_path": (_c_int, []),
     "texo_mm_int4a8_last_path": (_c_int, []),
     "texo_mm_int4a8_force_path": (None, [_c_int]),

@@ -1261,7 +1261,8 @@ static bool launch_skinny(DeviceCtx& ctx, const int8_t* A, const int8_t* B, int8
 // `cached_col_sum` (may be null): colsum(B) computed earlier for these weights, padded to a
 // multiple of the 256-column tile; the pre-pass then only sums the rows of A.
 static bool launch_tensor(DeviceCtx& ctx, const int8_t* A, const int8_t* B, int8_t* C, int M, int N,
-                          int K, const Quant& q, int force, const int* cached_col_sum = nullptr) {
+                          int K, const Quant& q, int force, const int* cached_col_sum = nullptr,
+                          const int* cached_row_sum = nullptr) {
   static bool configured[MAX_DEVICES] = {};
   if (!configured[ctx.device]) {
     cudaFuncSetAttribute(umma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
@@ -1298,6 +1299,10 @@ static bool launch_tensor(DeviceCtx& ctx, const int8_t* A, const int8_t* B, int8
   if (cached_col_sum) {
     sums_q.za = 0;  // nothing to do for the columns
     col_sum = const_cast<int*>(cached_col_sum);
+  }
+  if (cached_row_sum) {
+    sums_q.zb = 0;  // rowsum(A) came with the activations (their producer computed it)
+    row_sum = const_cast<int*>(cached_row_sum);
   }
   const bool sums_launched =
       launch_sums(A, B, row_sum, col_sum, M, N, K, sums_q, pairs > 0 ? ctx.sm_count : 0);
@@ -1513,10 +1518,33 @@ extern "C" void texo_mm_int8_release_weights(texo_int8_weights* w) {
   delete w;
 }
 
+static void solve_prepared_with(const int8_t* A, const int* row_sum_A, const texo_int8_weights* w,
+                                int8_t* C, int M, float scale_A, float scale_B, float scale_C,
+                                int zero_point_A, int zero_point_B, int zero_point_C);
+
 // Same operation as `solve` with B, K, N taken from the handle.
 extern "C" void texo_mm_int8_solve_prepared(const int8_t* A, const texo_int8_weights* w, int8_t* C,
                                             int M, float scale_A, float scale_B, float scale_C,
                                             int zero_point_A, int zero_point_B, int zero_point_C) {
+  solve_prepared_with(A, nullptr, w, C, M, scale_A, scale_B, scale_C, zero_point_A, zero_point_B,
+                      zero_point_C);
+}
+
+// The same with rowsum(A) supplied by the caller: row_sum_A [M] int32 (device), row m holding
+// sum_k A[m,k] - what texo_rms_norm_quant_solve writes next to the activations it produces.
+// With both sums known beforehand a call is the tensor kernel alone, no pre-pass.  A null
+// row_sum_A is texo_mm_int8_solve_prepared.
+extern "C" void texo_mm_int8_solve_presummed(const int8_t* A, const int* row_sum_A,
+                                             const texo_int8_weights* w, int8_t* C, int M,
+                                             float scale_A, float scale_B, float scale_C,
+                                             int zero_point_A, int zero_point_B, int zero_point_C) {
+  solve_prepared_with(A, row_sum_A, w, C, M, scale_A, scale_B, scale_C, zero_point_A, zero_point_B,
+                      zero_point_C);
+}
+
+static void solve_prepared_with(const int8_t* A, const int* row_sum_A, const texo_int8_weights* w,
+                                int8_t* C, int M, float scale_A, float scale_B, float scale_C,
+                                int zero_point_A, int zero_point_B, int zero_point_C) {
   using namespace texo;
   using namespace texo::i8;
   if (!w || M <= 0) {
@@ -1529,7 +1557,7 @@ extern "C" void texo_mm_int8_solve_prepared(const int8_t* A, const texo_int8_wei
   const int force = forced_path();
   if (w->col_sum && ctx.device == w->device && A && C && M > 32 && force != PATH_GENERIC &&
       force != PATH_SKINNY && tensor_path_ok(A, w->B, M, w->N, w->K)) {
-    if (launch_tensor(ctx, A, w->B, C, M, w->N, w->K, q, force, w->col_sum)) return;
+    if (launch_tensor(ctx, A, w->B, C, M, w->N, w->K, q, force, w->col_sum, row_sum_A)) return;
   }
   // Decode shapes get colsum(B) for free inside the skinny kernel; what the handle adds
   // there is the promise that B is unchanged, so the kernel may load weights before the

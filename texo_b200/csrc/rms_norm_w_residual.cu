@@ -43,6 +43,17 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
   return total;
 }
 
+__device__ __forceinline__ int block_sum_int(int v, int* scratch) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  if (threadIdx.x % 32 == 0) scratch[threadIdx.x / 32] = v;
+  __syncthreads();
+  int total = 0;
+#pragma unroll
+  for (int w = 0; w < THREADS / 32; ++w) total += scratch[w];
+  return total;
+}
+
 struct QuantOut {
   float scale, rscale;
   int zero_point;
@@ -66,10 +77,12 @@ template <int VEC, bool QUANT>
 __global__ void __launch_bounds__(THREADS)
     row_kernel(const float* __restrict__ x, const float* __restrict__ residual,
                const float* __restrict__ weight, float* __restrict__ out, int8_t* __restrict__ q,
-               float* __restrict__ z_out, int C, float eps, QuantOut qo) {
+               float* __restrict__ z_out, int* __restrict__ q_row_sum, int C, float eps, QuantOut qo) {
   __shared__ float scratch[THREADS / 32];
+  __shared__ int iscratch[THREADS / 32];
   const size_t row = size_t(blockIdx.x) * C;
   const int c4 = C / 4;
+  int qsum = 0;
   const float4* x4 = reinterpret_cast<const float4*>(x + row);
   const float4* r4 = reinterpret_cast<const float4*>(residual + row);
   float4 z[VEC];
@@ -106,12 +119,17 @@ __global__ void __launch_bounds__(THREADS)
       if (QUANT) {
         const uint32_t packed = i8::pack_sat_s8(quantize_one(y.x, qo), quantize_one(y.y, qo),
                                                 quantize_one(y.z, qo), quantize_one(y.w, qo));
+        qsum = __dp4a(int(packed), 0x01010101, qsum);
         __stcs(reinterpret_cast<unsigned int*>(q + row) + c, packed);
         if (z_out) __stcs(reinterpret_cast<float4*>(z_out + row) + c, z[i]);
       } else {
         __stcs(reinterpret_cast<float4*>(out + row) + c, y);
       }
     }
+  }
+  if (QUANT && q_row_sum) {
+    const int total = block_sum_int(qsum, iscratch);
+    if (threadIdx.x == 0) q_row_sum[blockIdx.x] = total;
   }
 }
 
@@ -120,9 +138,12 @@ template <bool QUANT>
 __global__ void __launch_bounds__(THREADS)
     generic_kernel(const float* __restrict__ x, const float* __restrict__ residual,
                    const float* __restrict__ weight, float* __restrict__ out,
-                   int8_t* __restrict__ q, float* __restrict__ z_out, int C, float eps, QuantOut qo) {
+                   int8_t* __restrict__ q, float* __restrict__ z_out, int* __restrict__ q_row_sum,
+                   int C, float eps, QuantOut qo) {
   __shared__ float scratch[THREADS / 32];
+  __shared__ int iscratch[THREADS / 32];
   const size_t row = size_t(blockIdx.x) * C;
+  int qsum = 0;
   float sum = 0.f;
   for (int j = threadIdx.x; j < C; j += THREADS) {
     const float z = __fadd_rn(x[row + j], residual[row + j]);
@@ -133,11 +154,17 @@ __global__ void __launch_bounds__(THREADS)
     const float z = __fadd_rn(x[row + j], residual[row + j]);
     const float y = z * inv_rms * weight[j];
     if (QUANT) {
-      q[row + j] = int8_t(quantize_one(y, qo));
+      const int v = quantize_one(y, qo);
+      qsum += v;
+      q[row + j] = int8_t(v);
       if (z_out) z_out[row + j] = z;
     } else {
       out[row + j] = y;
     }
+  }
+  if (QUANT && q_row_sum) {
+    const int total = block_sum_int(qsum, iscratch);
+    if (threadIdx.x == 0) q_row_sum[blockIdx.x] = total;
   }
 }
 
@@ -148,7 +175,7 @@ inline int& last_path() {
 
 template <bool QUANT>
 static void launch(const float* x, const float* residual, const float* weight, float* out, int8_t* q,
-                   float* z_out, int N, int C, float eps, const QuantOut& qo) {
+                   float* z_out, int* q_row_sum, int N, int C, float eps, const QuantOut& qo) {
   if (N <= 0 || C <= 0) return;
   auto aligned = [](const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; };
   const bool vec = C % 4 == 0 && C <= THREADS * 4 * MAX_VEC && aligned(x, 16) && aligned(residual, 16) &&
@@ -157,16 +184,16 @@ static void launch(const float* x, const float* residual, const float* weight, f
   if (vec) {
     const int need = (C / 4 + THREADS - 1) / THREADS;
     if (need <= 2)
-      row_kernel<2, QUANT><<<N, THREADS>>>(x, residual, weight, out, q, z_out, C, eps, qo);
+      row_kernel<2, QUANT><<<N, THREADS>>>(x, residual, weight, out, q, z_out, q_row_sum, C, eps, qo);
     else if (need <= 4)
-      row_kernel<4, QUANT><<<N, THREADS>>>(x, residual, weight, out, q, z_out, C, eps, qo);
+      row_kernel<4, QUANT><<<N, THREADS>>>(x, residual, weight, out, q, z_out, q_row_sum, C, eps, qo);
     else if (need <= 8)
-      row_kernel<8, QUANT><<<N, THREADS>>>(x, residual, weight, out, q, z_out, C, eps, qo);
+      row_kernel<8, QUANT><<<N, THREADS>>>(x, residual, weight, out, q, z_out, q_row_sum, C, eps, qo);
     else
-      row_kernel<MAX_VEC, QUANT><<<N, THREADS>>>(x, residual, weight, out, q, z_out, C, eps, qo);
+      row_kernel<MAX_VEC, QUANT><<<N, THREADS>>>(x, residual, weight, out, q, z_out, q_row_sum, C, eps, qo);
     last_path() = 2;
   } else {
-    generic_kernel<QUANT><<<N, THREADS>>>(x, residual, weight, out, q, z_out, C, eps, qo);
+    generic_kernel<QUANT><<<N, THREADS>>>(x, residual, weight, out, q, z_out, q_row_sum, C, eps, qo);
     last_path() = 1;
   }
   ++launch_counter();
@@ -185,15 +212,18 @@ extern "C" void solve(const float* x, const float* residual, const float* weight
     return;
   }
   const int slot = profile_start();
-  rn::launch<false>(x, residual, weight, out, nullptr, nullptr, N, C, eps, rn::QuantOut{1.f, 1.f, 0, 0});
+  rn::launch<false>(x, residual, weight, out, nullptr, nullptr, nullptr, N, C, eps,
+                    rn::QuantOut{1.f, 1.f, 0, 0});
   profile_stop(slot);
 }
 
 // q [N,C] int8 = quantised RMSNorm(x + residual) * weight; z_out [N,C] FP32 (may be null)
-// receives x + residual.  scale must be finite and non-zero.
+// receives x + residual; q_row_sum [N] int32 (may be null) receives sum_j q[n,j], which the
+// INT8 matmul needs for its zero-point correction (texo_mm_int8_solve_presummed) and would
+// otherwise recompute by reading q again.  scale must be finite and non-zero.
 extern "C" void texo_rms_norm_quant_solve(const float* x, const float* residual, const float* weight,
-                                          int8_t* q, float* z_out, int N, int C, float eps,
-                                          float scale, int zero_point) {
+                                          int8_t* q, float* z_out, int* q_row_sum, int N, int C,
+                                          float eps, float scale, int zero_point) {
   using namespace texo;
   if (N <= 0 || C <= 0) return;
   if (!x || !residual || !weight || !q || !(scale == scale) || scale == 0.f) {
@@ -207,7 +237,7 @@ extern "C" void texo_rms_norm_quant_solve(const float* x, const float* residual,
     qo.fast_div = 1;
   }
   const int slot = profile_start();
-  rn::launch<true>(x, residual, weight, nullptr, q, z_out, N, C, eps, qo);
+  rn::launch<true>(x, residual, weight, nullptr, q, z_out, q_row_sum, N, C, eps, qo);
   profile_stop(slot);
 }
 

@@ -231,9 +231,11 @@ def rms_norm_w_residual(x: torch.Tensor, residual: torch.Tensor, weight: torch.T
 
 def rms_norm_quant(x: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, eps: float,
                    scale: float, zero_point: int, out: torch.Tensor | None = None,
-                   z_out: torch.Tensor | None = None) -> torch.Tensor:
+                   z_out: torch.Tensor | None = None,
+                   row_sum_out: torch.Tensor | None = None) -> torch.Tensor:
     """q[N,C] int8 = clamp(rint(rms_norm_w_residual(...) / scale) + zero_point); z_out, if
-    given, receives x + residual.  The int8 activations feed mm_int8 / mm_int4a8 as A."""
+    given, receives x + residual, row_sum_out (int32 [N]) the row sums of q.  The int8
+    activations feed mm_int8 / mm_int4a8 as A, the row sums Int8Weights.matmul(row_sum=...)."""
     _check_norm_inputs(x, residual, weight)
     if not (scale == scale) or scale == 0.0:
         raise ValueError("scale must be finite and non-zero")
@@ -247,10 +249,15 @@ def rms_norm_quant(x: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor
         _check_cuda("z_out", z_out, torch.float32)
         if z_out.shape != x.shape:
             raise ValueError("z_out has the wrong shape")
+    if row_sum_out is not None:
+        _check_cuda("row_sum_out", row_sum_out, torch.int32)
+        if tuple(row_sum_out.shape) != (x.shape[0],):
+            raise ValueError("row_sum_out must be [N]")
     lib = _lib.load()
     with torch.cuda.device(x.device), _DefaultStreamOrder(x.device):
         lib.texo_rms_norm_quant_solve(x.data_ptr(), residual.data_ptr(), weight.data_ptr(),
                                       out.data_ptr(), z_out.data_ptr() if z_out is not None else None,
+                                      row_sum_out.data_ptr() if row_sum_out is not None else None,
                                       x.shape[0], x.shape[1], eps, scale, zero_point)
     return out
 
@@ -295,7 +302,9 @@ class Int8Weights:
 
     def matmul(self, A: torch.Tensor, scale_A: float, scale_B: float, scale_C: float,
                zero_point_A: int, zero_point_B: int, zero_point_C: int,
-               out: torch.Tensor | None = None) -> torch.Tensor:
+               out: torch.Tensor | None = None, row_sum: torch.Tensor | None = None) -> torch.Tensor:
+        """`row_sum` (int32 [M], optional): the row sums of A, if their producer computed them
+        (rms_norm_quant(row_sum_out=...)); the call then runs no pre-pass at all."""
         _check_cuda("A", A, torch.int8)
         if A.dim() != 2 or A.shape[1] != self.K:
             raise ValueError(f"A must be [M, {self.K}]")
@@ -304,10 +313,14 @@ class Int8Weights:
             out = torch.empty((M, self.N), dtype=torch.int8, device=A.device)
         else:
             _check_cuda("out", out, torch.int8)
+        if row_sum is not None:
+            _check_cuda("row_sum", row_sum, torch.int32)
+            if tuple(row_sum.shape) != (M,):
+                raise ValueError("row_sum must be [M]")
         with torch.cuda.device(A.device), _DefaultStreamOrder(A.device):
-            self._lib.texo_mm_int8_solve_prepared(A.data_ptr(), self._handle, out.data_ptr(), M,
-                                                  scale_A, scale_B, scale_C, zero_point_A,
-                                                  zero_point_B, zero_point_C)
+            self._lib.texo_mm_int8_solve_presummed(
+                A.data_ptr(), row_sum.data_ptr() if row_sum is not None else None, self._handle,
+                out.data_ptr(), M, scale_A, scale_B, scale_C, zero_point_A, zero_point_B, zero_point_C)
         return out
 
     def close(self) -> None:
