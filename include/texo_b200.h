@@ -121,6 +121,14 @@ void texo_mm_int8_swiglu_solve(const int8_t* A, const int8_t* B_gu, int8_t* H, i
                                int zero_point_A, int zero_point_gate, int zero_point_up,
                                int zero_point_H);
 
+/* INT8 matmul with a dequantising drain (the reference reaches the same values with mm_int8
+ * into an int8 C followed by a separate dequantisation pass; fused here, no counterpart as
+ * one operator): Y [M,N] FP16 (16-bit words) = half(float(dot) * scale_A * scale_B) with
+ * dot = sum_k (A-zA)(B-zB) exact, the two FP32 multiplies in this order, one round-to-nearest
+ * conversion to FP16. */
+void texo_mm_int8_dequant_solve(const int8_t* A, const int8_t* B, void* Y, int M, int N, int K,
+                                float scale_A, float scale_B, int zero_point_A, int zero_point_B);
+
 /* W4A8: packed-INT4 weights against INT8 activations, INT8 output.  No counterpart in the
  * reference (its mm_int4 takes FP16 activations, src/mm_int4.cu:386-390); it combines the
  * reference's weight format - w_q [N,K/2] uint8, high nibble = even k, value = nibble - 8

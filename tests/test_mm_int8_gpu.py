@@ -513,3 +513,35 @@ def test_fused_swiglu_epilogue(lib, oracle, shape, paths):
             assert np.all(np.abs(got - want)[differ] <= 1) and np.all(near_tie[differ]), (shape, force)
             assert differ.mean() < 2e-3, (shape, force, differ.mean())
     assert lib.texo_mm_int8_status() == 0
+
+
+@pytest.mark.parametrize("shape,paths", [((300, 1008, 1040), (0, 2, 4, 1)), ((128, 256, 512), (0, 2, 1)),
+                                         ((16, 512, 2048), (0,)), ((65, 67, 31), (0,)), ((40, 24, 0), (0,)),
+                                         ((300, 1000, 1040), (0,)),
+                                         ((256, 264, 33040), (0,))])
+def test_dequantising_fp16_drain(lib, oracle, shape, paths):
+    """half(float(dot) * sA * sB) straight from the accumulators: bit-exact against the exact
+    integer dot followed by the same two FP32 multiplies and one rounding to FP16."""
+    m, n, k = shape
+    rng = np.random.default_rng(m + n)
+    a = rng.integers(-128, 128, (m, k), dtype=np.int8)
+    b = rng.integers(-128, 128, (k, n), dtype=np.int8)
+    A, B = _dev(a) if k else None, _dev(b) if k else None
+    for sa, sb, za, zb in ((0.02, 0.03, 3, -5), (0.001, 0.004, 0, 0), (0.5, 2.0, -7, 9)):
+        sa32, sb32 = np.float32(sa), np.float32(sb)
+        dots = oracle.mm_int8_dots(a, b, m, n, k, za, zb) if k else np.zeros((m, n), np.int64)
+        with np.errstate(over="ignore"):  # values beyond FP16 become infinities on both sides
+            want = ((dots.astype(np.float32) * sa32) * sb32).astype(np.float16)
+        for force in paths:
+            lib.texo_mm_int8_force_path(force)
+            Y = torch.full((m, n), 7.0, dtype=torch.float16, device="cuda")
+            lib.texo_mm_int8_dequant_solve(A.data_ptr() if k else None, B.data_ptr() if k else None,
+                                           Y.data_ptr(), m, n, k, float(sa32), float(sb32), za, zb)
+            torch.cuda.synchronize()
+            path = lib.texo_mm_int8_last_path()
+            lib.texo_mm_int8_force_path(0)
+            if force:
+                assert path == force, (shape, force, path)
+            got = Y.cpu().numpy()
+            assert np.array_equal(got.view(np.uint16), want.view(np.uint16)), (shape, force, (sa, sb, za, zb))
+    assert lib.texo_mm_int8_status() == 0

@@ -1289,9 +1289,10 @@ static bool launch_tensor(DeviceCtx& ctx, const int8_t* A, const int8_t* B, int8
   int* row_sum = static_cast<int*>(device_scratch(ctx, row_bytes + size_t(np) * 4));
   if (!row_sum) return false;
   int* col_sum = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(row_sum) + row_bytes);
-  // 16-byte row stores need aligned rows of the output (H [M, N/2] in the SwiGLU form)
-  const int c_vector_ok =
-      (reinterpret_cast<uintptr_t>(C) & 15) == 0 && (q.swiglu ? (N / 2) % 16 == 0 : N % 16 == 0);
+  // 16-byte row stores need aligned rows of the output (H [M, N/2] in the SwiGLU form, FP16
+  // [M, N] in the dequantising form)
+  const int c_vector_ok = (reinterpret_cast<uintptr_t>(C) & 15) == 0 &&
+                          (q.swiglu ? (N / 2) % 16 == 0 : q.out_f16 ? N % 8 == 0 : N % 16 == 0);
   const int pairs = (force == PATH_TENSOR || (force != PATH_TENSOR_PAIR && M <= BM))
                         ? 0 : max_active_pairs(ctx);
   Quant sums_q = q;
@@ -1448,6 +1449,49 @@ extern "C" void texo_mm_int8_swiglu_solve(const int8_t* A, const int8_t* B_gu, i
       launch_tensor(ctx, A, B_gu, H, M, N, K, q, force == PATH_SKINNY ? PATH_AUTO : force))
     return;
   swiglu_generic_kernel<<<dim3((F + 15) / 16, (M + 15) / 16), 256>>>(A, B_gu, H, M, F, K, q);
+  ++launch_counter();
+  last_path() = PATH_GENERIC;
+}
+
+namespace texo {
+namespace i8 {
+// Any shape / alignment for the dequantising form: one output per thread, int64 dot.
+__global__ void __launch_bounds__(256)
+    dequant_generic_kernel(const int8_t* __restrict__ A, const int8_t* __restrict__ B,
+                           __half* __restrict__ Y, int M, int N, int K, Quant q) {
+  const int n = blockIdx.x * 16 + threadIdx.x % 16, m = blockIdx.y * 16 + threadIdx.x / 16;
+  if (m >= M || n >= N) return;
+  long long dot = 0;
+  for (int k = 0; k < K; ++k)
+    dot += (long long)(int(A[size_t(m) * K + k]) - q.za) * (int(B[size_t(k) * N + n]) - q.zb);
+  Y[size_t(m) * N + n] = __float2half_rn(__fmul_rn(__fmul_rn(float(dot), q.sa), q.sb));
+}
+}  // namespace i8
+}  // namespace texo
+
+// INT8 matmul with a dequantising drain: Y [M,N] FP16 = half(float(dot) * scale_A * scale_B),
+// dot = sum_k (A - zA)(B - zB) exact, FP32 multiplies in this order, one rounding to FP16.
+// The int8 C and the separate dequantisation pass over it never exist.
+extern "C" void texo_mm_int8_dequant_solve(const int8_t* A, const int8_t* B, void* Y, int M, int N,
+                                           int K, float scale_A, float scale_B, int zero_point_A,
+                                           int zero_point_B) {
+  using namespace texo;
+  using namespace texo::i8;
+  if (M <= 0 || N <= 0) return;
+  if (K < 0 || !Y || (K > 0 && (!A || !B))) {
+    note_host_error(STATUS_BAD_ARGUMENT);
+    return;
+  }
+  Quant q = make_quant(scale_A, scale_B, 1.0f, zero_point_A, zero_point_B, 0, K);
+  q.out_f16 = 1;
+  DeviceCtx& ctx = device_ctx();
+  const int force = forced_path();
+  if (force != PATH_GENERIC && ctx.cc_major >= 10 && tensor_path_ok(A, B, M, N, K) &&
+      launch_tensor(ctx, A, B, static_cast<int8_t*>(Y), M, N, K, q,
+                    force == PATH_SKINNY ? PATH_AUTO : force))
+    return;
+  dequant_generic_kernel<<<dim3((N + 15) / 16, (M + 15) / 16), 256>>>(A, B, static_cast<__half*>(Y),
+                                                                    M, N, K, q);
   ++launch_counter();
   last_path() = PATH_GENERIC;
 }

@@ -5,6 +5,7 @@
 #pragma once
 #include <cstdint>
 #include <type_traits>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
 #include "ptx.cuh"
@@ -38,6 +39,9 @@ struct Quant {
   int swiglu;
   float s_up, s_out;
   int z_up, z_out;
+  // Dequantising drain (out_f16 != 0): no requantisation, the output is FP16 [M, N],
+  // y = half(float(dot) * sa * sb).
+  int out_f16;
 };
 
 // Host side: fills the derived fields.  The branch-free division is exact only while no
@@ -48,7 +52,7 @@ struct Quant {
 // lets the tail run in integers (see requantize_fast).  Anything else (including NaN or
 // infinite scales) takes the plain IEEE division, element by element.
 inline Quant make_quant(float sa, float sb, float sc, int za, int zb, int zc, int K) {
-  Quant q = {sa, sb, sc, za, zb, zc, 0.f, 0, nullptr, nullptr, 0, 0.f, 0.f, 0, 0};
+  Quant q = {sa, sb, sc, za, zb, zc, 0.f, 0, nullptr, nullptr, 0, 0.f, 0.f, 0, 0, 0};
   auto within = [](float v, float lo, float hi) {
     const float a = v < 0 ? -v : v;
     return a >= lo && a <= hi;  // false for NaN
@@ -273,6 +277,60 @@ __device__ __forceinline__ void drain_half_swiglu(uint32_t tmem_row_addr, int co
   }
 }
 
+// The dequantising form of drain_half (below): y = half(float(dot) * sA * sB), 32 halves per
+// 32-column chunk.  Y is FP16 [M, N].
+template <bool WIDE>
+__device__ __forceinline__ void drain_half_f16(uint32_t tmem_row_addr, int col0, int n_tile0, int m,
+                                               bool row_ok, __half* __restrict__ Y,
+                                               const int* __restrict__ row_sum,
+                                               const int* __restrict__ col_sum, int N, int K,
+                                               const Quant& q, int y_vector_ok) {
+  using Wide = typename std::conditional<WIDE, long long, unsigned>::type;
+  using Signed = typename std::conditional<WIDE, long long, int>::type;
+  const Wide rt_row = row_factor<WIDE>(row_sum, m, row_ok, K, q);
+  const Wide zb_term = Wide(Signed(q.zb)) * rt_row;
+  __half* y_row = Y + size_t(row_ok ? m : 0) * N;
+#pragma unroll 1
+  for (int chunk = 0; chunk < 4; ++chunk) {
+    const int col = col0 + chunk * 32;
+    const int n0 = n_tile0 + col;
+    uint32_t v[32];
+    tmem_ld_32x32(tmem_row_addr + col, v);
+    tmem_ld_wait();
+    if (n0 >= N) continue;  // warp-uniform
+    uint32_t packed[16];
+#pragma unroll
+    for (int g = 0; g < 8; ++g) {
+      int4 cs = make_int4(0, 0, 0, 0);
+      if (q.za != 0) cs = __ldcg(reinterpret_cast<const int4*>(col_sum + n0 + g * 4));
+      const int csv[4] = {cs.x, cs.y, cs.z, cs.w};
+      float y[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const Wide dot = Wide(Signed(int(v[g * 4 + e]))) + zb_term - Wide(Signed(q.za)) * Wide(Signed(csv[e]));
+        y[e] = __fmul_rn(__fmul_rn(float(Signed(dot)), q.sa), q.sb);
+      }
+      const __half2 lo = __floats2half2_rn(y[0], y[1]), hi = __floats2half2_rn(y[2], y[3]);
+      packed[2 * g] = *reinterpret_cast<const uint32_t*>(&lo);
+      packed[2 * g + 1] = *reinterpret_cast<const uint32_t*>(&hi);
+    }
+    if (row_ok) {
+      if (y_vector_ok && n0 + 32 <= N) {
+        int4* dst = reinterpret_cast<int4*>(y_row + n0);
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          dst[i] = make_int4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+      } else {
+        for (int e = 0; e < 32 && n0 + e < N; ++e) {
+          const uint32_t word = packed[e / 2];
+          const unsigned short bits = (e & 1) ? (unsigned short)(word >> 16) : (unsigned short)(word & 0xffff);
+          reinterpret_cast<unsigned short*>(y_row)[n0 + e] = bits;
+        }
+      }
+    }
+  }
+}
+
 // Drains 128 columns [col0, col0+128) of one accumulator for this thread's row: zero-point
 // identity, FP32 requantisation, 32 int8 per 32-column chunk, vector stores when possible.
 template <bool WIDE>
@@ -284,6 +342,11 @@ __device__ __forceinline__ void drain_half(uint32_t tmem_row_addr, int col0, int
   if (q.swiglu) {
     drain_half_swiglu<WIDE>(tmem_row_addr, col0, n_tile0, m, row_ok, C, row_sum, col_sum, N, K, q,
                             c_vector_ok);
+    return;
+  }
+  if (q.out_f16) {
+    drain_half_f16<WIDE>(tmem_row_addr, col0, n_tile0, m, row_ok, reinterpret_cast<__half*>(C),
+                         row_sum, col_sum, N, K, q, c_vector_ok);
     return;
   }
   const auto rt_row = row_factor<WIDE>(row_sum, m, row_ok, K, q);

@@ -11,7 +11,7 @@ import torch
 
 from . import _lib
 
-__all__ = ["mm_int8", "mm_int8_per_channel", "mm_int8_swiglu", "mm_int4", "mm_int4a8", "dequantization", "rms_norm_w_residual",
+__all__ = ["mm_int8", "mm_int8_per_channel", "mm_int8_swiglu", "mm_int8_dequant", "mm_int4", "mm_int4a8", "dequantization", "rms_norm_w_residual",
            "rms_norm_quant", "mm_int8_host", "Int8Weights", "last_path", "status", "force_path"]
 
 
@@ -129,6 +129,31 @@ def mm_int8_swiglu(A: torch.Tensor, B_gu: torch.Tensor, scale_A: float, scale_ga
         lib.texo_mm_int8_swiglu_solve(A.data_ptr() if K else None, B_gu.data_ptr() if K else None,
                                       out.data_ptr(), M, F, K, scale_A, scale_gate, scale_up, scale_H,
                                       zero_point_A, zero_point_gate, zero_point_up, zero_point_H)
+    return out
+
+
+def mm_int8_dequant(A: torch.Tensor, B: torch.Tensor, scale_A: float, scale_B: float,
+                    zero_point_A: int, zero_point_B: int,
+                    out: torch.Tensor | None = None) -> torch.Tensor:
+    """Y[M,N] fp16 = half(float(sum_k (A - zA)(B - zB)) * scale_A * scale_B)."""
+    _check_cuda("A", A, torch.int8)
+    _check_cuda("B", B, torch.int8)
+    if A.dim() != 2 or B.dim() != 2 or A.shape[1] != B.shape[0]:
+        raise ValueError(f"shape mismatch: A {tuple(A.shape)} B {tuple(B.shape)}")
+    M, K = A.shape
+    N = B.shape[1]
+    if M <= 0 or N <= 0:
+        raise ValueError("M and N must be positive")
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.float16, device=A.device)
+    else:
+        _check_cuda("out", out, torch.float16)
+        if tuple(out.shape) != (M, N):
+            raise ValueError("out has the wrong shape")
+    lib = _lib.load()
+    with torch.cuda.device(A.device), _DefaultStreamOrder(A.device):
+        lib.texo_mm_int8_dequant_solve(A.data_ptr() if K else None, B.data_ptr() if K else None,
+                                       out.data_ptr(), M, N, K, scale_A, scale_B, zero_point_A, zero_point_B)
     return out
 
 
