@@ -621,8 +621,9 @@ def run_ours(args, spec, workload):
 def run_layer_sweep(args):
     """BASELINE config 5: the four INT8 projections of a transformer layer at M = 8192, weight
     columns sharded over the ranks (strong scaling: the layer is fixed, each GPU owns N/g
-    columns), with and without the all-gather of C.  Prints one JSON line with one entry per
-    projection; `value` is the aggregate TOPS of the four GEMMs without the gather."""
+    columns), without the all-gather of C, with an NCCL all-gather after the matmul, and with
+    the gather fused into the matmul's epilogue (peer stores).  Prints one JSON line with one
+    entry per projection; `value` is the aggregate TOPS of the four GEMMs without the gather."""
     import torch
     import torch.distributed as dist
 
@@ -681,9 +682,22 @@ def run_layer_sweep(args):
 
         ms = timed(gemm)
         ms_g = timed(gemm_gather) if world > 1 else ms
+        # the gather fused into the matmul's epilogue: every rank stores its slab into all
+        # ranks' copies of C (symmetric memory); one barrier per call makes the result usable
+        ms_f = ms
+        if world > 1:
+            out = sharded.GatheredOutput(M, N, dev)
+
+            def gemm_fused_gather():
+                sharded.mm_int8_allgather(A, B, out, *q)
+                out.wait()
+
+            ms_f = timed(gemm_fused_gather)
+            del out
         ops = 2.0 * M * N * K
         results.append({"layer": name, "K": K, "N": N, "slab": n1 - n0, "gemm_ms": ms,
-                        "gemm_plus_gather_ms": ms_g, "tops": ops / (ms * 1e-3) / 1e12})
+                        "gemm_plus_gather_ms": ms_g, "gemm_fused_gather_ms": ms_f,
+                        "tops": ops / (ms * 1e-3) / 1e12})
         total_ops += ops
         total_ms += ms
         del A, B, C
@@ -717,8 +731,9 @@ def main():
     spec = workload_spec(args.workload)
     if args.steps is None:
         # about a second of GPU work, so that clocks under load are actually sampled
-        args.steps = {"int8_8192": 2000, "int8_8192_presummed": 2000, "int8_decode": 10000, "int4_w4a16": 1500, "int4_w4a8": 3000,
-                      "dequant": 5000, "rmsnorm_quant": 4000, "int8_swiglu": 2500}[args.workload]
+        args.steps = {"int8_8192": 2000, "int8_8192_presummed": 2000, "int8_decode": 10000,
+                      "int4_w4a16": 1500, "int4_w4a8": 3000, "dequant": 5000, "rmsnorm_quant": 4000,
+                      "int8_swiglu": 2500}[args.workload]
         if args.impl == "reference":
             args.steps = 5
     if args.impl == "reference":

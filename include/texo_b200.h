@@ -129,6 +129,20 @@ void texo_mm_int8_swiglu_solve(const int8_t* A, const int8_t* B_gu, int8_t* H, i
 void texo_mm_int8_dequant_solve(const int8_t* A, const int8_t* B, void* Y, int M, int N, int K,
                                 float scale_A, float scale_B, int zero_point_A, int zero_point_B);
 
+/* mm_int8 on one GPU's column slab of the weights with the all-gather of C fused into the
+ * epilogue (the reference has no multi-GPU code).  C_all is a HOST array of n_gpus (<= 8)
+ * DEVICE pointers: entry r is GPU r's copy of the full output [M, ld_c], this process's own
+ * copy and peer mappings of the others (torch symmetric memory, CUDA IPC, cuMem).  The call
+ * computes C[:, col_offset : col_offset + N_slab] from A [M,K] and B_slab [K,N_slab] exactly
+ * as texo_mm_int8_solve and stores every finished piece into all n_gpus copies (plain stores
+ * over NVLink, no multicast, no waiting on other GPUs).  After all GPUs' calls have completed
+ * and the caller has synchronised them, every copy holds the whole C.  Returns 0, or -1 for
+ * invalid arguments. */
+int texo_mm_int8_solve_allgather(const int8_t* A, const int8_t* B_slab, int8_t* const* C_all,
+                                 int n_gpus, int M, int N_slab, int K, int ld_c, int col_offset,
+                                 float scale_A, float scale_B, float scale_C, int zero_point_A,
+                                 int zero_point_B, int zero_point_C);
+
 /* W4A8: packed-INT4 weights against INT8 activations, INT8 output.  No counterpart in the
  * reference (its mm_int4 takes FP16 activations, src/mm_int4.cu:386-390); it combines the
  * reference's weight format - w_q [N,K/2] uint8, high nibble = even k, value = nibble - 8

@@ -545,3 +545,40 @@ def test_dequantising_fp16_drain(lib, oracle, shape, paths):
             got = Y.cpu().numpy()
             assert np.array_equal(got.view(np.uint16), want.view(np.uint16)), (shape, force, (sa, sb, za, zb))
     assert lib.texo_mm_int8_status() == 0
+
+
+@pytest.mark.parametrize("shape,paths", [((300, 512, 1040), (0, 2, 4, 1)), ((16, 512, 1024), (0, 3)),
+                                         ((65, 67, 31), (0,))])
+def test_fused_allgather_stores_into_every_copy(lib, oracle, shape, paths):
+    """The all-gather form on one GPU: the 'peers' are three buffers on the same device.  The
+    slab must land at its column offset in every copy, bit-exact, and nothing else may change."""
+    import ctypes
+
+    m, n, k = shape
+    rng = np.random.default_rng(k)
+    a = rng.integers(-128, 128, (m, k), dtype=np.int8)
+    b = rng.integers(-128, 128, (k, n), dtype=np.int8)
+    q = (0.02, 0.03, float(np.float32(0.02 * 0.03 * 128 * 74 * np.sqrt(k) / 50)), 3, -5, 1)
+    want = oracle.mm_int8(a, b, m, n, k, q)
+    A, B = _dev(a), _dev(b)
+    ld, off = n + 272, 144 if n % 16 == 0 else 101
+    for force in paths:
+        copies = [torch.full((m, ld), 55, dtype=torch.int8, device="cuda") for _ in range(3)]
+        ptrs = (ctypes.c_void_p * 3)(*[c.data_ptr() for c in copies])
+        lib.texo_mm_int8_force_path(force)
+        rc = lib.texo_mm_int8_solve_allgather(A.data_ptr(), B.data_ptr(), ctypes.cast(ptrs, ctypes.c_void_p),
+                                              3, m, n, k, ld, off, *q)
+        torch.cuda.synchronize()
+        path = lib.texo_mm_int8_last_path()
+        lib.texo_mm_int8_force_path(0)
+        assert rc == 0
+        if force:
+            assert path == force
+        for c in copies:
+            host = c.cpu().numpy()
+            assert np.array_equal(host[:, off:off + n], want), (shape, force)
+            assert np.all(host[:, :off] == 55) and np.all(host[:, off + n:] == 55)
+    bad = (ctypes.c_void_p * 1)(0)
+    assert lib.texo_mm_int8_solve_allgather(A.data_ptr(), B.data_ptr(), ctypes.cast(bad, ctypes.c_void_p),
+                                            1, m, n, k, ld, off, *q) == -1
+    assert lib.texo_mm_int8_status() == 16  # bad argument, reported and cleared

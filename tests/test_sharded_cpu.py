@@ -75,6 +75,43 @@ def test_two_rank_gather_equals_unsharded(tmp_path, oracle, N):
         assert np.array_equal(np.load(tmp_path / f"c{r}.npy"), want)
 
 
+def _oracle_w4a8_solver(A, w, sa, sb, sc, za, zb, zc):
+    o = harness.load_oracle()
+    M, K = A.shape
+    out = o.mm_int4a8(A.numpy(), w.numpy(), M, w.shape[0], K, (sa, sb, sc, za, zb, zc))
+    return torch.from_numpy(out)
+
+
+def _w4a8_worker(rank, world, port, N, result_dir):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        M, K = 24, 96
+        A = torch.from_numpy(harness.hashed_int8(1, 0, np.arange(M), np.arange(K)))
+        n0, n1 = sharded.column_slab(N, world, rank)
+        w_slab = torch.from_numpy(harness.hashed_int8(1, 2, np.arange(n0, n1), np.arange(K // 2)).view(np.uint8))
+        q = (0.02, 0.03, 0.4, 3, -5, 1)
+        C = sharded.mm_int4a8_sharded(A, w_slab, N, *q, gather=True, solver=_oracle_w4a8_solver)
+        np.save(os.path.join(result_dir, f"w{rank}.npy"), C.numpy())
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("N", [256, 200])
+def test_two_rank_w4a8_gather_equals_unsharded(tmp_path, oracle, N):
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    mp.spawn(_w4a8_worker, args=(2, port, N, str(tmp_path)), nprocs=2, join=True)
+    M, K = 24, 96
+    A = harness.hashed_int8(1, 0, np.arange(M), np.arange(K))
+    w = harness.hashed_int8(1, 2, np.arange(N), np.arange(K // 2)).view(np.uint8)
+    want = oracle.mm_int4a8(A, w, M, N, K, (0.02, 0.03, 0.4, 3, -5, 1))
+    for r in range(2):
+        assert np.array_equal(np.load(tmp_path / f"w{r}.npy"), want)
+
+
 def _failing_worker(rank, world, port, result_dir):
     import datetime
 

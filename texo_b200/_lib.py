@@ -27,6 +27,9 @@ _SIGNATURES = {
                                          _c_int, _c_int, _c_int, _c_int]),
     "texo_mm_int8_dequant_solve": (None, [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int,
                                           _c_float, _c_float, _c_int, _c_int]),
+    "texo_mm_int8_solve_allgather": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int,
+                                             _c_int, _c_int, _c_float, _c_float, _c_float,
+                                             _c_int, _c_int, _c_int]),
     "texo_mm_int8_solve_noalloc": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int,
                                             _c_float, _c_float, _c_float, _c_int, _c_int, _c_int]),
     "texo_mm_int8_solve_host": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int,

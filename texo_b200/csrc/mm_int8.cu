@@ -141,7 +141,12 @@ __global__ void __launch_bounds__(G_THREADS)
       const float sb = q.sb_vec ? q.sb_vec[n] : q.sb;
       const long long zb = q.sb_vec ? (q.zb_vec ? q.zb_vec[n] : 0) : q.zb;
       const long long dot = tot[i][j] - zb * tra[i] - (long long)q.za * tcb[j] + kza * zb;
-      C[size_t(m) * N + n] = int8_t(requantize(float(dot), q.sa, sb, q.sc, zc));
+      const int8_t value = int8_t(requantize(float(dot), q.sa, sb, q.sc, zc));
+      if (q.n_peers > 0) {
+        for (int p = 0; p < q.n_peers; ++p) q.peers[p][size_t(m) * q.ldc + q.n_off + n] = value;
+      } else {
+        C[size_t(m) * N + n] = value;
+      }
     }
   }
 }
@@ -789,7 +794,7 @@ template <int ROWS, bool FAST>
 __device__ __forceinline__ void skinny_store_rows(const uint32_t (&v)[32], const int* row_sum,
                                                   long long kza, long long col_term, float sb_n,
                                                   int zb_n, const Quant& q, float zc, int M,
-                                                  int8_t* out, size_t stride) {
+                                                  int8_t* out, size_t stride, int col) {
   int r[ROWS];
 #pragma unroll
   for (int m = 0; m < ROWS; ++m) {
@@ -802,6 +807,17 @@ __device__ __forceinline__ void skinny_store_rows(const uint32_t (&v)[32], const
     } else {
       r[m] = requantize(float(dot), q.sa, sb_n, q.sc, zc);
     }
+  }
+  if (q.n_peers > 0) {
+    // `out` is C + n of a private result; the gathered form stores at column n_off + n of
+    // every peer's [M, ldc] matrix instead (n recovered from the pointer difference)
+    for (int p = 0; p < q.n_peers; ++p) {
+      int8_t* dst = q.peers[p] + q.n_off + col;
+#pragma unroll
+      for (int m = 0; m < ROWS; ++m)
+        if (m < M) dst[size_t(m) * q.ldc] = int8_t(r[m]);
+    }
+    return;
   }
 #pragma unroll
   for (int m = 0; m < ROWS; ++m)
@@ -1107,17 +1123,17 @@ __global__ void __launch_bounds__(S_THREADS, 1)
           if (R == 16) {
             if (fast)
               skinny_store_rows<16, true>(v, bars->row_sum, kza, col_term, sb_n, zb_n, q, zc, M,
-                                          C + n, size_t(N));
+                                          C + n, size_t(N), n);
             else
               skinny_store_rows<16, false>(v, bars->row_sum, kza, col_term, sb_n, zb_n, q, zc, M,
-                                           C + n, size_t(N));
+                                           C + n, size_t(N), n);
           } else {
             if (fast)
               skinny_store_rows<32, true>(v, bars->row_sum, kza, col_term, sb_n, zb_n, q, zc, M,
-                                          C + n, size_t(N));
+                                          C + n, size_t(N), n);
             else
               skinny_store_rows<32, false>(v, bars->row_sum, kza, col_term, sb_n, zb_n, q, zc, M,
-                                           C + n, size_t(N));
+                                           C + n, size_t(N), n);
           }
         }
       }
@@ -1291,8 +1307,13 @@ static bool launch_tensor(DeviceCtx& ctx, const int8_t* A, const int8_t* B, int8
   int* col_sum = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(row_sum) + row_bytes);
   // 16-byte row stores need aligned rows of the output (H [M, N/2] in the SwiGLU form, FP16
   // [M, N] in the dequantising form)
-  const int c_vector_ok = (reinterpret_cast<uintptr_t>(C) & 15) == 0 &&
-                          (q.swiglu ? (N / 2) % 16 == 0 : q.out_f16 ? N % 8 == 0 : N % 16 == 0);
+  int c_vector_ok = (reinterpret_cast<uintptr_t>(C) & 15) == 0 &&
+                    (q.swiglu ? (N / 2) % 16 == 0 : q.out_f16 ? N % 8 == 0 : N % 16 == 0);
+  if (q.n_peers > 0) {
+    c_vector_ok = q.ldc % 16 == 0 && q.n_off % 16 == 0;
+    for (int p = 0; p < q.n_peers; ++p)
+      c_vector_ok = c_vector_ok && (reinterpret_cast<uintptr_t>(q.peers[p]) & 15) == 0;
+  }
   const int pairs = (force == PATH_TENSOR || (force != PATH_TENSOR_PAIR && M <= BM))
                         ? 0 : max_active_pairs(ctx);
   Quant sums_q = q;
@@ -1494,6 +1515,41 @@ extern "C" void texo_mm_int8_dequant_solve(const int8_t* A, const int8_t* B, voi
                                                                     M, N, K, q);
   ++launch_counter();
   last_path() = PATH_GENERIC;
+}
+
+// mm_int8 on this GPU's column slab of the weights with the all-gather of C fused into the
+// drain.  C_all: HOST array of n_gpus DEVICE pointers, entry r = GPU r's copy of the full
+// output [M, ld_c] (this process's own copy included; the others are peer mappings of the
+// same allocation, e.g. from torch symmetric memory or CUDA IPC).  The call computes
+// C[:, col_offset : col_offset + N_slab] = requantised A x B_slab and writes every finished
+// piece into all n_gpus copies with plain stores, so when every GPU's call has completed (the
+// caller synchronises them, e.g. with a barrier on the symmetric-memory handle) each copy holds
+// the whole row-major C.  The kernel never waits for another GPU.
+extern "C" int texo_mm_int8_solve_allgather(const int8_t* A, const int8_t* B_slab,
+                                            int8_t* const* C_all, int n_gpus, int M, int N_slab,
+                                            int K, int ld_c, int col_offset, float scale_A,
+                                            float scale_B, float scale_C, int zero_point_A,
+                                            int zero_point_B, int zero_point_C) {
+  using namespace texo;
+  using namespace texo::i8;
+  if (M <= 0 || N_slab <= 0) return 0;
+  if (!C_all || n_gpus < 1 || n_gpus > MAX_PEERS || col_offset < 0 || ld_c < col_offset + N_slab) {
+    note_host_error(STATUS_BAD_ARGUMENT);
+    return -1;
+  }
+  Quant q = make_quant(scale_A, scale_B, scale_C, zero_point_A, zero_point_B, zero_point_C, K);
+  q.n_peers = n_gpus;
+  q.ldc = ld_c;
+  q.n_off = col_offset;
+  for (int r = 0; r < n_gpus; ++r) {
+    if (!C_all[r]) {
+      note_host_error(STATUS_BAD_ARGUMENT);
+      return -1;
+    }
+    q.peers[r] = C_all[r];
+  }
+  solve_with(A, B_slab, C_all[0], M, N_slab, K, q);
+  return 0;
 }
 
 // The same operator with one weight scale (and optionally one weight zero point) per output

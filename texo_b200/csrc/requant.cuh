@@ -42,7 +42,14 @@ struct Quant {
   // Dequantising drain (out_f16 != 0): no requantisation, the output is FP16 [M, N],
   // y = half(float(dot) * sa * sb).
   int out_f16;
+  // Fused all-gather (n_peers > 0): the [M, N] result is a column slab of a wider matrix
+  // [M, ldc] that every GPU of the node holds; each finished piece is stored at column
+  // n_off + n of ALL of them (plain stores into peer-mapped memory over NVLink), so the
+  // gather rides under the main loop and no collective follows.  The C argument is unused.
+  int n_peers, ldc, n_off;
+  int8_t* peers[8];
 };
+constexpr int MAX_PEERS = 8;
 
 // Host side: fills the derived fields.  The branch-free division is exact only while no
 // intermediate leaves the normal range, so it is enabled when the scales bound every
@@ -52,7 +59,7 @@ struct Quant {
 // lets the tail run in integers (see requantize_fast).  Anything else (including NaN or
 // infinite scales) takes the plain IEEE division, element by element.
 inline Quant make_quant(float sa, float sb, float sc, int za, int zb, int zc, int K) {
-  Quant q = {sa, sb, sc, za, zb, zc, 0.f, 0, nullptr, nullptr, 0, 0.f, 0.f, 0, 0, 0};
+  Quant q = {sa, sb, sc, za, zb, zc, 0.f, 0, nullptr, nullptr, 0, 0.f, 0.f, 0, 0, 0, 0, 0, 0, {}};
   auto within = [](float v, float lo, float hi) {
     const float a = v < 0 ? -v : v;
     return a >= lo && a <= hi;  // false for NaN
@@ -362,7 +369,20 @@ __device__ __forceinline__ void drain_half(uint32_t tmem_row_addr, int col0, int
     uint32_t packed[8];
     // col_sum is padded to a multiple of the tile width: never out of bounds.
     requantize_chunk_auto<WIDE>(v, col_sum + n0, rt_row, q, n0, N, packed);
-    if (row_ok) {
+    if (row_ok && q.n_peers > 0) {
+      const size_t at = size_t(m) * q.ldc + q.n_off + n0;
+      for (int p = 0; p < q.n_peers; ++p) {
+        int8_t* dst_row = q.peers[p] + at;
+        if (c_vector_ok && n0 + 32 <= N) {
+          int4* dst = reinterpret_cast<int4*>(dst_row);
+          dst[0] = make_int4(packed[0], packed[1], packed[2], packed[3]);
+          dst[1] = make_int4(packed[4], packed[5], packed[6], packed[7]);
+        } else {
+          for (int e = 0; e < 32 && n0 + e < N; ++e)
+            dst_row[e] = int8_t((packed[e / 4] >> (8 * (e % 4))) & 0xff);
+        }
+      }
+    } else if (row_ok) {
       if (c_vector_ok && n0 + 32 <= N) {
         int4* dst = reinterpret_cast<int4*>(c_row + n0);
         dst[0] = make_int4(packed[0], packed[1], packed[2], packed[3]);

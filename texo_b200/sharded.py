@@ -8,12 +8,13 @@ NCCL/NVLink is optional.  One process per GPU (torch.distributed).
 """
 from __future__ import annotations
 
+import ctypes
 from typing import Callable
 
 import torch
 import torch.distributed as dist
 
-from . import ops
+from . import _lib, ops
 
 SLAB_ALIGN = 128  # keeps every slab a whole number of MMA tile columns / TMA boxes
 
@@ -98,3 +99,72 @@ def mm_int4_sharded(x: torch.Tensor, w_q_slab: torch.Tensor, scales_slab: torch.
     else:
         y_slab = x.new_empty((x.shape[0], 0))
     return all_gather_columns(y_slab, N, group) if gather else y_slab
+
+
+def mm_int4a8_sharded(A: torch.Tensor, w_q_slab: torch.Tensor, N: int, scale_A: float, scale_B: float,
+                      scale_C: float, zero_point_A: int, zero_point_B: int, zero_point_C: int,
+                      gather: bool = False, group=None,
+                      solver: Callable[..., torch.Tensor] | None = None) -> torch.Tensor:
+    """W4A8: output columns are rows of w_q [N, K/2], so a rank's slab is `shard_rows(w_q)`."""
+    solver = solver or ops.mm_int4a8
+    rank, world = dist.get_rank(group), dist.get_world_size(group)
+    n0, n1 = column_slab(N, world, rank)
+    if w_q_slab.shape[0] != n1 - n0:
+        raise ValueError(f"rank {rank}: slab has {w_q_slab.shape[0]} rows, expected {n1 - n0}")
+    if n1 > n0:
+        C_slab = solver(A, w_q_slab, scale_A, scale_B, scale_C, zero_point_A, zero_point_B,
+                        zero_point_C)
+    else:
+        C_slab = A.new_empty((A.shape[0], 0), dtype=torch.int8)
+    return all_gather_columns(C_slab, N, group) if gather else C_slab
+
+
+class GatheredOutput:
+    """The full row-major C [M, N] of a column-sharded matmul, one copy per GPU of the node,
+    allocated from torch symmetric memory so that every rank can store into every copy.
+
+    `mm_int8_allgather` writes this rank's column slab into all copies from inside the matmul's
+    epilogue (peer stores over NVLink); after `wait()` every rank's `tensor` holds the whole C.
+    No NCCL collective moves data."""
+
+    def __init__(self, M: int, N: int, device: torch.device, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        if self.world > 8:
+            raise ValueError("at most 8 GPUs")
+        self.M, self.N = M, N
+        self.tensor = symm_mem.empty((M, N), dtype=torch.int8, device=device)
+        self.handle = symm_mem.rendezvous(self.tensor, self.group)
+        ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self._ptr_array = (ctypes.c_void_p * self.world)(*ptrs)
+
+    def wait(self) -> None:
+        """All ranks' stores into every copy are complete and visible after this returns on
+        the current stream (call it on every rank)."""
+        self.handle.barrier()
+
+
+def mm_int8_allgather(A: torch.Tensor, B_slab: torch.Tensor, out: GatheredOutput, scale_A: float,
+                      scale_B: float, scale_C: float, zero_point_A: int, zero_point_B: int,
+                      zero_point_C: int) -> torch.Tensor:
+    """Column-sharded mm_int8 with the gather fused into the kernel: returns out.tensor, complete
+    on every rank once out.wait() has run."""
+    n0, n1 = column_slab(out.N, out.world, out.rank)
+    if tuple(B_slab.shape) != (A.shape[1], n1 - n0) or A.shape[0] != out.M:
+        raise ValueError(f"rank {out.rank}: operands do not match the gathered output")
+    if not (A.is_cuda and B_slab.is_cuda and A.dtype == torch.int8 and B_slab.dtype == torch.int8
+            and A.is_contiguous() and B_slab.is_contiguous()):
+        raise ValueError("A and B_slab must be contiguous CUDA int8 tensors")
+    if n1 > n0:
+        lib = _lib.load()
+        with torch.cuda.device(A.device), ops._DefaultStreamOrder(A.device):
+            rc = lib.texo_mm_int8_solve_allgather(
+                A.data_ptr(), B_slab.data_ptr(), ctypes.cast(out._ptr_array, ctypes.c_void_p),
+                out.world, out.M, n1 - n0, A.shape[1], out.N, n0, scale_A, scale_B, scale_C,
+                zero_point_A, zero_point_B, zero_point_C)
+        if rc != 0:
+            raise RuntimeError("texo_mm_int8_solve_allgather rejected its arguments")
+    return out.tensor
