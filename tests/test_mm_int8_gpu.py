@@ -111,7 +111,7 @@ def test_tensor_path_matches_oracle(lib, oracle, shape):
         want = oracle.mm_int8(a, b, m, n, k, q)
         assert np.count_nonzero(np.abs(want.astype(np.int32)) < 127) > want.size // 2
         # automatic choice, then each tensor kernel on its own (2 = one CTA, 4 = CTA pair)
-        for force, allowed in ((0, (2, 3, 4)), (2, (2,)), (4, (4,)), (3, (3,) if m <= 32 else (2, 4))):
+        for force, allowed in ((0, (2, 3, 4)), (2, (2,)), (4, (4,)), (3, (3,) if m <= 128 else (2, 4))):
             lib.texo_mm_int8_force_path(force)
             got = run_case(lib, a, b, m, n, k, q)
             path = lib.texo_mm_int8_last_path()
@@ -121,9 +121,12 @@ def test_tensor_path_matches_oracle(lib, oracle, shape):
     assert lib.texo_mm_int8_status() == 0
 
 
-SKINNY_SHAPES = [  # M <= 32 with aligned rows -> skinny (decode) path; whole and split tiles
+SKINNY_SHAPES = [  # M <= 128 with aligned rows -> skinny (decode) path; whole and split tiles
     (16, 256, 128), (16, 256, 1024), (1, 16, 16), (16, 512, 256), (7, 272, 144), (32, 1008, 1040),
     (17, 4096, 4096), (3, 48, 2048), (32, 256, 19200), (16, 3584, 8192),
+    # 33..128 rows: 64- and 128-row accumulators, whole tiles only, row sums from a pre-pass
+    (33, 256, 128), (64, 512, 1024), (48, 272, 144), (100, 1008, 1040), (128, 7168, 2048),
+    (65, 40000, 256), (128, 256, 19200),
 ]
 
 
@@ -319,12 +322,15 @@ def test_prepared_decode_calls_chained_without_sync(lib, oracle):
 
 def test_wide_dot_on_tensor_path(lib, oracle):
     """K > 33025: |dot| can exceed int32, the epilogue must use 64-bit correction."""
-    for m, n, k, want_path in ((128, 256, 33040, 2), (384, 256, 33040, 4)):
+    for m, n, k, force, want_path in ((128, 256, 33040, 2, 2), (128, 256, 33040, 0, 3),
+                                      (384, 256, 33040, 0, 4)):
         a = np.full((m, k), 127, np.int8)
         b = np.full((k, n), 127, np.int8)
         a[::2] = -128
         q = (1.0, 1.0, 33554432.0, -128, -128, 0)
+        lib.texo_mm_int8_force_path(force)
         got = run_case(lib, a, b, m, n, k, q)
+        lib.texo_mm_int8_force_path(0)
         assert lib.texo_mm_int8_last_path() == want_path
         assert np.array_equal(got, oracle.mm_int8(a, b, m, n, k, q))
 

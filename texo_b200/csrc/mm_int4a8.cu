@@ -11,11 +11,9 @@
 // oracle built from those two pinned pieces.
 //
 // Tensor path: CTA pairs, 256 x 256 output tile, 128 k per stage.  Per stage and CTA: TMA
-// brings 128 rows of A (16 KiB, K-major, 128-byte swizzle); eight unpack warps fetch this
-// CTA's 128 weight rows as packed nibbles (8 KiB) from global memory / L2 straight into
-// registers, three k blocks ahead of their use, and expand them to bytes 0..15 into a
-// K-major, 128-byte-swizzled operand tile (16 KiB) - the packed bytes never occupy shared
-// memory, whose bandwidth is what limits this kernel; the even CTA issues
+// brings 128 rows of A (16 KiB, K-major, 128-byte swizzle) and this CTA's 128 weight rows as
+// packed nibbles (8 KiB); eight unpack warps expand the nibbles to bytes 0..15 directly into
+// a K-major, 128-byte-swizzled operand tile (16 KiB); the even CTA issues
 // tcgen05.mma.cta_group::2.kind::i8 with A signed and B UNSIGNED, accumulating int32 in TMEM.
 // Keeping the nibbles unsigned makes the unpack five integer instructions per eight
 // weights; the offset moves into the zero point:
@@ -135,12 +133,12 @@ __global__ void __launch_bounds__(SUM_WARPS * 32)
 // --------------------------------------------------------------- tensor path
 constexpr int BK = 128;    // k per stage = one 128-byte swizzle row of int8
 constexpr int UMMA_K = 32;  // k per kind::i8 instruction
-constexpr int Q_STAGES = 6;
+constexpr int Q_STAGES = 5;
 constexpr int Q_RING = 4;
-constexpr int Q_A_BYTES = 128 * BK;  // this CTA's 128 rows of A
-constexpr int Q_B_BYTES = 128 * BK;  // this CTA's 128 weight rows as bytes 0..15
-constexpr int Q_STAGE_BYTES = Q_A_BYTES + Q_B_BYTES;
-constexpr int Q_AHEAD = 3;  // k blocks of packed weights in flight per unpack thread
+constexpr int Q_A_BYTES = 128 * BK;          // this CTA's 128 rows of A
+constexpr int Q_B_BYTES = 128 * BK;          // this CTA's 128 weight rows as bytes 0..15
+constexpr int Q_RAW_BYTES = 128 * (BK / 2);  // the same rows as packed nibbles
+constexpr int Q_STAGE_BYTES = Q_A_BYTES + Q_B_BYTES + Q_RAW_BYTES;
 constexpr int Q_SMEM_BYTES = Q_STAGES * Q_STAGE_BYTES + 1024 + 256;
 constexpr int Q_UNPACK_WARPS = 8, Q_UNPACK_WARP0 = 2;  // measured: 8 warps 2.52 POP/s, 4 warps 2.32, 2 warps 1.77
 constexpr int Q_EPI_WARPS = 8, Q_EPI_WARP0 = Q_UNPACK_WARP0 + Q_UNPACK_WARPS;
@@ -148,8 +146,9 @@ constexpr int Q_THREADS = (Q_EPI_WARP0 + Q_EPI_WARPS) * 32;
 constexpr int Q_ACC_COLS = 256, Q_TMEM_COLS = 512;
 
 struct PairBarriers {
-  uint64_t ready[Q_STAGES];  // even CTA: A bytes of both CTAs landed AND all unpack warps arrived
-  uint64_t ring[Q_RING];     // per CTA: MMA commits that free stages (see the producer)
+  uint64_t ready[Q_STAGES];     // even CTA: A bytes of both CTAs landed AND all unpack warps arrived
+  uint64_t raw_full[Q_STAGES];  // per CTA: packed nibbles landed
+  uint64_t ring[Q_RING];        // per CTA: MMA commits that free stages (see the producer)
   uint64_t acc_full[2];         // per CTA
   uint64_t acc_empty[2];        // even CTA: epilogue warps of both CTAs arrive
   uint32_t tmem_base;
@@ -172,7 +171,7 @@ __device__ __forceinline__ void unpack32(const uint4& packed, uint4& first, uint
 
 template <bool WIDE>
 __global__ void __launch_bounds__(Q_THREADS, 1)
-    pair_kernel(const __grid_constant__ CUtensorMap map_a, const uint8_t* __restrict__ W,
+    pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_raw,
                 int8_t* __restrict__ C, const int* __restrict__ row_sum,
                 const int* __restrict__ w_sum, int M, int N, int K, Quant q, int tiles_m, int tiles_n,
                 int c_vector_ok, int* status) {
@@ -188,8 +187,10 @@ __global__ void __launch_bounds__(Q_THREADS, 1)
   const int num_kb = (K + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < Q_STAGES; ++s)
+    for (int s = 0; s < Q_STAGES; ++s) {
       mbar_init(&bars->ready[s], 1 + 2 * Q_UNPACK_WARPS);  // producer's expect_tx + unpack warps
+      mbar_init(&bars->raw_full[s], 1);
+    }
     for (int r = 0; r < Q_RING; ++r) mbar_init(&bars->ring[r], 1);
     for (int b = 0; b < 2; ++b) {
       mbar_init(&bars->acc_full[b], 1);
@@ -198,6 +199,7 @@ __global__ void __launch_bounds__(Q_THREADS, 1)
     bars->abort_flag = 0;
     fence_barrier_init();
     tma_prefetch_desc(&map_a);
+    tma_prefetch_desc(&map_raw);
   }
   if (warp == 1) {
     tmem_alloc_pair(&bars->tmem_base, Q_TMEM_COLS);
@@ -223,6 +225,7 @@ __global__ void __launch_bounds__(Q_THREADS, 1)
       int tm, tn;
       i8::pair_tile_coords(tile, tiles_m, tiles_n, tm, tn);
       const int m0 = tm * 256 + int(rank) * 128;
+      const int n0 = tn * 256 + int(rank) * 128;
       for (int kb = 0; kb < num_kb && ok; ++kb, ++g) {
         if (lane == 0) {
           if (g >= Q_STAGES) {
@@ -235,9 +238,12 @@ __global__ void __launch_bounds__(Q_THREADS, 1)
           }
           if (ok) {
             uint8_t* sa = smem + stage * Q_STAGE_BYTES;
+            uint8_t* sraw = sa + Q_A_BYTES + Q_B_BYTES;
             const uint32_t ready_even = map_to_cta(smem_u32(&bars->ready[stage]), 0);
             if (rank == 0) mbar_arrive_expect_tx(&bars->ready[stage], 2 * Q_A_BYTES);
             tma_load_2d_pair(sa, &map_a, ready_even, kb * BK, m0);
+            mbar_arrive_expect_tx(&bars->raw_full[stage], Q_RAW_BYTES);
+            tma_load_2d(sraw, &map_raw, &bars->raw_full[stage], kb * (BK / 2), n0);
           }
         }
         ok = __shfl_sync(0xffffffffu, ok, 0);
@@ -296,79 +302,28 @@ __global__ void __launch_bounds__(Q_THREADS, 1)
     }
   } else if (warp < Q_EPI_WARP0) {
     // ------------------------------------------------------- nibble unpacking
-    // 512 sixteen-byte pieces per stage (128 rows x 4), two per thread: consecutive threads
-    // take consecutive pieces, so four threads read one row's 64 contiguous bytes; the two
-    // 16-byte chunks a piece expands to go to the 128-byte-swizzled positions 2p and 2p+1 of
-    // its row (bank-conflict free: the eight threads of a store phase cover two rows of
-    // opposite parity).  A load cursor runs Q_AHEAD k blocks ahead of the unpack cursor.
-    const int t = (warp - Q_UNPACK_WARP0) * 32 + lane;  // 0 .. 255
-    const int kbytes = K / 2;
-    struct Cursor {
-      int tile, kb, n0;
-      bool valid;
-    };
-    auto start = [&](Cursor& c) {
-      c.tile = cluster_id;
-      c.kb = 0;
-      c.valid = c.tile < num_tiles;
-      int tm, tn;
-      i8::pair_tile_coords(c.valid ? c.tile : 0, tiles_m, tiles_n, tm, tn);
-      c.n0 = tn * 256 + int(rank) * 128;
-    };
-    auto advance = [&](Cursor& c) {
-      if (++c.kb == num_kb) {
-        c.kb = 0;
-        c.tile += num_clusters;
-        c.valid = c.tile < num_tiles;
-        int tm, tn;
-        i8::pair_tile_coords(c.valid ? c.tile : 0, tiles_m, tiles_n, tm, tn);
-        c.n0 = tn * 256 + int(rank) * 128;
-      }
-    };
-    auto fetch = [&](const Cursor& c, uint4 (&dst)[2]) {
-#pragma unroll
-      for (int i = 0; i < 2; ++i) {
-        const int piece = t + 256 * i;
-        const int n = c.n0 + (piece >> 2), kbyte = c.kb * (BK / 2) + (piece & 3) * 16;
-        dst[i] = make_uint4(0, 0, 0, 0);
-        if (c.valid && n < N && kbyte < kbytes)
-          dst[i] = __ldg(reinterpret_cast<const uint4*>(W + size_t(n) * kbytes + kbyte));
-      }
-    };
-    Cursor load_at, unpack_at;
-    start(load_at);
-    start(unpack_at);
-    uint4 held[Q_AHEAD][2];
-#pragma unroll
-    for (int j = 0; j < Q_AHEAD; ++j) {
-      fetch(load_at, held[j]);
-      advance(load_at);
-    }
-    int g = 0;          // global k-block number of the next unpack
-    int observed = -1;  // highest commit number seen complete
+    const int t = (warp - Q_UNPACK_WARP0) * 32 + lane;  // 0 .. 32 * Q_UNPACK_WARPS - 1
+    int stage = 0;
+    uint32_t phase = 0;
     bool ok = true;
-    while (ok && unpack_at.valid) {
-#pragma unroll
-      for (int j = 0; j < Q_AHEAD; ++j) {
-        if (!ok || !unpack_at.valid) break;
-        const int stage = g % Q_STAGES;
-        if (g >= Q_STAGES) {
-          const int c = (g - Q_STAGES + 1) >> 1;  // commit covering block g - Q_STAGES
-          if (c > observed) {
-            ok = mbar_wait(&bars->ring[c & (Q_RING - 1)], (c >> 2) & 1, abort_flag, status,
-                           STATUS_TIMEOUT_EMPTY);
-            ok = __all_sync(0xffffffffu, ok);
-            observed = c;
-            if (!ok) break;
-          }
-        }
+    for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+      for (int kb = 0; kb < num_kb && ok; ++kb) {
+        ok = mbar_wait(&bars->raw_full[stage], phase, abort_flag, status, STATUS_TIMEOUT_FULL);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
         uint8_t* sb = smem + stage * Q_STAGE_BYTES + Q_A_BYTES;
+        const uint8_t* sraw = sb + Q_B_BYTES;
+        // 512 sixteen-byte pieces (128 rows x 4): consecutive threads take consecutive pieces,
+        // so loads are contiguous; the two 16-byte chunks a piece expands to go to the
+        // 128-byte-swizzled positions 2p and 2p+1 of its row (bank-conflict free: the eight
+        // threads of a store phase cover two rows of opposite parity).
 #pragma unroll
-        for (int i = 0; i < 2; ++i) {
-          const int piece = t + 256 * i;
+        for (int i = 0; i < 512 / (32 * Q_UNPACK_WARPS); ++i) {
+          const int piece = t + 32 * Q_UNPACK_WARPS * i;
           const int row = piece >> 2, p = piece & 3;
+          const uint4 packed = *reinterpret_cast<const uint4*>(sraw + piece * 16);
           uint4 first, second;
-          unpack32(held[j][i], first, second);
+          unpack32(packed, first, second);
           uint8_t* dst = sb + row * 128;
           *reinterpret_cast<uint4*>(dst + (((2 * p) ^ (row & 7)) << 4)) = first;
           *reinterpret_cast<uint4*>(dst + (((2 * p + 1) ^ (row & 7)) << 4)) = second;
@@ -376,10 +331,10 @@ __global__ void __launch_bounds__(Q_THREADS, 1)
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) mbar_arrive_remote(map_to_cta(smem_u32(&bars->ready[stage]), 0));
-        fetch(load_at, held[j]);
-        advance(load_at);
-        advance(unpack_at);
-        ++g;
+        if (++stage == Q_STAGES) {
+          stage = 0;
+          phase ^= 1;
+        }
       }
     }
   } else {
@@ -476,9 +431,11 @@ static bool launch_tensor(DeviceCtx& ctx, const int8_t* A, const uint8_t* W, int
                           int K, const Quant& q, bool wide) {
   const int pairs = max_active_pairs(ctx);
   if (pairs <= 0) return false;
-  CUtensorMap map_a;
+  CUtensorMap map_a, map_raw;
   if (!make_tensor_map_2d(&map_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, A, M, K, K, 128, BK,
-                          CU_TENSOR_MAP_SWIZZLE_128B)) {
+                          CU_TENSOR_MAP_SWIZZLE_128B) ||
+      !make_tensor_map_2d(&map_raw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, W, N, K / 2, K / 2, 128, BK / 2,
+                          CU_TENSOR_MAP_SWIZZLE_NONE)) {
     note_host_error(STATUS_TENSORMAP_FAILED);
     return false;
   }
@@ -523,10 +480,10 @@ static bool launch_tensor(DeviceCtx& ctx, const int8_t* A, const uint8_t* W, int
     const bool overlap = sums_launched && overlap_ok && attempt == 0;
     cfg.numAttrs = overlap ? 2 : 1;
     const cudaError_t err =
-        wide ? cudaLaunchKernelEx(&cfg, pair_kernel<true>, map_a, W, C, rs, ws, M, N, K, q, tiles_m,
-                                  tiles_n, c_vector_ok, ctx.status)
-             : cudaLaunchKernelEx(&cfg, pair_kernel<false>, map_a, W, C, rs, ws, M, N, K, q, tiles_m,
-                                  tiles_n, c_vector_ok, ctx.status);
+        wide ? cudaLaunchKernelEx(&cfg, pair_kernel<true>, map_a, map_raw, C, rs, ws, M, N, K, q,
+                                  tiles_m, tiles_n, c_vector_ok, ctx.status)
+             : cudaLaunchKernelEx(&cfg, pair_kernel<false>, map_a, map_raw, C, rs, ws, M, N, K, q,
+                                  tiles_m, tiles_n, c_vector_ok, ctx.status);
     if (err == cudaSuccess || !overlap) break;
     cudaGetLastError();  // the attribute was refused: launch again, fully serialised
     overlap_ok = false;

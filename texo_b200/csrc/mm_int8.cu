@@ -15,7 +15,7 @@
 //                    MMAs of tile i+1), eight epilogue warps apply the zero-point identity
 //                       sum (a-zA)(b-zB) = sum ab - zB*rowsum(A) - zA*colsum(B) + K*zA*zB
 //                    and requantise.  Needs 16-byte aligned A/B and K % 16 == N % 16 == 0.
-//   * skinny path  - M <= 32 (decode): HBM-bound; weights stream through the same TMA/UMMA
+//   * skinny path  - M <= 128 (decode, small batches): HBM-bound; weights stream through the same TMA/UMMA
 //                    machinery with the roles of the operands swapped (weights are the
 //                    128-row operand, activations the narrow one) and the K range split over
 //                    CTAs so all SMs pull on HBM; colsum(B) falls out of an extra all-ones
@@ -671,7 +671,7 @@ __global__ void __launch_bounds__(MMA_THREADS, 1)
 }
 
 // --------------------------------------------------------------- skinny path
-// M <= 32 (decode): the job is to stream B [K,N] from HBM exactly once.  Operand roles are
+// M <= 128 (decode and small batches): the job is to stream B [K,N] from HBM exactly once.  Operand roles are
 // swapped: a 128-column box of B is the 128-row MMA operand (N-major in memory = M-major
 // operand, again no transposed copy), the activations are the narrow operand.  The
 // activation tile carries one extra all-ones row (written once into every ring slot at
@@ -694,7 +694,8 @@ __global__ void __launch_bounds__(MMA_THREADS, 1)
 // owned tiles come LAST and need no reduction, so the kernel's tail is a plain drain.
 // Nobody ever waits for another CTA.
 // Nearly all of an SM's shared memory goes to the ring (M <= 16: 6 stages of 32 KiB weights +
-// 4 KiB activations; 16 < M <= 32: 5 stages of 32 KiB + 6 KiB): each SM has to keep about
+// 4 KiB activations; M <= 32 / 64: 5 stages of 32 KiB + 6 / 10 KiB; M <= 128: 4 stages of
+// 32 + 18 KiB): each SM has to keep about
 // 100 KiB in flight to cover HBM latency at its share of the bandwidth, and a ring that deep
 // measured faster than a shallow one that would let two CTAs share an SM.  The kernel is
 // launched with programmatic stream serialisation all the same: the next call's CTA starts on
@@ -704,20 +705,27 @@ __global__ void __launch_bounds__(MMA_THREADS, 1)
 // that count, so nothing is shared and no reduction runs at all: 112 CTAs streaming one
 // 256-column tile each reach the same HBM rate as 148 and finish without a flush.
 constexpr int S_MAX_STAGES = 6;
+constexpr int S_MAX_ROWS = 128;  // activation rows this path takes
 constexpr int S_BOX_BYTES = 128 * 128;     // one 128 k-row x 128 column box of B
 constexpr int S_W_BYTES = 2 * S_BOX_BYTES;  // the two boxes of a 256-column tile
-constexpr int S_ACC_COLS = 64;  // TMEM columns per accumulator (M + ones + padding <= 48)
-constexpr int S_TMEM_COLS = 4 * S_ACC_COLS;  // two halves per tile, double buffered
+// R = activation rows per MMA (16, 32, 64 or 128; M <= R).  TMEM: one accumulator per
+// 128-column half, R + 16 columns wide (rows + the ones row + padding), two halves per tile,
+// double buffered except for R = 128, whose two 144-column halves leave no room for a second
+// set.
+__host__ __device__ constexpr int skinny_acc_cols(int R) { return R <= 32 ? 64 : (R == 64 ? 128 : 144); }
+__host__ __device__ constexpr int skinny_acc_buffers(int R) { return R == 128 ? 1 : 2; }
+__host__ __device__ constexpr int skinny_tmem_cols(int R) { return R <= 32 ? 256 : 512; }
 __host__ __device__ constexpr int skinny_act_bytes(int R) { return (R + 16) * 128; }
-__host__ __device__ constexpr int skinny_stages(int R) { return R == 16 ? 6 : 5; }
+__host__ __device__ constexpr int skinny_stages(int R) { return R == 16 ? 6 : (R == 128 ? 4 : 5); }
 __host__ __device__ constexpr int skinny_smem_bytes(int R) {
-  return skinny_stages(R) * (S_W_BYTES + skinny_act_bytes(R)) + 1024 + 512;
+  return skinny_stages(R) * (S_W_BYTES + skinny_act_bytes(R)) + 1024 /*alignment*/ +
+         1024 /*SkinnyBarriers*/;
 }
 constexpr int S_TILE_N = 256;  // two 128-column boxes side by side, see above
 constexpr int S_EPI_WARPS = 4;
 constexpr int S_THREADS = 64 + S_EPI_WARPS * 32;
 
-struct SkinnyBarriers {
+struct SkinnyBarriers {  // at most 1024 bytes, see skinny_smem_bytes
   uint64_t full[S_MAX_STAGES];
   uint64_t empty[S_MAX_STAGES];
   uint64_t acc_full[2];
@@ -725,8 +733,10 @@ struct SkinnyBarriers {
   uint32_t tmem_base;
   int abort_flag;
   int last_flag;
-  int row_sum[32];
+  int row_sum[128];
 };
+
+static_assert(sizeof(SkinnyBarriers) <= 1024, "SkinnyBarriers outgrew its shared-memory reserve");
 
 // First unit of CTA `c` when `units` are dealt to `ctas` CTAs as evenly as possible.
 __host__ __device__ __forceinline__ long long skinny_first_unit(long long units, int ctas, int c) {
@@ -746,10 +756,12 @@ struct SkinnySchedule {
   int num_kb, ctas, owned, shared_tiles;
   long long shared_units, su, su_end;
   int next_owned, cta;
-  __device__ SkinnySchedule(int tiles, int num_kb_, int ctas_, int cta_)
+  // whole_tiles: no tile is split between CTAs (CTA c takes tiles c, c + G, ...), for the
+  // row counts whose epilogue has no reduction path.
+  __device__ SkinnySchedule(int tiles, int num_kb_, int ctas_, int cta_, bool whole_tiles = false)
       : num_kb(num_kb_), ctas(ctas_), cta(cta_) {
-    owned = tiles / ctas;
-    shared_tiles = tiles - owned * ctas;
+    owned = whole_tiles ? (tiles - cta_ + ctas_ - 1) / ctas_ : tiles / ctas;
+    shared_tiles = whole_tiles ? 0 : tiles - owned * ctas;
     shared_units = (long long)shared_tiles * num_kb;
     su = skinny_first_unit(shared_units, ctas, cta);
     su_end = skinny_first_unit(shared_units, ctas, cta + 1);
@@ -794,7 +806,8 @@ template <int ROWS, bool FAST>
 __device__ __forceinline__ void skinny_store_rows(const uint32_t (&v)[32], const int* row_sum,
                                                   long long kza, long long col_term, float sb_n,
                                                   int zb_n, const Quant& q, float zc, int M,
-                                                  int8_t* out, size_t stride, int col) {
+                                                  int8_t* out, size_t stride, int col,
+                                                  int row0 = 0) {
   int r[ROWS];
 #pragma unroll
   for (int m = 0; m < ROWS; ++m) {
@@ -812,7 +825,7 @@ __device__ __forceinline__ void skinny_store_rows(const uint32_t (&v)[32], const
     // `out` is C + n of a private result; the gathered form stores at column n_off + n of
     // every peer's [M, ldc] matrix instead (n recovered from the pointer difference)
     for (int p = 0; p < q.n_peers; ++p) {
-      int8_t* dst = q.peers[p] + q.n_off + col;
+      int8_t* dst = q.peers[p] + size_t(row0) * q.ldc + q.n_off + col;
 #pragma unroll
       for (int m = 0; m < ROWS; ++m)
         if (m < M) dst[size_t(m) * q.ldc] = int8_t(r[m]);
@@ -827,8 +840,8 @@ __device__ __forceinline__ void skinny_store_rows(const uint32_t (&v)[32], const
 __global__ void __launch_bounds__(S_THREADS, 1)
     skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_act,
                   const int8_t* __restrict__ A, int8_t* __restrict__ C, int* __restrict__ workspace,
-                  int* __restrict__ counters, int M, int N, int K, Quant q, int R,
-                  int weights_stable, int* status) {
+                  int* __restrict__ counters, const int* __restrict__ row_sum_g, int M, int N, int K,
+                  Quant q, int R, int weights_stable, int* status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~uintptr_t(1023));
@@ -843,10 +856,11 @@ __global__ void __launch_bounds__(S_THREADS, 1)
   const int num_kb = (K + BK - 1) / BK;
   const int tiles = (N + S_TILE_N - 1) / S_TILE_N;
   const int n_mma = R + 16;  // activation rows + the ones row + zero padding
+  const int acc_cols = skinny_acc_cols(R), acc_buffers = skinny_acc_buffers(R);
 
   // Producer state lives outside the role branch: the first ring fill is issued before the
   // CTA-wide set-up barrier, so HBM latency overlaps TMEM allocation and the fills below.
-  SkinnySchedule prod_sched(tiles, num_kb, gridDim.x, blockIdx.x);
+  SkinnySchedule prod_sched(tiles, num_kb, gridDim.x, blockIdx.x, R > 32);
   int p_stage = 0, p_tile = 0, p_kb = 0, p_kb1 = 0, p_shared = -1;
   uint32_t p_phase = 0;
   bool p_ok = true;
@@ -874,7 +888,7 @@ __global__ void __launch_bounds__(S_THREADS, 1)
     // were still being written; the loads proper then start after griddepcontrol.wait and
     // find their data in L2.
     if (lane == 0) {
-      SkinnySchedule early(tiles, num_kb, gridDim.x, blockIdx.x);
+      SkinnySchedule early(tiles, num_kb, gridDim.x, blockIdx.x, R > 32);
       int e_tile = 0, e_kb = 0, e_kb1 = 0, e_shared = -1;
       for (int i = 0; i < S_STAGES; ++i) {
         if (e_kb == e_kb1 && !early.next(e_tile, e_kb, e_kb1, e_shared)) break;
@@ -925,7 +939,7 @@ __global__ void __launch_bounds__(S_THREADS, 1)
     if (threadIdx.x >= 32 && threadIdx.x < 64) bars->row_sum[threadIdx.x - 32] = 0;
     fence_proxy_async_smem();
     if (warp == 1) {
-      tmem_alloc(&bars->tmem_base, S_TMEM_COLS);
+      tmem_alloc(&bars->tmem_base, skinny_tmem_cols(R));
       tmem_relinquish();
     }
   }
@@ -961,7 +975,7 @@ __global__ void __launch_bounds__(S_THREADS, 1)
     // activations K-major.
     const uint32_t idesc = umma_idesc(/*D=s32*/ 2, /*A=s8*/ 1, /*B=s8*/ 1, /*A M-major*/ 1,
                                       /*B K-major*/ 0, 128, uint32_t(n_mma));
-    SkinnySchedule sched(tiles, num_kb, gridDim.x, blockIdx.x);
+    SkinnySchedule sched(tiles, num_kb, gridDim.x, blockIdx.x, R > 32);
     int stage = 0;
     uint32_t phase = 0;
     int buf = 0;
@@ -984,7 +998,7 @@ __global__ void __launch_bounds__(S_THREADS, 1)
             const uint32_t sact = sw + S_W_BYTES;
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
-              const uint32_t tmem_d = tmem_base + (buf * 2 + half) * S_ACC_COLS;
+              const uint32_t tmem_d = tmem_base + (buf * 2 + half) * acc_cols;
 #pragma unroll
               for (int j = 0; j < BK / UMMA_K; ++j) {
                 const uint64_t da = smem_desc(sw + half * S_BOX_BYTES + j * UMMA_K * 128, 16, 1024,
@@ -1004,7 +1018,7 @@ __global__ void __launch_bounds__(S_THREADS, 1)
       }
       if (lane == 0 && ok) umma_commit(&bars->acc_full[buf]);
       __syncwarp();
-      if (++buf == 2) {
+      if (++buf == acc_buffers) {
         buf = 0;
         buf_phase ^= 1;
       }
@@ -1015,8 +1029,11 @@ __global__ void __launch_bounds__(S_THREADS, 1)
     const int quarter = warp % 4;     // TMEM lanes 32*quarter .. +31
     const int et = threadIdx.x - 64;  // 0..127 among the epilogue threads
     asm volatile("griddepcontrol.wait;" ::: "memory");  // before reading A / touching C, workspace
-    // rowsum(A) for the zero-point identity: the activations are tiny, every CTA sums them.
-    if (q.zb != 0 || q.zb_vec != nullptr) {
+    // rowsum(A) for the zero-point identity.  Up to 32 rows the activations are tiny and every
+    // CTA sums them itself; beyond that a pre-pass has done it once (row_sum_g).
+    if ((q.zb != 0 || q.zb_vec != nullptr) && R > 32) {
+      for (int m = et; m < M; m += S_EPI_WARPS * 32) bars->row_sum[m] = __ldcg(row_sum_g + m);
+    } else if (q.zb != 0 || q.zb_vec != nullptr) {
       for (int m = ew; m < M; m += S_EPI_WARPS) {
         const int4* a = reinterpret_cast<const int4*>(A + size_t(m) * K);
         int acc = 0;
@@ -1036,7 +1053,7 @@ __global__ void __launch_bounds__(S_THREADS, 1)
     const long long kza = (long long)K * q.za;
     const float zc = float(q.zc);
     const int ws_rows = M + 1;  // workspace rows per shared tile: M dot rows + the colsum row
-    SkinnySchedule sched(tiles, num_kb, gridDim.x, blockIdx.x);
+    SkinnySchedule sched(tiles, num_kb, gridDim.x, blockIdx.x, R > 32);
     int buf = 0;
     uint32_t buf_phase = 0;
     bool ok = true;
@@ -1057,9 +1074,51 @@ __global__ void __launch_bounds__(S_THREADS, 1)
       if (!ok) break;
       tc_fence_after_sync();
       const int cur = buf;
-      if (++buf == 2) {
+      if (++buf == acc_buffers) {
         buf = 0;
         buf_phase ^= 1;
+      }
+      if (R > 32) {
+        // 64 or 128 activation rows: whole tiles only (no partial sums to flush); each thread
+        // requantises its column 32 rows at a time.
+#pragma unroll 1
+        for (int half = 0; half < 2; ++half) {
+          const uint32_t taddr = tmem_base + (cur * 2 + half) * acc_cols + (uint32_t(quarter * 32) << 16);
+          const int n_local = quarter * 32 + lane;
+          const int n = tile * S_TILE_N + half * 128 + n_local;
+          uint32_t ones[16];  // accumulator column R: colsum(B) of this thread's column
+          tmem_ld_32x16(taddr + R, ones);
+          tmem_ld_wait();
+          const long long col_term = (long long)q.za * int(ones[0]);
+          float sb_n = q.sb;
+          int zb_n = q.zb;
+          if (q.sb_vec && n < N) {
+            sb_n = __ldg(q.sb_vec + n);
+            zb_n = q.zb_vec ? __ldg(q.zb_vec + n) : 0;
+          }
+          const bool fast = q.fast_div && (!q.sb_vec || channel_in_fast_range(sb_n, zb_n));
+#pragma unroll 1
+          for (int r0 = 0; r0 < R; r0 += 32) {
+            uint32_t v[32];
+            tmem_ld_32x32(taddr + r0, v);
+            tmem_ld_wait();
+            if (half == 1 && r0 + 32 >= R) {
+              // everything is in registers or stored: hand the TMEM buffer back
+              tc_fence_before_sync();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(&bars->acc_empty[cur]);
+            }
+            if (n < N && r0 < M) {
+              if (fast)
+                skinny_store_rows<32, true>(v, bars->row_sum + r0, kza, col_term, sb_n, zb_n, q, zc,
+                                            M - r0, C + size_t(r0) * N + n, size_t(N), n, r0);
+              else
+                skinny_store_rows<32, false>(v, bars->row_sum + r0, kza, col_term, sb_n, zb_n, q, zc,
+                                             M - r0, C + size_t(r0) * N + n, size_t(N), n, r0);
+            }
+          }
+        }
+        continue;
       }
 #pragma unroll 1
       for (int half = 0; half < 2; ++half) {
@@ -1067,7 +1126,7 @@ __global__ void __launch_bounds__(S_THREADS, 1)
         uint32_t cs_raw;  // colsum(B) for this thread's column
         {
           const uint32_t taddr =
-              tmem_base + (cur * 2 + half) * S_ACC_COLS + (uint32_t(quarter * 32) << 16);
+              tmem_base + (cur * 2 + half) * acc_cols + (uint32_t(quarter * 32) << 16);
           tmem_ld_32x32(taddr, v);
           uint32_t hi[16];
           if (R == 32) tmem_ld_32x16(taddr + 32, hi);
@@ -1144,7 +1203,7 @@ __global__ void __launch_bounds__(S_THREADS, 1)
   __syncthreads();
   if (warp == 1) {
     tc_fence_after_sync();
-    tmem_dealloc(tmem_base, S_TMEM_COLS);
+    tmem_dealloc(tmem_base, skinny_tmem_cols(R));
   }
 }
 
@@ -1209,7 +1268,7 @@ static int max_active_pairs(DeviceCtx& ctx) {
   return cached[ctx.device];
 }
 
-// Skinny (decode) path: M <= 32.
+// Skinny (decode) path: M <= 128.
 // `weights_stable`: the caller guarantees that B has not been written since before the
 // previous call on this stream started (prepared weights), see the kernel's first ring fill.
 static bool launch_skinny(DeviceCtx& ctx, const int8_t* A, const int8_t* B, int8_t* C, int M, int N,
@@ -1220,7 +1279,7 @@ static bool launch_skinny(DeviceCtx& ctx, const int8_t* A, const int8_t* B, int8
                          skinny_smem_bytes(16));
     configured[ctx.device] = true;
   }
-  const int R = M <= 16 ? 16 : 32;
+  const int R = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
   CUtensorMap map_w, map_act;
   if (!make_tensor_map_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, B, K, N, N, BK, 128,
                           CU_TENSOR_MAP_SWIZZLE_128B) ||
@@ -1238,10 +1297,26 @@ static bool launch_skinny(DeviceCtx& ctx, const int8_t* A, const int8_t* B, int8
     const int per_cta = (tiles + ctx.sm_count - 1) / ctx.sm_count;
     if (tiles % per_cta == 0 && (tiles / per_cta) * 4 >= ctx.sm_count * 3) grid = tiles / per_cta;
   }
+  // More than 32 rows: whole tiles only (CTA c takes tiles c, c + grid, ...), and rowsum(A)
+  // comes from a pre-pass instead of being recomputed by every CTA.
+  const int* row_sum_g = nullptr;
+  if (R > 32) {
+    const int per_cta = (tiles + ctx.sm_count - 1) / ctx.sm_count;
+    grid = (tiles + per_cta - 1) / per_cta;
+    if (q.zb != 0 || q.zb_vec != nullptr) {
+      int* sums = static_cast<int*>(device_scratch(ctx, size_t(M) * sizeof(int) + 256));
+      if (!sums) return false;
+      Quant rows_only = q;
+      rows_only.za = 0;
+      rows_only.zb = 1;
+      launch_sums(A, B, sums, nullptr, M, N, K, rows_only, 0);
+      row_sum_g = sums;
+    }
+  }
   // Tiles that are split between CTAs (see the schedule above) need the workspace:
   // counters[shared][2] (padded) | partial sums [shared][2][M+1][128] int32, one slot per
   // 128-column half.
-  const int shared_tiles = tiles - tiles / grid * grid;
+  const int shared_tiles = R > 32 ? 0 : tiles - tiles / grid * grid;
   const size_t counter_bytes = (size_t(shared_tiles) * 2 * 4 + 255) & ~size_t(255);
   const size_t ws_bytes = size_t(shared_tiles) * 2 * (M + 1) * 128 * 4;
   uint8_t* base = static_cast<uint8_t*>(device_workspace(ctx, counter_bytes + ws_bytes + 256));
@@ -1261,8 +1336,8 @@ static bool launch_skinny(DeviceCtx& ctx, const int8_t* A, const int8_t* B, int8
   static bool overlap_ok = true;
   for (int attempt = 0; attempt < 2; ++attempt) {
     cfg.numAttrs = (overlap_ok && attempt == 0) ? 1 : 0;
-    if (cudaLaunchKernelEx(&cfg, skinny_kernel, map_w, map_act, A, C, ws, counters, M, N, K, q, R,
-                           weights_stable, ctx.status) == cudaSuccess ||
+    if (cudaLaunchKernelEx(&cfg, skinny_kernel, map_w, map_act, A, C, ws, counters, row_sum_g, M, N,
+                           K, q, R, weights_stable, ctx.status) == cudaSuccess ||
         cfg.numAttrs == 0)
       break;
     cudaGetLastError();  // attribute refused: launch again, fully serialised
@@ -1399,7 +1474,7 @@ static void solve_with(const int8_t* A, const int8_t* B, int8_t* C, int M, int N
   const bool vectors_ok = (reinterpret_cast<uintptr_t>(q.sb_vec) & 15) == 0 &&
                           (reinterpret_cast<uintptr_t>(q.zb_vec) & 15) == 0;
   if (force != PATH_GENERIC && ctx.cc_major >= 10 && vectors_ok && tensor_path_ok(A, B, M, N, K)) {
-    if (M <= 32 && (force == PATH_AUTO || force == PATH_SKINNY) &&
+    if (M <= S_MAX_ROWS && (force == PATH_AUTO || force == PATH_SKINNY) &&
         launch_skinny(ctx, A, B, C, M, N, K, q))
       return;
     if (launch_tensor(ctx, A, B, C, M, N, K, q, force)) return;
@@ -1655,14 +1730,14 @@ static void solve_prepared_with(const int8_t* A, const int* row_sum_A, const tex
   const Quant q =
       make_quant(scale_A, scale_B, scale_C, zero_point_A, zero_point_B, zero_point_C, w->K);
   const int force = forced_path();
-  if (w->col_sum && ctx.device == w->device && A && C && M > 32 && force != PATH_GENERIC &&
+  if (w->col_sum && ctx.device == w->device && A && C && M > S_MAX_ROWS && force != PATH_GENERIC &&
       force != PATH_SKINNY && tensor_path_ok(A, w->B, M, w->N, w->K)) {
     if (launch_tensor(ctx, A, w->B, C, M, w->N, w->K, q, force, w->col_sum, row_sum_A)) return;
   }
   // Decode shapes get colsum(B) for free inside the skinny kernel; what the handle adds
   // there is the promise that B is unchanged, so the kernel may load weights before the
   // previous call on the stream has completed.
-  if (ctx.device == w->device && A && C && M <= 32 && ctx.cc_major >= 10 &&
+  if (ctx.device == w->device && A && C && M <= S_MAX_ROWS && ctx.cc_major >= 10 &&
       (force == PATH_AUTO || force == PATH_SKINNY) && tensor_path_ok(A, w->B, M, w->N, w->K) &&
       launch_skinny(ctx, A, w->B, C, M, w->N, w->K, q, /*weights_stable=*/1))
     return;
