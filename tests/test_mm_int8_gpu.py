@@ -143,9 +143,17 @@ def test_skinny_path_matches_oracle(lib, oracle):
                 q[2] = float(np.float32(q[0] * q[1] * 20 * 74 * np.sqrt(k) / 30))
                 q = tuple(q)
                 got = run_case(lib, a, b, m, n, k, q)
-                assert lib.texo_mm_int8_last_path() == 3, (m, n, k)
+                # (with no zero point at all and more than 64 rows the one-CTA tensor kernel runs)
+                expect = 2 if (q[3] == 0 and q[4] == 0 and m > 64) else 3
+                assert lib.texo_mm_int8_last_path() == expect, (m, n, k)
                 want = oracle.mm_int8(a, b, m, n, k, q)
                 assert np.array_equal(got, want), ((m, n, k), q, rep)
+                if expect != 3:  # the skinny kernel takes these shapes too when asked
+                    lib.texo_mm_int8_force_path(3)
+                    got = run_case(lib, a, b, m, n, k, q)
+                    lib.texo_mm_int8_force_path(0)
+                    assert lib.texo_mm_int8_last_path() == 3
+                    assert np.array_equal(got, want), ((m, n, k), q, rep, "forced")
     assert lib.texo_mm_int8_status() == 0
 
 
