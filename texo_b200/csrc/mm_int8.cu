@@ -495,6 +495,7 @@ constexpr int P_A_BYTES = BM * BK;   // 128 rows x 128 k-bytes
 constexpr int P_B_BYTES = BK * 128;  // 128 k-rows x 128 n-bytes (this CTA's half of the columns)
 constexpr int P_STAGE_BYTES = P_A_BYTES + P_B_BYTES;
 constexpr int P_SMEM_BYTES = P_STAGES * P_STAGE_BYTES + 1024 + 256;
+constexpr int P_GATHER_SMEM_BYTES = EPI_WARPS * 4096;  // staging tiles of the fused all-gather
 
 struct PairBarriers {
   uint64_t full[P_STAGES];  // used in the even CTA: bytes of both CTAs' loads
@@ -649,8 +650,12 @@ __global__ void __launch_bounds__(MMA_THREADS, 1)
       if (!ok) break;
       tc_fence_after_sync();
       const int m = tm * 256 + int(rank) * 128 + quarter * 32 + lane;
+      // fused all-gather: a 4 KiB tile per epilogue warp behind the barriers (the host adds
+      // P_GATHER_SMEM_BYTES to the launch for such calls)
+      uint8_t* gather_stage =
+          q.n_peers > 0 ? smem + P_STAGES * P_STAGE_BYTES + 256 + ew * 4096 : nullptr;
       drain_half<WIDE>(tmem_base + acc * ACC_COLS + (uint32_t(quarter * 32) << 16), half * 128,
-                       tn * 256, m, m < M, C, row_sum, col_sum, N, K, q, c_vector_ok);
+                       tn * 256, m, m < M, C, row_sum, col_sum, N, K, q, c_vector_ok, gather_stage);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&bars->acc_empty[acc]), 0));
@@ -1363,9 +1368,9 @@ static bool launch_tensor(DeviceCtx& ctx, const int8_t* A, const int8_t* B, int8
     cudaFuncSetAttribute(umma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     cudaFuncSetAttribute(umma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     cudaFuncSetAttribute(umma_pair_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                         P_SMEM_BYTES);
+                         P_SMEM_BYTES + P_GATHER_SMEM_BYTES);
     cudaFuncSetAttribute(umma_pair_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                         P_SMEM_BYTES);
+                         P_SMEM_BYTES + P_GATHER_SMEM_BYTES);
     configured[ctx.device] = true;
   }
   // One TMA box shape serves both kernels: A 128 rows x 128 k-bytes, B 128 k-rows x 128 columns.
@@ -1413,7 +1418,7 @@ static bool launch_tensor(DeviceCtx& ctx, const int8_t* A, const int8_t* B, int8
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2 * std::min(tiles_m * tiles_n, pairs));
     cfg.blockDim = dim3(MMA_THREADS);
-    cfg.dynamicSmemBytes = P_SMEM_BYTES;
+    cfg.dynamicSmemBytes = P_SMEM_BYTES + (q.n_peers > 0 ? P_GATHER_SMEM_BYTES : 0);
     cfg.stream = 0;
     cudaLaunchAttribute attrs[2];
     attrs[0].id = cudaLaunchAttributeClusterDimension;

@@ -345,7 +345,8 @@ __device__ __forceinline__ void drain_half(uint32_t tmem_row_addr, int col0, int
                                            bool row_ok, int8_t* __restrict__ C,
                                            const int* __restrict__ row_sum,
                                            const int* __restrict__ col_sum, int N, int K,
-                                           const Quant& q, int c_vector_ok) {
+                                           const Quant& q, int c_vector_ok,
+                                           uint8_t* gather_stage = nullptr) {
   if (q.swiglu) {
     drain_half_swiglu<WIDE>(tmem_row_addr, col0, n_tile0, m, row_ok, C, row_sum, col_sum, N, K, q,
                             c_vector_ok);
@@ -358,6 +359,13 @@ __device__ __forceinline__ void drain_half(uint32_t tmem_row_addr, int col0, int
   }
   const auto rt_row = row_factor<WIDE>(row_sum, m, row_ok, K, q);
   int8_t* c_row = C + size_t(row_ok ? m : 0) * N;
+  // Fused all-gather, whole 128-column half inside the matrix: the warp's 32 rows x 128 bytes
+  // go through a 4 KiB shared-memory tile so that every store instruction writes four
+  // complete 128-byte row segments.  Stores into a peer's memory travel over NVLink as they
+  // are issued; 16-byte pieces scattered over 32 rows used a fifth of the link rate.
+  const bool staged = q.n_peers > 0 && gather_stage != nullptr && c_vector_ok &&
+                      n_tile0 + col0 + 128 <= N;  // warp-uniform
+  const int lane = threadIdx.x % 32;
 #pragma unroll 1
   for (int chunk = 0; chunk < 4; ++chunk) {
     const int col = col0 + chunk * 32;
@@ -369,7 +377,14 @@ __device__ __forceinline__ void drain_half(uint32_t tmem_row_addr, int col0, int
     uint32_t packed[8];
     // col_sum is padded to a multiple of the tile width: never out of bounds.
     requantize_chunk_auto<WIDE>(v, col_sum + n0, rt_row, q, n0, N, packed);
-    if (row_ok && q.n_peers > 0) {
+    if (staged) {
+      // row `lane` of the tile, 16-byte pieces 2*chunk and 2*chunk+1, XOR-swizzled by the row
+      uint8_t* row = gather_stage + lane * 128;
+      *reinterpret_cast<int4*>(row + (((2 * chunk) ^ (lane & 7)) << 4)) =
+          make_int4(packed[0], packed[1], packed[2], packed[3]);
+      *reinterpret_cast<int4*>(row + (((2 * chunk + 1) ^ (lane & 7)) << 4)) =
+          make_int4(packed[4], packed[5], packed[6], packed[7]);
+    } else if (row_ok && q.n_peers > 0) {
       const size_t at = size_t(m) * q.ldc + q.n_off + n0;
       for (int p = 0; p < q.n_peers; ++p) {
         int8_t* dst_row = q.peers[p] + at;
@@ -392,6 +407,25 @@ __device__ __forceinline__ void drain_half(uint32_t tmem_row_addr, int col0, int
           c_row[n0 + e] = int8_t((packed[e / 4] >> (8 * (e % 4))) & 0xff);
       }
     }
+  }
+  if (staged) {
+    __syncwarp();
+    const unsigned rows_ok = __ballot_sync(0xffffffffu, row_ok);  // bit r: row r is inside M
+    const int m_base = m - lane;  // first row of this warp's 32
+    const int piece = lane & 7;
+    for (int p = 0; p < q.n_peers; ++p) {
+      int8_t* dst = q.peers[p] + q.n_off + n_tile0 + col0 + piece * 16;
+#pragma unroll
+      for (int it = 0; it < 8; ++it) {
+        const int r = it * 4 + (lane >> 3);
+        if ((rows_ok >> r) & 1u) {
+          const int4 value =
+              *reinterpret_cast<const int4*>(gather_stage + r * 128 + ((piece ^ (r & 7)) << 4));
+          *reinterpret_cast<int4*>(dst + size_t(m_base + r) * q.ldc) = value;
+        }
+      }
+    }
+    __syncwarp();  // the tile is rewritten by the next call
   }
 }
 
