@@ -40,6 +40,19 @@ UNIT = "TOPS"
 SEED = 2024
 
 
+# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of ONE launch of each workload's
+# dominant kernel, from the ncu captures summarised under profiles/ (bytes; null where no
+# capture has been taken).  Writes still sitting in L2 when the kernel ends are not in it.
+NCU_TRAFFIC = {
+    "int8_8192": (395.0e6, "profiles/int8_8192_umma_pair_kernel.md"),
+    "int8_8192_presummed": (395.0e6, "profiles/int8_8192_umma_pair_kernel.md"),
+    "int8_decode": (239.0e6, "profiles/int8_decode_skinny_kernel.md"),
+    "int4_w4a16": (324.4e6, "profiles/int4_w4a16_tensor_kernel.md"),
+    "int4_w4a8": (106.9e6, "profiles/int4_w4a8_pair_kernel.md"),
+    "dequant": (482.8e6, "profiles/dequant_rows_vec4_kernel.md"),
+    "rmsnorm_quant": (826.5e6, "profiles/rmsnorm_quant_row_kernel.md"),
+}
+
 # ----------------------------------------------------------------------------- workloads
 def workload_spec(name: str):
     if name == "int8_8192":
@@ -581,6 +594,8 @@ def run_ours(args, spec, workload):
                     "frac": achieved / peak, "traffic": None,
                     "peak_source": f"{factor:g} x {'measured' if peaks else 'fallback'} bf16 "
                                    f"{'sustained' if long_run else 'burst'} ({base:.0f} TFLOP/s)"}
+    if workload in NCU_TRAFFIC:
+        roofline["traffic"], roofline["traffic_source"] = NCU_TRAFFIC[workload]
     roofline["kernel_ms"] = kernel_avg_ms
     if single_launch_steps:
         roofline["kernel_launches_timed"] = launches
