@@ -155,7 +155,8 @@ int texo_mm_int8_solve_allgather(const int8_t* A, const int8_t* B_slab, int8_t* 
 void texo_mm_int4a8_solve(const int8_t* A, const uint8_t* w_q, int8_t* C, int M, int N, int K,
                           float scale_A, float scale_B, float scale_C, int zero_point_A,
                           int zero_point_B, int zero_point_C);
-/* mm_int4a8 diagnostics: path 1 = generic SIMT kernel, 2 = tcgen05 kind::i8 CTA-pair kernel. */
+/* mm_int4a8 diagnostics: path 1 = generic SIMT kernel, 2 = tcgen05 kind::i8 CTA-pair kernel,
+ * 3 = streaming (decode) kernel, M <= 32. */
 int texo_mm_int4a8_last_path(void);
 void texo_mm_int4a8_force_path(int path);
 int texo_mm_int4a8_status(void);

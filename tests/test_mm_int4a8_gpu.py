@@ -69,9 +69,11 @@ def _quant(rng, k, zero_a=None, zero_b=None):
     return (float(sa), float(sb), float(sc), za, zb, int(rng.integers(-8, 9)))
 
 
-SHAPES = [  # (M, N, K); K % 32 == 0 and aligned rows -> tensor path; partial tiles included
+SHAPES = [  # (M, N, K); K % 32 == 0 and aligned rows -> tensor paths; partial tiles included
     (256, 256, 128), (256, 256, 32), (256, 512, 1024), (130, 272, 160), (1, 16, 32),
     (300, 1008, 1056), (512, 768, 2048), (16, 4096, 512), (2000, 48, 4096),
+    # decode shapes (M <= 32): the streaming kernel, whole and split tiles, ragged N and K
+    (16, 256, 128), (16, 7168, 2048), (32, 1008, 1056), (7, 272, 160), (17, 40000, 256), (3, 48, 4096),
 ]
 
 
@@ -86,7 +88,9 @@ def test_tensor_and_generic_paths_match_oracle(lib, oracle, shape):
         want = oracle.mm_int4a8(a, w, m, n, k, q)
         if m >= 16:  # (a single activation row can push every output the same way)
             assert np.count_nonzero(np.abs(want.astype(np.int32)) < 127) > want.size // 3
-        for force, expect in ((0, 2), (1, 1)):
+        # automatic choice (decode shapes stream, the rest take the CTA-pair kernel), then the
+        # CTA-pair and the generic kernel on their own
+        for force, expect in ((0, 3 if m <= 32 else 2), (2, 2), (1, 1)):
             got = run_case(lib, a, w, m, n, k, q, force=force)
             assert lib.texo_mm_int4a8_last_path() == expect, (shape, force)
             assert np.array_equal(got, want), (shape, q, force)
@@ -114,7 +118,7 @@ def test_unaligned_pointers_fall_back_and_stay_exact(lib, oracle):
     w = rng.integers(0, 256, (n, k // 2), dtype=np.uint8)
     q = _quant(rng, k)
     want = oracle.mm_int4a8(a, w, m, n, k, q)
-    for offsets, path in (((1, 0, 0), 1), ((0, 3, 0), 1), ((0, 0, 7), 2), ((16, 16, 1), 2)):
+    for offsets, path in (((1, 0, 0), 1), ((0, 3, 0), 1), ((0, 0, 7), 2), ((16, 16, 1), 2)):  # m = 130
         got = run_case(lib, a, w, m, n, k, q, offsets=offsets)
         assert lib.texo_mm_int4a8_last_path() == path, offsets
         assert np.array_equal(got, want), offsets

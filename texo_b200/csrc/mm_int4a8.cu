@@ -22,6 +22,8 @@
 // 32-byte row stores).  rowsum(A) and the nibble sums come from a small pre-pass that the
 // pair kernel overlaps by programmatic dependent launch.
 //
+// Decode path (M <= 32): the INT8 operator's streaming kernel (skinny.cuh) in its packed-weight
+// form - w_q crosses HBM once, four extra warps unpack it next to the tensor core.
 // Generic path: any shape with even K, any alignment, K = 0: SIMT tiles with int64 totals.
 #include <algorithm>
 #include <cmath>
@@ -33,6 +35,7 @@
 #include "host_common.h"
 #include "ptx.cuh"
 #include "requant.cuh"
+#include "skinny.cuh"
 
 namespace texo {
 namespace w4a8 {
@@ -378,7 +381,7 @@ __global__ void __launch_bounds__(Q_THREADS, 1)
 }
 
 // ------------------------------------------------------------------ dispatch
-enum Path { PATH_AUTO = 0, PATH_GENERIC = 1, PATH_TENSOR = 2 };
+enum Path { PATH_AUTO = 0, PATH_GENERIC = 1, PATH_TENSOR = 2, PATH_SKINNY = 3 };
 
 inline int& forced_path() {
   static int path = [] {
@@ -519,6 +522,12 @@ extern "C" void solve(const int8_t* A, const uint8_t* w_q, int8_t* C, int M, int
     // the 32-bit (mod 2^32) correction is exact while |dot| < 2^31
     const double bound = double(K) * (128.0 + std::abs(double(zero_point_A))) *
                          (15.0 + std::abs(double(zb_eff)));
+    // decode shapes: the streaming kernel shared with mm_int8, unpacking on the fly
+    if (M <= 32 && (force == PATH_AUTO || force == PATH_SKINNY) &&
+        i8::launch_skinny<true>(ctx, A, w_q, C, M, N, K, q)) {
+      last_path() = PATH_SKINNY;
+      return;
+    }
     if (launch_tensor(ctx, A, w_q, C, M, N, K, q, bound >= 2147483648.0)) return;
   }
   i8::Quant q = i8::make_quant(scale_A, scale_B, scale_C, zero_point_A, 0, zero_point_C, K);
