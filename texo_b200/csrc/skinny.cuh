@@ -75,8 +75,12 @@ constexpr int S_THREADS = 64 + S_EPI_WARPS * 32;
 // even k, value - 8).  A stage then holds the TMA-loaded packed rows of the tile (256 rows x
 // 64 bytes), the operand tile eight extra warps unpack them into (256 rows x 128 bytes of
 // u = nibble, K-major, 128-byte swizzle; the -8 lives in the zero point, see mm_int4a8.cu),
-// and the activations.  Half the weight bytes cross HBM; shared memory carries 16 + 16 + 32 +
-// 32 KiB per stage (packed in, packed out, operand in, operand out), which is what bounds it.
+// and the activations.  Half the weight bytes cross HBM, but shared memory carries 16 + 16 +
+// 32 + 32 KiB of weights per k block (packed in, packed out, operand in, operand out) plus the
+// activations, about 104 KiB at 128 bytes per clock: that, not HBM, bounds this form (measured:
+// the unpack step alone takes ~900 clocks per k block; M=16, N=28672, K=8192 in 48 us against
+// 92 us on the CTA-pair kernel and 40 us for the same shape with INT8 weights).  Deeper packed
+// rings, a separate activation ring and 8 or 16 unpack warps were tried and changed nothing.
 constexpr int S_W4_UNPACK_WARPS = 4;  // (320 threads: the epilogue keeps its ~170 registers)
 constexpr int S_W4_THREADS = S_THREADS + S_W4_UNPACK_WARPS * 32;
 constexpr int S_W4_PACKED_BYTES = 256 * (S_BK / 2);
