@@ -1,17 +1,18 @@
 /*
  * C ABI of the B200 quantized-matmul library.
  *
- * Two packagings of the same three operators are built:
+ * Two packagings of the same operators are built:
  *
- *   libmm_int8.so, libmm_int4.so, libdequantization.so
- *       each exports the single symbol `solve` with exactly the prototype the reference's
- *       per-operator harness declares, so tests/mm_int8.cpp, tests/mm_int4.cpp and
- *       tests/dequantization.cpp of frezcirno/Texo link against them unchanged.
+ *   libmm_int8.so, libmm_int4.so, libdequantization.so, librms_norm_w_residual.so
+ *       each exports the single symbol `solve` with exactly the prototype the reference
+ *       declares for that operator, so tests/mm_int8.cpp, tests/mm_int4.cpp and
+ *       tests/dequantization.cpp of frezcirno/Texo link against them unchanged
+ *       (libmm_int4a8.so follows the same convention for an operator the reference lacks).
  *
  *   libtexo_b200.so
- *       all three in one library; the sources are compiled with -Dsolve=<name>, the
+ *       all of them in one library; the sources are compiled with -Dsolve=<name>, the
  *       reference's own convention for co-linking operators (its Makefile:129-148), giving
- *       the texo_*_solve names below.
+ *       the texo_*_solve names below, plus the entry points without a reference counterpart.
  *
  * Common contract (reference docs/operators.md:9-12, src/mm_int8.cu:530-592): every pointer
  * is a DEVICE pointer owned by the caller, row-major and contiguous; inputs are never
@@ -180,7 +181,8 @@ void texo_rms_norm_quant_solve(const float* x, const float* residual, const floa
  * C <= 16384, 16-byte aligned pointers). */
 int texo_rms_norm_last_path(void);
 
-/* Which device path the last mm_int8 call took: 1 generic, 2 tensor (tcgen05), 3 skinny. */
+/* Which device path the last mm_int8 call took: 1 generic, 2 one-CTA tensor kernel (tcgen05),
+ * 3 skinny (streaming, M <= 128), 4 CTA-pair tensor kernel. */
 int texo_mm_int8_last_path(void);
 /* Force a path for the following calls (0 = automatic).  A forced path is still skipped
  * when its preconditions do not hold.  Also settable with TEXO_MM_INT8_PATH. */
