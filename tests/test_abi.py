@@ -14,7 +14,7 @@ def _declared_functions():
 
 def test_header_declares_the_operator_entry_points():
     names = _declared_functions()
-    for op in ("mm_int8", "mm_int4", "dequantization"):
+    for op in ("mm_int8", "mm_int4", "dequantization", "mm_int4a8", "rms_norm_w_residual"):
         assert f"texo_{op}_solve" in names
     assert len(names) == len(set(names))
 
@@ -26,7 +26,7 @@ def test_combined_library_exports_every_declared_symbol(libs):
 
 
 def test_per_operator_libraries_export_solve(libs):
-    for op in ("mm_int8", "mm_int4", "dequantization"):
+    for op in ("mm_int8", "mm_int4", "dequantization", "mm_int4a8", "rms_norm_w_residual"):
         lib = ctypes.CDLL(libs[op])
         assert hasattr(lib, "solve"), op
 
