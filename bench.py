@@ -2,7 +2,8 @@
 """Benchmark of the quantized-matmul hot path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload int8_8192|int8_8192_presummed|int8_decode|int4_w4a16|int4_w4a8|int8_swiglu|dequant|rmsnorm_quant|layer_sweep]
+                    [--workload int8_8192 | int8_8192_presummed | int8_decode | int4_w4a16 |
+                                int4_w4a8 | int8_swiglu | dequant | rmsnorm_quant | layer_sweep]
 
 One "step" is one `solve` call over one batch of synthetic input.  The default workload is
 the INT8 quantized matmul M=N=K=8192 (uniform int8 inputs, per-tensor scales and non-zero
