@@ -193,7 +193,7 @@ void texo_mm_int8_force_path(int path);
 int texo_mm_int8_status(void);
 
 /* mm_int4: 1 = generic FP32 kernel, 2 = tcgen05 kind::f16 CTA-pair kernel (needs 16-byte
- * aligned x / w_q, K % 64 == 0, group_size 64 or 128). */
+ * aligned x / w_q, K % 64 == 0, group_size 16, 32, 64 or 128). */
 int texo_mm_int4_last_path(void);
 void texo_mm_int4_force_path(int path);
 int texo_mm_int4_status(void);

@@ -55,7 +55,7 @@ def test_pinned_example(lib):
 
 
 def _takes_tensor_path(k, g):
-    return k % 64 == 0 and g in (64, 128)
+    return k % 64 == 0 and g in (16, 32, 64, 128)
 
 
 def test_harness_default_cases(lib, oracle):
@@ -86,10 +86,12 @@ def test_harness_default_cases(lib, oracle):
 
 @pytest.mark.parametrize("shape", [(128, 128, 64, 64), (256, 256, 128, 128), (300, 520, 1024, 64),
                                    (512, 768, 2048, 128), (257, 255, 1984, 64), (1, 4096, 4096, 128),
-                                   (1000, 3, 192, 64)])
+                                   (1000, 3, 192, 64), (300, 520, 1024, 32), (256, 256, 64, 32),
+                                   (257, 255, 1984, 16), (512, 768, 2048, 32), (130, 66, 128, 16)])
 def test_tensor_path_full_matrix(lib, oracle, shape):
     """tcgen05 kind::f16 CTA-pair kernel: partial tiles in M and N, K not a multiple of the
-    group pair, both supported group sizes; every output within the reference tolerance."""
+    group pair, all four supported group sizes (a group is a quarter, half, one or two 64-k
+    stages); every output within the reference tolerance."""
     m, n, k, g = shape
     x, w, s = oracle.int4_inputs(m, n, k, g, 100 + m)
     got = run_case(lib, x, w, s, m, n, k, g)
