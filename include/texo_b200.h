@@ -61,6 +61,12 @@ void texo_mm_int4_solve(const void* x, const uint8_t* w_q, const void* scales, v
 int texo_mm_int8_solve_noalloc(const int8_t* A, const int8_t* B, int8_t* C, int M, int N, int K,
                                float scale_A, float scale_B, float scale_C, int zero_point_A,
                                int zero_point_B, int zero_point_C);
+/* Error state of texo_mm_int8_solve_noalloc on the current device, read without allocating
+ * (no counterpart in the reference; texo_mm_int8_status is not for these callers, its status
+ * block is cudaMalloc'd).  0 = all such calls since the last query completed; 1-5 = a bounded
+ * device-side wait gave up in one of them and its C is incomplete; -3 = device set-up failed.
+ * Blocking 4-byte copy out of the fixed scratch array; clears the word when it was set. */
+int texo_mm_int8_noalloc_status(void);
 
 /* Host-buffer form of texo_mm_int8_solve: A, B, C are HOST pointers (pinned for full speed).
  * Does what the reference harness does around `solve` (upload, run, download:
@@ -143,6 +149,16 @@ int texo_mm_int8_solve_allgather(const int8_t* A, const int8_t* B_slab, int8_t* 
                                  int n_gpus, int M, int N_slab, int K, int ld_c, int col_offset,
                                  float scale_A, float scale_B, float scale_C, int zero_point_A,
                                  int zero_point_B, int zero_point_C);
+/* The same with the NVLink multicast (NVLS) mapping of that allocation as well (no reference
+ * counterpart): C_multicast is the multicast address of the [M, ld_c] matrix (torch symmetric
+ * memory handle.multicast_ptr + the tensor's offset, or a cuMem multicast mapping), 16-byte
+ * aligned, or null.  With it each whole 128-byte row segment leaves this GPU once
+ * (multimem.st, replicated by NVSwitch into every copy) instead of once per peer. */
+int texo_mm_int8_solve_allgather_multicast(const int8_t* A, const int8_t* B_slab, int8_t* const* C_all,
+                                           int8_t* C_multicast, int n_gpus, int M, int N_slab, int K,
+                                           int ld_c, int col_offset, float scale_A, float scale_B,
+                                           float scale_C, int zero_point_A, int zero_point_B,
+                                           int zero_point_C);
 
 /* W4A8: packed-INT4 weights against INT8 activations, INT8 output.  No counterpart in the
  * reference (its mm_int4 takes FP16 activations, src/mm_int4.cu:386-390); it combines the
@@ -189,7 +205,10 @@ int texo_mm_int8_last_path(void);
 void texo_mm_int8_force_path(int path);
 /* Reads and clears the error state of the current device: 0 = none, 1-5 = a bounded
  * device-side wait gave up (kernel returned early, results invalid), 16 = bad argument,
- * 17 = tensor-map creation failed (call fell back to the generic path).  Synchronises. */
+ * 17 = tensor-map creation failed (call fell back to the generic path), 18 = a kernel launch
+ * was refused (call fell back to the generic path).  Synchronises.  After a non-zero device
+ * code (1-5) the split-K workspace of the decode path is re-zeroed here, so poll this after
+ * any suspected failure before trusting later decode-shaped results. */
 int texo_mm_int8_status(void);
 
 /* mm_int4: 1 = generic FP32 kernel, 2 = tcgen05 kind::f16 CTA-pair kernel (needs 16-byte

@@ -40,6 +40,19 @@ int oracle_max_threads(void) {
 #endif
 }
 
+/* Sets the number of OpenMP threads the row-parallel loops below use (launchers such as
+ * torchrun export OMP_NUM_THREADS=1, which would otherwise time the CPU baseline on one
+ * core).  Returns the number then in effect. */
+int oracle_set_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+  return omp_get_max_threads();
+#else
+  (void)n;
+  return 1;
+#endif
+}
+
 /* FP32 requantisation in the contractual order of src/mm_int8.cu:12-25:
  * float(dot) * sA * sB / sC, round-to-nearest-even, + zC, clamp, int8. */
 static inline int8_t requantize_f32(int64_t dot, float sa, float sb, float sc, int zc) {

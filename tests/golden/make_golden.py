@@ -4,10 +4,15 @@
 
 mm_int8_harness.npz   the 56 default cases of the reference harness
                       (frezcirno/Texo tests/mm_int8.cpp:139-254): inputs, quantisation
-                      parameters, pointer offsets and the expected bytes.  Expected bytes are
-                      the values pinned in the reference test file where it pins them
-                      (:210-221), otherwise the harness's own double-precision formula
-                      (:39-48) - i.e. exactly what the harness would compare against.
+                      parameters, pointer offsets and the expected bytes.  Of the 56
+                      expectations, 2 are reference-held: the bytes the reference test file
+                      pins (:210-221, meta "pinned": true).  The other 54 are ORACLE-GENERATED:
+                      the oracle's restatement (mode 1) of the harness's double-precision
+                      formula (:39-48), i.e. what the harness would compute and compare
+                      against - they are not bytes produced by reference code.  (The reference's
+                      compiled CPU loop itself checks the oracle in
+                      tests/test_oracle.py::test_reference_cpu_loops_accept_the_oracle, and
+                      its recompiled kernel checks the GPU path in the -m gpu tests.)
 mm_int4_example.npz   the pinned example of tests/mm_int4.cpp:110-117 with the value of its
                       double reference (:35-45).
 The inputs come from the restated generators in oracle/harness_inputs.cpp (same mt19937

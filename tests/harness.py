@@ -34,6 +34,12 @@ class Oracle:
     def threads(self) -> int:
         return self.lib.oracle_max_threads()
 
+    def set_threads(self, n: int) -> int:
+        """OpenMP threads for the row-parallel loops (overrides OMP_NUM_THREADS); returns the
+        count in effect."""
+        self.lib.oracle_set_threads.restype = _i
+        return self.lib.oracle_set_threads(int(n))
+
     # ---------------------------------------------------------------- mm_int8
     def mm_int8(self, A, B, M, N, K, q, mode: int = 0, rows: tuple[int, int] | None = None):
         """q = (sA, sB, sC, zA, zB, zC); mode 0 = FP32 epilogue (normative), 1 = double."""

@@ -103,7 +103,7 @@ def test_tensor_path_full_matrix(lib, oracle, shape):
 @pytest.mark.parametrize("shape", [(4096, 4096, 4096, 128, 0, 24), (8192, 520, 8192, 32, 5, 12),
                                    (4096, 8192, 8192, 128, 11, 8)])
 def test_large_sampled_rows(lib, oracle, shape):
-    """tests/mm_int4.cpp:178-179 plus BASELINE config 4 (M=4096 K=8192 N=8192, G=128)."""
+    """tests/mm_int4.cpp:178-179 plus the large weight-only shape M=4096 K=8192 N=8192, G=128."""
     m, n, k, g, seed, nrows = shape
     x, w, s = oracle.int4_inputs(m, n, k, g, seed)
     dx = torch.from_numpy(x.view(np.int16)).cuda()

@@ -172,7 +172,7 @@ def test_generic_path_matches_oracle(lib, oracle, shape):
 
 
 def test_config1_full_matrix(lib, oracle):
-    """BASELINE config 1: M=512 K=1024 N=512, harness seeds, scales .02/.03/.5, zp 3/-5/1;
+    """The reference's CPU-runnable case M=512 K=1024 N=512, harness seeds, scales .02/.03/.5, zp 3/-5/1;
     and the same with scale_C = 16 so that few outputs saturate."""
     M, N, K = 512, 512, 1024
     A, B = oracle.random_int8(M * K, 42).reshape(M, K), oracle.random_int8(K * N, 123).reshape(K, N)
@@ -365,10 +365,12 @@ def _ref_lib():
 
 
 LARGE = [  # (M, N, K, sampled oracle rows)
-    (8192, 8192, 8192, 16),   # BASELINE config 2
-    (16, 28672, 8192, 16),    # config 3 (decode)
-    (8192, 1280, 8192, 8),    # config 5 QKV slab of one of 8 GPUs
-    (8192, 1024, 28672, 4),   # config 5 down-projection slab
+    (8192, 8192, 8192, 16),   # the large square tensor-bound case
+    (16, 28672, 8192, 16),    # decode: 16 activation rows against an MLP up-projection
+    (8192, 1280, 8192, 8),    # transformer layer at M = 8192, one of 8 column slabs: QKV (N = 10240)
+    (8192, 1024, 28672, 4),   # ... down projection (K = 28672, N = 8192)
+    (8192, 7168, 8192, 4),    # ... gate/up projection (N = 57344)
+    (8192, 1024, 8192, 8),    # ... output projection (N = 8192)
 ]
 
 
@@ -526,6 +528,54 @@ def test_fused_swiglu_epilogue(lib, oracle, shape, paths):
             near_tie = np.abs(np.abs(t - np.floor(t)) - 0.5) < 1e-4 * np.maximum(1.0, np.abs(t))
             assert np.all(np.abs(got - want)[differ] <= 1) and np.all(near_tie[differ]), (shape, force)
             assert differ.mean() < 2e-3, (shape, force, differ.mean())
+    assert lib.texo_mm_int8_status() == 0
+
+
+def _ref_swiglu_lib():
+    path = os.path.join(harness.ORACLE_DIR, "_ref", "libref_swiglu.so")
+    if not os.path.exists(path):
+        return None
+    ref = ctypes.CDLL(path)
+    ref.solve.restype = None
+    ref.solve.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int]
+    return ref
+
+
+@pytest.mark.parametrize("shape", [(300, 504, 1040), (1024, 1024, 4096), (128, 256, 512)])
+def test_fused_swiglu_equals_the_reference_swiglu_kernel(lib, oracle, shape):
+    """Pins the activation of the fused epilogue on reference code: the dequantised gate and up
+    values (exact integer dots from the oracle, two FP32 multiplies each) go through the
+    reference's own swiglu operator (src/swiglu.cu of frezcirno/Texo, recompiled for sm_100a,
+    input = [gate | up] halves) on the same GPU; its FP32 output, requantised in FP32 as
+    clamp(rint(h / scale_H) + zero_point_H), must equal the fused kernel's int8 output byte for
+    byte (same FP32 operations in the same order, same approximate exponential)."""
+    ref = _ref_swiglu_lib()
+    if ref is None:
+        pytest.skip("oracle/_ref/libref_swiglu.so not built (reference checkout absent at build time)")
+    m, f, k = shape
+    rng = np.random.default_rng(11 + f + k)
+    a = rng.integers(-128, 128, (m, k), dtype=np.int8)
+    b = rng.integers(-128, 128, (k, 2 * f), dtype=np.int8)
+    sa, za = np.float32(0.02), 3
+    spread = 128 * 74 * np.sqrt(k)
+    s_gate, s_up = np.float32(1.5 / (float(sa) * spread)), np.float32(2.0 / (float(sa) * spread))
+    s_h, z_gate, z_up, z_h = np.float32(0.03), -5, 4, 1
+    b_gate, b_up = np.ascontiguousarray(b[:, 0::2]), np.ascontiguousarray(b[:, 1::2])
+    gate = (oracle.mm_int8_dots(a, b_gate, m, f, k, za, z_gate).astype(np.float32) * sa) * s_gate
+    up = (oracle.mm_int8_dots(a, b_up, m, f, k, za, z_up).astype(np.float32) * sa) * s_up
+    packed = torch.from_numpy(np.concatenate([gate.ravel(), up.ravel()])).cuda()
+    h = torch.empty(m * f, dtype=torch.float32, device="cuda")
+    ref.solve(packed.data_ptr(), h.data_ptr(), 2 * m * f)
+    torch.cuda.synchronize()
+    h = h.cpu().numpy().reshape(m, f)
+    want = np.clip(np.rint(h / s_h) + np.float32(z_h), -128, 127).astype(np.int8)
+    assert want.dtype == np.int8 and (np.abs(want.astype(int)) < 127).mean() > 0.5
+    A, B = _dev(a), _dev(b)
+    H = torch.full((m, f), 77, dtype=torch.int8, device="cuda")
+    lib.texo_mm_int8_swiglu_solve(A.data_ptr(), B.data_ptr(), H.data_ptr(), m, f, k, float(sa), float(s_gate),
+                                  float(s_up), float(s_h), za, z_gate, z_up, z_h)
+    torch.cuda.synchronize()
+    assert np.array_equal(H.cpu().numpy(), want), shape
     assert lib.texo_mm_int8_status() == 0
 
 

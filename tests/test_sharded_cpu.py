@@ -112,6 +112,32 @@ def test_two_rank_w4a8_gather_equals_unsharded(tmp_path, oracle, N):
         assert np.array_equal(np.load(tmp_path / f"w{r}.npy"), want)
 
 
+def _upload_worker(rank, world, port, result_dir):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        for M in (24, 25):  # divisible by the world size (split upload) and not (whole upload)
+            host = torch.from_numpy(harness.hashed_int8(3, 0, np.arange(M), np.arange(40)))
+            dev = torch.full((M, 40), 99, dtype=torch.int8)  # a CPU tensor stands in for device memory
+            sharded.upload_replicated_rows(host, dev)
+            assert torch.equal(dev, host), (rank, M)
+        with open(os.path.join(result_dir, f"up{rank}.txt"), "w") as fh:
+            fh.write("ok")
+    finally:
+        dist.destroy_process_group()
+
+
+def test_replicated_upload_in_row_shares(tmp_path):
+    """Each rank carries 1/world of the rows of a replicated matrix and an all-gather completes
+    it: every rank ends with the whole matrix."""
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    mp.spawn(_upload_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    assert (tmp_path / "up0.txt").exists() and (tmp_path / "up1.txt").exists()
+
+
 def _failing_worker(rank, world, port, result_dir):
     import datetime
 

@@ -3,8 +3,8 @@
 Every rank materialises the same logical A and only its own column slab of B from the
 counter-based generator, runs the single-GPU operator on it, and the gathered C must equal
 the oracle's unsharded result bit for bit - once with an NCCL all-gather after the matmul and
-once with the gather fused into the matmul's epilogue (stores into the peers' copies of C in
-symmetric memory).  Skipped when fewer than two GPUs are visible."""
+with the gather fused into the matmul's epilogue (stores into the peers' copies of C in
+symmetric memory: per-peer stores, and multimem stores through the NVLink multicast mapping).  Skipped when fewer than two GPUs are visible."""
 import os
 import socket
 
@@ -33,14 +33,18 @@ def _worker(rank, world, port, M, N, K, q, out_dir):
         C = sharded.mm_int8_sharded(A, B_slab, N, *q, gather=True)
         torch.cuda.synchronize()
         np.save(os.path.join(out_dir, f"c{rank}.npy"), C.cpu().numpy())
-        # the same with the gather fused into the matmul's epilogue (peer stores, no collective)
-        out = sharded.GatheredOutput(M, N, torch.device("cuda", rank))
-        out.tensor.fill_(99)
-        out.wait()
-        sharded.mm_int8_allgather(A, B_slab, out, *q)
-        out.wait()
-        torch.cuda.synchronize()
-        np.save(os.path.join(out_dir, f"f{rank}.npy"), out.tensor.cpu().numpy())
+        # the same with the gather fused into the matmul's epilogue (no collective): once with
+        # per-peer stores, once through the NVLink multicast mapping where the platform has one
+        for tag, multicast in (("f", False), ("m", True)):
+            out = sharded.GatheredOutput(M, N, torch.device("cuda", rank), multicast=multicast)
+            out.tensor.fill_(99)
+            out.wait()
+            sharded.mm_int8_allgather(A, B_slab, out, *q)
+            out.wait()
+            torch.cuda.synchronize()
+            np.save(os.path.join(out_dir, f"{tag}{rank}.npy"), out.tensor.cpu().numpy())
+            if multicast:
+                np.save(os.path.join(out_dir, f"mc{rank}.npy"), np.array([int(out.multicast_ptr != 0)]))
         # decode-shaped rows take the skinny kernel, which stores to the peers as well
         out16 = sharded.GatheredOutput(16, N, torch.device("cuda", rank))
         out16.tensor.fill_(99)
@@ -71,5 +75,7 @@ def test_two_gpu_slabs_gather_to_the_unsharded_result(tmp_path, oracle):
     want = oracle.mm_int8(A, B, M, N, K, q)
     for r in range(2):
         assert np.array_equal(np.load(tmp_path / f"c{r}.npy"), want)
-        assert np.array_equal(np.load(tmp_path / f"f{r}.npy"), want), "fused all-gather"
+        assert np.array_equal(np.load(tmp_path / f"f{r}.npy"), want), "fused all-gather, peer stores"
+        assert np.array_equal(np.load(tmp_path / f"m{r}.npy"), want), (
+            "fused all-gather, multicast=%d" % int(np.load(tmp_path / f"mc{r}.npy")[0]))
         assert np.array_equal(np.load(tmp_path / f"g{r}.npy"), want[:16]), "fused all-gather, decode rows"

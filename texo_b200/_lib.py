@@ -30,8 +30,12 @@ _SIGNATURES = {
     "texo_mm_int8_solve_allgather": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int,
                                              _c_int, _c_int, _c_float, _c_float, _c_float,
                                              _c_int, _c_int, _c_int]),
+    "texo_mm_int8_solve_allgather_multicast": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int,
+                                                        _c_int, _c_int, _c_int, _c_int, _c_float,
+                                                        _c_float, _c_float, _c_int, _c_int, _c_int]),
     "texo_mm_int8_solve_noalloc": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int,
                                             _c_float, _c_float, _c_float, _c_int, _c_int, _c_int]),
+    "texo_mm_int8_noalloc_status": (_c_int, []),
     "texo_mm_int8_solve_host": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int,
                                          _c_float, _c_float, _c_float, _c_int, _c_int, _c_int]),
     "texo_mm_int8_prepare_weights": (_c_ptr, [_c_ptr, _c_int, _c_int]),

@@ -135,7 +135,10 @@ struct TensorBarriers {
 
 // Four packed bytes (eight nibbles, k ascending: high nibble first) -> eight FP16 values
 // q - 8.  0x6400 is 1024.0: OR-ing a nibble into mantissa bits 0-3 gives 1024 + v, into bits
-// 4-7 gives 1024 + 16 v; one HFMA2 per byte removes the offsets exactly.
+// 4-7 gives 1024 + 16 v; one HFMA2 per byte removes the offsets exactly.  This is the
+// byte-permute + one-HFMA2 conversion of the reference's dequant() (frezcirno/Texo
+// src/mm_int4.cu:141-148; same magic constant, mask, multipliers (1/16, 1) and addends
+// (-72, -1032)), applied here to a whole word on its way into the swizzled operand tile.
 __device__ __forceinline__ uint4 unpack8(uint32_t word) {
   const __half2 mul = __halves2half2(__float2half(0.0625f), __float2half(1.0f));
   const __half2 add = __halves2half2(__float2half(-72.0f), __float2half(-1032.0f));
@@ -474,8 +477,13 @@ static bool launch_tensor(DeviceCtx& ctx, const __half* x, const uint8_t* w_q, c
   const int tiles_n = (N + 255) / 256, tiles_m = (M + 255) / 256;
   cfg.gridDim = dim3(2 * std::min(tiles_n * tiles_m, pairs[ctx.device]));
   const int slot = profile_start();
-  cudaLaunchKernelEx(&cfg, tensor_kernel, map_x, map_raw, scales, y, M, N, K, G, tiles_n, tiles_m,
-                     ctx.status);
+  if (cudaLaunchKernelEx(&cfg, tensor_kernel, map_x, map_raw, scales, y, M, N, K, G, tiles_n, tiles_m,
+                         ctx.status) != cudaSuccess) {
+    cudaGetLastError();
+    profile_stop(slot);
+    note_host_error(STATUS_LAUNCH_FAILED);
+    return false;  // the caller falls back to the generic kernel
+  }
   profile_stop(slot);
   ++launch_counter();
   last_path() = 2;

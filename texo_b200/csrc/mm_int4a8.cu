@@ -479,17 +479,23 @@ static bool launch_tensor(DeviceCtx& ctx, const int8_t* A, const uint8_t* W, int
   const int* rs = row_sum;
   const int* ws = w_sum;
   static bool overlap_ok = true;
+  cudaError_t err = cudaSuccess;
   for (int attempt = 0; attempt < 2; ++attempt) {
     const bool overlap = sums_launched && overlap_ok && attempt == 0;
     cfg.numAttrs = overlap ? 2 : 1;
-    const cudaError_t err =
-        wide ? cudaLaunchKernelEx(&cfg, pair_kernel<true>, map_a, map_raw, C, rs, ws, M, N, K, q,
-                                  tiles_m, tiles_n, c_vector_ok, ctx.status)
-             : cudaLaunchKernelEx(&cfg, pair_kernel<false>, map_a, map_raw, C, rs, ws, M, N, K, q,
-                                  tiles_m, tiles_n, c_vector_ok, ctx.status);
+    err = wide ? cudaLaunchKernelEx(&cfg, pair_kernel<true>, map_a, map_raw, C, rs, ws, M, N, K, q,
+                                    tiles_m, tiles_n, c_vector_ok, ctx.status)
+               : cudaLaunchKernelEx(&cfg, pair_kernel<false>, map_a, map_raw, C, rs, ws, M, N, K, q,
+                                    tiles_m, tiles_n, c_vector_ok, ctx.status);
     if (err == cudaSuccess || !overlap) break;
     cudaGetLastError();  // the attribute was refused: launch again, fully serialised
     overlap_ok = false;
+  }
+  if (err != cudaSuccess) {
+    cudaGetLastError();
+    profile_stop(slot);
+    note_host_error(STATUS_LAUNCH_FAILED);
+    return false;  // the caller falls back to the generic kernel
   }
   profile_stop(slot);
   ++launch_counter();

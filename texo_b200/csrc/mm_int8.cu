@@ -273,14 +273,22 @@ static bool launch_sums(const int8_t* A, const int8_t* B, int* row_sum, int* col
   if (col_items + row_items == 0) return false;
   // Ask for the largest shared-memory carve-out although the kernel needs little: an SM can
   // only host a tensor-kernel CTA next to this block if it is already configured that way.
-  static bool configured = false;
-  if (!configured) {
+  // (function attributes are per device)
+  static bool configured[MAX_DEVICES] = {};
+  int device = 0;
+  cudaGetDevice(&device);
+  if (device >= 0 && device < MAX_DEVICES && !configured[device]) {
     cudaFuncSetAttribute(sums_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
                          cudaSharedmemCarveoutMaxShared);
-    configured = true;
+    configured[device] = true;
   }
   const int grid = max_blocks > 0 ? std::min(col_items + row_items, max_blocks) : col_items + row_items;
   sums_kernel<<<grid, SUM_THREADS>>>(A, B, row_sum, col_sum, M, N, K, col_items, row_items);
+  if (cudaPeekAtLastError() != cudaSuccess) {
+    cudaGetLastError();
+    note_host_error(STATUS_LAUNCH_FAILED);
+    return false;
+  }
   ++launch_counter();
   return true;
 }
@@ -833,18 +841,24 @@ static bool launch_tensor(DeviceCtx& ctx, const int8_t* A, const int8_t* B, int8
     const int* cs = col_sum;
     static bool overlap_supported[MAX_DEVICES] = {true, true, true, true, true, true, true, true,
                                                   true, true, true, true, true, true, true, true};
+    cudaError_t err = cudaSuccess;
     for (int attempt = 0; attempt < 2; ++attempt) {
       const bool overlap = sums_launched && attempt == 0 &&
                            (ctx.device >= 16 || overlap_supported[ctx.device]);
       cfg.numAttrs = overlap ? 2 : 1;
-      cudaError_t err =
-          K <= 33025 ? cudaLaunchKernelEx(&cfg, umma_pair_kernel<false>, map_a, map_b, C, rs, cs, M, N,
-                                          K, q, tiles_m, tiles_n, c_vector_ok, ctx.status)
-                     : cudaLaunchKernelEx(&cfg, umma_pair_kernel<true>, map_a, map_b, C, rs, cs, M, N,
-                                          K, q, tiles_m, tiles_n, c_vector_ok, ctx.status);
+      err = K <= 33025 ? cudaLaunchKernelEx(&cfg, umma_pair_kernel<false>, map_a, map_b, C, rs, cs, M, N,
+                                            K, q, tiles_m, tiles_n, c_vector_ok, ctx.status)
+                       : cudaLaunchKernelEx(&cfg, umma_pair_kernel<true>, map_a, map_b, C, rs, cs, M, N,
+                                            K, q, tiles_m, tiles_n, c_vector_ok, ctx.status);
       if (err == cudaSuccess || !overlap) break;
       cudaGetLastError();  // the attribute was refused: launch again, fully serialised
       if (ctx.device < 16) overlap_supported[ctx.device] = false;
+    }
+    if (err != cudaSuccess) {
+      cudaGetLastError();
+      profile_stop(slot);
+      note_host_error(STATUS_LAUNCH_FAILED);
+      return false;  // the caller falls back to the generic kernel
     }
     last_path() = PATH_TENSOR_PAIR;
   } else {
@@ -858,6 +872,12 @@ static bool launch_tensor(DeviceCtx& ctx, const int8_t* A, const int8_t* B, int8
       umma_kernel<true><<<grid, MMA_THREADS, SMEM_BYTES>>>(map_a, map_b, C, row_sum, col_sum, M, N,
                                                           K, q, tiles_m, tiles_n, c_vector_ok,
                                                           ctx.status);
+    if (cudaPeekAtLastError() != cudaSuccess) {
+      cudaGetLastError();
+      profile_stop(slot);
+      note_host_error(STATUS_LAUNCH_FAILED);
+      return false;
+    }
     last_path() = PATH_TENSOR;
   }
   profile_stop(slot);
@@ -1012,15 +1032,23 @@ extern "C" void texo_mm_int8_dequant_solve(const int8_t* A, const int8_t* B, voi
 // piece into all n_gpus copies with plain stores, so when every GPU's call has completed (the
 // caller synchronises them, e.g. with a barrier on the symmetric-memory handle) each copy holds
 // the whole row-major C.  The kernel never waits for another GPU.
-extern "C" int texo_mm_int8_solve_allgather(const int8_t* A, const int8_t* B_slab,
-                                            int8_t* const* C_all, int n_gpus, int M, int N_slab,
-                                            int K, int ld_c, int col_offset, float scale_A,
-                                            float scale_B, float scale_C, int zero_point_A,
-                                            int zero_point_B, int zero_point_C) {
+//
+// texo_mm_int8_solve_allgather_multicast: the same with C_multicast, the NVLink multicast
+// (NVLS) mapping of that allocation (torch symmetric memory: handle.multicast_ptr; cuMem:
+// the address a multicast object is mapped at), or null.  With it, whole 128-byte row
+// segments of the CTA-pair kernel's drain are written with ONE multimem.st that NVSwitch
+// replicates into every copy; without it (and for ragged edges and the other kernels) every
+// copy is written with its own store.  C_multicast must be 16-byte aligned and cover the same
+// [M, ld_c] matrix as the entries of C_all.
+extern "C" int texo_mm_int8_solve_allgather_multicast(
+    const int8_t* A, const int8_t* B_slab, int8_t* const* C_all, int8_t* C_multicast, int n_gpus,
+    int M, int N_slab, int K, int ld_c, int col_offset, float scale_A, float scale_B, float scale_C,
+    int zero_point_A, int zero_point_B, int zero_point_C) {
   using namespace texo;
   using namespace texo::i8;
   if (M <= 0 || N_slab <= 0) return 0;
-  if (!C_all || n_gpus < 1 || n_gpus > MAX_PEERS || col_offset < 0 || ld_c < col_offset + N_slab) {
+  if (!C_all || n_gpus < 1 || n_gpus > MAX_PEERS || col_offset < 0 || ld_c < col_offset + N_slab ||
+      (reinterpret_cast<uintptr_t>(C_multicast) & 15) != 0) {
     note_host_error(STATUS_BAD_ARGUMENT);
     return -1;
   }
@@ -1028,6 +1056,7 @@ extern "C" int texo_mm_int8_solve_allgather(const int8_t* A, const int8_t* B_sla
   q.n_peers = n_gpus;
   q.ldc = ld_c;
   q.n_off = col_offset;
+  q.mc = C_multicast;
   for (int r = 0; r < n_gpus; ++r) {
     if (!C_all[r]) {
       note_host_error(STATUS_BAD_ARGUMENT);
@@ -1037,6 +1066,16 @@ extern "C" int texo_mm_int8_solve_allgather(const int8_t* A, const int8_t* B_sla
   }
   solve_with(A, B_slab, C_all[0], M, N_slab, K, q);
   return 0;
+}
+
+extern "C" int texo_mm_int8_solve_allgather(const int8_t* A, const int8_t* B_slab,
+                                            int8_t* const* C_all, int n_gpus, int M, int N_slab,
+                                            int K, int ld_c, int col_offset, float scale_A,
+                                            float scale_B, float scale_C, int zero_point_A,
+                                            int zero_point_B, int zero_point_C) {
+  return texo_mm_int8_solve_allgather_multicast(A, B_slab, C_all, nullptr, n_gpus, M, N_slab, K, ld_c,
+                                                col_offset, scale_A, scale_B, scale_C, zero_point_A,
+                                                zero_point_B, zero_point_C);
 }
 
 // The same operator with one weight scale (and optionally one weight zero point) per output
@@ -1190,8 +1229,13 @@ struct NoAllocDevice {
 };
 
 // Once per device, with that device current: resolve the device address of the array (the
-// name `noalloc_scratch` in host code is only a handle, never a device pointer) and opt the
-// kernels into their shared-memory size.  Returns nullptr on a CUDA error.
+// name `noalloc_scratch` in host code is only a handle, never a device pointer), opt the
+// kernels into their shared-memory sizes, and make the driver load the code of every kernel
+// the entry point can launch.  With lazy module loading a kernel's code is brought onto the
+// device at its first launch, which may take device memory; asking for each kernel's
+// attributes here moves that cost into the set-up, so that later calls - whichever path
+// their shapes and zero points select - find everything resident.  Returns nullptr on a
+// CUDA error.
 static NoAllocDevice* noalloc_device() {
   static NoAllocDevice table[MAX_DEVICES];
   int device = 0;
@@ -1207,15 +1251,23 @@ static NoAllocDevice* noalloc_device() {
       return nullptr;
     }
     d.scratch = static_cast<int*>(address);
+    cudaFuncAttributes attr;
     if (cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess ||
         cudaDeviceGetAttribute(&d.cc_major, cudaDevAttrComputeCapabilityMajor, device) != cudaSuccess ||
         cudaFuncSetAttribute(umma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              SMEM_BYTES) != cudaSuccess ||
         cudaFuncSetAttribute(umma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             SMEM_BYTES) != cudaSuccess) {
+                             SMEM_BYTES) != cudaSuccess ||
+        cudaFuncSetAttribute(sums_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                             cudaSharedmemCarveoutMaxShared) != cudaSuccess ||
+        cudaFuncGetAttributes(&attr, sums_kernel) != cudaSuccess ||
+        cudaFuncGetAttributes(&attr, generic_kernel) != cudaSuccess ||
+        cudaFuncGetAttributes(&attr, umma_kernel<false>) != cudaSuccess ||
+        cudaFuncGetAttributes(&attr, umma_kernel<true>) != cudaSuccess) {
       cudaGetLastError();
       return nullptr;
     }
+    tensor_map_encoder();  // resolve the driver entry point now, not at the first tensor call
     d.ready = true;
   }
   return &d;
@@ -1230,10 +1282,12 @@ static NoAllocDevice* noalloc_device() {
 // N <= 32768), -3 when the one-time device set-up failed.  Output is bit-identical to
 // `solve`.  The first call on each device performs the set-up above, so make that call
 // outside of any stream capture.  All calls share the one scratch array, which still holds
-// the previous call's sums when the next one starts (the part that must start at zero is
-// cleared on the stream); two calls whose kernels overlap on the GPU (different host
-// threads or streams) would race on it - issue them one after another, as `solve` requires
-// anyway.
+// the previous call's sums when the next one starts; nothing in it has to start at zero
+// (every entry a call reads is first rewritten by that call's own pre-pass with plain
+// stores, and the status word is only ever set, by a kernel that gave up, and cleared by
+// texo_mm_int8_noalloc_status).  Two calls whose kernels overlap on the GPU (different host
+// threads or streams) would race on the array - issue them one after another, as `solve`
+// requires anyway.
 extern "C" int texo_mm_int8_solve_noalloc(const int8_t* A, const int8_t* B, int8_t* C, int M, int N,
                                           int K, float scale_A, float scale_B, float scale_C,
                                           int zero_point_A, int zero_point_B, int zero_point_C) {
@@ -1285,4 +1339,30 @@ extern "C" int texo_mm_int8_solve_noalloc(const int8_t* A, const int8_t* B, int8
   ++launch_counter();
   last_path() = PATH_GENERIC;
   return 0;
+}
+
+// Error state of the allocation-free entry point on the current device, read without
+// allocating anything (texo_mm_int8_status goes through the library's cudaMalloc'd status
+// block and is therefore not for these callers).  The tensor kernel's waits are bounded; one
+// that runs out records a code (1-5, see ptx.cuh) in the status word that lives at the end of
+// the fixed scratch array and the kernel returns early, leaving C incomplete - the call
+// itself had long returned 0.  This copies the word out (a blocking 4-byte copy: it waits for
+// the calls issued so far), clears it if it was set, and returns it: 0 = every
+// texo_mm_int8_solve_noalloc call since the last query ran to completion.  -3 when the
+// device set-up failed.
+extern "C" int texo_mm_int8_noalloc_status(void) {
+  using namespace texo::i8;
+  NoAllocDevice* dev = noalloc_device();
+  if (!dev) return -3;
+  int* word = dev->scratch + NOALLOC_MAX_M + NOALLOC_MAX_N;
+  int code = 0;
+  if (cudaMemcpy(&code, word, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) {
+    cudaGetLastError();
+    return -3;
+  }
+  if (code != 0) {
+    const int zero = 0;
+    cudaMemcpy(word, &zero, sizeof(int), cudaMemcpyHostToDevice);
+  }
+  return code;
 }

@@ -21,6 +21,7 @@ enum : int {
   STATUS_TIMEOUT_FLAG = 5,       // split-K partner never arrived
   STATUS_BAD_ARGUMENT = 16,
   STATUS_TENSORMAP_FAILED = 17,
+  STATUS_LAUNCH_FAILED = 18,     // a kernel launch was refused; the call fell back or did nothing
 };
 
 // About one second at B200 clocks; a healthy wait is microseconds.

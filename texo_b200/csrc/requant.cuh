@@ -48,6 +48,11 @@ struct Quant {
   // gather rides under the main loop and no collective follows.  The C argument is unused.
   int n_peers, ldc, n_off;
   int8_t* peers[8];
+  // Optional NVLink multicast mapping of the same [M, ldc] matrix (null = none): one
+  // multimem.st to mc + offset is replicated by the switch into every GPU's copy, so a slab
+  // leaves this GPU once instead of once per peer.  Used by the staged (whole 128-byte row
+  // segment) stores of the CTA-pair drain; everything else keeps the per-peer stores.
+  int8_t* mc;
 };
 constexpr int MAX_PEERS = 8;
 
@@ -59,7 +64,7 @@ constexpr int MAX_PEERS = 8;
 // lets the tail run in integers (see requantize_fast).  Anything else (including NaN or
 // infinite scales) takes the plain IEEE division, element by element.
 inline Quant make_quant(float sa, float sb, float sc, int za, int zb, int zc, int K) {
-  Quant q = {sa, sb, sc, za, zb, zc, 0.f, 0, nullptr, nullptr, 0, 0.f, 0.f, 0, 0, 0, 0, 0, 0, {}};
+  Quant q = {sa, sb, sc, za, zb, zc, 0.f, 0, nullptr, nullptr, 0, 0.f, 0.f, 0, 0, 0, 0, 0, 0, {}, nullptr};
   auto within = [](float v, float lo, float hi) {
     const float a = v < 0 ? -v : v;
     return a >= lo && a <= hi;  // false for NaN
@@ -204,6 +209,15 @@ __device__ __forceinline__ typename std::conditional<WIDE, long long, unsigned>:
   if (row_ok && (q.zb != 0 || q.zb_vec != nullptr || (q.swiglu && q.z_up != 0)))
     rt -= Wide(Signed(__ldcg(row_sum + m)));
   return rt;
+}
+
+// 16 bytes to a multicast address: the switch replicates the store into every GPU bound to
+// the multicast object (the bits are not interpreted; .v4.f32 is just the 16-byte form).
+__device__ __forceinline__ void multimem_st_16(void* mc_addr, const int4& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_addr),
+               "f"(__int_as_float(v.x)), "f"(__int_as_float(v.y)), "f"(__int_as_float(v.z)),
+               "f"(__int_as_float(v.w))
+               : "memory");
 }
 
 constexpr int P_GROUP_M = 8;  // pair-tile rows per raster group
@@ -413,6 +427,19 @@ __device__ __forceinline__ void drain_half(uint32_t tmem_row_addr, int col0, int
     const unsigned rows_ok = __ballot_sync(0xffffffffu, row_ok);  // bit r: row r is inside M
     const int m_base = m - lane;  // first row of this warp's 32
     const int piece = lane & 7;
+    if (q.mc != nullptr) {
+      // one store per piece into the multicast mapping: NVSwitch writes all copies
+      int8_t* dst = q.mc + q.n_off + n_tile0 + col0 + piece * 16;
+#pragma unroll
+      for (int it = 0; it < 8; ++it) {
+        const int r = it * 4 + (lane >> 3);
+        if ((rows_ok >> r) & 1u) {
+          const int4 value =
+              *reinterpret_cast<const int4*>(gather_stage + r * 128 + ((piece ^ (r & 7)) << 4));
+          multimem_st_16(dst + size_t(m_base + r) * q.ldc, value);
+        }
+      }
+    } else
     for (int p = 0; p < q.n_peers; ++p) {
       int8_t* dst = q.peers[p] + q.n_off + n_tile0 + col0 + piece * 16;
 #pragma unroll

@@ -735,14 +735,20 @@ static bool launch_skinny(DeviceCtx& ctx, const int8_t* A, const void* B, int8_t
   int* ws = reinterpret_cast<int*>(base + counter_bytes);
   int* counters = reinterpret_cast<int*>(base);
   static bool overlap_ok = true;
+  cudaError_t err = cudaSuccess;
   for (int attempt = 0; attempt < 2; ++attempt) {
     cfg.numAttrs = (overlap_ok && attempt == 0) ? 1 : 0;
-    if (cudaLaunchKernelEx(&cfg, skinny_kernel<W4>, map_w, map_act, A, C, ws, counters, row_sum_g, M, N,
-                           K, q, R, weights_stable, ctx.status) == cudaSuccess ||
-        cfg.numAttrs == 0)
-      break;
+    err = cudaLaunchKernelEx(&cfg, skinny_kernel<W4>, map_w, map_act, A, C, ws, counters, row_sum_g, M, N,
+                             K, q, R, weights_stable, ctx.status);
+    if (err == cudaSuccess || cfg.numAttrs == 0) break;
     cudaGetLastError();  // attribute refused: launch again, fully serialised
     overlap_ok = false;
+  }
+  if (err != cudaSuccess) {
+    cudaGetLastError();
+    profile_stop(slot);
+    note_host_error(STATUS_LAUNCH_FAILED);
+    return false;  // the caller falls back to another kernel
   }
   profile_stop(slot);
   ++launch_counter();

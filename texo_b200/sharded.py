@@ -119,6 +119,26 @@ def mm_int4a8_sharded(A: torch.Tensor, w_q_slab: torch.Tensor, N: int, scale_A: 
     return all_gather_columns(C_slab, N, group) if gather else C_slab
 
 
+def upload_replicated_rows(host: torch.Tensor, dev: torch.Tensor, group=None) -> torch.Tensor:
+    """Fill the replicated device matrix `dev` [M, K] on every rank from identical HOST copies
+    `host` [M, K] (pinned for full speed) with each rank carrying only 1/world of the rows over
+    its own PCIe link: rank r uploads rows [r*M/g, (r+1)*M/g) and an NCCL all-gather over
+    NVLink delivers every rank's rows to all.  The whole job then moves M*K bytes
+    host->device once, as a single GPU would, instead of once per rank.  Needs M % world == 0
+    (otherwise every rank uploads everything).  Asynchronous on the current stream."""
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    M = host.shape[0]
+    if world == 1 or M % world != 0:
+        dev.copy_(host, non_blocking=True)
+        return dev
+    rank = dist.get_rank(group)
+    rows = M // world
+    mine = torch.empty((rows,) + tuple(dev.shape[1:]), dtype=dev.dtype, device=dev.device)
+    mine.copy_(host[rank * rows:(rank + 1) * rows], non_blocking=True)
+    dist.all_gather_into_tensor(dev.view(world * rows, *dev.shape[1:]), mine, group=group)
+    return dev
+
+
 class GatheredOutput:
     """The full row-major C [M, N] of a column-sharded matmul, one copy per GPU of the node,
     allocated from torch symmetric memory so that every rank can store into every copy.
@@ -127,7 +147,13 @@ class GatheredOutput:
     epilogue (peer stores over NVLink); after `wait()` every rank's `tensor` holds the whole C.
     No NCCL collective moves data."""
 
-    def __init__(self, M: int, N: int, device: torch.device, group=None):
+    def __init__(self, M: int, N: int, device: torch.device, group=None, multicast: bool | None = None):
+        """`multicast`: use the NVLink multicast (NVLS) mapping of the allocation when the
+        platform offers one, so that whole row segments leave each GPU once and NVSwitch
+        replicates them (default: yes unless TEXO_NO_MULTICAST=1); without it every copy is
+        written with its own peer store."""
+        import os
+
         import torch.distributed._symmetric_memory as symm_mem
 
         self.group = group if group is not None else dist.group.WORLD
@@ -138,8 +164,14 @@ class GatheredOutput:
         self.M, self.N = M, N
         self.tensor = symm_mem.empty((M, N), dtype=torch.int8, device=device)
         self.handle = symm_mem.rendezvous(self.tensor, self.group)
-        ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        # the tensor may sit at an offset inside the symmetric allocation
+        offset = int(self.tensor.data_ptr()) - int(self.handle.buffer_ptrs[self.rank])
+        ptrs = [int(p) + offset for p in self.handle.buffer_ptrs]
         self._ptr_array = (ctypes.c_void_p * self.world)(*ptrs)
+        if multicast is None:
+            multicast = os.environ.get("TEXO_NO_MULTICAST", "0") != "1"
+        mc = int(getattr(self.handle, "multicast_ptr", 0) or 0)
+        self.multicast_ptr = mc + offset if (multicast and mc and self.world > 1) else 0
 
     def wait(self) -> None:
         """All ranks' stores into every copy are complete and visible after this returns on
@@ -161,10 +193,10 @@ def mm_int8_allgather(A: torch.Tensor, B_slab: torch.Tensor, out: GatheredOutput
     if n1 > n0:
         lib = _lib.load()
         with torch.cuda.device(A.device), ops._DefaultStreamOrder(A.device):
-            rc = lib.texo_mm_int8_solve_allgather(
+            rc = lib.texo_mm_int8_solve_allgather_multicast(
                 A.data_ptr(), B_slab.data_ptr(), ctypes.cast(out._ptr_array, ctypes.c_void_p),
-                out.world, out.M, n1 - n0, A.shape[1], out.N, n0, scale_A, scale_B, scale_C,
-                zero_point_A, zero_point_B, zero_point_C)
+                out.multicast_ptr or None, out.world, out.M, n1 - n0, A.shape[1], out.N, n0,
+                scale_A, scale_B, scale_C, zero_point_A, zero_point_B, zero_point_C)
         if rc != 0:
             raise RuntimeError("texo_mm_int8_solve_allgather rejected its arguments")
     return out.tensor
