@@ -172,6 +172,15 @@ int texo_mm_int8_solve_allgather_multicast(const int8_t* A, const int8_t* B_slab
 void texo_mm_int4a8_solve(const int8_t* A, const uint8_t* w_q, int8_t* C, int M, int N, int K,
                           float scale_A, float scale_B, float scale_C, int zero_point_A,
                           int zero_point_B, int zero_point_C);
+/* W4A8 with per-output-channel weight quantisation (no counterpart in the reference): scale_B
+ * [N] FP32 and zero_point_B [N] int32 (each within [-128, 127]) are DEVICE arrays, one entry
+ * per row of w_q; zero_point_B may be null (all zero).  Column n:
+ *   C[m,n] = clamp(rint(float(sum_k (A-zA)(q[n,k]-zB[n])) * scale_A * scale_B[n] / scale_C) + zC)
+ * in the FP32 operation order of texo_mm_int4a8_solve.  Arrays 16-byte aligned and N % 4 == 0
+ * for the tensor-core paths (otherwise the generic kernel runs). */
+void texo_mm_int4a8_solve_per_channel(const int8_t* A, const uint8_t* w_q, int8_t* C, int M, int N,
+                                      int K, float scale_A, const float* scale_B, float scale_C,
+                                      int zero_point_A, const int* zero_point_B, int zero_point_C);
 /* mm_int4a8 diagnostics: path 1 = generic SIMT kernel, 2 = tcgen05 kind::i8 CTA-pair kernel,
  * 3 = streaming (decode) kernel, M <= 32. */
 int texo_mm_int4a8_last_path(void);
@@ -197,8 +206,8 @@ void texo_rms_norm_quant_solve(const float* x, const float* residual, const floa
  * C <= 16384, 16-byte aligned pointers). */
 int texo_rms_norm_last_path(void);
 
-/* Which device path the last mm_int8 call took: 1 generic, 2 one-CTA tensor kernel (tcgen05),
- * 3 skinny (streaming, M <= 128), 4 CTA-pair tensor kernel. */
+/* Which device path the last mm_int8 call took (also the SwiGLU and FP16 forms): 1 generic,
+ * 2 one-CTA tensor kernel (tcgen05), 3 skinny (streaming, M <= 128), 4 CTA-pair tensor kernel. */
 int texo_mm_int8_last_path(void);
 /* Force a path for the following calls (0 = automatic).  A forced path is still skipped
  * when its preconditions do not hold.  Also settable with TEXO_MM_INT8_PATH. */
@@ -212,7 +221,9 @@ void texo_mm_int8_force_path(int path);
 int texo_mm_int8_status(void);
 
 /* mm_int4: 1 = generic FP32 kernel, 2 = tcgen05 kind::f16 CTA-pair kernel (needs 16-byte
- * aligned x / w_q, K % 64 == 0, group_size 16, 32, 64 or 128). */
+ * aligned x / w_q, K % 64 == 0, group_size 16, 32, 64 or 128), 3 = streaming (decode) kernel
+ * (M <= 16, group_size 128, K % 128 == 0, aligned x / w_q): packed weights read once from HBM
+ * straight into registers, mma.sync on 16-row activation tiles. */
 int texo_mm_int4_last_path(void);
 void texo_mm_int4_force_path(int path);
 int texo_mm_int4_status(void);

@@ -58,6 +58,10 @@ def _takes_tensor_path(k, g):
     return k % 64 == 0 and g in (16, 32, 64, 128)
 
 
+def _takes_decode_path(m, k, g):
+    return m <= 16 and g == 128 and k % 128 == 0
+
+
 def test_harness_default_cases(lib, oracle):
     cases, seed = harness.mm_int4_harness_shapes()
     for m, n, k, g, sd, zero_x, off in cases:
@@ -68,7 +72,8 @@ def test_harness_default_cases(lib, oracle):
             got = run_case(lib, x, w, s, m, n, k, g, off)
             path = lib.texo_mm_int4_last_path()
             lib.texo_mm_int4_force_path(0)
-            assert path == (2 if force == 0 and _takes_tensor_path(k, g) else 1), (m, n, k, g, force)
+            want_path = 1 if force == 1 else 3 if _takes_decode_path(m, k, g) else 2 if _takes_tensor_path(k, g) else 1
+            assert path == want_path, (m, n, k, g, force)
             assert harness.int4_within_tolerance(got, want, ATOL, RTOL), (m, n, k, g, force)
     # zero scales: first, middle, last group and an all-zero column (tests/mm_int4.cpp:166-175)
     m, n, k, g = 70, 136, 512, 32
@@ -94,9 +99,54 @@ def test_tensor_path_full_matrix(lib, oracle, shape):
     stages); every output within the reference tolerance."""
     m, n, k, g = shape
     x, w, s = oracle.int4_inputs(m, n, k, g, 100 + m)
-    got = run_case(lib, x, w, s, m, n, k, g)
+    lib.texo_mm_int4_force_path(2)  # (few-row shapes would otherwise take the decode kernel)
+    try:
+        got = run_case(lib, x, w, s, m, n, k, g)
+    finally:
+        lib.texo_mm_int4_force_path(0)
     assert lib.texo_mm_int4_last_path() == 2
     assert harness.int4_within_tolerance(got, oracle.mm_int4(x, w, s, m, n, k, g), ATOL, RTOL)
+    assert lib.texo_mm_int4_status() == 0
+
+
+@pytest.mark.parametrize("shape", [(1, 4096, 4096), (16, 4096, 4096), (7, 100, 256), (16, 4100, 1024),
+                                   (3, 33, 128), (16, 520, 2048), (9, 31, 8192), (16, 8192, 8192),
+                                   (2, 1000, 384), (16, 288, 3968)])
+def test_decode_path_full_matrix(lib, oracle, shape):
+    """The streaming kernel for M <= 16, G = 128 (packed weights read once from HBM into
+    registers, mma.sync on a permuted k order, K split over the warps of a CTA): ragged N,
+    every way of splitting K (K / 128 odd, divisible by 2, 4, 8, 16), one to sixteen rows, odd
+    output offset; every output within the reference tolerance, guard bands intact."""
+    m, n, k = shape
+    x, w, s = oracle.int4_inputs(m, n, k, 128, 300 + m + n)
+    got = run_case(lib, x, w, s, m, n, k, 128, y_offset=1 if n % 2 else 0)
+    assert lib.texo_mm_int4_last_path() == 3
+    assert harness.int4_within_tolerance(got, oracle.mm_int4(x, w, s, m, n, k, 128), ATOL, RTOL)
+    assert lib.texo_mm_int4_status() == 0
+
+
+def test_decode_path_large_sampled_columns(lib, oracle):
+    """The decode shape of an MLP up-projection, 16 x 28672 x 8192, G = 128: sampled output
+    columns against the oracle, and the whole result against the CTA-pair tensor kernel."""
+    m, n, k, g = 16, 28672, 8192, 128
+    rng = np.random.default_rng(5)
+    x = harness.float_to_half_bits(rng.normal(0, 1, (m, k)))
+    w = rng.integers(0, 256, (n, k // 2), dtype=np.uint8)
+    s = harness.float_to_half_bits(rng.uniform(0.01, 0.11, (n, k // g)))
+    dx, dw, ds = (torch.from_numpy(t.view(np.int16) if t.dtype == np.uint16 else t).cuda() for t in (x, w, s))
+    ys = []
+    for force in (0, 2):
+        lib.texo_mm_int4_force_path(force)
+        dy = torch.full((m, n), float("nan"), dtype=torch.float16, device="cuda")
+        lib.texo_mm_int4_solve(dx.data_ptr(), dw.data_ptr(), ds.data_ptr(), dy.data_ptr(), m, n, k, g)
+        torch.cuda.synchronize()
+        assert lib.texo_mm_int4_last_path() == (3 if force == 0 else 2)
+        ys.append(dy.float().cpu().numpy())
+    lib.texo_mm_int4_force_path(0)
+    assert np.all(np.abs(ys[0] - ys[1]) <= 0.02 + 0.02 * np.abs(ys[1]))  # both within 0.01 of the truth
+    cols = np.unique(np.linspace(0, n - 1, 48).astype(int))
+    want = oracle.mm_int4(x, np.ascontiguousarray(w[cols]), np.ascontiguousarray(s[cols]), m, len(cols), k, g)
+    assert harness.int4_within_tolerance(ys[0][:, cols], want, ATOL, RTOL)
     assert lib.texo_mm_int4_status() == 0
 
 

@@ -221,3 +221,55 @@ def test_python_operator(lib, oracle):
     assert np.array_equal(got, oracle.mm_int4a8(a, w, m, n, k, q))
     with pytest.raises(ValueError):
         ops.mm_int4a8(torch.zeros((4, 6), dtype=torch.int8), torch.zeros((4, 3), dtype=torch.uint8), *q)
+
+
+@pytest.mark.parametrize("shape,forces", [((300, 272, 1024), (0, 1)), ((16, 1024, 2048), (0, 2, 1)),
+                                          ((32, 264, 4096), (0,)), ((9, 7, 38), (0,)),
+                                          ((1000, 520, 512), (0,)), ((256, 256, 33024), (0,))])
+def test_per_channel_weight_quantisation(lib, oracle, shape, forces):
+    """One weight scale and zero point per output column (row of w_q), on every device path:
+    bit-exact against the per-channel INT8 oracle applied to the weights unpacked in the
+    reference's nibble order (both pieces pinned); with constant vectors the result must equal
+    the per-tensor call byte for byte."""
+    m, n, k = shape
+    rng = np.random.default_rng(3 * n + k)
+    a = rng.integers(-128, 128, (m, k), dtype=np.int8)
+    w = rng.integers(0, 256, (n, k // 2), dtype=np.uint8)
+    unpacked = np.empty((n, k), dtype=np.int8)
+    unpacked[:, 0::2] = (w >> 4).astype(np.int8) - 8
+    unpacked[:, 1::2] = (w & 15).astype(np.int8) - 8
+    sa, za, zc = 0.021, 3, -2
+    sb = rng.uniform(0.005, 0.05, n).astype(np.float32)
+    sb[::7] *= np.float32(1e-9)  # some columns outside the range of the branch-free division
+    zb = rng.integers(-8, 8, n).astype(np.int32)
+    sc = float(np.float32(sa * 0.03 * (340 * np.sqrt(k) + 12 * k) / 60))
+    want = oracle.mm_int8_per_channel(a, np.ascontiguousarray(unpacked.T), m, n, k, sa, sb, sc, za, zb, zc)
+    assert np.count_nonzero(np.abs(want.astype(int)) < 127) > want.size // 3
+    A, W = _dev(a), _dev(w)
+    S, Z = torch.from_numpy(sb).cuda(), torch.from_numpy(zb).cuda()
+    for force in forces:
+        lib.texo_mm_int4a8_force_path(force)
+        for zvec in (Z, None):
+            C = torch.full((m, n), 77, dtype=torch.int8, device="cuda")
+            lib.texo_mm_int4a8_solve_per_channel(A.data_ptr(), W.data_ptr(), C.data_ptr(), m, n, k, sa,
+                                                 S.data_ptr(), sc, za, zvec.data_ptr() if zvec is not None else None,
+                                                 zc)
+            torch.cuda.synchronize()
+            if force:
+                assert lib.texo_mm_int4a8_last_path() == force, (shape, force)
+            expect = want if zvec is not None else oracle.mm_int8_per_channel(
+                a, np.ascontiguousarray(unpacked.T), m, n, k, sa, sb, sc, za, None, zc)
+            assert np.array_equal(C.cpu().numpy(), expect), (shape, force, zvec is not None)
+        lib.texo_mm_int4a8_force_path(0)
+    # constant vectors == the per-tensor entry point
+    q = (sa, float(np.float32(0.03)), sc, za, -5, zc)
+    const_s = torch.full((n,), q[1], dtype=torch.float32, device="cuda")
+    const_z = torch.full((n,), -5, dtype=torch.int32, device="cuda")
+    C1 = torch.empty((m, n), dtype=torch.int8, device="cuda")
+    C2 = torch.empty((m, n), dtype=torch.int8, device="cuda")
+    lib.texo_mm_int4a8_solve_per_channel(A.data_ptr(), W.data_ptr(), C1.data_ptr(), m, n, k, q[0],
+                                         const_s.data_ptr(), q[2], q[3], const_z.data_ptr(), q[5])
+    lib.texo_mm_int4a8_solve(A.data_ptr(), W.data_ptr(), C2.data_ptr(), m, n, k, *q)
+    torch.cuda.synchronize()
+    assert torch.equal(C1, C2)
+    assert lib.texo_mm_int4a8_status() == 0

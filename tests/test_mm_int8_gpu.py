@@ -343,6 +343,28 @@ def test_wide_dot_on_tensor_path(lib, oracle):
         assert np.array_equal(got, oracle.mm_int8(a, b, m, n, k, q))
 
 
+def test_stateless_call_on_the_pair_path_is_one_launch(lib, oracle):
+    """The CTA-pair kernel computes rowsum(A) / colsum(B) itself (its epilogue warps, while the
+    first tile's MMAs run): a stateless call with both zero points is a single launch, and
+    repeated calls with different operands on the same scratch stay bit-exact."""
+    rng = np.random.default_rng(77)
+    for (m, n, k), q in (((512, 512, 1024), (0.02, 0.03, 0.5, 3, -5, 1)),
+                         ((300, 1008, 1040), (0.02, 0.03, 12.0, -7, 6, -2)),
+                         ((2048, 272, 4096), (0.01, 0.02, 9.0, 0, 4, 0)),
+                         ((1000, 2064, 512), (0.01, 0.02, 3.0, 5, 0, 3))):
+        a = rng.integers(-128, 128, (m, k), dtype=np.int8)
+        b = rng.integers(-128, 128, (k, n), dtype=np.int8)
+        A, B = _dev(a), _dev(b)
+        C = torch.full((m, n), 55, dtype=torch.int8, device="cuda")
+        before = lib.texo_kernel_launches()
+        lib.texo_mm_int8_solve(A.data_ptr(), B.data_ptr(), C.data_ptr(), m, n, k, *q)
+        torch.cuda.synchronize()
+        assert lib.texo_mm_int8_last_path() == 4
+        assert lib.texo_kernel_launches() - before == 1
+        assert np.array_equal(C.cpu().numpy(), oracle.mm_int8(a, b, m, n, k, q)), (m, n, k)
+    assert lib.texo_mm_int8_status() == 0
+
+
 def test_huge_k_takes_generic_path(lib, oracle):
     m, n, k = 4, 16, (1 << 17) + 16
     rng = np.random.default_rng(3)
@@ -491,9 +513,11 @@ def test_per_channel_weight_quantisation(lib, oracle, shape, paths):
     assert lib.texo_mm_int8_status() == 0
 
 
-@pytest.mark.parametrize("shape,paths", [((300, 504, 1040), (0, 2, 4, 1)), ((128, 256, 512), (0, 2, 1)),
-                                         ((16, 512, 2048), (0,)), ((65, 33, 31), (0,)),
-                                         ((1024, 1024, 4096), (0,))])
+@pytest.mark.parametrize("shape,paths", [((300, 504, 1040), (0, 2, 4, 1)), ((128, 256, 512), (0, 3, 2, 1)),
+                                         ((16, 512, 2048), (0, 3)), ((65, 33, 31), (0,)),
+                                         ((1024, 1024, 4096), (0,)), ((7, 1000, 4096), (3,)),
+                                         ((32, 136, 1040), (3,)), ((64, 520, 1024), (3, 2)),
+                                         ((100, 264, 2048), (3,))])
 def test_fused_swiglu_epilogue(lib, oracle, shape, paths):
     """Gate/up projection with up * silu(gate) and requantisation fused into the drain.  The
     dequantised gate and up values are bit-defined; the activation uses the GPU's approximate
@@ -541,7 +565,8 @@ def _ref_swiglu_lib():
     return ref
 
 
-@pytest.mark.parametrize("shape", [(300, 504, 1040), (1024, 1024, 4096), (128, 256, 512)])
+@pytest.mark.parametrize("shape", [(300, 504, 1040), (1024, 1024, 4096), (128, 256, 512), (16, 512, 2048),
+                                   (48, 1000, 1024)])
 def test_fused_swiglu_equals_the_reference_swiglu_kernel(lib, oracle, shape):
     """Pins the activation of the fused epilogue on reference code: the dequantised gate and up
     values (exact integer dots from the oracle, two FP32 multiplies each) go through the
@@ -579,10 +604,12 @@ def test_fused_swiglu_equals_the_reference_swiglu_kernel(lib, oracle, shape):
     assert lib.texo_mm_int8_status() == 0
 
 
-@pytest.mark.parametrize("shape,paths", [((300, 1008, 1040), (0, 2, 4, 1)), ((128, 256, 512), (0, 2, 1)),
-                                         ((16, 512, 2048), (0,)), ((65, 67, 31), (0,)), ((40, 24, 0), (0,)),
+@pytest.mark.parametrize("shape,paths", [((300, 1008, 1040), (0, 2, 4, 1)), ((128, 256, 512), (0, 3, 2, 1)),
+                                         ((16, 512, 2048), (0, 3)), ((65, 67, 31), (0,)), ((40, 24, 0), (0,)),
                                          ((300, 1000, 1040), (0,)),
-                                         ((256, 264, 33040), (0,))])
+                                         ((256, 264, 33040), (0,)), ((5, 1008, 4096), (3,)),
+                                         ((32, 144, 1040), (3,)), ((64, 528, 1024), (3, 2)),
+                                         ((100, 272, 2048), (3,))])
 def test_dequantising_fp16_drain(lib, oracle, shape, paths):
     """half(float(dot) * sA * sB) straight from the accumulators: bit-exact against the exact
     integer dot followed by the same two FP32 multiplies and one rounding to FP16."""

@@ -46,6 +46,8 @@ _SIGNATURES = {
     "texo_dequantization_solve": (None, [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int]),
     "texo_mm_int4a8_solve": (None, [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int,
                                     _c_float, _c_float, _c_float, _c_int, _c_int, _c_int]),
+    "texo_mm_int4a8_solve_per_channel": (None, [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int,
+                                                _c_float, _c_ptr, _c_float, _c_int, _c_ptr, _c_int]),
     "texo_rms_norm_w_residual_solve": (None, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_float]),
     "texo_rms_norm_quant_solve": (None, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int,
                                          _c_float, _c_float, _c_int]),

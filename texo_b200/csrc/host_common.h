@@ -30,7 +30,15 @@ struct DeviceCtx {
   // (the kernel that consumes it cleans up after itself); zeroed when (re)allocated.
   void* workspace = nullptr;
   size_t workspace_bytes = 0;
+  // Device-wide "work items finished" counter of the INT8 CTA-pair kernel (status word
+  // STATUS_WORD_ITEMS_DONE): it only ever grows; this is the value it will show when every
+  // call launched so far has finished its items.
+  unsigned items_expected = 0;
 };
+
+// Layout of the 64-int status block: word 0 = first device error code, word 8 = the item
+// counter above, word 32 = scratch of the wait self-test.
+constexpr int STATUS_WORD_ITEMS_DONE = 8;
 
 inline int& host_status() {
   static int value = 0;
@@ -105,6 +113,9 @@ inline int read_and_clear_status() {
       cudaMemset(ctx.status, 0, sizeof(int));
       // a kernel that gave up may have left partial sums behind
       if (ctx.workspace) cudaMemset(ctx.workspace, 0, ctx.workspace_bytes);
+      // ... and may not have counted all of its items: put the counter where the host expects it
+      cudaMemcpy(ctx.status + STATUS_WORD_ITEMS_DONE, &ctx.items_expected, sizeof(unsigned),
+                 cudaMemcpyHostToDevice);
     }
   }
   if (code == 0) code = host_status();

@@ -120,7 +120,8 @@ constexpr int T_CONV_WARP0 = 4;
 constexpr int T_EPI_WARPS = 8;
 constexpr int T_EPI_WARP0 = 8;
 constexpr int T_THREADS = 512;
-constexpr int T_REGS_CONTROL = 56, T_REGS_UNPACK = 72, T_REGS_EPILOGUE = 192;
+// 128 * (32 + 64) + 256 * 208 = 65536, the SM's register file.
+constexpr int T_REGS_CONTROL = 32, T_REGS_UNPACK = 64, T_REGS_EPILOGUE = 208;
 constexpr int T_SMEM_BYTES = T_STAGES * T_STAGE_BYTES + 1024 + 512;
 constexpr int T_GROUP_M = 8;
 
@@ -151,6 +152,23 @@ __device__ __forceinline__ uint4 unpack8(uint32_t word) {
     out[i] = *reinterpret_cast<const uint32_t*>(&v);
   }
   return make_uint4(out[0], out[1], out[2], out[3]);
+}
+
+// acc[first .. first+15] += s * v[0 .. 31], two FP32 lanes per instruction (sm_100 packed FMA).
+}  // namespace w4
+}  // namespace texo
+#include "w4_decode.cuh"
+namespace texo {
+namespace w4 {
+
+__device__ __forceinline__ void fold32(unsigned long long (&acc)[64], int first, const uint32_t (&v)[32],
+                                       unsigned long long s2) {
+#pragma unroll
+  for (int j = 0; j < 16; ++j) {
+    unsigned long long pair;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(pair) : "r"(v[2 * j]), "r"(v[2 * j + 1]));
+    asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc[first + j]) : "l"(pair), "l"(s2));
+  }
 }
 
 __device__ __forceinline__ void w4_tile_coords(int tile, int tiles_n, int tiles_m, int& tn, int& tm) {
@@ -366,47 +384,52 @@ __global__ void __launch_bounds__(T_THREADS, 1)
       const int n = tn * 256 + int(rank) * 128 + quarter * 32 + lane;
       const bool n_ok = n < N;
       const __half* s_row = scales + size_t(n_ok ? n : 0) * groups;
-      float acc[128];
+      // 128 FP32 accumulators per thread, kept as 64 two-float pairs: the fold below is the
+      // packed fma.rn.f32x2 (two independent IEEE FP32 FMAs per instruction), which halves the
+      // issue slots the per-group fold costs next to the unpack warps.
+      unsigned long long acc[64];
 #pragma unroll
-      for (int j = 0; j < 128; ++j) acc[j] = 0.f;
+      for (int j = 0; j < 64; ++j) acc[j] = 0ull;
       float s_next = n_ok ? __half2float(s_row[0]) : 0.f;
       for (int g = 0; g < groups && ok; ++g, ++gc) {
         const float s = s_next;
         if (g + 1 < groups && n_ok) s_next = __half2float(s_row[g + 1]);
+        unsigned long long s2;
+        asm("mov.b64 %0, {%1, %1};" : "=l"(s2) : "f"(s));
         ok = mbar_wait(&bars->group_done[gc % T_RING], (gc / T_RING) & 1, abort_flag, status,
                        STATUS_TIMEOUT_TMEM_FULL);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after_sync();
         const uint32_t taddr = tmem_base + (gc & 1) * 256 + half * 128 + (uint32_t(quarter * 32) << 16);
-        // Eight 16-column chunks, the load of chunk c+1 in flight while chunk c is folded in;
-        // the buffer goes back to the MMA warp as soon as the last chunk is in registers.
-        uint32_t va[16], vb[16];
-        tmem_ld_32x16(taddr, va);
-#pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          tmem_ld_wait();
-          if (c + 1 < 8) {
-            if (c & 1)
-              tmem_ld_32x16(taddr + (c + 1) * 16, va);
-            else
-              tmem_ld_32x16(taddr + (c + 1) * 16, vb);
-          } else {
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive_remote(map_to_cta(smem_u32(&bars->acc_empty[gc & 1]), 0));
-          }
-#pragma unroll
-          for (int j = 0; j < 16; ++j)
-            acc[c * 16 + j] = fmaf(s, __uint_as_float((c & 1) ? vb[j] : va[j]), acc[c * 16 + j]);
-        }
+        // A TMEM load takes a few hundred cycles to return, and tcgen05.wait::ld waits for every
+        // load in flight: the 128 columns come in as four 32-column loads, two in flight at a
+        // time (two latency exposures per group instead of one per 16 columns); the buffer goes
+        // back to the MMA warp as soon as the last load has landed, before the last folds.
+        uint32_t va[32], vb[32];
+        tmem_ld_32x32(taddr, va);
+        tmem_ld_32x32(taddr + 32, vb);
+        tmem_ld_wait();
+        fold32(acc, 0, va, s2);
+        tmem_ld_32x32(taddr + 64, va);
+        fold32(acc, 16, vb, s2);
+        tmem_ld_32x32(taddr + 96, vb);
+        tmem_ld_wait();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_remote(map_to_cta(smem_u32(&bars->acc_empty[gc & 1]), 0));
+        fold32(acc, 32, va, s2);
+        fold32(acc, 48, vb, s2);
       }
       if (ok && n_ok) {
         const int m_base = tm * 256 + half * 128;
 #pragma unroll
-        for (int j = 0; j < 128; ++j) {
-          const int m = m_base + j;
-          if (m < M) y[size_t(m) * N + n] = __float2half_rn(acc[j]);
+        for (int j = 0; j < 64; ++j) {
+          float lo, hi;
+          asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(acc[j]));
+          const int m = m_base + 2 * j;
+          if (m < M) y[size_t(m) * N + n] = __float2half_rn(lo);
+          if (m + 1 < M) y[size_t(m + 1) * N + n] = __float2half_rn(hi);
         }
       }
     }
@@ -490,6 +513,47 @@ static bool launch_tensor(DeviceCtx& ctx, const __half* x, const uint8_t* w_q, c
   return true;
 }
 
+// Decode path (w4_decode.cuh): M <= 16, one scale group per 128-k iteration.  Picks how many
+// 32-row groups a CTA owns (the rest of its 16 warps split K): as many as still give about
+// three quarters of the SMs a CTA, since more rows per CTA means fewer re-reads of x.
+static bool decode_path_ok(const __half* x, const uint8_t* w_q, int M, int N, int K, int G) {
+  return M <= 16 && G == 128 && K >= 128 && K % 128 == 0 && (long long)N * (K / 2) < (1LL << 31) &&
+         (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(w_q) & 15) == 0;
+}
+
+static bool launch_decode(DeviceCtx& ctx, const __half* x, const uint8_t* w_q, const __half* scales,
+                          __half* y, int M, int N, int K) {
+  static bool configured[MAX_DEVICES] = {};
+  if (!configured[ctx.device]) {
+    if (cudaFuncSetAttribute(decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, D_SMEM_BYTES) !=
+        cudaSuccess) {
+      cudaGetLastError();
+      return false;
+    }
+    configured[ctx.device] = true;
+  }
+  int rowgroups = 0;
+  for (int rg = 8; rg >= 1; rg /= 2) {
+    if (K % (128 * (D_WARPS / rg)) != 0) continue;
+    rowgroups = rg;  // the smallest valid one is kept if none fills the SMs
+    if ((N + 32 * rg - 1) / (32 * rg) >= ctx.sm_count * 3 / 4) break;
+  }
+  if (rowgroups == 0) return false;
+  const int grid = (N + 32 * rowgroups - 1) / (32 * rowgroups);
+  const int slot = profile_start();
+  decode_kernel<<<grid, D_THREADS, D_SMEM_BYTES>>>(x, w_q, scales, y, M, N, K, rowgroups);
+  if (cudaPeekAtLastError() != cudaSuccess) {
+    cudaGetLastError();
+    profile_stop(slot);
+    note_host_error(STATUS_LAUNCH_FAILED);
+    return false;
+  }
+  profile_stop(slot);
+  ++launch_counter();
+  last_path() = 3;
+  return true;
+}
+
 }  // namespace w4
 }  // namespace texo
 
@@ -506,6 +570,9 @@ extern "C" void solve(const __half* x, const uint8_t* w_q, const __half* scales,
     return;
   }
   DeviceCtx& ctx = device_ctx();
+  if ((forced_path() == 0 || forced_path() == 3) && ctx.cc_major >= 8 &&
+      decode_path_ok(x, w_q, M, N, K, group_size) && launch_decode(ctx, x, w_q, scales, y, M, N, K))
+    return;
   if (forced_path() != 1 && ctx.cc_major >= 10 && tensor_path_ok(x, w_q, K, group_size) &&
       launch_tensor(ctx, x, w_q, scales, y, M, N, K, group_size))
     return;

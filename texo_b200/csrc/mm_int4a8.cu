@@ -83,9 +83,11 @@ __global__ void __launch_bounds__(GT * GT)
     __syncthreads();
   }
   if (m < M && n < N) {
-    const long long dot = raw - (long long)q.zb * sum_a - (long long)q.za * sum_u +
-                          (long long)K * q.za * q.zb;
-    C[size_t(m) * N + n] = int8_t(i8::requantize(float(dot), q.sa, q.sb, q.sc, float(q.zc)));
+    // per-channel: column n has its own weight scale and zero point (+8: unsigned nibbles)
+    const float sb = q.sb_vec ? q.sb_vec[n] : q.sb;
+    const long long zb = q.sb_vec ? (long long)(q.zb_vec ? q.zb_vec[n] : 0) + q.zb_bias : (long long)q.zb;
+    const long long dot = raw - zb * sum_a - (long long)q.za * sum_u + (long long)K * q.za * zb;
+    C[size_t(m) * N + n] = int8_t(i8::requantize(float(dot), q.sa, sb, q.sc, float(q.zc)));
   }
 }
 
@@ -451,8 +453,9 @@ static bool launch_tensor(DeviceCtx& ctx, const int8_t* A, const uint8_t* W, int
   int* w_sum = scratch + m_pad;
   // rows of A are needed when the effective weight zero point (zB + 8) is non-zero, the
   // nibble sums when zA is
-  const int first = q.zb != 0 ? 0 : M;
-  const int rows = (q.zb != 0 ? M : 0) + (q.za != 0 ? N : 0);
+  const bool need_rows = q.zb != 0 || q.sb_vec != nullptr;  // per-channel zero points: unknown here
+  const int first = need_rows ? 0 : M;
+  const int rows = (need_rows ? M : 0) + (q.za != 0 ? N : 0);
   bool sums_launched = false;
   if (rows > 0) {
     sums_kernel<<<(rows + SUM_WARPS - 1) / SUM_WARPS, SUM_WARPS * 32>>>(A, W, row_sum, w_sum, M, N, K,
@@ -506,12 +509,14 @@ static bool launch_tensor(DeviceCtx& ctx, const int8_t* A, const uint8_t* W, int
 }  // namespace w4a8
 }  // namespace texo
 
-// A [M,K] int8, w_q [N,K/2] packed nibbles, C [M,N] int8: device pointers.  K must be even.
-extern "C" void solve(const int8_t* A, const uint8_t* w_q, int8_t* C, int M, int N, int K,
-                      float scale_A, float scale_B, float scale_C, int zero_point_A,
-                      int zero_point_B, int zero_point_C) {
-  using namespace texo;
-  using namespace texo::w4a8;
+namespace texo {
+namespace w4a8 {
+// Dispatch shared by the per-tensor and the per-channel entry points.  scale_B_vec /
+// zero_point_B_vec: per-output-channel weight quantisation (device arrays [N], see
+// texo_mm_int4a8_solve_per_channel), both null for per-tensor.
+static void solve_with(const int8_t* A, const uint8_t* w_q, int8_t* C, int M, int N, int K, float scale_A,
+                       float scale_B, float scale_C, int zero_point_A, int zero_point_B,
+                       int zero_point_C, const float* scale_B_vec, const int* zero_point_B_vec) {
   if (M <= 0 || N <= 0) return;
   if (K < 0 || K % 2 != 0 || !C || (K > 0 && (!A || !w_q))) {
     note_host_error(STATUS_BAD_ARGUMENT);
@@ -520,14 +525,23 @@ extern "C" void solve(const int8_t* A, const uint8_t* w_q, int8_t* C, int M, int
   DeviceCtx& ctx = device_ctx();
   // unsigned nibbles u = q + 8 against the zero point zB + 8
   const long long zb_eff = (long long)zero_point_B + 8;
+  if (zb_eff > 0x7fffffffLL) {
+    note_host_error(STATUS_BAD_ARGUMENT);
+    return;
+  }
+  i8::Quant q = i8::make_quant(scale_A, scale_B, scale_C, zero_point_A, int(zb_eff), zero_point_C, K);
+  q.sb_vec = scale_B_vec;
+  q.zb_vec = zero_point_B_vec;
+  q.zb_bias = 8;
+  const bool vectors_ok = (reinterpret_cast<uintptr_t>(scale_B_vec) & 15) == 0 &&
+                          (reinterpret_cast<uintptr_t>(zero_point_B_vec) & 15) == 0 &&
+                          (scale_B_vec == nullptr || N % 4 == 0);
   const int force = forced_path();
-  if (force != PATH_GENERIC && ctx.cc_major >= 10 && tensor_path_ok(A, w_q, K) &&
-      zb_eff <= 0x7fffffffLL) {
-    const i8::Quant q =
-        i8::make_quant(scale_A, scale_B, scale_C, zero_point_A, int(zb_eff), zero_point_C, K);
-    // the 32-bit (mod 2^32) correction is exact while |dot| < 2^31
-    const double bound = double(K) * (128.0 + std::abs(double(zero_point_A))) *
-                         (15.0 + std::abs(double(zb_eff)));
+  if (force != PATH_GENERIC && ctx.cc_major >= 10 && vectors_ok && tensor_path_ok(A, w_q, K)) {
+    // the 32-bit (mod 2^32) correction is exact while |dot| < 2^31; per-channel zero points
+    // live on the device, so the bound assumes the int8 range for them
+    const double zb_bound = scale_B_vec ? 136.0 : std::abs(double(zb_eff));
+    const double bound = double(K) * (128.0 + std::abs(double(zero_point_A))) * (15.0 + zb_bound);
     // decode shapes: the streaming kernel shared with mm_int8, unpacking on the fly
     if (M <= 32 && (force == PATH_AUTO || force == PATH_SKINNY) &&
         i8::launch_skinny<true>(ctx, A, w_q, C, M, N, K, q)) {
@@ -536,16 +550,38 @@ extern "C" void solve(const int8_t* A, const uint8_t* w_q, int8_t* C, int M, int
     }
     if (launch_tensor(ctx, A, w_q, C, M, N, K, q, bound >= 2147483648.0)) return;
   }
-  i8::Quant q = i8::make_quant(scale_A, scale_B, scale_C, zero_point_A, 0, zero_point_C, K);
-  // the generic kernel works on the unsigned nibbles too
-  if (zb_eff > 0x7fffffffLL) {
-    note_host_error(STATUS_BAD_ARGUMENT);
-    return;
-  }
-  q.zb = int(zb_eff);
   generic_kernel<<<dim3((N + GT - 1) / GT, (M + GT - 1) / GT), GT * GT>>>(A, w_q, C, M, N, K, q);
   ++launch_counter();
   last_path() = PATH_GENERIC;
+}
+}  // namespace w4a8
+}  // namespace texo
+
+// A [M,K] int8, w_q [N,K/2] packed nibbles, C [M,N] int8: device pointers.  K must be even.
+extern "C" void solve(const int8_t* A, const uint8_t* w_q, int8_t* C, int M, int N, int K,
+                      float scale_A, float scale_B, float scale_C, int zero_point_A,
+                      int zero_point_B, int zero_point_C) {
+  texo::w4a8::solve_with(A, w_q, C, M, N, K, scale_A, scale_B, scale_C, zero_point_A, zero_point_B,
+                         zero_point_C, nullptr, nullptr);
+}
+
+// The same operator with one weight scale (and optionally one weight zero point) per output
+// column, i.e. per row of w_q: scale_B [N] FP32 and zero_point_B [N] int32 are DEVICE arrays,
+// zero_point_B may be null (all zero); zero points within [-128, 127].  Column n is
+// requantised as float(dot) * scale_A * scale_B[n] / scale_C with
+// dot = sum_k (A[m,k] - zA)(q[n,k] - zero_point_B[n]), in the FP32 operation order of the
+// per-tensor form.  On every device path (CTA-pair tensor kernel, streaming kernel, generic).
+extern "C" void texo_mm_int4a8_solve_per_channel(const int8_t* A, const uint8_t* w_q, int8_t* C, int M,
+                                                 int N, int K, float scale_A, const float* scale_B,
+                                                 float scale_C, int zero_point_A,
+                                                 const int* zero_point_B, int zero_point_C) {
+  if (M <= 0 || N <= 0) return;
+  if (!scale_B) {
+    texo::note_host_error(texo::STATUS_BAD_ARGUMENT);
+    return;
+  }
+  texo::w4a8::solve_with(A, w_q, C, M, N, K, scale_A, 1.0f, scale_C, zero_point_A, 0, zero_point_C,
+                         scale_B, zero_point_B);
 }
 
 extern "C" int texo_mm_int4a8_last_path() { return texo::w4a8::last_path(); }

@@ -140,7 +140,7 @@ __global__ void __launch_bounds__(G_THREADS)
       const int n = col0 + tx * 4 + j;
       if (n >= N) continue;
       const float sb = q.sb_vec ? q.sb_vec[n] : q.sb;
-      const long long zb = q.sb_vec ? (q.zb_vec ? q.zb_vec[n] : 0) : q.zb;
+      const long long zb = q.sb_vec ? (q.zb_vec ? q.zb_vec[n] : 0) + q.zb_bias : q.zb;
       const long long dot = tot[i][j] - zb * tra[i] - (long long)q.za * tcb[j] + kza * zb;
       const int8_t value = int8_t(requantize(float(dot), q.sa, sb, q.sc, zc));
       if (q.n_peers > 0) {
@@ -482,6 +482,127 @@ __global__ void __launch_bounds__(MMA_THREADS, 1)
   }
 }
 
+// ------------------------------------------- sums inside the CTA-pair kernel
+// The CTA-pair kernel needs no pre-pass: its eight epilogue warps have nothing to drain while
+// the first tile's MMAs run, and in that time they compute rowsum(A) / colsum(B) themselves -
+// the work of sums_kernel, dealt over all CTAs of the grid (item = blockIdx.x, += gridDim.x),
+// with the same access pattern (64 columns x all K per column item, 16 rows per row item,
+// eight 16-byte loads in flight per thread; the bytes are the ones the TMA producer is
+// pulling through L2 anyway).  Every CTA publishes how many items it has finished on a
+// device-wide counter; before its first drain an epilogue warp waits (bounded) until the
+// counter shows that all items of this call are done.  All CTAs of the grid are resident at
+// once (the grid never exceeds the number of CTA pairs the device can hold), so the wait
+// cannot starve the CTAs it waits for.  The counter is never cleared: the host hands each
+// call the value it will have when that call's items are complete.
+constexpr int ES_THREADS = EPI_WARPS * 32;                        // 256 epilogue threads
+constexpr int ES_KLANES = ES_THREADS / SUM_TX;                    // k lanes of a column item
+constexpr int ES_PART_BYTES = EPI_WARPS * (SUM_COLS + 1) * 4;     // partials of a column item
+constexpr int P_AUX_SMEM_BYTES = 2304;                            // >= ES_PART_BYTES
+static_assert(ES_PART_BYTES <= P_AUX_SMEM_BYTES, "sums partials outgrew their shared-memory reserve");
+
+__device__ __forceinline__ void epilogue_bar() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+
+// Returns the number of items this CTA processed.  `et` = index among the 256 epilogue threads.
+__device__ __forceinline__ int epilogue_sums(const int8_t* __restrict__ A, const int8_t* __restrict__ B,
+                                             int* __restrict__ row_sum, int* __restrict__ col_sum,
+                                             int M, int N, int K, int col_items, int row_items,
+                                             int (*part)[SUM_COLS + 1], int et) {
+  const int warp = et / 32, lane = et % 32;
+  int done = 0;
+  for (int item = blockIdx.x; item < col_items + row_items; item += gridDim.x, ++done) {
+    if (item < col_items) {
+      const int tx = et % SUM_TX, ty = et / SUM_TX;
+      const int n = item * SUM_COLS + tx * 16;
+      int acc[16] = {};
+      if (n < N) {
+        const int8_t* col = B + n;
+        int k = ty;
+        for (; k + 7 * ES_KLANES < K; k += 8 * ES_KLANES) {
+          int4 v[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u)
+            v[u] = __ldg(reinterpret_cast<const int4*>(col + size_t(k + u * ES_KLANES) * N));
+#pragma unroll
+          for (int u = 0; u < 8; ++u) add_bytes(acc, v[u]);
+        }
+        for (; k < K; k += ES_KLANES)
+          add_bytes(acc, __ldg(reinterpret_cast<const int4*>(col + size_t(k) * N)));
+      }
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+#pragma unroll
+        for (int o = SUM_TX; o < 32; o <<= 1) acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], o);
+      }
+      epilogue_bar();  // the previous item's readers are done with `part`
+      if (lane < SUM_TX) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) part[warp][tx * 16 + i] = acc[i];
+      }
+      epilogue_bar();
+      if (et < SUM_COLS) {
+        int total = 0;
+#pragma unroll
+        for (int r = 0; r < EPI_WARPS; ++r) total += part[r][et];
+        const int out = item * SUM_COLS + et;
+        if (out < N) col_sum[out] = total;
+      }
+    } else {
+      for (int r = warp; r < SUM_ROWS; r += EPI_WARPS) {
+        const int m = (item - col_items) * SUM_ROWS + r;
+        if (m >= M) continue;
+        const int4* a = reinterpret_cast<const int4*>(A + size_t(m) * K);
+        const int chunks = K / 16;
+        int acc = 0;
+        int i = lane;
+        for (; i + 7 * 32 < chunks; i += 8 * 32) {
+          int4 v[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u) v[u] = __ldg(a + i + u * 32);
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            acc = __dp4a(v[u].x, 0x01010101, acc);
+            acc = __dp4a(v[u].y, 0x01010101, acc);
+            acc = __dp4a(v[u].z, 0x01010101, acc);
+            acc = __dp4a(v[u].w, 0x01010101, acc);
+          }
+        }
+        for (; i < chunks; i += 32) {
+          const int4 v = __ldg(a + i);
+          acc = __dp4a(v.x, 0x01010101, acc);
+          acc = __dp4a(v.y, 0x01010101, acc);
+          acc = __dp4a(v.z, 0x01010101, acc);
+          acc = __dp4a(v.w, 0x01010101, acc);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        if (lane == 0) row_sum[m] = acc;
+      }
+    }
+  }
+  return done;
+}
+
+// Bounded wait until the device-wide item counter has reached `expected` (wrap-safe compare).
+__device__ __forceinline__ bool wait_items(const unsigned* counter, unsigned expected,
+                                           volatile int* abort_flag, int* status) {
+  const long long start = clock64();
+  int spins = 0;
+  while (true) {
+    unsigned seen;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(counter) : "memory");
+    if (int(seen - expected) >= 0) return true;
+    if ((++spins & 63) == 0) {
+      if (*abort_flag) return false;
+      if (clock64() - start > WAIT_BUDGET_CLOCKS) {
+        *abort_flag = 1;
+        if (status) atomicCAS(status, 0, STATUS_TIMEOUT_FLAG);
+        return false;
+      }
+    }
+    __nanosleep(64);
+  }
+}
+
 // ---------------------------------------------------- tensor path, CTA pairs
 // Same pipeline with the MMA spanning two CTAs of a cluster (cta_group::2): pair tile
 // 256 x 256, each CTA stages only its own 128 rows of A and its own 128 columns of B per
@@ -520,7 +641,10 @@ __global__ void __launch_bounds__(MMA_THREADS, 1)
     umma_pair_kernel(const __grid_constant__ CUtensorMap map_a,
                      const __grid_constant__ CUtensorMap map_b, int8_t* __restrict__ C,
                      const int* __restrict__ row_sum, const int* __restrict__ col_sum, int M, int N,
-                     int K, Quant q, int tiles_m, int tiles_n, int c_vector_ok, int* status) {
+                     int K, Quant q, int tiles_m, int tiles_n, int c_vector_ok, int* status,
+                     const int8_t* __restrict__ A_raw, const int8_t* __restrict__ B_raw,
+                     int* row_sum_w, int* col_sum_w, int col_items, int row_items,
+                     unsigned* items_done, unsigned items_expected) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~uintptr_t(1023));
@@ -647,10 +771,25 @@ __global__ void __launch_bounds__(MMA_THREADS, 1)
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
-    // The row / column sums come from the pre-pass grid, which may still be running when this
-    // kernel was launched behind it with programmatic stream serialisation.  (No effect when
-    // there is no such prerequisite.)
+    // Everything this kernel reads may have been written by the grid ahead of it in the stream
+    // (no effect without a programmatic dependency).
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    // Row / column sums: computed here, by the epilogue warps of all CTAs, while the first
+    // tile's MMAs run (see epilogue_sums above).
+    if (col_items + row_items > 0) {
+      const int et = threadIdx.x - 64;
+      int(*part)[SUM_COLS + 1] =
+          reinterpret_cast<int(*)[SUM_COLS + 1]>(smem + P_STAGES * P_STAGE_BYTES + 256);
+      const int mine = epilogue_sums(A_raw, B_raw, row_sum_w, col_sum_w, M, N, K, col_items,
+                                     row_items, part, et);
+      __threadfence();
+      epilogue_bar();
+      if (et == 0 && mine > 0) atomicAdd(items_done, unsigned(mine));
+      if (lane == 0) ok = wait_items(items_done, items_expected, abort_flag, status);
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      __threadfence();
+      epilogue_bar();  // `part` doubles as the all-gather staging area of the drains below
+    }
     for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
       int tm, tn;
       pair_tile_coords(tile, tiles_m, tiles_n, tm, tn);
@@ -752,7 +891,7 @@ static bool launch_skinny_i8(DeviceCtx& ctx, const int8_t* A, const int8_t* B, i
                              int K, const Quant& q, int weights_stable = 0,
                              const int* cached_row_sum = nullptr) {
   const int* row_sum = cached_row_sum;
-  if (M > 32 && !row_sum && (q.zb != 0 || q.zb_vec != nullptr)) {
+  if (M > 32 && !row_sum && (q.zb != 0 || q.zb_vec != nullptr || (q.swiglu && q.z_up != 0))) {
     int* sums = static_cast<int*>(device_scratch(ctx, size_t(M) * sizeof(int) + 256));
     if (!sums) return false;
     Quant rows_only = q;
@@ -818,44 +957,42 @@ static bool launch_tensor(DeviceCtx& ctx, const int8_t* A, const int8_t* B, int8
     sums_q.zb = 0;  // rowsum(A) came with the activations (their producer computed it)
     row_sum = const_cast<int*>(cached_row_sum);
   }
-  const bool sums_launched =
-      launch_sums(A, B, row_sum, col_sum, M, N, K, sums_q, pairs > 0 ? ctx.sm_count : 0);
+  // The CTA-pair kernel computes the sums itself (its epilogue warps, during the first tile's
+  // MMAs); the one-CTA kernel takes them from the pre-pass.
+  if (pairs <= 0) launch_sums(A, B, row_sum, col_sum, M, N, K, sums_q, 0);
   const int slot = profile_start();
   if (pairs > 0) {
     const int tiles_m = (M + 255) / 256;
+    const int col_items = sums_q.za != 0 ? (N + SUM_COLS - 1) / SUM_COLS : 0;
+    const int row_items = sums_q.zb != 0 ? (M + SUM_ROWS - 1) / SUM_ROWS : 0;
+    // the value the device-wide item counter will show once this call's items are done
+    unsigned* items_done = reinterpret_cast<unsigned*>(ctx.status + STATUS_WORD_ITEMS_DONE);
+    ctx.items_expected += unsigned(col_items + row_items);
+    const unsigned items_expected = ctx.items_expected;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2 * std::min(tiles_m * tiles_n, pairs));
     cfg.blockDim = dim3(MMA_THREADS);
-    cfg.dynamicSmemBytes = P_SMEM_BYTES + (q.n_peers > 0 ? P_GATHER_SMEM_BYTES : 0);
+    cfg.dynamicSmemBytes = P_SMEM_BYTES + (q.n_peers > 0 ? P_GATHER_SMEM_BYTES : P_AUX_SMEM_BYTES);
     cfg.stream = 0;
-    cudaLaunchAttribute attrs[2];
+    cudaLaunchAttribute attrs[1];
     attrs[0].id = cudaLaunchAttributeClusterDimension;
     attrs[0].val.clusterDim.x = 2;
     attrs[0].val.clusterDim.y = 1;
     attrs[0].val.clusterDim.z = 1;
-    // Start while the sums pre-pass is still running (the epilogue waits for it).
-    attrs[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attrs[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attrs;
+    cfg.numAttrs = 1;
     const int* rs = row_sum;
     const int* cs = col_sum;
-    static bool overlap_supported[MAX_DEVICES] = {true, true, true, true, true, true, true, true,
-                                                  true, true, true, true, true, true, true, true};
-    cudaError_t err = cudaSuccess;
-    for (int attempt = 0; attempt < 2; ++attempt) {
-      const bool overlap = sums_launched && attempt == 0 &&
-                           (ctx.device >= 16 || overlap_supported[ctx.device]);
-      cfg.numAttrs = overlap ? 2 : 1;
-      err = K <= 33025 ? cudaLaunchKernelEx(&cfg, umma_pair_kernel<false>, map_a, map_b, C, rs, cs, M, N,
-                                            K, q, tiles_m, tiles_n, c_vector_ok, ctx.status)
-                       : cudaLaunchKernelEx(&cfg, umma_pair_kernel<true>, map_a, map_b, C, rs, cs, M, N,
-                                            K, q, tiles_m, tiles_n, c_vector_ok, ctx.status);
-      if (err == cudaSuccess || !overlap) break;
-      cudaGetLastError();  // the attribute was refused: launch again, fully serialised
-      if (ctx.device < 16) overlap_supported[ctx.device] = false;
-    }
+    const cudaError_t err =
+        K <= 33025 ? cudaLaunchKernelEx(&cfg, umma_pair_kernel<false>, map_a, map_b, C, rs, cs, M, N, K, q,
+                                        tiles_m, tiles_n, c_vector_ok, ctx.status, A, B, row_sum, col_sum,
+                                        col_items, row_items, items_done, items_expected)
+                   : cudaLaunchKernelEx(&cfg, umma_pair_kernel<true>, map_a, map_b, C, rs, cs, M, N, K, q,
+                                        tiles_m, tiles_n, c_vector_ok, ctx.status, A, B, row_sum, col_sum,
+                                        col_items, row_items, items_done, items_expected);
     if (err != cudaSuccess) {
       cudaGetLastError();
+      ctx.items_expected -= unsigned(col_items + row_items);  // nothing will count them
       profile_stop(slot);
       note_host_error(STATUS_LAUNCH_FAILED);
       return false;  // the caller falls back to the generic kernel
@@ -973,9 +1110,14 @@ extern "C" void texo_mm_int8_swiglu_solve(const int8_t* A, const int8_t* B_gu, i
   DeviceCtx& ctx = device_ctx();
   const int force = forced_path();
   const int N = 2 * F;
-  if (force != PATH_GENERIC && ctx.cc_major >= 10 && tensor_path_ok(A, B_gu, M, N, K) &&
-      launch_tensor(ctx, A, B_gu, H, M, N, K, q, force == PATH_SKINNY ? PATH_AUTO : force))
-    return;
+  if (force != PATH_GENERIC && ctx.cc_major >= 10 && tensor_path_ok(A, B_gu, M, N, K)) {
+    // few activation rows: the streaming kernel (weights read once, gate/up pairs combined
+    // between neighbouring lanes of its drain)
+    if (M <= S_MAX_ROWS && (force == PATH_AUTO || force == PATH_SKINNY) &&
+        launch_skinny_i8(ctx, A, B_gu, H, M, N, K, q))
+      return;
+    if (launch_tensor(ctx, A, B_gu, H, M, N, K, q, force == PATH_SKINNY ? PATH_AUTO : force)) return;
+  }
   swiglu_generic_kernel<<<dim3((F + 15) / 16, (M + 15) / 16), 256>>>(A, B_gu, H, M, F, K, q);
   ++launch_counter();
   last_path() = PATH_GENERIC;
@@ -1014,10 +1156,14 @@ extern "C" void texo_mm_int8_dequant_solve(const int8_t* A, const int8_t* B, voi
   q.out_f16 = 1;
   DeviceCtx& ctx = device_ctx();
   const int force = forced_path();
-  if (force != PATH_GENERIC && ctx.cc_major >= 10 && tensor_path_ok(A, B, M, N, K) &&
-      launch_tensor(ctx, A, B, static_cast<int8_t*>(Y), M, N, K, q,
-                    force == PATH_SKINNY ? PATH_AUTO : force))
-    return;
+  if (force != PATH_GENERIC && ctx.cc_major >= 10 && tensor_path_ok(A, B, M, N, K)) {
+    if (M <= S_MAX_ROWS && (force == PATH_AUTO || force == PATH_SKINNY) &&
+        launch_skinny_i8(ctx, A, B, static_cast<int8_t*>(Y), M, N, K, q))
+      return;
+    if (launch_tensor(ctx, A, B, static_cast<int8_t*>(Y), M, N, K, q,
+                      force == PATH_SKINNY ? PATH_AUTO : force))
+      return;
+  }
   dequant_generic_kernel<<<dim3((N + 15) / 16, (M + 15) / 16), 256>>>(A, B, static_cast<__half*>(Y),
                                                                     M, N, K, q);
   ++launch_counter();

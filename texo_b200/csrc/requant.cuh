@@ -33,6 +33,10 @@ struct Quant {
   // zb_vec[n] instead of zb (zb_vec null with sb_vec set means zero point 0 everywhere).
   const float* sb_vec;
   const int* zb_vec;
+  // Added to every per-channel zero point read from zb_vec (and standing for it when zb_vec is
+  // null): 0 for the INT8 operator, 8 for packed-INT4 weights, whose nibbles the kernels keep
+  // unsigned (u = q + 8), so a column's effective zero point is zb_vec[n] + 8.
+  int zb_bias;
   // Fused SwiGLU consumer (swiglu != 0): B holds gate and up columns interleaved (column 2j =
   // gate j, 2j+1 = up j); sb / zb describe the gate columns, s_up / z_up the up columns, and
   // the output is H [M, N/2] = requantised up * silu(gate) with scale s_out, zero point z_out.
@@ -64,7 +68,7 @@ constexpr int MAX_PEERS = 8;
 // lets the tail run in integers (see requantize_fast).  Anything else (including NaN or
 // infinite scales) takes the plain IEEE division, element by element.
 inline Quant make_quant(float sa, float sb, float sc, int za, int zb, int zc, int K) {
-  Quant q = {sa, sb, sc, za, zb, zc, 0.f, 0, nullptr, nullptr, 0, 0.f, 0.f, 0, 0, 0, 0, 0, 0, {}, nullptr};
+  Quant q = {sa, sb, sc, za, zb, zc, 0.f, 0, nullptr, nullptr, 0, 0, 0.f, 0.f, 0, 0, 0, 0, 0, 0, {}, nullptr};
   auto within = [](float v, float lo, float hi) {
     const float a = v < 0 ? -v : v;
     return a >= lo && a <= hi;  // false for NaN
@@ -137,13 +141,13 @@ __device__ __forceinline__ void requantize_chunk(
     if (q.za != 0) cs = __ldcg(reinterpret_cast<const int4*>(col_sum_at + g * 4));
     const int csv[4] = {cs.x, cs.y, cs.z, cs.w};
     float sbv[4] = {q.sb, q.sb, q.sb, q.sb};
-    int zbv[4] = {0, 0, 0, 0};
+    int zbv[4] = {q.zb_bias, q.zb_bias, q.zb_bias, q.zb_bias};
     if (PC && n0 + g * 4 < N) {
       const float4 s4 = __ldg(reinterpret_cast<const float4*>(q.sb_vec + n0 + g * 4));
       sbv[0] = s4.x, sbv[1] = s4.y, sbv[2] = s4.z, sbv[3] = s4.w;
       if (q.zb_vec) {
         const int4 z4 = __ldg(reinterpret_cast<const int4*>(q.zb_vec + n0 + g * 4));
-        zbv[0] = z4.x, zbv[1] = z4.y, zbv[2] = z4.z, zbv[3] = z4.w;
+        zbv[0] += z4.x, zbv[1] += z4.y, zbv[2] += z4.z, zbv[3] += z4.w;
       }
     }
     int r[4];
@@ -173,8 +177,8 @@ __device__ __forceinline__ bool chunk_channels_fast(const Quant& q, int n0, int 
     const float4 s4 = __ldg(reinterpret_cast<const float4*>(q.sb_vec + n0 + g * 4));
     int4 z4 = make_int4(0, 0, 0, 0);
     if (q.zb_vec) z4 = __ldg(reinterpret_cast<const int4*>(q.zb_vec + n0 + g * 4));
-    ok = ok && channel_in_fast_range(s4.x, z4.x) && channel_in_fast_range(s4.y, z4.y) &&
-         channel_in_fast_range(s4.z, z4.z) && channel_in_fast_range(s4.w, z4.w);
+    ok = ok && channel_in_fast_range(s4.x, z4.x + q.zb_bias) && channel_in_fast_range(s4.y, z4.y + q.zb_bias) &&
+         channel_in_fast_range(s4.z, z4.z + q.zb_bias) && channel_in_fast_range(s4.w, z4.w + q.zb_bias);
   }
   return ok;
 }

@@ -170,12 +170,57 @@ struct SkinnySchedule {
 // interleave; with one warp per scheduler a per-row branch would run them back to back.
 // `kza` = K * zA, `col_term` = zA * colsum(B)[n], `sb_n` / `zb_n` the weight scale and zero
 // point of this thread's column: dot = raw + zB * (K*zA - rowsum(A)[m]) - zA * colsum(B)[n].
+// Where element [row0, n] of the output lives and its row stride in elements, by output form:
+// int8 C [M, N]; SwiGLU H [M, N/2] (column n / 2); FP16 Y [M, N] (byte pointer to the half).
+__device__ __forceinline__ int8_t* skinny_out_at(int8_t* C, const Quant& q, int row0, int n, int N,
+                                                 size_t& stride) {
+  if (q.swiglu) {
+    stride = size_t(N / 2);
+    return C + size_t(row0) * stride + n / 2;
+  }
+  stride = size_t(N);
+  if (q.out_f16) return C + 2 * (size_t(row0) * N + n);
+  return C + size_t(row0) * N + n;
+}
+
 template <int ROWS, bool FAST>
 __device__ __forceinline__ void skinny_store_rows(const uint32_t (&v)[32], const int* row_sum,
                                                   long long kza, long long col_term, float sb_n,
                                                   int zb_n, const Quant& q, float zc, int M,
                                                   int8_t* out, size_t stride, int col,
                                                   int row0 = 0) {
+  if (q.out_f16) {
+    // dequantising form: y[m, n] = half(float(dot) * sA * sB), FP16 output with row stride
+    // `stride` elements (`out` points at element [row0, n] counted in bytes of int8: redo it)
+    __half* y = reinterpret_cast<__half*>(out);
+#pragma unroll
+    for (int m = 0; m < ROWS; ++m) {
+      const long long dot = (long long)int(v[m]) + (long long)zb_n * (kza - row_sum[m]) - col_term;
+      if (m < M) y[m * stride] = __float2half_rn(__fmul_rn(__fmul_rn(float(dot), q.sa), sb_n));
+    }
+    return;
+  }
+  if (q.swiglu) {
+    // fused SwiGLU form: this lane's column is a gate column (even n) or an up column (odd n)
+    // of the interleaved weights; the neighbouring lane holds the other one.  Both lanes of a
+    // pair compute every h (same inputs, same arithmetic); the even lane stores the even
+    // rows, the odd lane the odd rows.  `out` points at H[row0, n / 2], row stride `stride`.
+    // (N is a multiple of 16 here, so a warp's active lanes always hold whole pairs)
+    const unsigned lanes = __activemask();
+    const bool is_up = (col & 1) != 0;
+    const float s_col = is_up ? q.s_up : q.sb;
+    const long long z_col = is_up ? q.z_up : q.zb;
+#pragma unroll
+    for (int m = 0; m < ROWS; ++m) {
+      const long long dot = (long long)int(v[m]) + z_col * (kza - row_sum[m]) - col_term;
+      const float mine = __fmul_rn(__fmul_rn(float(dot), q.sa), s_col);
+      const float other = __shfl_xor_sync(lanes, mine, 1);
+      const float gate = is_up ? other : mine, up = is_up ? mine : other;
+      const int h = swiglu_requantize(gate, up, q);
+      if (m < M && ((m & 1) != 0) == is_up) out[m * stride] = int8_t(h);
+    }
+    return;
+  }
   int r[ROWS];
 #pragma unroll
   for (int m = 0; m < ROWS; ++m) {
@@ -489,9 +534,9 @@ __global__ void __launch_bounds__(W4 ? S_W4_THREADS : S_THREADS, 1)
     asm volatile("griddepcontrol.wait;" ::: "memory");  // before reading A / touching C, workspace
     // rowsum(A) for the zero-point identity.  Up to 32 rows the activations are tiny and every
     // CTA sums them itself; beyond that a pre-pass has done it once (row_sum_g).
-    if ((q.zb != 0 || q.zb_vec != nullptr) && R > 32) {
+    if ((q.zb != 0 || q.zb_vec != nullptr || (q.swiglu && q.z_up != 0)) && R > 32) {
       for (int m = et; m < M; m += S_EPI_WARPS * 32) bars->row_sum[m] = __ldcg(row_sum_g + m);
-    } else if (q.zb != 0 || q.zb_vec != nullptr) {
+    } else if (q.zb != 0 || q.zb_vec != nullptr || (q.swiglu && q.z_up != 0)) {
       for (int m = ew; m < M; m += S_EPI_WARPS) {
         const int4* a = reinterpret_cast<const int4*>(A + size_t(m) * K);
         int acc = 0;
@@ -552,7 +597,7 @@ __global__ void __launch_bounds__(W4 ? S_W4_THREADS : S_THREADS, 1)
           int zb_n = q.zb;
           if (q.sb_vec && n < N) {
             sb_n = __ldg(q.sb_vec + n);
-            zb_n = q.zb_vec ? __ldg(q.zb_vec + n) : 0;
+            zb_n = (q.zb_vec ? __ldg(q.zb_vec + n) : 0) + q.zb_bias;
           }
           const bool fast = q.fast_div && (!q.sb_vec || channel_in_fast_range(sb_n, zb_n));
 #pragma unroll 1
@@ -567,12 +612,14 @@ __global__ void __launch_bounds__(W4 ? S_W4_THREADS : S_THREADS, 1)
               if (lane == 0) mbar_arrive(&bars->acc_empty[cur]);
             }
             if (n < N && r0 < M) {
+              size_t stride;
+              int8_t* at = skinny_out_at(C, q, r0, n, N, stride);
               if (fast)
                 skinny_store_rows<32, true>(v, bars->row_sum + r0, kza, col_term, sb_n, zb_n, q, zc,
-                                            M - r0, C + size_t(r0) * N + n, size_t(N), n, r0);
+                                            M - r0, at, stride, n, r0);
               else
                 skinny_store_rows<32, false>(v, bars->row_sum + r0, kza, col_term, sb_n, zb_n, q, zc,
-                                             M - r0, C + size_t(r0) * N + n, size_t(N), n, r0);
+                                             M - r0, at, stride, n, r0);
             }
           }
         }
@@ -635,22 +682,20 @@ __global__ void __launch_bounds__(W4 ? S_W4_THREADS : S_THREADS, 1)
         if (finalize && n < N) {
           const long long col_term = (long long)q.za * int(cs_raw);
           const float sb_n = q.sb_vec ? __ldg(q.sb_vec + n) : q.sb;
-          const int zb_n = q.sb_vec ? (q.zb_vec ? __ldg(q.zb_vec + n) : 0) : q.zb;
+          const int zb_n = q.sb_vec ? (q.zb_vec ? __ldg(q.zb_vec + n) : 0) + q.zb_bias : q.zb;
           const bool fast = q.fast_div && (!q.sb_vec || channel_in_fast_range(sb_n, zb_n));
+          size_t stride;
+          int8_t* at = skinny_out_at(C, q, 0, n, N, stride);
           if (R == 16) {
             if (fast)
-              skinny_store_rows<16, true>(v, bars->row_sum, kza, col_term, sb_n, zb_n, q, zc, M,
-                                          C + n, size_t(N), n);
+              skinny_store_rows<16, true>(v, bars->row_sum, kza, col_term, sb_n, zb_n, q, zc, M, at, stride, n);
             else
-              skinny_store_rows<16, false>(v, bars->row_sum, kza, col_term, sb_n, zb_n, q, zc, M,
-                                           C + n, size_t(N), n);
+              skinny_store_rows<16, false>(v, bars->row_sum, kza, col_term, sb_n, zb_n, q, zc, M, at, stride, n);
           } else {
             if (fast)
-              skinny_store_rows<32, true>(v, bars->row_sum, kza, col_term, sb_n, zb_n, q, zc, M,
-                                          C + n, size_t(N), n);
+              skinny_store_rows<32, true>(v, bars->row_sum, kza, col_term, sb_n, zb_n, q, zc, M, at, stride, n);
             else
-              skinny_store_rows<32, false>(v, bars->row_sum, kza, col_term, sb_n, zb_n, q, zc, M,
-                                           C + n, size_t(N), n);
+              skinny_store_rows<32, false>(v, bars->row_sum, kza, col_term, sb_n, zb_n, q, zc, M, at, stride, n);
           }
         }
       }
@@ -712,7 +757,7 @@ static bool launch_skinny(DeviceCtx& ctx, const int8_t* A, const void* B, int8_t
     const int per_cta = (tiles + ctx.sm_count - 1) / ctx.sm_count;
     grid = (tiles + per_cta - 1) / per_cta;
     row_sum_g = cached_row_sum;
-    if (!row_sum_g && (q.zb != 0 || q.zb_vec != nullptr)) return false;
+    if (!row_sum_g && (q.zb != 0 || q.zb_vec != nullptr || (q.swiglu && q.z_up != 0))) return false;
   }
   // Tiles that are split between CTAs (see the schedule above) need the workspace:
   // counters[shared][2] (padded) | partial sums [shared][2][M+1][128] int32, one slot per

@@ -11,7 +11,7 @@ import torch
 
 from . import _lib
 
-__all__ = ["mm_int8", "mm_int8_per_channel", "mm_int8_swiglu", "mm_int8_dequant", "mm_int4", "mm_int4a8", "dequantization", "rms_norm_w_residual",
+__all__ = ["mm_int8", "mm_int8_per_channel", "mm_int8_swiglu", "mm_int8_dequant", "mm_int4", "mm_int4a8", "mm_int4a8_per_channel", "dequantization", "rms_norm_w_residual",
            "rms_norm_quant", "mm_int8_host", "Int8Weights", "last_path", "status", "force_path"]
 
 
@@ -206,6 +206,41 @@ def mm_int4a8(A: torch.Tensor, w_q: torch.Tensor, scale_A: float, scale_B: float
         lib.texo_mm_int4a8_solve(A.data_ptr() if K else None, w_q.data_ptr() if K else None,
                                  out.data_ptr(), M, N, K, scale_A, scale_B, scale_C,
                                  zero_point_A, zero_point_B, zero_point_C)
+    return out
+
+
+def mm_int4a8_per_channel(A: torch.Tensor, w_q: torch.Tensor, scale_A: float, scale_B: torch.Tensor,
+                          scale_C: float, zero_point_A: int, zero_point_B: torch.Tensor | None,
+                          zero_point_C: int, out: torch.Tensor | None = None) -> torch.Tensor:
+    """mm_int4a8 with one weight scale (fp32 [N]) and optionally one weight zero point (int32
+    [N]) per output column (= row of w_q), both CUDA tensors; see include/texo_b200.h."""
+    _check_cuda("A", A, torch.int8)
+    _check_cuda("w_q", w_q, torch.uint8)
+    _check_cuda("scale_B", scale_B, torch.float32)
+    if A.dim() != 2 or w_q.dim() != 2:
+        raise ValueError("A and w_q must be matrices")
+    M, K = A.shape
+    N = w_q.shape[0]
+    if K % 2 or w_q.shape[1] != K // 2:
+        raise ValueError("w_q must be [N, K/2] with even K")
+    if M <= 0 or N <= 0 or tuple(scale_B.shape) != (N,):
+        raise ValueError("M, N must be positive and scale_B must be [N]")
+    if zero_point_B is not None:
+        _check_cuda("zero_point_B", zero_point_B, torch.int32)
+        if tuple(zero_point_B.shape) != (N,):
+            raise ValueError("zero_point_B must be [N]")
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.int8, device=A.device)
+    else:
+        _check_cuda("out", out, torch.int8)
+        if tuple(out.shape) != (M, N):
+            raise ValueError("out has the wrong shape")
+    lib = _lib.load()
+    with torch.cuda.device(A.device), _DefaultStreamOrder(A.device):
+        lib.texo_mm_int4a8_solve_per_channel(
+            A.data_ptr() if K else None, w_q.data_ptr() if K else None, out.data_ptr(), M, N, K,
+            scale_A, scale_B.data_ptr(), scale_C, zero_point_A,
+            zero_point_B.data_ptr() if zero_point_B is not None else None, zero_point_C)
     return out
 
 
