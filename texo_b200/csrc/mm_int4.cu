@@ -181,6 +181,22 @@ __device__ __forceinline__ void w4_tile_coords(int tile, int tiles_n, int tiles_
   tm = in_group / group_n;
 }
 
+// -DW4_STALL_PROBE: the first CTA's warps accumulate the clock cycles they spend waiting on
+// each kind of barrier and in their own work, and store them behind the status word
+// (status[16..]) when they finish - a way to see which role bounds the pipeline.
+#ifdef W4_STALL_PROBE
+#define PROBE_DECL long long probe_t0 = 0, probe_wait_a = 0, probe_wait_b = 0, probe_work = 0
+#define PROBE_BEGIN() probe_t0 = clock64()
+#define PROBE_END(var) var += clock64() - probe_t0
+#define PROBE_STORE(slot, value) \
+  if (blockIdx.x == 0 && lane == 0) status[16 + (slot)] = int((value) >> 10)
+#else
+#define PROBE_DECL
+#define PROBE_BEGIN()
+#define PROBE_END(var)
+#define PROBE_STORE(slot, value)
+#endif
+
 __global__ void __launch_bounds__(T_THREADS, 1)
     tensor_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_raw,
                   const __half* __restrict__ scales, __half* __restrict__ y, int M, int N, int K,
@@ -232,6 +248,7 @@ __global__ void __launch_bounds__(T_THREADS, 1)
     int kbg = 0;        // global k-block number of the next load
     int observed = -1;  // highest commit seen
     bool ok = true;
+    PROBE_DECL;
     for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
       int tn, tm;
       w4_tile_coords(tile, tiles_n, tiles_m, tn, tm);
@@ -243,8 +260,10 @@ __global__ void __launch_bounds__(T_THREADS, 1)
             // the commit of the last scale group that touches block kbg - T_STAGES
             const int c = ((kbg - T_STAGES + 1) * T_BK - 1) / G;
             if (c > observed) {
+              PROBE_BEGIN();
               ok = mbar_wait(&bars->group_done[c % T_RING], (c / T_RING) & 1, abort_flag, status,
                              STATUS_TIMEOUT_EMPTY);
+              PROBE_END(probe_wait_a);
               observed = c;
             }
           }
@@ -262,6 +281,7 @@ __global__ void __launch_bounds__(T_THREADS, 1)
         if (++stage == T_STAGES) stage = 0;
       }
     }
+    PROBE_STORE(0, probe_wait_a);  // producer: waiting for a stage to be released
   } else if (warp == 1) {
     // ------------------------------------------- MMA issuer (even CTA only)
     if (rank == 0) {
@@ -271,12 +291,15 @@ __global__ void __launch_bounds__(T_THREADS, 1)
       int step = 0;  // k-step inside the current stage (T_BK / 16 of them)
       int gc = 0;    // global group (= commit) number
       bool ok = true;
+      PROBE_DECL;
       for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
         for (int g = 0; g < groups && ok; ++g, ++gc) {
           const int buf = gc & 1;
           if (lane == 0) {
+            PROBE_BEGIN();
             ok = mbar_wait(&bars->acc_empty[buf], ((gc >> 1) & 1) ^ 1, abort_flag, status,
                            STATUS_TIMEOUT_TMEM_EMPTY);
+            PROBE_END(probe_wait_a);
             tc_fence_after_sync();
           }
           ok = __shfl_sync(0xffffffffu, ok, 0);
@@ -288,7 +311,9 @@ __global__ void __launch_bounds__(T_THREADS, 1)
           if (lane == 0) {
             if (steps_per_group >= 4) {
               for (int kk = 0; kk < steps_per_group / 4 && ok; ++kk) {
+                PROBE_BEGIN();
                 ok = mbar_wait(&bars->ready[stage], phase, abort_flag, status, STATUS_TIMEOUT_FULL);
+                PROBE_END(probe_wait_b);
                 if (ok) {
                   tc_fence_after_sync();
                   const uint32_t sx = smem_u32(smem + stage * T_STAGE_BYTES);
@@ -308,7 +333,9 @@ __global__ void __launch_bounds__(T_THREADS, 1)
             } else {
               // part of a stage: `step` is the first k-step of this group inside the stage
               if (step == 0) {
+                PROBE_BEGIN();
                 ok = mbar_wait(&bars->ready[stage], phase, abort_flag, status, STATUS_TIMEOUT_FULL);
+                PROBE_END(probe_wait_b);
                 tc_fence_after_sync();
               }
               if (ok) {
@@ -335,6 +362,8 @@ __global__ void __launch_bounds__(T_THREADS, 1)
           __syncwarp();
         }
       }
+      PROBE_STORE(1, probe_wait_a);  // MMA warp: waiting for an accumulator to be drained
+      PROBE_STORE(2, probe_wait_b);  // MMA warp: waiting for a stage's operands
     }
    }
   } else if (warp < T_EPI_WARP0) {
@@ -344,11 +373,15 @@ __global__ void __launch_bounds__(T_THREADS, 1)
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
+    PROBE_DECL;
     for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
       for (int kb = 0; kb < num_kb && ok; ++kb) {
+        PROBE_BEGIN();
         ok = mbar_wait(&bars->raw_full[stage], phase, abort_flag, status, STATUS_TIMEOUT_FULL);
         ok = __all_sync(0xffffffffu, ok);
+        PROBE_END(probe_wait_a);
         if (!ok) break;
+        PROBE_BEGIN();
         uint8_t* sw = smem + stage * T_STAGE_BYTES + T_X_BYTES;
         const uint8_t* sraw = sw + T_W_BYTES;
 #pragma unroll
@@ -364,11 +397,16 @@ __global__ void __launch_bounds__(T_THREADS, 1)
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) mbar_arrive_remote(map_to_cta(smem_u32(&bars->ready[stage]), 0));
+        PROBE_END(probe_work);
         if (++stage == T_STAGES) {
           stage = 0;
           phase ^= 1;
         }
       }
+    }
+    if (cw == 0) {
+      PROBE_STORE(3, probe_wait_a);  // unpack warp: waiting for packed rows to land
+      PROBE_STORE(4, probe_work);    // unpack warp: unpacking
     }
   } else {
     // ---------------------------------------------------------------- epilogue
@@ -378,6 +416,7 @@ __global__ void __launch_bounds__(T_THREADS, 1)
     const int half = ew / 4;       // which 128 of the 256 accumulator columns (m)
     int gc = 0;
     bool ok = true;
+    PROBE_DECL;
     for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
       int tn, tm;
       w4_tile_coords(tile, tiles_n, tiles_m, tn, tm);
@@ -396,10 +435,13 @@ __global__ void __launch_bounds__(T_THREADS, 1)
         if (g + 1 < groups && n_ok) s_next = __half2float(s_row[g + 1]);
         unsigned long long s2;
         asm("mov.b64 %0, {%1, %1};" : "=l"(s2) : "f"(s));
+        PROBE_BEGIN();
         ok = mbar_wait(&bars->group_done[gc % T_RING], (gc / T_RING) & 1, abort_flag, status,
                        STATUS_TIMEOUT_TMEM_FULL);
         ok = __all_sync(0xffffffffu, ok);
+        PROBE_END(probe_wait_a);
         if (!ok) break;
+        PROBE_BEGIN();
         tc_fence_after_sync();
         const uint32_t taddr = tmem_base + (gc & 1) * 256 + half * 128 + (uint32_t(quarter * 32) << 16);
         // A TMEM load takes a few hundred cycles to return, and tcgen05.wait::ld waits for every
@@ -420,6 +462,7 @@ __global__ void __launch_bounds__(T_THREADS, 1)
         if (lane == 0) mbar_arrive_remote(map_to_cta(smem_u32(&bars->acc_empty[gc & 1]), 0));
         fold32(acc, 32, va, s2);
         fold32(acc, 48, vb, s2);
+        PROBE_END(probe_work);
       }
       if (ok && n_ok) {
         const int m_base = tm * 256 + half * 128;
@@ -432,6 +475,10 @@ __global__ void __launch_bounds__(T_THREADS, 1)
           if (m + 1 < M) y[size_t(m + 1) * N + n] = __float2half_rn(hi);
         }
       }
+    }
+    if (ew == 0) {
+      PROBE_STORE(5, probe_wait_a);  // epilogue warp: waiting for a group's MMAs
+      PROBE_STORE(6, probe_work);    // epilogue warp: draining (incl. the TMEM load latency)
     }
   }
 
@@ -533,7 +580,7 @@ static bool launch_decode(DeviceCtx& ctx, const __half* x, const uint8_t* w_q, c
     configured[ctx.device] = true;
   }
   int rowgroups = 0;
-  for (int rg = 8; rg >= 1; rg /= 2) {
+  for (int rg = D_WARPS; rg >= 1; rg /= 2) {
     if (K % (128 * (D_WARPS / rg)) != 0) continue;
     rowgroups = rg;  // the smallest valid one is kept if none fills the SMs
     if ((N + 32 * rg - 1) / (32 * rg) >= ctx.sm_count * 3 / 4) break;
@@ -587,3 +634,13 @@ extern "C" void solve(const __half* x, const uint8_t* w_q, const __half* scales,
 extern "C" int texo_mm_int4_last_path(void) { return texo::w4::last_path(); }
 extern "C" void texo_mm_int4_force_path(int path) { texo::w4::forced_path() = path; }
 extern "C" int texo_mm_int4_status(void) { return texo::read_and_clear_status(); }
+
+#ifdef W4_STALL_PROBE
+// Probe builds only: copies the seven stall counters (units of 1024 clock cycles) out of the
+// status block and clears them.
+extern "C" void texo_w4_probe_read(int* out7) {
+  texo::DeviceCtx& ctx = texo::device_ctx();
+  cudaMemcpy(out7, ctx.status + 16, 7 * sizeof(int), cudaMemcpyDeviceToHost);
+  cudaMemset(ctx.status + 16, 0, 7 * sizeof(int));
+}
+#endif

@@ -515,15 +515,17 @@ __device__ __forceinline__ int epilogue_sums(const int8_t* __restrict__ A, const
       const int n = item * SUM_COLS + tx * 16;
       int acc[16] = {};
       if (n < N) {
+        // (sixteen 16-byte loads in flight per thread: the phase is bound by load latency
+        // under the tensor kernel's own L2 traffic, not by the additions)
         const int8_t* col = B + n;
         int k = ty;
-        for (; k + 7 * ES_KLANES < K; k += 8 * ES_KLANES) {
-          int4 v[8];
+        for (; k + 15 * ES_KLANES < K; k += 16 * ES_KLANES) {
+          int4 v[16];
 #pragma unroll
-          for (int u = 0; u < 8; ++u)
+          for (int u = 0; u < 16; ++u)
             v[u] = __ldg(reinterpret_cast<const int4*>(col + size_t(k + u * ES_KLANES) * N));
 #pragma unroll
-          for (int u = 0; u < 8; ++u) add_bytes(acc, v[u]);
+          for (int u = 0; u < 16; ++u) add_bytes(acc, v[u]);
         }
         for (; k < K; k += ES_KLANES)
           add_bytes(acc, __ldg(reinterpret_cast<const int4*>(col + size_t(k) * N)));
@@ -554,12 +556,12 @@ __device__ __forceinline__ int epilogue_sums(const int8_t* __restrict__ A, const
         const int chunks = K / 16;
         int acc = 0;
         int i = lane;
-        for (; i + 7 * 32 < chunks; i += 8 * 32) {
-          int4 v[8];
+        for (; i + 15 * 32 < chunks; i += 16 * 32) {
+          int4 v[16];
 #pragma unroll
-          for (int u = 0; u < 8; ++u) v[u] = __ldg(a + i + u * 32);
+          for (int u = 0; u < 16; ++u) v[u] = __ldg(a + i + u * 32);
 #pragma unroll
-          for (int u = 0; u < 8; ++u) {
+          for (int u = 0; u < 16; ++u) {
             acc = __dp4a(v[u].x, 0x01010101, acc);
             acc = __dp4a(v[u].y, 0x01010101, acc);
             acc = __dp4a(v[u].z, 0x01010101, acc);
@@ -785,7 +787,9 @@ __global__ void __launch_bounds__(MMA_THREADS, 1)
       __threadfence();
       epilogue_bar();
       if (et == 0 && mine > 0) atomicAdd(items_done, unsigned(mine));
-      if (lane == 0) ok = wait_items(items_done, items_expected, abort_flag, status);
+      // (a pair that owns no tile was only here to help with the sums: nothing to wait for)
+      if (lane == 0 && cluster_id < num_tiles)
+        ok = wait_items(items_done, items_expected, abort_flag, status);
       ok = __shfl_sync(0xffffffffu, ok, 0);
       __threadfence();
       epilogue_bar();  // `part` doubles as the all-gather staging area of the drains below
@@ -970,7 +974,11 @@ static bool launch_tensor(DeviceCtx& ctx, const int8_t* A, const int8_t* B, int8
     ctx.items_expected += unsigned(col_items + row_items);
     const unsigned items_expected = ctx.items_expected;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(2 * std::min(tiles_m * tiles_n, pairs));
+    // One pair per tile up to what the device holds; a small problem gets extra pairs that own
+    // no tile and only help with the sums (about four items per CTA), so that e.g. four tiles'
+    // worth of CTAs do not have to add up the whole of A and B by themselves.
+    const int helper_pairs = (col_items + row_items + 7) / 8;
+    cfg.gridDim = dim3(2 * std::min(std::max(tiles_m * tiles_n, helper_pairs), pairs));
     cfg.blockDim = dim3(MMA_THREADS);
     cfg.dynamicSmemBytes = P_SMEM_BYTES + (q.n_peers > 0 ? P_GATHER_SMEM_BYTES : P_AUX_SMEM_BYTES);
     cfg.stream = 0;
