@@ -182,7 +182,9 @@ void texo_mm_int4a8_solve_per_channel(const int8_t* A, const uint8_t* w_q, int8_
                                       int K, float scale_A, const float* scale_B, float scale_C,
                                       int zero_point_A, const int* zero_point_B, int zero_point_C);
 /* mm_int4a8 diagnostics: path 1 = generic SIMT kernel, 2 = tcgen05 kind::i8 CTA-pair kernel,
- * 3 = streaming (decode) kernel, M <= 32. */
+ * 3 = TMA + tcgen05 streaming kernel (M <= 32), 4 = register-streaming decode kernel (M <= 16,
+ * K % 128 == 0, aligned A / w_q): packed weights read once from HBM straight into registers,
+ * mma.sync s8 x u8. */
 int texo_mm_int4a8_last_path(void);
 void texo_mm_int4a8_force_path(int path);
 int texo_mm_int4a8_status(void);
@@ -221,7 +223,9 @@ void texo_mm_int8_force_path(int path);
 int texo_mm_int8_status(void);
 
 /* mm_int4: 1 = generic FP32 kernel, 2 = tcgen05 kind::f16 CTA-pair kernel (needs 16-byte
- * aligned x / w_q, K % 64 == 0, group_size 16, 32, 64 or 128), 3 = streaming (decode) kernel
+ * aligned x / w_q, K % 64 == 0, group_size 16, 32, 64 or 128; unpacked weights reach the MMA
+ * through tensor memory), 4 = the same with both operands in shared memory (only when
+ * forced), 3 = streaming (decode) kernel
  * (M <= 16, group_size 128, K % 128 == 0, aligned x / w_q): packed weights read once from HBM
  * straight into registers, mma.sync on 16-row activation tiles. */
 int texo_mm_int4_last_path(void);
@@ -232,6 +236,10 @@ int texo_mm_int4_status(void);
  * second) on a barrier nothing completes, and returns the status code the kernel recorded
  * (5), or a negative value if the kernel did not return normally.  Nothing faults or hangs. */
 int texo_selftest_wait_timeout(void);
+
+/* Hits / misses of the library's cache of encoded TMA descriptors (a call with a pointer and
+ * shape seen before skips the driver's descriptor encoding); either pointer may be null. */
+void texo_tensor_map_cache_stats(long long* hits, long long* misses);
 
 /* Number of kernels the library has launched so far in this process. */
 long long texo_kernel_launches(void);

@@ -92,21 +92,26 @@ def test_harness_default_cases(lib, oracle):
 @pytest.mark.parametrize("shape", [(128, 128, 64, 64), (256, 256, 128, 128), (300, 520, 1024, 64),
                                    (512, 768, 2048, 128), (257, 255, 1984, 64), (1, 4096, 4096, 128),
                                    (1000, 3, 192, 64), (300, 520, 1024, 32), (256, 256, 64, 32),
-                                   (257, 255, 1984, 16), (512, 768, 2048, 32), (130, 66, 128, 16)])
+                                   (257, 255, 1984, 16), (512, 768, 2048, 32), (130, 66, 128, 16),
+                                   (200, 300, 8192, 128), (577, 1030, 4096, 64)])
 def test_tensor_path_full_matrix(lib, oracle, shape):
     """tcgen05 kind::f16 CTA-pair kernel: partial tiles in M and N, K not a multiple of the
     group pair, all four supported group sizes (a group is a quarter, half, one or two 64-k
     stages); every output within the reference tolerance."""
     m, n, k, g = shape
     x, w, s = oracle.int4_inputs(m, n, k, g, 100 + m)
-    lib.texo_mm_int4_force_path(2)  # (few-row shapes would otherwise take the decode kernel)
-    try:
-        got = run_case(lib, x, w, s, m, n, k, g)
-    finally:
-        lib.texo_mm_int4_force_path(0)
-    assert lib.texo_mm_int4_last_path() == 2
-    assert harness.int4_within_tolerance(got, oracle.mm_int4(x, w, s, m, n, k, g), ATOL, RTOL)
-    assert lib.texo_mm_int4_status() == 0
+    want = oracle.mm_int4(x, w, s, m, n, k, g)
+    # 2 = weights fed to the MMA through tensor memory (the default), 4 = both operands in
+    # shared memory; forcing either also keeps few-row shapes off the decode kernel
+    for force in (2, 4):
+        lib.texo_mm_int4_force_path(force)
+        try:
+            got = run_case(lib, x, w, s, m, n, k, g)
+        finally:
+            lib.texo_mm_int4_force_path(0)
+        assert lib.texo_mm_int4_last_path() == force
+        assert harness.int4_within_tolerance(got, want, ATOL, RTOL), (shape, force)
+        assert lib.texo_mm_int4_status() == 0
 
 
 @pytest.mark.parametrize("shape", [(1, 4096, 4096), (16, 4096, 4096), (7, 100, 256), (16, 4100, 1024),

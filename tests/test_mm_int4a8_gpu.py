@@ -72,8 +72,10 @@ def _quant(rng, k, zero_a=None, zero_b=None):
 SHAPES = [  # (M, N, K); K % 32 == 0 and aligned rows -> tensor paths; partial tiles included
     (256, 256, 128), (256, 256, 32), (256, 512, 1024), (130, 272, 160), (1, 16, 32),
     (300, 1008, 1056), (512, 768, 2048), (16, 4096, 512), (2000, 48, 4096),
-    # decode shapes (M <= 32): the streaming kernel, whole and split tiles, ragged N and K
+    # decode shapes (M <= 32): the streaming kernels, whole and split tiles, ragged N and K,
+    # every way the register-streaming kernel splits K over its warps (K / 128 = 1, 3, 16, 24, 64)
     (16, 256, 128), (16, 7168, 2048), (32, 1008, 1056), (7, 272, 160), (17, 40000, 256), (3, 48, 4096),
+    (9, 1000, 384), (16, 4100, 3072), (1, 4096, 8192), (16, 33, 256),
 ]
 
 
@@ -88,9 +90,12 @@ def test_tensor_and_generic_paths_match_oracle(lib, oracle, shape):
         want = oracle.mm_int4a8(a, w, m, n, k, q)
         if m >= 16:  # (a single activation row can push every output the same way)
             assert np.count_nonzero(np.abs(want.astype(np.int32)) < 127) > want.size // 3
-        # automatic choice (decode shapes stream, the rest take the CTA-pair kernel), then the
-        # CTA-pair and the generic kernel on their own
-        for force, expect in ((0, 3 if m <= 32 else 2), (2, 2), (1, 1)):
+        # automatic choice (up to 16 rows and K % 128 == 0: the register-streaming decode kernel;
+        # other decode shapes: the TMA streaming kernel; the rest: the CTA-pair kernel), then
+        # the streaming, CTA-pair and generic kernels on their own
+        auto = 4 if (m <= 16 and k % 128 == 0) else 3 if m <= 32 else 2
+        cases = [(0, auto), (2, 2), (1, 1)] + ([(3, 3)] if m <= 32 else [])
+        for force, expect in cases:
             got = run_case(lib, a, w, m, n, k, q, force=force)
             assert lib.texo_mm_int4a8_last_path() == expect, (shape, force)
             assert np.array_equal(got, want), (shape, q, force)

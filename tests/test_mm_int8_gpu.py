@@ -365,6 +365,29 @@ def test_stateless_call_on_the_pair_path_is_one_launch(lib, oracle):
     assert lib.texo_mm_int8_status() == 0
 
 
+def test_repeated_calls_reuse_cached_tensor_maps(lib):
+    """A call with pointers and a shape seen before takes its TMA descriptors from the
+    library's cache instead of encoding them again; new operands miss."""
+    import ctypes
+
+    hits, misses = ctypes.c_longlong(0), ctypes.c_longlong(0)
+    A = torch.zeros((256, 512), dtype=torch.int8, device="cuda")
+    B = torch.zeros((512, 256), dtype=torch.int8, device="cuda")
+    C = torch.empty((256, 256), dtype=torch.int8, device="cuda")
+    q = (1.0, 1.0, 1.0, 0, 0, 0)
+    lib.texo_mm_int8_solve(A.data_ptr(), B.data_ptr(), C.data_ptr(), 256, 256, 512, *q)
+    lib.texo_tensor_map_cache_stats(ctypes.byref(hits), ctypes.byref(misses))
+    h0, m0 = hits.value, misses.value
+    lib.texo_mm_int8_solve(A.data_ptr(), B.data_ptr(), C.data_ptr(), 256, 256, 512, *q)
+    lib.texo_tensor_map_cache_stats(ctypes.byref(hits), ctypes.byref(misses))
+    assert hits.value - h0 == 2 and misses.value == m0  # the A and B descriptors, both cached
+    B2 = torch.zeros((512, 256), dtype=torch.int8, device="cuda")
+    lib.texo_mm_int8_solve(A.data_ptr(), B2.data_ptr(), C.data_ptr(), 256, 256, 512, *q)
+    lib.texo_tensor_map_cache_stats(ctypes.byref(hits), ctypes.byref(misses))
+    assert misses.value == m0 + 1
+    torch.cuda.synchronize()
+
+
 def test_huge_k_takes_generic_path(lib, oracle):
     m, n, k = 4, 16, (1 << 17) + 16
     rng = np.random.default_rng(3)

@@ -65,6 +65,7 @@ _SIGNATURES = {
     "texo_mm_int4_status": (_c_int, []),
     "texo_selftest_wait_timeout": (_c_int, []),
     "texo_kernel_launches": (ctypes.c_longlong, []),
+    "texo_tensor_map_cache_stats": (None, [ctypes.POINTER(ctypes.c_longlong), ctypes.POINTER(ctypes.c_longlong)]),
     "texo_profile_enable": (None, [_c_int]),
     "texo_int8_issue_ceiling_tops": (ctypes.c_double, [_c_int, _c_int]),
     "texo_int8_issue_rate_tops": (ctypes.c_double, [_c_int, _c_int, _c_int]),

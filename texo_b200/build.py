@@ -22,7 +22,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OPS = ("mm_int8", "mm_int4", "dequantization", "mm_int4a8", "rms_norm_w_residual")
 EXTRA = ("capi", "peak_probe", "host_api")  # only in the combined library
-HEADERS = ("ptx.cuh", "host_common.h", "requant.cuh", "skinny.cuh", "w4_decode.cuh")
+HEADERS = ("ptx.cuh", "host_common.h", "requant.cuh", "skinny.cuh", "w4_decode.cuh", "w4a8_decode.cuh")
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

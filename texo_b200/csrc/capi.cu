@@ -68,3 +68,11 @@ extern "C" int texo_selftest_wait_timeout(void) {
   const int code = texo::read_and_clear_status();
   return reached_host == 1 ? code : -3;
 }
+
+// Hits and misses of the tensor-map cache since the process started (host_common.h); no
+// counterpart in the reference, which builds no descriptors on this path.
+extern "C" void texo_tensor_map_cache_stats(long long* hits, long long* misses) {
+  const texo::TensorMapCache& cache = texo::tensor_map_cache();
+  if (hits) *hits = cache.hits;
+  if (misses) *misses = cache.misses;
+}

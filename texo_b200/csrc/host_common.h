@@ -190,10 +190,47 @@ inline TensorMapEncodeFn tensor_map_encoder() {
 // Row-major 2-D tensor [rows, cols] of `elem_bytes` elements; box = box_rows x box_cols.
 // Out-of-range parts of a box read as zero.  Returns false if the driver rejects it (base
 // not 16-byte aligned, row pitch not a multiple of 16 bytes, ...).
+//
+// A descriptor is a pure function of these arguments (it holds an address and a shape, not
+// data), and inference calls repeat the same handful of (pointer, shape) combinations, so the
+// encoded maps are kept in a small per-process cache: a hit replaces the driver call (a
+// microsecond or two of host time, a noticeable share of a launch-bound call) by a compare.
+// The reference keeps its per-process state the same way (its src/mm_int8.cu:511-527).
+struct TensorMapKey {
+  const void* base;
+  uint64_t rows, cols, pitch;
+  uint32_t box_rows, box_cols;
+  int type, swizzle;
+  bool operator==(const TensorMapKey& o) const {
+    return base == o.base && rows == o.rows && cols == o.cols && pitch == o.pitch &&
+           box_rows == o.box_rows && box_cols == o.box_cols && type == o.type && swizzle == o.swizzle;
+  }
+};
+constexpr int TENSOR_MAP_CACHE_SLOTS = 32;
+struct TensorMapCache {
+  TensorMapKey key[TENSOR_MAP_CACHE_SLOTS];
+  CUtensorMap map[TENSOR_MAP_CACHE_SLOTS];
+  int used = 0, next = 0;
+  long long hits = 0, misses = 0;
+};
+inline TensorMapCache& tensor_map_cache() {
+  static TensorMapCache cache;
+  return cache;
+}
+
 inline bool make_tensor_map_2d(CUtensorMap* map, CUtensorMapDataType type, size_t elem_bytes,
                                const void* base, uint64_t rows, uint64_t cols,
                                uint64_t row_pitch_bytes, uint32_t box_rows, uint32_t box_cols,
                                CUtensorMapSwizzle swizzle) {
+  TensorMapCache& cache = tensor_map_cache();
+  const TensorMapKey key = {base, rows, cols, row_pitch_bytes, box_rows, box_cols, int(type), int(swizzle)};
+  for (int i = 0; i < cache.used; ++i) {
+    if (cache.key[i] == key) {
+      *map = cache.map[i];
+      ++cache.hits;
+      return true;
+    }
+  }
   TensorMapEncodeFn encode = tensor_map_encoder();
   if (!encode) return false;
   cuuint64_t dims[2] = {cols, rows};
@@ -201,9 +238,16 @@ inline bool make_tensor_map_2d(CUtensorMap* map, CUtensorMapDataType type, size_
   cuuint32_t box[2] = {box_cols, box_rows};
   cuuint32_t elem_strides[2] = {1, 1};
   (void)elem_bytes;
-  return encode(map, type, 2, const_cast<void*>(base), dims, strides, box, elem_strides,
-                CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  if (encode(map, type, 2, const_cast<void*>(base), dims, strides, box, elem_strides,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return false;
+  ++cache.misses;
+  const int slot = cache.used < TENSOR_MAP_CACHE_SLOTS ? cache.used++ : cache.next;
+  cache.next = (slot + 1) % TENSOR_MAP_CACHE_SLOTS;
+  cache.key[slot] = key;
+  cache.map[slot] = *map;
+  return true;
 }
 
 }  // namespace texo

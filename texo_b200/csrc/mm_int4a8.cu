@@ -36,6 +36,7 @@
 #include "ptx.cuh"
 #include "requant.cuh"
 #include "skinny.cuh"
+#include "w4a8_decode.cuh"
 
 namespace texo {
 namespace w4a8 {
@@ -383,7 +384,7 @@ __global__ void __launch_bounds__(Q_THREADS, 1)
 }
 
 // ------------------------------------------------------------------ dispatch
-enum Path { PATH_AUTO = 0, PATH_GENERIC = 1, PATH_TENSOR = 2, PATH_SKINNY = 3 };
+enum Path { PATH_AUTO = 0, PATH_GENERIC = 1, PATH_TENSOR = 2, PATH_SKINNY = 3, PATH_DECODE = 4 };
 
 inline int& forced_path() {
   static int path = [] {
@@ -511,6 +512,47 @@ static bool launch_tensor(DeviceCtx& ctx, const int8_t* A, const uint8_t* W, int
 
 namespace texo {
 namespace w4a8 {
+// Decode kernel (w4a8_decode.cuh): up to 16 activation rows, weights straight from HBM into
+// registers.  Picks how many 32-row groups a CTA owns (the rest of its 16 warps split K): as
+// many as still give about three quarters of the SMs a CTA.
+static bool decode_path_ok(const int8_t* A, const uint8_t* w_q, int M, int N, int K) {
+  return M <= 16 && K >= 128 && K % 128 == 0 && K < (1 << 17) && (long long)N * (K / 2) < (1LL << 31) &&
+         (reinterpret_cast<uintptr_t>(A) & 15) == 0 && (reinterpret_cast<uintptr_t>(w_q) & 15) == 0;
+}
+
+static bool launch_decode(DeviceCtx& ctx, const int8_t* A, const uint8_t* w_q, int8_t* C, int M, int N,
+                          int K, const i8::Quant& q) {
+  static bool configured[MAX_DEVICES] = {};
+  if (!configured[ctx.device]) {
+    if (cudaFuncSetAttribute(decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, E_SMEM_BYTES) !=
+        cudaSuccess) {
+      cudaGetLastError();
+      return false;
+    }
+    configured[ctx.device] = true;
+  }
+  int rowgroups = 0;
+  for (int rg = E_WARPS; rg >= 1; rg /= 2) {
+    if (K % (128 * (E_WARPS / rg)) != 0) continue;
+    rowgroups = rg;  // the smallest valid one is kept if none fills the SMs
+    if ((N + 32 * rg - 1) / (32 * rg) >= ctx.sm_count * 3 / 4) break;
+  }
+  if (rowgroups == 0) return false;
+  const int grid = (N + 32 * rowgroups - 1) / (32 * rowgroups);
+  const int slot = profile_start();
+  decode_kernel<<<grid, E_THREADS, E_SMEM_BYTES>>>(A, w_q, C, M, N, K, q, rowgroups);
+  if (cudaPeekAtLastError() != cudaSuccess) {
+    cudaGetLastError();
+    profile_stop(slot);
+    note_host_error(STATUS_LAUNCH_FAILED);
+    return false;
+  }
+  profile_stop(slot);
+  ++launch_counter();
+  last_path() = PATH_DECODE;
+  return true;
+}
+
 // Dispatch shared by the per-tensor and the per-channel entry points.  scale_B_vec /
 // zero_point_B_vec: per-output-channel weight quantisation (device arrays [N], see
 // texo_mm_int4a8_solve_per_channel), both null for per-tensor.
@@ -537,6 +579,9 @@ static void solve_with(const int8_t* A, const uint8_t* w_q, int8_t* C, int M, in
                           (reinterpret_cast<uintptr_t>(zero_point_B_vec) & 15) == 0 &&
                           (scale_B_vec == nullptr || N % 4 == 0);
   const int force = forced_path();
+  if ((force == PATH_AUTO || force == PATH_DECODE) && ctx.cc_major >= 8 && K > 0 &&
+      decode_path_ok(A, w_q, M, N, K) && launch_decode(ctx, A, w_q, C, M, N, K, q))
+    return;
   if (force != PATH_GENERIC && ctx.cc_major >= 10 && vectors_ok && tensor_path_ok(A, w_q, K)) {
     // the 32-bit (mod 2^32) correction is exact while |dot| < 2^31; per-channel zero points
     // live on the device, so the bound assumes the int8 range for them

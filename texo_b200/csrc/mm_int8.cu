@@ -975,9 +975,10 @@ static bool launch_tensor(DeviceCtx& ctx, const int8_t* A, const int8_t* B, int8
     const unsigned items_expected = ctx.items_expected;
     cudaLaunchConfig_t cfg = {};
     // One pair per tile up to what the device holds; a small problem gets extra pairs that own
-    // no tile and only help with the sums (about four items per CTA), so that e.g. four tiles'
-    // worth of CTAs do not have to add up the whole of A and B by themselves.
-    const int helper_pairs = (col_items + row_items + 7) / 8;
+    // no tile and only help with the sums (one item per CTA: an item is one memory round trip),
+    // so that e.g. four tiles' worth of CTAs do not have to add up the whole of A and B by
+    // themselves, one item after the other.
+    const int helper_pairs = (col_items + row_items + 1) / 2;
     cfg.gridDim = dim3(2 * std::min(std::max(tiles_m * tiles_n, helper_pairs), pairs));
     cfg.blockDim = dim3(MMA_THREADS);
     cfg.dynamicSmemBytes = P_SMEM_BYTES + (q.n_peers > 0 ? P_GATHER_SMEM_BYTES : P_AUX_SMEM_BYTES);
