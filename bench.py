@@ -3,8 +3,8 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
                     [--workload int8_8192 | int8_512 | int8_8192_presummed | int8_decode |
-                                int4_w4a16 | int4_w4a8 | int8_swiglu | dequant | rmsnorm_quant |
-                                layer_sweep] [--no-extras] [--no-cpu-baseline]
+                                int4_w4a16 | int4_w4a16_decode | int4_w4a8 | int4_w4a8_decode |
+                                int8_swiglu | dequant | rmsnorm_quant | layer_sweep] [--no-extras] [--no-cpu-baseline]
 
 One "step" is one `solve` call over one batch of synthetic input.  The default workload is
 the INT8 quantized matmul M=N=K=8192 (uniform int8 inputs, per-tensor scales and non-zero
@@ -108,6 +108,14 @@ def workload_spec(name: str):
         return dict(op="mm_int4a8", M=4096, N=8192, K=8192, dtype="int8",
                     desc="W4A8 matmul M=4096 K=8192 N=8192: packed INT4 weights, INT8 activations, "
                          "per-tensor scales and zero points")
+    if name == "int4_w4a16_decode":
+        return dict(op="mm_int4", M=16, N=28672, K=8192, G=128, dtype="f16",
+                    desc="W4A16 decode-shaped matmul M=16 K=8192 N=28672 G=128 (HBM-bound: the packed "
+                         "weights are read once)")
+    if name == "int4_w4a8_decode":
+        return dict(op="mm_int4a8", M=16, N=28672, K=8192, dtype="int8",
+                    desc="W4A8 decode-shaped matmul M=16 K=8192 N=28672 (HBM-bound: the packed weights "
+                         "are read once)")
     if name == "dequant":
         return dict(op="dequantization", M=8192, N=8192, T=128, dtype="f32",
                     desc="tile-scale dequantization 8192x8192 T=128")
@@ -160,7 +168,8 @@ def algorithmic_work(spec):
 
 
 def hbm_bound(spec) -> bool:
-    return spec["op"] in ("dequantization", "rms_norm_quant") or (spec["op"] == "mm_int8" and spec["M"] <= 32)
+    return spec["op"] in ("dequantization", "rms_norm_quant") or (
+        spec["op"] in ("mm_int8", "mm_int4", "mm_int4a8") and spec["M"] <= 32)
 
 
 # ------------------------------------------------------------------------- clock sampling
@@ -600,7 +609,7 @@ def build_workload(ctx: Ctx, spec, with_e2e: bool = True, strong: bool = False):
     elif spec["op"] == "mm_int4a8":
         M, N, K = spec["M"], spec["N"], spec["K"]
         A = torch.randint(-128, 128, (M, K), generator=g_a, device=dev, dtype=torch.int8)
-        nsets = 3
+        nsets = max(3, int(np.ceil(3 * 126e6 / (N * K // 2))))
         Ws = [torch.randint(0, 256, (N, K // 2), generator=g_b, device=dev, dtype=torch.uint8)
               for _ in range(nsets)]
         Cs = [torch.empty((M, N), device=dev, dtype=torch.int8) for _ in range(nsets)]
@@ -629,7 +638,7 @@ def build_workload(ctx: Ctx, spec, with_e2e: bool = True, strong: bool = False):
     elif spec["op"] == "mm_int4":
         M, N, K, G = spec["M"], spec["N"], spec["K"], spec["G"]
         x = torch.randn((M, K), generator=g_a, device=dev).to(torch.float16)
-        nsets = 2
+        nsets = 2 if M > 32 else max(3, int(np.ceil(3 * 126e6 / (N * K // 2))))
         Ws = [torch.randint(0, 256, (N, K // 2), generator=g_b, device=dev, dtype=torch.uint8)
               for _ in range(nsets)]
         Ss = [(torch.rand((N, K // G), generator=g_b, device=dev) * 0.1 + 0.01).to(torch.float16)
@@ -1146,7 +1155,8 @@ def run_ours(args, spec, workload):
     reference_gpu = None
     if world == 1 and workload == "int8_8192" and not args.no_extras:
         configs = {}
-        for name in ("int8_512", "int8_decode", "int4_w4a16", "int4_w4a8", "dequant"):
+        for name in ("int8_512", "int8_decode", "int4_w4a16", "int4_w4a16_decode", "int4_w4a8",
+                     "int4_w4a8_decode", "dequant"):
             configs[name] = quick_config(ctx, name, 20, 5, ceilings)
         for G in (64, 32, 16):
             s = dict(workload_spec("int4_w4a16"), G=G)
@@ -1239,7 +1249,8 @@ def main():
         # about a second of GPU work, so that clocks under load are actually sampled
         args.steps = {"int8_8192": 2000, "int8_8192_presummed": 2000, "int8_decode": 10000,
                       "int4_w4a16": 1500, "int4_w4a8": 3000, "dequant": 5000, "rmsnorm_quant": 4000,
-                      "int8_swiglu": 2500, "int8_512": 20000}[args.workload]
+                      "int8_swiglu": 2500, "int8_512": 20000, "int4_w4a16_decode": 10000,
+                      "int4_w4a8_decode": 10000}[args.workload]
         if args.impl == "reference":
             args.steps = 5
     if args.impl == "reference":

@@ -509,13 +509,21 @@ constexpr int V_BK = 64;                    // k per x stage / per ring slot of 
 constexpr int V_NM = 192;                   // activation rows per pair tile (UMMA N)
 constexpr int V_XROWS = V_NM / 2;           // rows of x each CTA stages
 constexpr int V_X_BYTES = V_XROWS * 128;    // 12 KiB
-constexpr int V_XSTAGES = 14;
+constexpr int V_XSTAGES = 12;
 constexpr int V_ASTAGES = 4;                // weight ring in TMEM: 4 x 32 columns
 constexpr int V_ACC_COLS = V_NM;
 constexpr int V_A_COL0 = 2 * V_ACC_COLS;    // first column of the weight ring
-constexpr int V_PREFETCH = 3;               // packed k blocks in flight per unpack thread
+// Packed weights in flight: every unpack thread copies its own row's 32 bytes of a k block into
+// a private place in shared memory with cp.async (no registers held, no barrier needed: a
+// thread only ever reads back what it copied itself) V_PREFETCH blocks ahead - 48 KiB in flight
+// per SM, enough to cover the L2 / HBM latency at the rate the MMA consumes them (three
+// blocks held in registers were not: the first version of this kernel ran at a third of the
+// rate it should have).
+constexpr int V_PREFETCH = 12;
+constexpr int V_RAW_SLOTS = V_PREFETCH + 1;
+constexpr int V_RAW_BYTES = 128 * 32;       // one k block of this CTA's 128 weight rows, packed
 constexpr int V_RING = 32;
-constexpr int V_SMEM_BYTES = V_XSTAGES * V_X_BYTES + 1024 + 1024;
+constexpr int V_SMEM_BYTES = V_XSTAGES * V_X_BYTES + V_RAW_SLOTS * V_RAW_BYTES + 1024 + 1024;
 constexpr int V_REGS_CONTROL = 32, V_REGS_UNPACK = 96, V_REGS_EPILOGUE = 192;  // 128*(32+96) + 256*192 = 65536
 static_assert(V_A_COL0 + V_ASTAGES * 32 <= 512, "TMEM holds 512 columns");
 
@@ -535,7 +543,8 @@ __global__ void __launch_bounds__(T_THREADS, 1)
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~uintptr_t(1023));
-  TsBarriers* bars = reinterpret_cast<TsBarriers*>(smem + V_XSTAGES * V_X_BYTES);
+  uint8_t* raw_ring = smem + V_XSTAGES * V_X_BYTES;
+  TsBarriers* bars = reinterpret_cast<TsBarriers*>(raw_ring + V_RAW_SLOTS * V_RAW_BYTES);
   volatile int* abort_flag = &bars->abort_flag;
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   const uint32_t rank = cluster_ctarank();
@@ -672,38 +681,36 @@ __global__ void __launch_bounds__(T_THREADS, 1)
       const int n = min(tn * 256 + int(rank) * 128 + row, N - 1);  // rows past N: loaded, never stored
       return reinterpret_cast<const uint4*>(w_q + size_t(n) * (K / 2) + size_t(kb) * (V_BK / 2));
     };
-    uint4 raw[V_PREFETCH][2];
-#pragma unroll
-    for (int d = 0; d < V_PREFETCH; ++d) {
-      if (d < total_blocks) {
-        const uint4* src = packed_at(d);
-        raw[d][0] = __ldg(src);
-        raw[d][1] = __ldg(src + 1);
+    // this thread's 32 bytes in ring slot `slot`
+    auto raw_at = [&](int slot) { return raw_ring + slot * V_RAW_BYTES + row * 32; };
+    auto copy_block = [&](int b) {  // one cp.async group per k block (an empty one past the end)
+      if (b < total_blocks) {
+        const uint4* src = packed_at(b);
+        const uint32_t dst = smem_u32(raw_at(b % V_RAW_SLOTS));
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + 16), "l"(src + 1) : "memory");
       }
-    }
+      asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    for (int d = 0; d < V_PREFETCH; ++d) copy_block(d);
     int observed = -1;
     bool ok = true;
 #pragma unroll 1
-    for (int b0 = 0; b0 < total_blocks && ok; b0 += V_PREFETCH) {
-#pragma unroll
-      for (int d = 0; d < V_PREFETCH; ++d) {
-        const int b = b0 + d;
-        if (b >= total_blocks || !ok) break;
+    for (int b = 0; b < total_blocks && ok; ++b) {
+      {
+        asm volatile("cp.async.wait_group %0;" ::"n"(V_PREFETCH - 1) : "memory");  // block b has landed
         uint32_t out[32];
         {
-          const uint32_t words[8] = {raw[d][0].x, raw[d][0].y, raw[d][0].z, raw[d][0].w,
-                                     raw[d][1].x, raw[d][1].y, raw[d][1].z, raw[d][1].w};
+          const uint4 lo = *reinterpret_cast<const uint4*>(raw_at(b % V_RAW_SLOTS));
+          const uint4 hi = *reinterpret_cast<const uint4*>(raw_at(b % V_RAW_SLOTS) + 16);
+          const uint32_t words[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
 #pragma unroll
           for (int c = 0; c < 8; ++c) {
             const uint4 h = unpack8(words[c]);
             out[4 * c] = h.x, out[4 * c + 1] = h.y, out[4 * c + 2] = h.z, out[4 * c + 3] = h.w;
           }
         }
-        if (b + V_PREFETCH < total_blocks) {
-          const uint4* src = packed_at(b + V_PREFETCH);
-          raw[d][0] = __ldg(src);
-          raw[d][1] = __ldg(src + 1);
-        }
+        copy_block(b + V_PREFETCH);  // into the slot of block b - 1, read an iteration ago
         if (b >= V_ASTAGES) {
           // the slot is free once the last scale group that read block b - V_ASTAGES is complete
           const int c = ((b - V_ASTAGES + 1) * V_BK - 1) / G;
