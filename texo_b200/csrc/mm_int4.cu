@@ -491,311 +491,6 @@ __global__ void __launch_bounds__(T_THREADS, 1)
   }
 }
 
-// ------------------------------------------- tensor path, weights through TMEM
-// The kernel above is bound by shared-memory bandwidth: per 16-k MMA step a CTA writes 4 KiB of
-// x and 1 KiB of packed weights (TMA), reads that 1 KiB and writes 4 KiB of unpacked weights
-// (unpack warps), and the MMA reads 8 KiB of operands - 18 KiB against the 16 KiB per 128
-// cycles an SM's shared memory moves; its MMA warp spends four fifths of its time blocked on
-// issue (measured with the stall probe), with the tensor pipe about half busy.  This kernel
-// takes the weights out of shared memory altogether: the unpack warps load the packed bytes
-// of their weight row straight from global memory into registers (several k blocks ahead),
-// expand them to FP16 and store them with tcgen05.st into a small ring in TENSOR memory, from
-// where the MMA reads its A operand (tcgen05.mma with the A operand in TMEM).  Shared memory
-// then carries only x: 3 KiB written and 3 KiB read per 96-cycle step.  TMEM holds two
-// 192-column FP32 accumulators (so a pair tile is 256 weight rows x 192 activation rows) and
-// the 4 x 32-column weight ring; the freed shared memory goes into a 14-stage ring for x.
-// Scale groups, commits, drain and register hand-over work as in the kernel above.
-constexpr int V_BK = 64;                    // k per x stage / per ring slot of weights
-constexpr int V_NM = 192;                   // activation rows per pair tile (UMMA N)
-constexpr int V_XROWS = V_NM / 2;           // rows of x each CTA stages
-constexpr int V_X_BYTES = V_XROWS * 128;    // 12 KiB
-constexpr int V_XSTAGES = 12;
-constexpr int V_ASTAGES = 4;                // weight ring in TMEM: 4 x 32 columns
-constexpr int V_ACC_COLS = V_NM;
-constexpr int V_A_COL0 = 2 * V_ACC_COLS;    // first column of the weight ring
-// Packed weights in flight: every unpack thread copies its own row's 32 bytes of a k block into
-// a private place in shared memory with cp.async (no registers held, no barrier needed: a
-// thread only ever reads back what it copied itself) V_PREFETCH blocks ahead - 48 KiB in flight
-// per SM, enough to cover the L2 / HBM latency at the rate the MMA consumes them (three
-// blocks held in registers were not: the first version of this kernel ran at a third of the
-// rate it should have).
-constexpr int V_PREFETCH = 12;
-constexpr int V_RAW_SLOTS = V_PREFETCH + 1;
-constexpr int V_RAW_BYTES = 128 * 32;       // one k block of this CTA's 128 weight rows, packed
-constexpr int V_RING = 32;
-constexpr int V_SMEM_BYTES = V_XSTAGES * V_X_BYTES + V_RAW_SLOTS * V_RAW_BYTES + 1024 + 1024;
-constexpr int V_REGS_CONTROL = 32, V_REGS_UNPACK = 96, V_REGS_EPILOGUE = 192;  // 128*(32+96) + 256*192 = 65536
-static_assert(V_A_COL0 + V_ASTAGES * 32 <= 512, "TMEM holds 512 columns");
-
-struct TsBarriers {
-  uint64_t x_full[V_XSTAGES];   // even CTA: x bytes of both CTAs landed
-  uint64_t a_full[V_ASTAGES];   // even CTA: all unpack warps of both CTAs have stored the slot
-  uint64_t group_done[V_RING];  // per CTA: MMAs of a scale group complete
-  uint64_t acc_empty[2];        // even CTA: epilogue warps of both CTAs arrived
-  uint32_t tmem_base;
-  int abort_flag;
-};
-
-__global__ void __launch_bounds__(T_THREADS, 1)
-    tensor_ts_kernel(const __grid_constant__ CUtensorMap map_x, const uint8_t* __restrict__ w_q,
-                     const __half* __restrict__ scales, __half* __restrict__ y, int M, int N, int K,
-                     int G, int tiles_n, int tiles_m, int* status) {
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
-                                             ~uintptr_t(1023));
-  uint8_t* raw_ring = smem + V_XSTAGES * V_X_BYTES;
-  TsBarriers* bars = reinterpret_cast<TsBarriers*>(raw_ring + V_RAW_SLOTS * V_RAW_BYTES);
-  volatile int* abort_flag = &bars->abort_flag;
-  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
-  const uint32_t rank = cluster_ctarank();
-  const int cluster_id = blockIdx.x / 2, num_clusters = gridDim.x / 2;
-  const int num_tiles = tiles_n * tiles_m;
-  const int num_kb = K / V_BK;
-  const int steps_per_group = G / 16;
-  const int groups = K / G;
-  const int my_tiles = cluster_id < num_tiles ? (num_tiles - cluster_id + num_clusters - 1) / num_clusters : 0;
-  const int total_blocks = my_tiles * num_kb;  // k blocks this pair works through, all tiles
-
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < V_XSTAGES; ++s) mbar_init(&bars->x_full[s], 1);
-    for (int s = 0; s < V_ASTAGES; ++s) mbar_init(&bars->a_full[s], 2 * T_CONV_WARPS);
-    for (int r = 0; r < V_RING; ++r) mbar_init(&bars->group_done[r], 1);
-    for (int b = 0; b < 2; ++b) mbar_init(&bars->acc_empty[b], 2 * T_EPI_WARPS);
-    bars->abort_flag = 0;
-    fence_barrier_init();
-    tma_prefetch_desc(&map_x);
-  }
-  if (warp == 1) {
-    tmem_alloc_pair(&bars->tmem_base, 512);
-    tmem_relinquish_pair();
-  }
-  tc_fence_before_sync();
-  __syncthreads();
-  cluster_sync_all();
-  tc_fence_after_sync();
-  const uint32_t tmem_base = bars->tmem_base;
-
-  if (warp < T_CONV_WARP0) {
-   asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(V_REGS_CONTROL));
-   if (warp == 0) {
-    // ------------------------------------------------------ TMA producer (x)
-    int stage = 0;
-    int observed = -1;
-    bool ok = true;
-    for (int b = 0; b < total_blocks && ok; ++b) {
-      if (lane == 0) {
-        const int tile = cluster_id + (b / num_kb) * num_clusters, kb = b % num_kb;
-        int tn, tm;
-        w4_tile_coords(tile, tiles_n, tiles_m, tn, tm);
-        if (b >= V_XSTAGES) {
-          // the commit of the last scale group that touches block b - V_XSTAGES
-          const int c = ((b - V_XSTAGES + 1) * V_BK - 1) / G;
-          if (c > observed) {
-            ok = mbar_wait(&bars->group_done[c % V_RING], (c / V_RING) & 1, abort_flag, status,
-                           STATUS_TIMEOUT_EMPTY);
-            observed = c;
-          }
-        }
-        if (ok) {
-          const uint32_t full_even = map_to_cta(smem_u32(&bars->x_full[stage]), 0);
-          if (rank == 0) mbar_arrive_expect_tx(&bars->x_full[stage], 2 * V_X_BYTES);
-          tma_load_2d_pair(smem + stage * V_X_BYTES, &map_x, full_even, kb * V_BK,
-                           tm * V_NM + int(rank) * V_XROWS);
-        }
-      }
-      ok = __shfl_sync(0xffffffffu, ok, 0);
-      if (++stage == V_XSTAGES) stage = 0;
-    }
-   } else if (warp == 1) {
-    // ------------------------------------------- MMA issuer (even CTA only)
-    if (rank == 0) {
-      constexpr uint32_t IDESC = umma_idesc(/*D=f32*/ 1, /*A=f16*/ 0, /*B=f16*/ 0, 0, 0, 256, V_NM);
-      int b = 0;     // k block (x stage b % V_XSTAGES, weight slot b % V_ASTAGES)
-      int step = 0;  // k-step inside the current block when a group is part of a block
-      int gc = 0;    // global group (= commit) number
-      bool ok = true;
-      for (int t = 0; t < my_tiles && ok; ++t) {
-        for (int g = 0; g < groups && ok; ++g, ++gc) {
-          const int buf = gc & 1;
-          if (lane == 0) {
-            ok = mbar_wait(&bars->acc_empty[buf], ((gc >> 1) & 1) ^ 1, abort_flag, status,
-                           STATUS_TIMEOUT_TMEM_EMPTY);
-            tc_fence_after_sync();
-          }
-          ok = __shfl_sync(0xffffffffu, ok, 0);
-          const uint32_t tmem_d = tmem_base + buf * V_ACC_COLS;
-          if (lane == 0) {
-            if (steps_per_group >= 4) {
-              for (int kk = 0; kk < steps_per_group / 4 && ok; ++kk, ++b) {
-                const int xs = b % V_XSTAGES, as = b % V_ASTAGES;
-                ok = mbar_wait(&bars->x_full[xs], (b / V_XSTAGES) & 1, abort_flag, status, STATUS_TIMEOUT_FULL) &&
-                     mbar_wait(&bars->a_full[as], (b / V_ASTAGES) & 1, abort_flag, status, STATUS_TIMEOUT_FULL);
-                if (ok) {
-                  tc_fence_after_sync();
-                  const uint32_t sx = smem_u32(smem + xs * V_X_BYTES);
-                  const uint32_t ta = tmem_base + V_A_COL0 + as * 32;
-#pragma unroll
-                  for (int j = 0; j < V_BK / 16; ++j)
-                    umma_f16_pair_ts(tmem_d, ta + j * 8, smem_desc(sx + j * 32, 16, 1024, SMEM_SWIZZLE_128B),
-                                     IDESC, (kk | j) != 0);
-                }
-              }
-            } else {
-              const int xs = b % V_XSTAGES, as = b % V_ASTAGES;
-              if (step == 0) {
-                ok = mbar_wait(&bars->x_full[xs], (b / V_XSTAGES) & 1, abort_flag, status, STATUS_TIMEOUT_FULL) &&
-                     mbar_wait(&bars->a_full[as], (b / V_ASTAGES) & 1, abort_flag, status, STATUS_TIMEOUT_FULL);
-                tc_fence_after_sync();
-              }
-              if (ok) {
-                const uint32_t sx = smem_u32(smem + xs * V_X_BYTES) + step * 32;
-                const uint32_t ta = tmem_base + V_A_COL0 + as * 32 + step * 8;
-                umma_f16_pair_ts(tmem_d, ta, smem_desc(sx, 16, 1024, SMEM_SWIZZLE_128B), IDESC, false);
-                if (steps_per_group == 2)
-                  umma_f16_pair_ts(tmem_d, ta + 8, smem_desc(sx + 32, 16, 1024, SMEM_SWIZZLE_128B), IDESC, true);
-              }
-              step += steps_per_group;
-              if (step == V_BK / 16) {
-                step = 0;
-                ++b;
-              }
-            }
-          }
-          ok = __shfl_sync(0xffffffffu, ok, 0);
-          if (lane == 0 && ok) umma_commit_pair(&bars->group_done[gc % V_RING], 3);
-          __syncwarp();
-        }
-      }
-    }
-   }
-  } else if (warp < T_EPI_WARP0) {
-    // ------------------------- weights: global -> registers -> FP16 -> tensor memory
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(V_REGS_UNPACK));
-    const int cw = warp - T_CONV_WARP0;  // = this warp's TMEM lane quarter
-    const int row = cw * 32 + lane;      // weight row of this thread within the CTA's 128
-    // address of this thread's 32 packed bytes (64 k) of k block b
-    auto packed_at = [&](int b) {
-      const int tile = cluster_id + (b / num_kb) * num_clusters, kb = b % num_kb;
-      int tn, tm;
-      w4_tile_coords(tile, tiles_n, tiles_m, tn, tm);
-      const int n = min(tn * 256 + int(rank) * 128 + row, N - 1);  // rows past N: loaded, never stored
-      return reinterpret_cast<const uint4*>(w_q + size_t(n) * (K / 2) + size_t(kb) * (V_BK / 2));
-    };
-    // this thread's 32 bytes in ring slot `slot`
-    auto raw_at = [&](int slot) { return raw_ring + slot * V_RAW_BYTES + row * 32; };
-    auto copy_block = [&](int b) {  // one cp.async group per k block (an empty one past the end)
-      if (b < total_blocks) {
-        const uint4* src = packed_at(b);
-        const uint32_t dst = smem_u32(raw_at(b % V_RAW_SLOTS));
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + 16), "l"(src + 1) : "memory");
-      }
-      asm volatile("cp.async.commit_group;" ::: "memory");
-    };
-    for (int d = 0; d < V_PREFETCH; ++d) copy_block(d);
-    int observed = -1;
-    bool ok = true;
-#pragma unroll 1
-    for (int b = 0; b < total_blocks && ok; ++b) {
-      {
-        asm volatile("cp.async.wait_group %0;" ::"n"(V_PREFETCH - 1) : "memory");  // block b has landed
-        uint32_t out[32];
-        {
-          const uint4 lo = *reinterpret_cast<const uint4*>(raw_at(b % V_RAW_SLOTS));
-          const uint4 hi = *reinterpret_cast<const uint4*>(raw_at(b % V_RAW_SLOTS) + 16);
-          const uint32_t words[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
-#pragma unroll
-          for (int c = 0; c < 8; ++c) {
-            const uint4 h = unpack8(words[c]);
-            out[4 * c] = h.x, out[4 * c + 1] = h.y, out[4 * c + 2] = h.z, out[4 * c + 3] = h.w;
-          }
-        }
-        copy_block(b + V_PREFETCH);  // into the slot of block b - 1, read an iteration ago
-        if (b >= V_ASTAGES) {
-          // the slot is free once the last scale group that read block b - V_ASTAGES is complete
-          const int c = ((b - V_ASTAGES + 1) * V_BK - 1) / G;
-          if (c > observed) {
-            ok = mbar_wait(&bars->group_done[c % V_RING], (c / V_RING) & 1, abort_flag, status,
-                           STATUS_TIMEOUT_EMPTY);
-            ok = __all_sync(0xffffffffu, ok);
-            observed = c;
-            if (!ok) break;
-          }
-        }
-        tc_fence_after_sync();
-        tmem_st_32x32(tmem_base + V_A_COL0 + (b % V_ASTAGES) * 32 + (uint32_t(cw * 32) << 16), out);
-        tmem_st_wait();
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive_remote(map_to_cta(smem_u32(&bars->a_full[b % V_ASTAGES]), 0));
-      }
-    }
-  } else {
-    // ---------------------------------------------------------------- epilogue
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(V_REGS_EPILOGUE));
-    const int ew = warp - T_EPI_WARP0;
-    const int quarter = warp % 4;  // TMEM lanes 32*quarter .. +31
-    const int half = ew / 4;       // which 96 of the 192 accumulator columns (m)
-    int gc = 0;
-    bool ok = true;
-    for (int t = 0; t < my_tiles && ok; ++t) {
-      const int tile = cluster_id + t * num_clusters;
-      int tn, tm;
-      w4_tile_coords(tile, tiles_n, tiles_m, tn, tm);
-      const int n = tn * 256 + int(rank) * 128 + quarter * 32 + lane;
-      const bool n_ok = n < N;
-      const __half* s_row = scales + size_t(n_ok ? n : 0) * groups;
-      unsigned long long acc[48];  // 96 FP32 accumulators as f32x2 pairs
-#pragma unroll
-      for (int j = 0; j < 48; ++j) acc[j] = 0ull;
-      float s_next = n_ok ? __half2float(s_row[0]) : 0.f;
-      for (int g = 0; g < groups && ok; ++g, ++gc) {
-        const float s = s_next;
-        if (g + 1 < groups && n_ok) s_next = __half2float(s_row[g + 1]);
-        unsigned long long s2;
-        asm("mov.b64 %0, {%1, %1};" : "=l"(s2) : "f"(s));
-        ok = mbar_wait(&bars->group_done[gc % V_RING], (gc / V_RING) & 1, abort_flag, status,
-                       STATUS_TIMEOUT_TMEM_FULL);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        tc_fence_after_sync();
-        const uint32_t taddr = tmem_base + (gc & 1) * V_ACC_COLS + half * 96 + (uint32_t(quarter * 32) << 16);
-        uint32_t va[32], vb[32];
-        tmem_ld_32x32(taddr, va);
-        tmem_ld_32x32(taddr + 32, vb);
-        tmem_ld_wait();
-        fold32(acc, 0, va, s2);
-        tmem_ld_32x32(taddr + 64, va);
-        fold32(acc, 16, vb, s2);
-        tmem_ld_wait();
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive_remote(map_to_cta(smem_u32(&bars->acc_empty[gc & 1]), 0));
-        fold32(acc, 32, va, s2);
-      }
-      if (ok && n_ok) {
-        const int m_base = tm * V_NM + half * 96;
-#pragma unroll
-        for (int j = 0; j < 48; ++j) {
-          float lo, hi;
-          asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(acc[j]));
-          const int m = m_base + 2 * j;
-          if (m < M) y[size_t(m) * N + n] = __float2half_rn(lo);
-          if (m + 1 < M) y[size_t(m + 1) * N + n] = __float2half_rn(hi);
-        }
-      }
-    }
-  }
-
-  tc_fence_before_sync();
-  __syncthreads();
-  cluster_sync_all();
-  if (warp == 1) {
-    tc_fence_after_sync();
-    tmem_dealloc_pair(tmem_base, 512);
-  }
-}
-
 inline int& last_path() {
   static int path = 0;
   return path;
@@ -865,62 +560,12 @@ static bool launch_tensor(DeviceCtx& ctx, const __half* x, const uint8_t* w_q, c
   return true;
 }
 
-// The TMEM-operand kernel: same preconditions as launch_tensor (the packed rows are read with
-// 16-byte loads: w_q 16-byte aligned and K % 64 == 0 give every row piece that alignment).
-static bool launch_tensor_ts(DeviceCtx& ctx, const __half* x, const uint8_t* w_q, const __half* scales,
-                             __half* y, int M, int N, int K, int G) {
-  static bool configured[MAX_DEVICES] = {};
-  static int pairs[MAX_DEVICES] = {};
-  cudaLaunchConfig_t cfg = {};
-  cfg.blockDim = dim3(T_THREADS);
-  cfg.dynamicSmemBytes = V_SMEM_BYTES;
-  cfg.stream = 0;
-  cudaLaunchAttribute attr;
-  attr.id = cudaLaunchAttributeClusterDimension;
-  attr.val.clusterDim.x = 2;
-  attr.val.clusterDim.y = 1;
-  attr.val.clusterDim.z = 1;
-  cfg.attrs = &attr;
-  cfg.numAttrs = 1;
-  if (!configured[ctx.device]) {
-    configured[ctx.device] = true;
-    cudaFuncSetAttribute(tensor_ts_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, V_SMEM_BYTES);
-    cfg.gridDim = dim3(2 * ctx.sm_count);
-    int n = 0;
-    if (cudaOccupancyMaxActiveClusters(&n, tensor_ts_kernel, &cfg) != cudaSuccess) {
-      cudaGetLastError();
-      n = 0;
-    }
-    pairs[ctx.device] = n;
-  }
-  if (pairs[ctx.device] <= 0) return false;
-  CUtensorMap map_x;
-  if (!make_tensor_map_2d(&map_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, x, M, K, size_t(K) * 2, V_XROWS,
-                          V_BK, CU_TENSOR_MAP_SWIZZLE_128B)) {
-    note_host_error(STATUS_TENSORMAP_FAILED);
-    return false;
-  }
-  const int tiles_n = (N + 255) / 256, tiles_m = (M + V_NM - 1) / V_NM;
-  cfg.gridDim = dim3(2 * std::min(tiles_n * tiles_m, pairs[ctx.device]));
-  const int slot = profile_start();
-  if (cudaLaunchKernelEx(&cfg, tensor_ts_kernel, map_x, w_q, scales, y, M, N, K, G, tiles_n, tiles_m,
-                         ctx.status) != cudaSuccess) {
-    cudaGetLastError();
-    profile_stop(slot);
-    note_host_error(STATUS_LAUNCH_FAILED);
-    return false;
-  }
-  profile_stop(slot);
-  ++launch_counter();
-  last_path() = 2;
-  return true;
-}
-
 // Decode path (w4_decode.cuh): M <= 16, one scale group per 128-k iteration.  Picks how many
 // 32-row groups a CTA owns (the rest of its 16 warps split K): as many as still give about
 // three quarters of the SMs a CTA, since more rows per CTA means fewer re-reads of x.
 static bool decode_path_ok(const __half* x, const uint8_t* w_q, int M, int N, int K, int G) {
-  return M <= 16 && G == 128 && K >= 128 && K % 128 == 0 && (long long)N * (K / 2) < (1LL << 31) &&
+  (void)N;
+  return M <= 16 && G == 128 && K >= 128 && K % 128 == 0 &&
          (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(w_q) & 15) == 0;
 }
 
@@ -943,8 +588,15 @@ static bool launch_decode(DeviceCtx& ctx, const __half* x, const uint8_t* w_q, c
   }
   if (rowgroups == 0) return false;
   const int grid = (N + 32 * rowgroups - 1) / (32 * rowgroups);
+  // the packed weights as a 2-D tensor [N, K/2] bytes; a box is one row group's 128 k
+  CUtensorMap map_w;
+  if (!make_tensor_map_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w_q, N, K / 2, K / 2, 32, 64,
+                          CU_TENSOR_MAP_SWIZZLE_NONE)) {
+    note_host_error(STATUS_TENSORMAP_FAILED);
+    return false;
+  }
   const int slot = profile_start();
-  decode_kernel<<<grid, D_THREADS, D_SMEM_BYTES>>>(x, w_q, scales, y, M, N, K, rowgroups);
+  decode_kernel<<<grid, D_THREADS, D_SMEM_BYTES>>>(map_w, x, scales, y, M, N, K, rowgroups, ctx.status);
   if (cudaPeekAtLastError() != cudaSuccess) {
     cudaGetLastError();
     profile_stop(slot);
@@ -976,15 +628,9 @@ extern "C" void solve(const __half* x, const uint8_t* w_q, const __half* scales,
   if ((forced_path() == 0 || forced_path() == 3) && ctx.cc_major >= 8 &&
       decode_path_ok(x, w_q, M, N, K, group_size) && launch_decode(ctx, x, w_q, scales, y, M, N, K))
     return;
-  // path 2 = the CTA-pair kernel with the weights fed through tensor memory; 4 = the older
-  // form with both operands in shared memory (kept for comparison, and as the fallback)
-  if (forced_path() != 1 && ctx.cc_major >= 10 && tensor_path_ok(x, w_q, K, group_size)) {
-    if (forced_path() != 4 && launch_tensor_ts(ctx, x, w_q, scales, y, M, N, K, group_size)) return;
-    if (launch_tensor(ctx, x, w_q, scales, y, M, N, K, group_size)) {
-      last_path() = 4;
-      return;
-    }
-  }
+  if (forced_path() != 1 && ctx.cc_major >= 10 && tensor_path_ok(x, w_q, K, group_size) &&
+      launch_tensor(ctx, x, w_q, scales, y, M, N, K, group_size))
+    return;
   dim3 grid((N + GT - 1) / GT, (M + GT - 1) / GT);
   const int slot = profile_start();
   generic_kernel<<<grid, G_THREADS>>>(x, w_q, scales, y, M, N, K, group_size);
