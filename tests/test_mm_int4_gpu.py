@@ -72,7 +72,8 @@ def test_harness_default_cases(lib, oracle):
             got = run_case(lib, x, w, s, m, n, k, g, off)
             path = lib.texo_mm_int4_last_path()
             lib.texo_mm_int4_force_path(0)
-            want_path = 1 if force == 1 else 3 if _takes_decode_path(m, k, g) else 2 if _takes_tensor_path(k, g) else 1
+            want_path = (1 if force == 1 else 3 if _takes_decode_path(m, k, g) else
+                         (4 if g <= 32 else 2) if _takes_tensor_path(k, g) else 1)
             assert path == want_path, (m, n, k, g, force)
             assert harness.int4_within_tolerance(got, want, ATOL, RTOL), (m, n, k, g, force)
     # zero scales: first, middle, last group and an all-zero column (tests/mm_int4.cpp:166-175)
@@ -93,7 +94,8 @@ def test_harness_default_cases(lib, oracle):
                                    (512, 768, 2048, 128), (257, 255, 1984, 64), (1, 4096, 4096, 128),
                                    (1000, 3, 192, 64), (300, 520, 1024, 32), (256, 256, 64, 32),
                                    (257, 255, 1984, 16), (512, 768, 2048, 32), (130, 66, 128, 16),
-                                   (200, 300, 8192, 128), (577, 1030, 4096, 64)])
+                                   (200, 300, 8192, 128), (577, 1030, 4096, 64), (577, 1030, 4096, 16),
+                                   (300, 200, 8192, 32)])
 def test_tensor_path_full_matrix(lib, oracle, shape):
     """tcgen05 kind::f16 CTA-pair kernel: partial tiles in M and N, K not a multiple of the
     group pair, all four supported group sizes (a group is a quarter, half, one or two 64-k
@@ -101,14 +103,18 @@ def test_tensor_path_full_matrix(lib, oracle, shape):
     m, n, k, g = shape
     x, w, s = oracle.int4_inputs(m, n, k, g, 100 + m)
     want = oracle.mm_int4(x, w, s, m, n, k, g)
-    lib.texo_mm_int4_force_path(2)  # (few-row shapes would otherwise take the decode kernel)
-    try:
-        got = run_case(lib, x, w, s, m, n, k, g)
-    finally:
-        lib.texo_mm_int4_force_path(0)
-    assert lib.texo_mm_int4_last_path() == 2
-    assert harness.int4_within_tolerance(got, want, ATOL, RTOL), shape
-    assert lib.texo_mm_int4_status() == 0
+    # 2 = a TMEM drain per scale group (any of the four group sizes); 4 = scale folded into the
+    # weight operand as an exact FP16 hi + lo pair, one drain per tile (G <= 32, where it is the
+    # default).  Forcing either also keeps few-row shapes off the decode kernel.
+    for force in ((2, 4) if g <= 32 else (2,)):
+        lib.texo_mm_int4_force_path(force)
+        try:
+            got = run_case(lib, x, w, s, m, n, k, g)
+        finally:
+            lib.texo_mm_int4_force_path(0)
+        assert lib.texo_mm_int4_last_path() == force
+        assert harness.int4_within_tolerance(got, want, ATOL, RTOL), (shape, force)
+        assert lib.texo_mm_int4_status() == 0
 
 
 @pytest.mark.parametrize("shape", [(1, 4096, 4096), (16, 4096, 4096), (7, 100, 256), (16, 4100, 1024),

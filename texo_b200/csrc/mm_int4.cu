@@ -491,6 +491,266 @@ __global__ void __launch_bounds__(T_THREADS, 1)
   }
 }
 
+// ------------------------------- tensor path for small scale groups (G <= 32)
+// With a drain per scale group the kernel above is bound by tensor-memory traffic: every group
+// moves the whole 128 x 256 FP32 accumulator out through tcgen05.ld (about as long as a
+// 128-k group's MMAs take, and the two do not overlap), so at G = 32 / 16 the drains cost 4x /
+// 8x the MMAs.  For small groups the scale goes INTO the weight operand instead - exactly:
+// w * s (a 4-bit integer times an 11-bit significand) does not fit FP16, but it is the exact
+// sum of two FP16 numbers, hi = RN(w * s) and lo = fma(w, s, -hi) (the rounding error of a
+// product is representable), so each k step issues two MMAs, x * hi and x * lo, into ONE
+// accumulator that runs over the whole K range and is drained once per tile.  Twice the MMA
+// work, no per-group drains: the time no longer depends on the group size (about 0.7 ms for
+// 4096 x 8192 x 8192 against 1.05 / 1.93 ms at G = 32 / 16).  The roundings are those of the
+// FP32 accumulation plus 2^-22 relative from hi + lo - well inside the reference tolerance,
+// unlike a single FP16 product (which the reference found breaks it, src/mm_int4.cu:36-38 of
+// frezcirno/Texo).
+constexpr int S_STAGES = 4;
+constexpr int S_STAGE_BYTES = T_X_BYTES + 2 * T_W_BYTES + T_RAW_BYTES;  // x | hi | lo | packed
+constexpr int S_SMEM_BYTES = S_STAGES * S_STAGE_BYTES + 1024 + 512;
+constexpr int S_REGS_CONTROL = 40, S_REGS_UNPACK = 88, S_REGS_EPILOGUE = 192;  // 128*(40+88) + 256*192 = 65536
+
+struct SplitBarriers {
+  uint64_t ready[S_STAGES];      // even CTA: x bytes of both CTAs landed AND all unpack warps arrived
+  uint64_t raw_full[S_STAGES];   // per CTA: packed nibbles landed
+  uint64_t stage_free[S_STAGES]; // per CTA: the MMAs that read the stage are complete
+  uint64_t acc_full[2];          // per CTA: a tile's MMAs are complete
+  uint64_t acc_empty[2];         // even CTA: epilogue warps of both CTAs arrived
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+__global__ void __launch_bounds__(T_THREADS, 1)
+    tensor_split_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_raw,
+                        const __half* __restrict__ scales, __half* __restrict__ y, int M, int N, int K,
+                        int G, int tiles_n, int tiles_m, int* status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~uintptr_t(1023));
+  SplitBarriers* bars = reinterpret_cast<SplitBarriers*>(smem + S_STAGES * S_STAGE_BYTES);
+  volatile int* abort_flag = &bars->abort_flag;
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  const uint32_t rank = cluster_ctarank();
+  const int cluster_id = blockIdx.x / 2, num_clusters = gridDim.x / 2;
+  const int num_tiles = tiles_n * tiles_m;
+  const int num_kb = K / T_BK;
+  const int groups = K / G;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S_STAGES; ++s) {
+      mbar_init(&bars->ready[s], 1 + 2 * T_CONV_WARPS);
+      mbar_init(&bars->raw_full[s], 1);
+      mbar_init(&bars->stage_free[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&bars->acc_full[b], 1);
+      mbar_init(&bars->acc_empty[b], 2 * T_EPI_WARPS);
+    }
+    bars->abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&map_x);
+    tma_prefetch_desc(&map_raw);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(&bars->tmem_base, 512);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = bars->tmem_base;
+
+  if (warp < T_CONV_WARP0) {
+   asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(S_REGS_CONTROL));
+   if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+      int tn, tm;
+      w4_tile_coords(tile, tiles_n, tiles_m, tn, tm);
+      const int n0 = tn * 256 + int(rank) * 128;
+      const int m0 = tm * 256 + int(rank) * 128;
+      for (int kb = 0; kb < num_kb && ok; ++kb) {
+        if (lane == 0) {
+          ok = mbar_wait(&bars->stage_free[stage], phase ^ 1, abort_flag, status, STATUS_TIMEOUT_EMPTY);
+          if (ok) {
+            uint8_t* sx = smem + stage * S_STAGE_BYTES;
+            uint8_t* sraw = sx + T_X_BYTES + 2 * T_W_BYTES;
+            const uint32_t ready_even = map_to_cta(smem_u32(&bars->ready[stage]), 0);
+            if (rank == 0) mbar_arrive_expect_tx(&bars->ready[stage], 2 * T_X_BYTES);
+            tma_load_2d_pair(sx, &map_x, ready_even, kb * T_BK, m0);
+            mbar_arrive_expect_tx(&bars->raw_full[stage], T_RAW_BYTES);
+            tma_load_2d(sraw, &map_raw, &bars->raw_full[stage], kb * (T_BK / 2), n0);
+          }
+        }
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (++stage == S_STAGES) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+    }
+   } else if (warp == 1) {
+    // ------------------------------------------- MMA issuer (even CTA only)
+    if (rank == 0) {
+      constexpr uint32_t IDESC = umma_idesc(/*D=f32*/ 1, /*A=f16*/ 0, /*B=f16*/ 0, 0, 0, 256, 256);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+        if (lane == 0) {
+          ok = mbar_wait_cluster(&bars->acc_empty[acc], acc_phase ^ 1, abort_flag, status,
+                                 STATUS_TIMEOUT_TMEM_EMPTY);
+          tc_fence_after_sync();
+        }
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        const uint32_t tmem_d = tmem_base + acc * 256;
+        for (int kb = 0; kb < num_kb && ok; ++kb) {
+          if (lane == 0) {
+            ok = mbar_wait(&bars->ready[stage], phase, abort_flag, status, STATUS_TIMEOUT_FULL);
+            if (ok) {
+              tc_fence_after_sync();
+              const uint32_t sx = smem_u32(smem + stage * S_STAGE_BYTES);
+              const uint32_t shi = sx + T_X_BYTES, slo = shi + T_W_BYTES;
+#pragma unroll
+              for (int j = 0; j < T_BK / 16; ++j) {
+                const uint64_t db = smem_desc(sx + j * 32, 16, 1024, SMEM_SWIZZLE_128B);
+                umma_f16_pair(tmem_d, smem_desc(shi + j * 32, 16, 1024, SMEM_SWIZZLE_128B), db, IDESC,
+                              (kb | j) != 0);
+                umma_f16_pair(tmem_d, smem_desc(slo + j * 32, 16, 1024, SMEM_SWIZZLE_128B), db, IDESC, 1);
+              }
+              umma_commit_pair(&bars->stage_free[stage], 3);  // both CTAs' stages reusable
+            }
+          }
+          ok = __shfl_sync(0xffffffffu, ok, 0);
+          if (++stage == S_STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (lane == 0 && ok) umma_commit_pair(&bars->acc_full[acc], 3);
+        __syncwarp();
+        if (++acc == 2) {
+          acc = 0;
+          acc_phase ^= 1;
+        }
+      }
+    }
+   }
+  } else if (warp < T_EPI_WARP0) {
+    // ------------------------- nibble unpacking + exact scaling into hi / lo
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(S_REGS_UNPACK));
+    const int cw = warp - T_CONV_WARP0;
+    const int row = cw * 32 + lane;  // this thread's weight row within the CTA's 128
+    const int gps = T_BK / G;        // scale groups per 64-k stage: 2 (G = 32) or 4 (G = 16)
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+      int tn, tm;
+      w4_tile_coords(tile, tiles_n, tiles_m, tn, tm);
+      const int n = min(tn * 256 + int(rank) * 128 + row, N - 1);
+      const __half* s_row = scales + size_t(n) * groups;
+      for (int kb = 0; kb < num_kb && ok; ++kb) {
+        // this stage's scales (2 or 4 consecutive halves), fetched before the wait
+        __half sc[4];
+#pragma unroll
+        for (int g = 0; g < 4; ++g) sc[g] = g < gps ? s_row[kb * gps + g] : __float2half(0.f);
+        ok = mbar_wait(&bars->raw_full[stage], phase, abort_flag, status, STATUS_TIMEOUT_FULL);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        uint8_t* shi = smem + stage * S_STAGE_BYTES + T_X_BYTES;
+        uint8_t* slo = shi + T_W_BYTES;
+        const uint8_t* sraw = slo + T_W_BYTES;
+        const uint4 lo16 = *reinterpret_cast<const uint4*>(sraw + row * 32);
+        const uint4 hi16 = *reinterpret_cast<const uint4*>(sraw + row * 32 + 16);
+        const uint32_t words[8] = {lo16.x, lo16.y, lo16.z, lo16.w, hi16.x, hi16.y, hi16.z, hi16.w};
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {  // chunk c = k 8c .. 8c+7 of the stage
+          const __half sg = G == 16 ? sc[c >> 1] : sc[c >> 2];  // group of k 8c..8c+7 within the stage
+          const __half2 s2 = __half2half2(sg);
+          const uint4 w = unpack8(words[c]);
+          const uint32_t win[4] = {w.x, w.y, w.z, w.w};
+          uint32_t h[4], l[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const __half2 wv = *reinterpret_cast<const __half2*>(&win[i]);
+            const __half2 hv = __hmul2(wv, s2);            // RN(w * s)
+            const __half2 lv = __hfma2(wv, s2, __hneg2(hv));  // w * s - hi, exact
+            h[i] = *reinterpret_cast<const uint32_t*>(&hv);
+            l[i] = *reinterpret_cast<const uint32_t*>(&lv);
+          }
+          const int at = row * 128 + ((c ^ (row & 7)) << 4);
+          *reinterpret_cast<uint4*>(shi + at) = make_uint4(h[0], h[1], h[2], h[3]);
+          *reinterpret_cast<uint4*>(slo + at) = make_uint4(l[0], l[1], l[2], l[3]);
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_remote(map_to_cta(smem_u32(&bars->ready[stage]), 0));
+        if (++stage == S_STAGES) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(S_REGS_EPILOGUE));
+    const int ew = warp - T_EPI_WARP0;
+    const int quarter = warp % 4;
+    const int half = ew / 4;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+      int tn, tm;
+      w4_tile_coords(tile, tiles_n, tiles_m, tn, tm);
+      const int n = tn * 256 + int(rank) * 128 + quarter * 32 + lane;
+      ok = mbar_wait(&bars->acc_full[acc], acc_phase, abort_flag, status, STATUS_TIMEOUT_TMEM_FULL);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const uint32_t taddr = tmem_base + acc * 256 + half * 128 + (uint32_t(quarter * 32) << 16);
+      const int m_base = tm * 256 + half * 128;
+#pragma unroll 1
+      for (int chunk = 0; chunk < 4; ++chunk) {
+        uint32_t v[32];
+        tmem_ld_32x32(taddr + chunk * 32, v);
+        tmem_ld_wait();
+        if (chunk == 3) {  // everything is in registers: hand the accumulator back
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&bars->acc_empty[acc]), 0));
+        }
+        if (n < N) {
+#pragma unroll
+          for (int jj = 0; jj < 32; ++jj) {
+            const int m = m_base + chunk * 32 + jj;
+            if (m < M) y[size_t(m) * N + n] = __float2half_rn(__uint_as_float(v[jj]));
+          }
+        }
+      }
+      if (++acc == 2) {
+        acc = 0;
+        acc_phase ^= 1;
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc_pair(tmem_base, 512);
+  }
+}
+
 inline int& last_path() {
   static int path = 0;
   return path;
@@ -507,6 +767,58 @@ inline int& forced_path() {
 static bool tensor_path_ok(const __half* x, const uint8_t* w_q, int K, int G) {
   return K > 0 && K % T_BK == 0 && (G == 16 || G == 32 || G == 64 || G == 128) &&
          (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(w_q) & 15) == 0;
+}
+
+// The split-scale kernel for small groups (see tensor_split_kernel): same operands and tensor maps.
+static bool launch_tensor_split(DeviceCtx& ctx, const __half* x, const uint8_t* w_q, const __half* scales,
+                                __half* y, int M, int N, int K, int G) {
+  static bool configured[MAX_DEVICES] = {};
+  static int pairs[MAX_DEVICES] = {};
+  cudaLaunchConfig_t cfg = {};
+  cfg.blockDim = dim3(T_THREADS);
+  cfg.dynamicSmemBytes = S_SMEM_BYTES;
+  cfg.stream = 0;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = 2;
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  if (!configured[ctx.device]) {
+    configured[ctx.device] = true;
+    cudaFuncSetAttribute(tensor_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S_SMEM_BYTES);
+    cfg.gridDim = dim3(2 * ctx.sm_count);
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, tensor_split_kernel, &cfg) != cudaSuccess) {
+      cudaGetLastError();
+      n = 0;
+    }
+    pairs[ctx.device] = n;
+  }
+  if (pairs[ctx.device] <= 0) return false;
+  CUtensorMap map_x, map_raw;
+  if (!make_tensor_map_2d(&map_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, x, M, K, size_t(K) * 2, 128,
+                          T_BK, CU_TENSOR_MAP_SWIZZLE_128B) ||
+      !make_tensor_map_2d(&map_raw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w_q, N, K / 2, K / 2, 128,
+                          T_BK / 2, CU_TENSOR_MAP_SWIZZLE_NONE)) {
+    note_host_error(STATUS_TENSORMAP_FAILED);
+    return false;
+  }
+  const int tiles_n = (N + 255) / 256, tiles_m = (M + 255) / 256;
+  cfg.gridDim = dim3(2 * std::min(tiles_n * tiles_m, pairs[ctx.device]));
+  const int slot = profile_start();
+  if (cudaLaunchKernelEx(&cfg, tensor_split_kernel, map_x, map_raw, scales, y, M, N, K, G, tiles_n, tiles_m,
+                         ctx.status) != cudaSuccess) {
+    cudaGetLastError();
+    profile_stop(slot);
+    note_host_error(STATUS_LAUNCH_FAILED);
+    return false;
+  }
+  profile_stop(slot);
+  ++launch_counter();
+  last_path() = 4;
+  return true;
 }
 
 static bool launch_tensor(DeviceCtx& ctx, const __half* x, const uint8_t* w_q, const __half* scales,
@@ -564,8 +876,7 @@ static bool launch_tensor(DeviceCtx& ctx, const __half* x, const uint8_t* w_q, c
 // 32-row groups a CTA owns (the rest of its 16 warps split K): as many as still give about
 // three quarters of the SMs a CTA, since more rows per CTA means fewer re-reads of x.
 static bool decode_path_ok(const __half* x, const uint8_t* w_q, int M, int N, int K, int G) {
-  (void)N;
-  return M <= 16 && G == 128 && K >= 128 && K % 128 == 0 &&
+  return M <= 16 && G == 128 && K >= 128 && K % 128 == 0 && (long long)N * (K / 2) < (1LL << 31) &&
          (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(w_q) & 15) == 0;
 }
 
@@ -588,15 +899,8 @@ static bool launch_decode(DeviceCtx& ctx, const __half* x, const uint8_t* w_q, c
   }
   if (rowgroups == 0) return false;
   const int grid = (N + 32 * rowgroups - 1) / (32 * rowgroups);
-  // the packed weights as a 2-D tensor [N, K/2] bytes; a box is one row group's 128 k
-  CUtensorMap map_w;
-  if (!make_tensor_map_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w_q, N, K / 2, K / 2, 32, 64,
-                          CU_TENSOR_MAP_SWIZZLE_NONE)) {
-    note_host_error(STATUS_TENSORMAP_FAILED);
-    return false;
-  }
   const int slot = profile_start();
-  decode_kernel<<<grid, D_THREADS, D_SMEM_BYTES>>>(map_w, x, scales, y, M, N, K, rowgroups, ctx.status);
+  decode_kernel<<<grid, D_THREADS, D_SMEM_BYTES>>>(x, w_q, scales, y, M, N, K, rowgroups);
   if (cudaPeekAtLastError() != cudaSuccess) {
     cudaGetLastError();
     profile_stop(slot);
@@ -628,9 +932,13 @@ extern "C" void solve(const __half* x, const uint8_t* w_q, const __half* scales,
   if ((forced_path() == 0 || forced_path() == 3) && ctx.cc_major >= 8 &&
       decode_path_ok(x, w_q, M, N, K, group_size) && launch_decode(ctx, x, w_q, scales, y, M, N, K))
     return;
-  if (forced_path() != 1 && ctx.cc_major >= 10 && tensor_path_ok(x, w_q, K, group_size) &&
-      launch_tensor(ctx, x, w_q, scales, y, M, N, K, group_size))
-    return;
+  if (forced_path() != 1 && ctx.cc_major >= 10 && tensor_path_ok(x, w_q, K, group_size)) {
+    // small groups: the scale goes into the weight operand (path 4), no per-group drain
+    if (group_size <= 32 && forced_path() != 2 &&
+        launch_tensor_split(ctx, x, w_q, scales, y, M, N, K, group_size))
+      return;
+    if (forced_path() != 4 && launch_tensor(ctx, x, w_q, scales, y, M, N, K, group_size)) return;
+  }
   dim3 grid((N + GT - 1) / GT, (M + GT - 1) / GT);
   const int slot = profile_start();
   generic_kernel<<<grid, G_THREADS>>>(x, w_q, scales, y, M, N, K, group_size);

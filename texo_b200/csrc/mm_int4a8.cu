@@ -516,8 +516,7 @@ namespace w4a8 {
 // registers.  Picks how many 32-row groups a CTA owns (the rest of its 16 warps split K): as
 // many as still give about three quarters of the SMs a CTA.
 static bool decode_path_ok(const int8_t* A, const uint8_t* w_q, int M, int N, int K) {
-  (void)N;
-  return M <= 16 && K >= 128 && K % 128 == 0 && K < (1 << 17) &&
+  return M <= 16 && K >= 128 && K % 128 == 0 && K < (1 << 17) && (long long)N * (K / 2) < (1LL << 31) &&
          (reinterpret_cast<uintptr_t>(A) & 15) == 0 && (reinterpret_cast<uintptr_t>(w_q) & 15) == 0;
 }
 
@@ -540,15 +539,8 @@ static bool launch_decode(DeviceCtx& ctx, const int8_t* A, const uint8_t* w_q, i
   }
   if (rowgroups == 0) return false;
   const int grid = (N + 32 * rowgroups - 1) / (32 * rowgroups);
-  // the packed weights as a 2-D tensor [N, K/2] bytes; a box is one row group's 128 k
-  CUtensorMap map_w;
-  if (!make_tensor_map_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w_q, N, K / 2, K / 2, 32, 64,
-                          CU_TENSOR_MAP_SWIZZLE_NONE)) {
-    note_host_error(STATUS_TENSORMAP_FAILED);
-    return false;
-  }
   const int slot = profile_start();
-  decode_kernel<<<grid, E_THREADS, E_SMEM_BYTES>>>(map_w, A, C, M, N, K, q, rowgroups, ctx.status);
+  decode_kernel<<<grid, E_THREADS, E_SMEM_BYTES>>>(A, w_q, C, M, N, K, q, rowgroups);
   if (cudaPeekAtLastError() != cudaSuccess) {
     cudaGetLastError();
     profile_stop(slot);

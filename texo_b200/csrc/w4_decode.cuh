@@ -3,11 +3,10 @@
 // 256-row CTA-pair tensor kernel would spend 15/16 of its MMA work on padding and take several
 // times the HBM time.
 //
-// The weights stay packed until they are in registers: a producer warp streams them through a
-// 128 KiB ring in shared memory with TMA (w4_stream.cuh: half a byte per weight, once in, once
-// out), each consumer warp owns 32 weight rows (four n8 tiles of mma.sync.m16n8k16, f16 x f16
-// -> f32) over a contiguous part of K and picks its 16-byte pieces out of the ring: the four
-// lanes of a quad hold 64 consecutive bytes (128 k) of one weight row.  The MMA's k slots are a
+// Each warp owns 32 weight rows (four n8 tiles of mma.sync.m16n8k16, f16 x f16 -> f32) over a
+// contiguous part of K.  The four lanes of a quad read 4 x 16 = 64 consecutive bytes (128 k)
+// of one weight row straight from global memory into registers (no shared-memory round trip
+// for the weights), D_DEPTH such loads in flight per thread and tile.  The MMA's k slots are a
 // free permutation as long as both operands agree on it: lane j of a quad supplies, in MMA
 // step s, its own nibbles 4s..4s+3, i.e. k = k0 + 32j + 4s + {0,1,2,3}; the matching x values
 // are 4 consecutive halves of an x row, read as 16-byte pieces (two steps each) from a
@@ -19,29 +18,28 @@
 // acc += s[n,g] * partial, so the only roundings are FP32 accumulations (the property the
 // reference kernel keeps, src/mm_int4.cu:31-38 of frezcirno/Texo).  K is split over the warps
 // of a CTA (and summed in a fixed order through shared memory at the end: deterministic) so
-// that narrow problems still fill the SMs.
+// that narrow problems still fill the SMs with loads in flight.
 //
 // Preconditions (otherwise the caller uses another kernel): M <= 16, group_size == 128,
-// K % (128 * ksplit) == 0, x and w_q 16-byte aligned.
+// K % (128 * ksplit) == 0, x and w_q 16-byte aligned, N * K / 2 < 2^31.
 #pragma once
 #include <cstdint>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
-#include "w4_stream.cuh"
-
 namespace texo {
 namespace w4 {
 
-constexpr int D_WARPS = w4s::W_CONSUMER_WARPS;
-constexpr int D_THREADS = w4s::W_THREADS;  // 16 consumer warps + the producer warp
+constexpr int D_WARPS = 16;
+constexpr int D_THREADS = D_WARPS * 32;
 constexpr int D_TILES = 4;   // n8 tiles (32 weight rows) per warp
+constexpr int D_DEPTH = 2;   // 128-k loads in flight per thread and tile
 constexpr int D_JBLK_BYTES = 16 * 64 + 16;        // 16 rows x 32 halves of one j, + bank-shift pad
 constexpr int D_XBLK_BYTES = 4 * D_JBLK_BYTES;    // one 128-k block of x
-constexpr int D_CHUNK_K = 1024;                   // k of x staged per buffer, over all k parts of the CTA
+constexpr int D_CHUNK_K = 2048;                   // k of x staged per buffer, over all k parts of the CTA
 constexpr int D_X_BYTES = (D_CHUNK_K / 128) * D_XBLK_BYTES;
 constexpr int D_RED_BYTES = D_WARPS * D_TILES * 4 * 32 * 4;  // FP32 partial results of every warp
-constexpr int D_SMEM_BYTES = 2 * D_X_BYTES + w4s::W_RING_BYTES + 1024 + 512;
+constexpr int D_SMEM_BYTES = 2 * D_X_BYTES + 128;
 static_assert(D_RED_BYTES <= 2 * D_X_BYTES, "the final reduction reuses the x buffers");
 
 __device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -65,7 +63,7 @@ __device__ __forceinline__ void stage_x(uint8_t* buf, const __half* __restrict__
                                         int k_first, int part_k, int ksplit, int span) {
   const int pieces_per_part = span / 8;  // 16-byte pieces (8 halves) per row and part
   const int pieces_per_row = ksplit * pieces_per_part;
-  for (int i = threadIdx.x; i < 16 * pieces_per_row; i += D_WARPS * 32) {
+  for (int i = threadIdx.x; i < 16 * pieces_per_row; i += D_THREADS) {
     const int m = i / pieces_per_row, piece = i % pieces_per_row;
     const int p = piece / pieces_per_part, within = (piece % pieces_per_part) * 8;
     const int k_in_part = k_first + within;
@@ -79,42 +77,35 @@ __device__ __forceinline__ void stage_x(uint8_t* buf, const __half* __restrict__
 // grid.x CTAs, each owning 32 * rowgroups weight rows; ksplit = D_WARPS / rowgroups warps share
 // a row group, each taking K / ksplit of the k range.
 __global__ void __launch_bounds__(D_THREADS, 1)
-    decode_kernel(const __grid_constant__ CUtensorMap map_w, const __half* __restrict__ x,
+    decode_kernel(const __half* __restrict__ x, const uint8_t* __restrict__ w_q,
                   const __half* __restrict__ scales, __half* __restrict__ y, int M, int N, int K,
-                  int rowgroups, int* status) {
+                  int rowgroups) {
   extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* ring = smem + 2 * D_X_BYTES;
-  w4s::StreamBarriers* bars = reinterpret_cast<w4s::StreamBarriers*>(ring + w4s::W_RING_BYTES);
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   const int r = lane / 4, j = lane % 4;
   const int ksplit = D_WARPS / rowgroups;
-  const int part_k = K / ksplit;        // a multiple of 128
-  const int iters = part_k / 128;       // 128-k iterations (= scale groups) of a warp
-  const int stages = w4s::stream_stages(rowgroups);
-  w4s::stream_init(bars, stages, rowgroups);
-  __syncthreads();
-  if (warp == D_WARPS) {  // the producer warp
-    w4s::stream_produce(&map_w, ring, bars, stages, rowgroups, ksplit, iters, part_k,
-                        blockIdx.x * rowgroups * 32, status);
-    return;
-  }
   const int rg = warp % rowgroups, part = warp / rowgroups;
+  const int part_k = K / ksplit;        // a multiple of 128
   const int span = D_CHUNK_K / ksplit;  // k per part per staged chunk, a multiple of 128
   const int ipc = span / 128;           // iterations per chunk
+  const int iters = part_k / 128;       // 128-k iterations (= scale groups) of this warp
   const int chunks = (iters + ipc - 1) / ipc;
   const int groups = K / 128;
   const int n_base = (blockIdx.x * rowgroups + rg) * 32;
 
-  // element offsets of the scales of the two output columns this thread holds per tile (C
-  // fragment: columns 2j, 2j+1), rows clamped so that the loads of a ragged last block stay
-  // inside the matrix
-  uint32_t s_off[D_TILES][2];
+  // byte offset of this lane's first 16 bytes in each tile's weight row (rows clamped so that
+  // loads of a ragged last block stay inside the matrix), and the element offsets of the
+  // scales of the two output columns this thread holds per tile (C fragment: columns 2j, 2j+1)
+  uint32_t w_off[D_TILES], s_off[D_TILES][2];
 #pragma unroll
-  for (int t = 0; t < D_TILES; ++t)
+  for (int t = 0; t < D_TILES; ++t) {
+    w_off[t] = uint32_t(min(n_base + t * 8 + r, N - 1)) * uint32_t(K / 2) + uint32_t(part) * uint32_t(part_k / 2) +
+               uint32_t(j * 16);
 #pragma unroll
     for (int e = 0; e < 2; ++e)
       s_off[t][e] = uint32_t(min(n_base + t * 8 + 2 * j + e, N - 1)) * uint32_t(groups) + uint32_t(part * iters);
+  }
 
   float total[D_TILES][4];
 #pragma unroll
@@ -122,28 +113,32 @@ __global__ void __launch_bounds__(D_THREADS, 1)
 #pragma unroll
     for (int e = 0; e < 4; ++e) total[t][e] = 0.f;
 
+  // weight ring: D_DEPTH iterations of 128 k in flight
+  uint4 ring[D_DEPTH][D_TILES];
+#pragma unroll
+  for (int d = 0; d < D_DEPTH; ++d)
+#pragma unroll
+    for (int t = 0; t < D_TILES; ++t)
+      ring[d][t] = d < iters ? __ldcs(reinterpret_cast<const uint4*>(w_q + w_off[t] + d * 64))
+                             : make_uint4(0, 0, 0, 0);
+
   stage_x(smem, x, M, K, 0, part_k, ksplit, span);
   asm volatile("cp.async.commit_group;" ::: "memory");
 
-  bool ok = true;
 #pragma unroll 1
-  for (int it = 0; it < iters; ++it) {
-    {
+  for (int it0 = 0; it0 < iters; it0 += D_DEPTH) {
+#pragma unroll
+    for (int d = 0; d < D_DEPTH; ++d) {
+      const int it = it0 + d;
+      if (it >= iters) break;  // uniform over the CTA
       const int c = it / ipc;
-      if (it % ipc == 0) {  // entering chunk c (uniform over the consumers)
-        w4s::consumer_sync();  // everyone is done with chunk c - 1, whose buffer is refilled now
+      if (it % ipc == 0) {  // entering chunk c (uniform over the CTA)
+        __syncthreads();    // everyone is done with chunk c - 1, whose buffer is refilled now
         if (c + 1 < chunks)
           stage_x(smem + ((c + 1) & 1) * D_X_BYTES, x, M, K, (c + 1) * span, part_k, ksplit, span);
         asm volatile("cp.async.commit_group;" ::: "memory");
         asm volatile("cp.async.wait_group 1;" ::: "memory");
-        w4s::consumer_sync();  // chunk c has landed for every thread
-      }
-      // this iteration's packed weights: four tiles x 16 bytes, out of the TMA ring
-      uint4 wq[D_TILES];
-      if (ok) ok = w4s::stream_take(ring, bars, stages, rowgroups, ksplit, it, part, rg, r, j, wq, status);
-      if (!ok) {  // a wait gave up: keep meeting the other consumers at the barriers, compute nothing
-#pragma unroll
-        for (int t = 0; t < D_TILES; ++t) wq[t] = make_uint4(0, 0, 0, 0);
+        __syncthreads();  // chunk c has landed for every thread
       }
       // x fragments of this 128-k block: rows r and r + 8, this lane's 64 bytes of each
       const uint8_t* xb = smem + (c & 1) * D_X_BYTES + (part * ipc + it % ipc) * D_XBLK_BYTES + j * D_JBLK_BYTES;
@@ -159,11 +154,17 @@ __global__ void __launch_bounds__(D_THREADS, 1)
         const uint4 lo = x_lo[q4], hi = x_hi[q4];
 #pragma unroll
         for (int t = 0; t < D_TILES; ++t) {
-          const uint32_t word = q4 == 0 ? wq[t].x : q4 == 1 ? wq[t].y : q4 == 2 ? wq[t].z : wq[t].w;
+          const uint32_t word = q4 == 0 ? ring[d][t].x : q4 == 1 ? ring[d][t].y : q4 == 2 ? ring[d][t].z : ring[d][t].w;
           const uint4 b = unpack8(word);  // 8 nibbles -> halves (k0,k1) (k2,k3) (k4,k5) (k6,k7)
           mma_16816(acc[t], lo.x, hi.x, lo.y, hi.y, b.x, b.y);
           mma_16816(acc[t], lo.z, hi.z, lo.w, hi.w, b.z, b.w);
         }
+      }
+      // this slot's next load: D_DEPTH iterations ahead
+      if (it + D_DEPTH < iters) {
+#pragma unroll
+        for (int t = 0; t < D_TILES; ++t)
+          ring[d][t] = __ldcs(reinterpret_cast<const uint4*>(w_q + w_off[t] + (it + D_DEPTH) * 64));
       }
       // fold the group's partial in with its scale
 #pragma unroll
@@ -181,13 +182,13 @@ __global__ void __launch_bounds__(D_THREADS, 1)
 
   // sum the k parts in a fixed order through shared memory (the x buffers are free now)
   float* red = reinterpret_cast<float*>(smem);
-  w4s::consumer_sync();
+  __syncthreads();
 #pragma unroll
   for (int t = 0; t < D_TILES; ++t)
 #pragma unroll
     for (int e = 0; e < 4; ++e) red[((warp * D_TILES + t) * 4 + e) * 32 + lane] = total[t][e];
-  w4s::consumer_sync();
-  if (part == 0 && ok) {
+  __syncthreads();
+  if (part == 0) {
 #pragma unroll
     for (int t = 0; t < D_TILES; ++t) {
       float out[4] = {0.f, 0.f, 0.f, 0.f};

@@ -1,15 +1,13 @@
 // W4A8 for few activation rows (decode): C [M,N] int8 = requantised A [M,K] (int8) times the
 // packed INT4 weights w_q [N,K/2], M <= 16.  Same plan as the W4A16 decode kernel
 // (w4_decode.cuh): the packed weights - the only large operand - are read from HBM exactly
-// once and stay packed until they are in registers: a producer warp streams them through a
-// 128 KiB ring in shared memory with TMA (w4_stream.cuh), the consumer warps pick their
-// 16-byte pieces out of it (four lanes of a quad cover 64 consecutive bytes = 128 k of one
-// weight row), expand them to unsigned bytes 0..15 in registers (two masks and two byte
-// permutes per eight weights) and multiply on the tensor cores with mma.sync.m16n8k32
-// (s8 x u8 -> s32).  Only half a byte per weight ever crosses shared memory, once in and once
-// out; the unpacked operand never does, which is what bounded the TMA + unpack-warps +
-// tcgen05 form of this path.  The k slots of an MMA are a free permutation as long as both
-// operands agree: lane j of a quad supplies, in step s, its own nibbles 8s..8s+7, i.e.
+// once, by 16-byte loads straight into registers (four lanes of a quad cover 64 consecutive
+// bytes = 128 k of one weight row, several such loads in flight per thread), expanded to
+// unsigned bytes 0..15 in registers (two masks and two byte permutes per eight weights) and
+// multiplied on the tensor cores by mma.sync.m16n8k32 (s8 x u8 -> s32).  Nothing of the
+// weights ever crosses shared memory, which is what bounded the TMA + unpack-warps form of
+// this path.  The k slots of an MMA are a free permutation as long as both operands agree:
+// lane j of a quad supplies, in step s, its own nibbles 8s..8s+7, i.e.
 // k = k0 + 32j + 8s + {0..7}; the matching activations are 8 consecutive bytes of a row of A,
 // read from a shared-memory copy of A in its natural order (rows padded by 16 bytes, which
 // makes the quad's 16-byte reads bank-conflict free).
@@ -21,28 +19,28 @@
 //   dot = sum a*u - (zB+8) rowsum(A) - zA rowsum(u) + K zA (zB+8),  u = q + 8.
 //
 // Preconditions (otherwise the caller uses another kernel): M <= 16, K % 128 == 0, K < 2^17,
-// A and w_q 16-byte aligned.
+// A and w_q 16-byte aligned, N * K / 2 < 2^31.
 #pragma once
 #include <cstdint>
 #include <cuda_runtime.h>
 
 #include "requant.cuh"
-#include "w4_stream.cuh"
 
 namespace texo {
 namespace w4a8 {
 
-constexpr int E_WARPS = w4s::W_CONSUMER_WARPS;
-constexpr int E_THREADS = w4s::W_THREADS;  // 16 consumer warps + the producer warp
+constexpr int E_WARPS = 16;
+constexpr int E_THREADS = E_WARPS * 32;
 constexpr int E_TILES = 4;   // n8 tiles (32 weight rows) per warp
+constexpr int E_DEPTH = 3;   // 128-k loads in flight per thread and tile
 constexpr int E_ROW_BYTES = 128 + 16;           // one 128-k block of one activation row + pad
 constexpr int E_ABLK_BYTES = 16 * E_ROW_BYTES;  // one 128-k block of A (16 rows)
-constexpr int E_CHUNK_K = 2048;                 // k of A staged per buffer, over all k parts of the CTA
+constexpr int E_CHUNK_K = 4096;                 // k of A staged per buffer, over all k parts of the CTA
 constexpr int E_A_BYTES = (E_CHUNK_K / 128) * E_ABLK_BYTES;
 // reduction area: per warp 4 tiles x 4 accumulators + 4 nibble sums + 2 row sums, x 32 lanes
 constexpr int E_RED_WORDS = E_TILES * 4 + E_TILES + 2;
 constexpr int E_RED_BYTES = E_WARPS * E_RED_WORDS * 32 * 4;
-constexpr int E_SMEM_BYTES = 2 * E_A_BYTES + w4s::W_RING_BYTES + 1024 + 512;
+constexpr int E_SMEM_BYTES = 2 * E_A_BYTES + 128;
 static_assert(E_RED_BYTES <= 2 * E_A_BYTES, "the final reduction reuses the activation buffers");
 
 __device__ __forceinline__ void mma_s8u8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -66,7 +64,7 @@ __device__ __forceinline__ void stage_a(uint8_t* buf, const int8_t* __restrict__
                                         int k_first, int part_k, int ksplit, int span) {
   const int pieces_per_part = span / 16;
   const int pieces_per_row = ksplit * pieces_per_part;
-  for (int i = threadIdx.x; i < 16 * pieces_per_row; i += E_WARPS * 32) {
+  for (int i = threadIdx.x; i < 16 * pieces_per_row; i += E_THREADS) {
     const int m = i / pieces_per_row, piece = i % pieces_per_row;
     const int p = piece / pieces_per_part, within = (piece % pieces_per_part) * 16;
     const int k_in_part = k_first + within;
@@ -81,30 +79,26 @@ __device__ __forceinline__ void stage_a(uint8_t* buf, const int8_t* __restrict__
 // a row group, each taking K / ksplit of the k range.  q.zb already includes the +8 of the
 // unsigned nibbles (per-channel: q.zb_bias = 8 is added to zb_vec[n]).
 __global__ void __launch_bounds__(E_THREADS, 1)
-    decode_kernel(const __grid_constant__ CUtensorMap map_w, const int8_t* __restrict__ A,
-                  int8_t* __restrict__ C, int M, int N, int K, i8::Quant q, int rowgroups, int* status) {
+    decode_kernel(const int8_t* __restrict__ A, const uint8_t* __restrict__ w_q, int8_t* __restrict__ C,
+                  int M, int N, int K, i8::Quant q, int rowgroups) {
   extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* ring = smem + 2 * E_A_BYTES;
-  w4s::StreamBarriers* bars = reinterpret_cast<w4s::StreamBarriers*>(ring + w4s::W_RING_BYTES);
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   const int r = lane / 4, j = lane % 4;
   const int ksplit = E_WARPS / rowgroups;
-  const int part_k = K / ksplit;        // a multiple of 128
-  const int iters = part_k / 128;
-  const int stages = w4s::stream_stages(rowgroups);
-  w4s::stream_init(bars, stages, rowgroups);
-  __syncthreads();
-  if (warp == E_WARPS) {  // the producer warp
-    w4s::stream_produce(&map_w, ring, bars, stages, rowgroups, ksplit, iters, part_k,
-                        blockIdx.x * rowgroups * 32, status);
-    return;
-  }
   const int rg = warp % rowgroups, part = warp / rowgroups;
+  const int part_k = K / ksplit;        // a multiple of 128
   const int span = E_CHUNK_K / ksplit;  // k per part per staged chunk, a multiple of 128
   const int ipc = span / 128;           // iterations per chunk
+  const int iters = part_k / 128;
   const int chunks = (iters + ipc - 1) / ipc;
   const int n_base = (blockIdx.x * rowgroups + rg) * 32;
+
+  uint32_t w_off[E_TILES];
+#pragma unroll
+  for (int t = 0; t < E_TILES; ++t)
+    w_off[t] = uint32_t(min(n_base + t * 8 + r, N - 1)) * uint32_t(K / 2) + uint32_t(part) * uint32_t(part_k / 2) +
+               uint32_t(j * 16);
 
   int acc[E_TILES][4];
   int usum[E_TILES];      // sum of this lane's nibbles of weight row n_base + 8t + r
@@ -116,28 +110,31 @@ __global__ void __launch_bounds__(E_THREADS, 1)
     for (int e = 0; e < 4; ++e) acc[t][e] = 0;
   }
 
+  uint4 ring[E_DEPTH][E_TILES];
+#pragma unroll
+  for (int d = 0; d < E_DEPTH; ++d)
+#pragma unroll
+    for (int t = 0; t < E_TILES; ++t)
+      ring[d][t] = d < iters ? __ldcs(reinterpret_cast<const uint4*>(w_q + w_off[t] + d * 64))
+                             : make_uint4(0, 0, 0, 0);
+
   stage_a(smem, A, M, K, 0, part_k, ksplit, span);
   asm volatile("cp.async.commit_group;" ::: "memory");
 
-  bool ok = true;
 #pragma unroll 1
-  for (int it = 0; it < iters; ++it) {
-    {
+  for (int it0 = 0; it0 < iters; it0 += E_DEPTH) {
+#pragma unroll
+    for (int d = 0; d < E_DEPTH; ++d) {
+      const int it = it0 + d;
+      if (it >= iters) break;  // uniform over the CTA
       const int c = it / ipc;
-      if (it % ipc == 0) {  // entering chunk c (uniform over the consumers)
-        w4s::consumer_sync();  // everyone is done with chunk c - 1, whose buffer is refilled now
+      if (it % ipc == 0) {  // entering chunk c (uniform over the CTA)
+        __syncthreads();    // everyone is done with chunk c - 1, whose buffer is refilled now
         if (c + 1 < chunks)
           stage_a(smem + ((c + 1) & 1) * E_A_BYTES, A, M, K, (c + 1) * span, part_k, ksplit, span);
         asm volatile("cp.async.commit_group;" ::: "memory");
         asm volatile("cp.async.wait_group 1;" ::: "memory");
-        w4s::consumer_sync();  // chunk c has landed for every thread
-      }
-      // this iteration's packed weights: four tiles x 16 bytes, out of the TMA ring
-      uint4 wq[E_TILES];
-      if (ok) ok = w4s::stream_take(ring, bars, stages, rowgroups, ksplit, it, part, rg, r, j, wq, status);
-      if (!ok) {  // a wait gave up: keep meeting the other consumers at the barriers, compute nothing
-#pragma unroll
-        for (int t = 0; t < E_TILES; ++t) wq[t] = make_uint4(0, 0, 0, 0);
+        __syncthreads();  // chunk c has landed for every thread
       }
       // this lane's 32 bytes of activation rows r and r + 8 in this 128-k block
       const uint8_t* ab = smem + (c & 1) * E_A_BYTES + (part * ipc + it % ipc) * E_ABLK_BYTES + j * 32;
@@ -159,8 +156,8 @@ __global__ void __launch_bounds__(E_THREADS, 1)
 #pragma unroll
         for (int t = 0; t < E_TILES; ++t) {
           // two packed words = 16 nibbles = this lane's k of steps 2h and 2h + 1
-          const uint32_t w0 = h == 0 ? wq[t].x : wq[t].z;
-          const uint32_t w1 = h == 0 ? wq[t].y : wq[t].w;
+          const uint32_t w0 = h == 0 ? ring[d][t].x : ring[d][t].z;
+          const uint32_t w1 = h == 0 ? ring[d][t].y : ring[d][t].w;
           const uint32_t e0 = (w0 >> 4) & 0x0f0f0f0fu, o0 = w0 & 0x0f0f0f0fu;  // even / odd k
           const uint32_t e1 = (w1 >> 4) & 0x0f0f0f0fu, o1 = w1 & 0x0f0f0f0fu;
           usum[t] = int(__dp4a(e0 + o0, 0x01010101u, unsigned(usum[t])));
@@ -168,6 +165,11 @@ __global__ void __launch_bounds__(E_THREADS, 1)
           mma_s8u8(acc[t], lo.x, hi.x, lo.y, hi.y, __byte_perm(e0, o0, 0x5140), __byte_perm(e0, o0, 0x7362));
           mma_s8u8(acc[t], lo.z, hi.z, lo.w, hi.w, __byte_perm(e1, o1, 0x5140), __byte_perm(e1, o1, 0x7362));
         }
+      }
+      if (it + E_DEPTH < iters) {
+#pragma unroll
+        for (int t = 0; t < E_TILES; ++t)
+          ring[d][t] = __ldcs(reinterpret_cast<const uint4*>(w_q + w_off[t] + (it + E_DEPTH) * 64));
       }
     }
   }
@@ -187,7 +189,7 @@ __global__ void __launch_bounds__(E_THREADS, 1)
 
   // add the k parts through shared memory (the activation buffers are free now)
   int* red = reinterpret_cast<int*>(smem);
-  w4s::consumer_sync();
+  __syncthreads();
   {
     int* mine = red + warp * E_RED_WORDS * 32 + lane;
 #pragma unroll
@@ -199,8 +201,8 @@ __global__ void __launch_bounds__(E_THREADS, 1)
     mine[(E_TILES * 5 + 0) * 32] = asum[0];
     mine[(E_TILES * 5 + 1) * 32] = asum[1];
   }
-  w4s::consumer_sync();
-  if (part == 0 && ok) {
+  __syncthreads();
+  if (part == 0) {
     // rowsum(A) of rows r and r + 8: parts of row group 0 (warps p * rowgroups)
     long long row_sum[2] = {0, 0};
     for (int p = 0; p < ksplit; ++p) {
