@@ -1239,12 +1239,17 @@ def main():
     ap.add_argument("--no-extras", action="store_true",
                     help="only the headline measurement (no configs / layers / parity / reference kernel)")
     ap.add_argument("--no-sustained", action="store_true")
+    ap.add_argument("--group-size", type=int, default=None,
+                    help="scale group size for the int4_w4a16 workload (16, 32, 64 or 128; default 128)")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup)
     if args.workload == "layer_sweep":
         run_layer_sweep(args)
         return
     spec = workload_spec(args.workload)
+    if args.group_size and spec["op"] == "mm_int4" and spec["M"] > 32:
+        spec["G"] = args.group_size
+        spec["desc"] = spec["desc"].replace("G=128", f"G={args.group_size}")
     if args.steps is None:
         # about a second of GPU work, so that clocks under load are actually sampled
         args.steps = {"int8_8192": 2000, "int8_8192_presummed": 2000, "int8_decode": 10000,

@@ -73,7 +73,7 @@ def test_harness_default_cases(lib, oracle):
             path = lib.texo_mm_int4_last_path()
             lib.texo_mm_int4_force_path(0)
             want_path = (1 if force == 1 else 3 if _takes_decode_path(m, k, g) else
-                         (4 if g <= 32 else 2) if _takes_tensor_path(k, g) else 1)
+                         (4 if g <= 64 else 2) if _takes_tensor_path(k, g) else 1)
             assert path == want_path, (m, n, k, g, force)
             assert harness.int4_within_tolerance(got, want, ATOL, RTOL), (m, n, k, g, force)
     # zero scales: first, middle, last group and an all-zero column (tests/mm_int4.cpp:166-175)
@@ -106,7 +106,7 @@ def test_tensor_path_full_matrix(lib, oracle, shape):
     # 2 = a TMEM drain per scale group (any of the four group sizes); 4 = scale folded into the
     # weight operand as an exact FP16 hi + lo pair, one drain per tile (G <= 32, where it is the
     # default).  Forcing either also keeps few-row shapes off the decode kernel.
-    for force in ((2, 4) if g <= 32 else (2,)):
+    for force in ((2, 4) if g <= 64 else (2,)):
         lib.texo_mm_int4_force_path(force)
         try:
             got = run_case(lib, x, w, s, m, n, k, g)

@@ -505,6 +505,7 @@ __global__ void __launch_bounds__(T_THREADS, 1)
 // FP32 accumulation plus 2^-22 relative from hi + lo - well inside the reference tolerance,
 // unlike a single FP16 product (which the reference found breaks it, src/mm_int4.cu:36-38 of
 // frezcirno/Texo).
+constexpr int W4_SPLIT_MAX_GROUP = 64;  // largest group size routed to this kernel by default
 constexpr int S_STAGES = 4;
 constexpr int S_STAGE_BYTES = T_X_BYTES + 2 * T_W_BYTES + T_RAW_BYTES;  // x | hi | lo | packed
 constexpr int S_SMEM_BYTES = S_STAGES * S_STAGE_BYTES + 1024 + 512;
@@ -647,7 +648,7 @@ __global__ void __launch_bounds__(T_THREADS, 1)
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(S_REGS_UNPACK));
     const int cw = warp - T_CONV_WARP0;
     const int row = cw * 32 + lane;  // this thread's weight row within the CTA's 128
-    const int gps = T_BK / G;        // scale groups per 64-k stage: 2 (G = 32) or 4 (G = 16)
+    const int gps = T_BK / G;        // scale groups per 64-k stage: 1 (G = 64), 2 (G = 32) or 4 (G = 16)
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
@@ -672,7 +673,8 @@ __global__ void __launch_bounds__(T_THREADS, 1)
         const uint32_t words[8] = {lo16.x, lo16.y, lo16.z, lo16.w, hi16.x, hi16.y, hi16.z, hi16.w};
 #pragma unroll
         for (int c = 0; c < 8; ++c) {  // chunk c = k 8c .. 8c+7 of the stage
-          const __half sg = G == 16 ? sc[c >> 1] : sc[c >> 2];  // group of k 8c..8c+7 within the stage
+          // the scale group of k 8c..8c+7 within the stage
+          const __half sg = G == 16 ? sc[c >> 1] : G == 32 ? sc[c >> 2] : sc[0];
           const __half2 s2 = __half2half2(sg);
           const uint4 w = unpack8(words[c]);
           const uint32_t win[4] = {w.x, w.y, w.z, w.w};
@@ -934,7 +936,7 @@ extern "C" void solve(const __half* x, const uint8_t* w_q, const __half* scales,
     return;
   if (forced_path() != 1 && ctx.cc_major >= 10 && tensor_path_ok(x, w_q, K, group_size)) {
     // small groups: the scale goes into the weight operand (path 4), no per-group drain
-    if (group_size <= 32 && forced_path() != 2 &&
+    if (group_size <= W4_SPLIT_MAX_GROUP && forced_path() != 2 &&
         launch_tensor_split(ctx, x, w_q, scales, y, M, N, K, group_size))
       return;
     if (forced_path() != 4 && launch_tensor(ctx, x, w_q, scales, y, M, N, K, group_size)) return;
