@@ -30,15 +30,12 @@ struct DeviceCtx {
   // (the kernel that consumes it cleans up after itself); zeroed when (re)allocated.
   void* workspace = nullptr;
   size_t workspace_bytes = 0;
-  // Device-wide "work items finished" counter of the INT8 CTA-pair kernel (status word
-  // STATUS_WORD_ITEMS_DONE): it only ever grows; this is the value it will show when every
-  // call launched so far has finished its items.
-  unsigned items_expected = 0;
+  // Epoch number of the last INT8 CTA-pair call: its epilogues mark finished sum items in the
+  // scratch with it (flags are compared, never cleared; the scratch is zeroed when allocated).
+  unsigned sums_epoch = 0;
+  void* item_flags = nullptr;  // used by nothing else, so that no other data can pass for an epoch
+  size_t item_flag_bytes = 0;
 };
-
-// Layout of the 64-int status block: word 0 = first device error code, word 8 = the item
-// counter above, word 32 = scratch of the wait self-test.
-constexpr int STATUS_WORD_ITEMS_DONE = 8;
 
 inline int& host_status() {
   static int value = 0;
@@ -84,6 +81,24 @@ inline void* device_scratch(DeviceCtx& ctx, size_t bytes) {
   return ctx.scratch;
 }
 
+// Grow-only, zero-initialised flag array of the INT8 CTA-pair kernel (see DeviceCtx::sums_epoch).
+inline unsigned* device_item_flags(DeviceCtx& ctx, size_t bytes) {
+  if (bytes > ctx.item_flag_bytes) {
+    if (ctx.item_flags) cudaFree(ctx.item_flags);
+    ctx.item_flags = nullptr;
+    ctx.item_flag_bytes = 0;
+    const size_t want = (bytes + 4095) & ~size_t(4095);
+    if (cudaMalloc(&ctx.item_flags, want) != cudaSuccess) {
+      cudaGetLastError();
+      std::fprintf(stderr, "texo_b200: flag allocation of %zu bytes failed\n", want);
+      return nullptr;
+    }
+    cudaMemsetAsync(ctx.item_flags, 0, want, 0);
+    ctx.item_flag_bytes = want;
+  }
+  return static_cast<unsigned*>(ctx.item_flags);
+}
+
 // Grow-only, zero-initialised workspace (see DeviceCtx::workspace).
 inline void* device_workspace(DeviceCtx& ctx, size_t bytes) {
   if (bytes > ctx.workspace_bytes) {
@@ -113,9 +128,6 @@ inline int read_and_clear_status() {
       cudaMemset(ctx.status, 0, sizeof(int));
       // a kernel that gave up may have left partial sums behind
       if (ctx.workspace) cudaMemset(ctx.workspace, 0, ctx.workspace_bytes);
-      // ... and may not have counted all of its items: put the counter where the host expects it
-      cudaMemcpy(ctx.status + STATUS_WORD_ITEMS_DONE, &ctx.items_expected, sizeof(unsigned),
-                 cudaMemcpyHostToDevice);
     }
   }
   if (code == 0) code = host_status();

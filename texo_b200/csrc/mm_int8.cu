@@ -483,126 +483,145 @@ __global__ void __launch_bounds__(MMA_THREADS, 1)
 }
 
 // ------------------------------------------- sums inside the CTA-pair kernel
-// The CTA-pair kernel needs no pre-pass: its eight epilogue warps have nothing to drain while
-// the first tile's MMAs run, and in that time they compute rowsum(A) / colsum(B) themselves -
-// the work of sums_kernel, dealt over all CTAs of the grid (item = blockIdx.x, += gridDim.x),
-// with the same access pattern (64 columns x all K per column item, 16 rows per row item,
-// eight 16-byte loads in flight per thread; the bytes are the ones the TMA producer is
-// pulling through L2 anyway).  Every CTA publishes how many items it has finished on a
-// device-wide counter; before its first drain an epilogue warp waits (bounded) until the
-// counter shows that all items of this call are done.  All CTAs of the grid are resident at
-// once (the grid never exceeds the number of CTA pairs the device can hold), so the wait
-// cannot starve the CTAs it waits for.  The counter is never cleared: the host hands each
-// call the value it will have when that call's items are complete.
+// The CTA-pair kernel needs no pre-pass: its eight epilogue warps compute rowsum(A) /
+// colsum(B) themselves, in the time they would otherwise spend waiting for accumulators.  The
+// work is cut into items (64 columns of B over all K, or 16 rows of A: the access pattern of
+// sums_kernel; the bytes are the ones the TMA producer is pulling through L2 anyway), put in
+// the order in which the tiles need them - the rows of the first eight tile rows, then the
+// column items from left to right (the raster walks eight tile rows column by column), then
+// the remaining rows - and dealt round robin over all CTAs of the grid (position blockIdx.x,
+// += gridDim.x).  Every finished item is published by storing the call's epoch number into
+// its flag (the flags are never cleared: an epoch is used once).  Before it drains a tile an
+// epilogue waits for exactly the flags of that tile's rows and columns - and while it waits,
+// for them or for the accumulator, it keeps working through its own items, so a CTA only ever
+// blocks when it has none left: no cycle of CTAs waiting for one another can form, and since
+// all CTAs of the grid are resident at once (the grid never exceeds what the device holds)
+// every item's owner is running.  The items the first wave of tiles needs are finished
+// within the first few microseconds, long before the first accumulators are.
 constexpr int ES_THREADS = EPI_WARPS * 32;                        // 256 epilogue threads
 constexpr int ES_KLANES = ES_THREADS / SUM_TX;                    // k lanes of a column item
 constexpr int ES_PART_BYTES = EPI_WARPS * (SUM_COLS + 1) * 4;     // partials of a column item
-constexpr int P_AUX_SMEM_BYTES = 2304;                            // >= ES_PART_BYTES
-static_assert(ES_PART_BYTES <= P_AUX_SMEM_BYTES, "sums partials outgrew their shared-memory reserve");
+constexpr int P_AUX_SMEM_BYTES = 2304;                            // >= ES_PART_BYTES + the decision words
+static_assert(ES_PART_BYTES + 64 <= P_AUX_SMEM_BYTES, "sums partials outgrew their shared-memory reserve");
+constexpr int ES_FIRST_ROW_ITEMS = P_GROUP_M * 256 / SUM_ROWS;    // row items of the first eight tile rows
 
 __device__ __forceinline__ void epilogue_bar() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
-// Returns the number of items this CTA processed.  `et` = index among the 256 epilogue threads.
-__device__ __forceinline__ int epilogue_sums(const int8_t* __restrict__ A, const int8_t* __restrict__ B,
-                                             int* __restrict__ row_sum, int* __restrict__ col_sum,
-                                             int M, int N, int K, int col_items, int row_items,
-                                             int (*part)[SUM_COLS + 1], int et) {
-  const int warp = et / 32, lane = et % 32;
-  int done = 0;
-  for (int item = blockIdx.x; item < col_items + row_items; item += gridDim.x, ++done) {
-    if (item < col_items) {
-      const int tx = et % SUM_TX, ty = et / SUM_TX;
-      const int n = item * SUM_COLS + tx * 16;
-      int acc[16] = {};
-      if (n < N) {
-        // (sixteen 16-byte loads in flight per thread: the phase is bound by load latency
-        // under the tensor kernel's own L2 traffic, not by the additions)
-        const int8_t* col = B + n;
-        int k = ty;
-        for (; k + 15 * ES_KLANES < K; k += 16 * ES_KLANES) {
-          int4 v[16];
-#pragma unroll
-          for (int u = 0; u < 16; ++u)
-            v[u] = __ldg(reinterpret_cast<const int4*>(col + size_t(k + u * ES_KLANES) * N));
-#pragma unroll
-          for (int u = 0; u < 16; ++u) add_bytes(acc, v[u]);
-        }
-        for (; k < K; k += ES_KLANES)
-          add_bytes(acc, __ldg(reinterpret_cast<const int4*>(col + size_t(k) * N)));
-      }
-#pragma unroll
-      for (int i = 0; i < 16; ++i) {
-#pragma unroll
-        for (int o = SUM_TX; o < 32; o <<= 1) acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], o);
-      }
-      epilogue_bar();  // the previous item's readers are done with `part`
-      if (lane < SUM_TX) {
-#pragma unroll
-        for (int i = 0; i < 16; ++i) part[warp][tx * 16 + i] = acc[i];
-      }
-      epilogue_bar();
-      if (et < SUM_COLS) {
-        int total = 0;
-#pragma unroll
-        for (int r = 0; r < EPI_WARPS; ++r) total += part[r][et];
-        const int out = item * SUM_COLS + et;
-        if (out < N) col_sum[out] = total;
-      }
-    } else {
-      for (int r = warp; r < SUM_ROWS; r += EPI_WARPS) {
-        const int m = (item - col_items) * SUM_ROWS + r;
-        if (m >= M) continue;
-        const int4* a = reinterpret_cast<const int4*>(A + size_t(m) * K);
-        const int chunks = K / 16;
-        int acc = 0;
-        int i = lane;
-        for (; i + 15 * 32 < chunks; i += 16 * 32) {
-          int4 v[16];
-#pragma unroll
-          for (int u = 0; u < 16; ++u) v[u] = __ldg(a + i + u * 32);
-#pragma unroll
-          for (int u = 0; u < 16; ++u) {
-            acc = __dp4a(v[u].x, 0x01010101, acc);
-            acc = __dp4a(v[u].y, 0x01010101, acc);
-            acc = __dp4a(v[u].z, 0x01010101, acc);
-            acc = __dp4a(v[u].w, 0x01010101, acc);
-          }
-        }
-        for (; i < chunks; i += 32) {
-          const int4 v = __ldg(a + i);
-          acc = __dp4a(v.x, 0x01010101, acc);
-          acc = __dp4a(v.y, 0x01010101, acc);
-          acc = __dp4a(v.z, 0x01010101, acc);
-          acc = __dp4a(v.w, 0x01010101, acc);
-        }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-        if (lane == 0) row_sum[m] = acc;
-      }
-    }
-  }
-  return done;
+// Position of a row / column item in the processing order described above.
+__device__ __forceinline__ int pos_of_row_item(int i, int row_items, int col_items) {
+  const int first = min(row_items, ES_FIRST_ROW_ITEMS);
+  return i < first ? i : i + col_items;
+}
+__device__ __forceinline__ int pos_of_col_item(int c, int row_items) {
+  return min(row_items, ES_FIRST_ROW_ITEMS) + c;
 }
 
-// Bounded wait until the device-wide item counter has reached `expected` (wrap-safe compare).
-__device__ __forceinline__ bool wait_items(const unsigned* counter, unsigned expected,
-                                           volatile int* abort_flag, int* status) {
-  const long long start = clock64();
-  int spins = 0;
-  while (true) {
-    unsigned seen;
-    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(counter) : "memory");
-    if (int(seen - expected) >= 0) return true;
-    if ((++spins & 63) == 0) {
-      if (*abort_flag) return false;
-      if (clock64() - start > WAIT_BUDGET_CLOCKS) {
-        *abort_flag = 1;
-        if (status) atomicCAS(status, 0, STATUS_TIMEOUT_FLAG);
-        return false;
+// Computes the item at position `pos` with the 256 epilogue threads of this CTA (`et` = index
+// among them) and publishes it.
+__device__ __forceinline__ void epilogue_sum_item(int pos, const int8_t* __restrict__ A,
+                                                  const int8_t* __restrict__ B, int* __restrict__ row_sum,
+                                                  int* __restrict__ col_sum, int M, int N, int K,
+                                                  int col_items, int row_items, int (*part)[SUM_COLS + 1],
+                                                  int et, unsigned* flags, unsigned epoch) {
+  const int warp = et / 32, lane = et % 32;
+  const int first_rows = min(row_items, ES_FIRST_ROW_ITEMS);
+  const bool is_col = pos >= first_rows && pos < first_rows + col_items;
+  if (is_col) {
+    const int item = pos - first_rows;
+    const int tx = et % SUM_TX, ty = et / SUM_TX;
+    const int n = item * SUM_COLS + tx * 16;
+    int acc[16] = {};
+    if (n < N) {
+      // (sixteen 16-byte loads in flight per thread: an item is bound by load latency under
+      // the tensor kernel's own L2 traffic, not by the additions)
+      const int8_t* col = B + n;
+      int k = ty;
+      for (; k + 15 * ES_KLANES < K; k += 16 * ES_KLANES) {
+        int4 v[16];
+#pragma unroll
+        for (int u = 0; u < 16; ++u)
+          v[u] = __ldg(reinterpret_cast<const int4*>(col + size_t(k + u * ES_KLANES) * N));
+#pragma unroll
+        for (int u = 0; u < 16; ++u) add_bytes(acc, v[u]);
       }
+      for (; k < K; k += ES_KLANES)
+        add_bytes(acc, __ldg(reinterpret_cast<const int4*>(col + size_t(k) * N)));
     }
-    __nanosleep(64);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+#pragma unroll
+      for (int o = SUM_TX; o < 32; o <<= 1) acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], o);
+    }
+    epilogue_bar();  // the previous item's readers are done with `part`
+    if (lane < SUM_TX) {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) part[warp][tx * 16 + i] = acc[i];
+    }
+    epilogue_bar();
+    if (et < SUM_COLS) {
+      int total = 0;
+#pragma unroll
+      for (int r = 0; r < EPI_WARPS; ++r) total += part[r][et];
+      const int out = item * SUM_COLS + et;
+      if (out < N) col_sum[out] = total;
+    }
+  } else {
+    const int item = pos < first_rows ? pos : pos - col_items;
+    for (int r = warp; r < SUM_ROWS; r += EPI_WARPS) {
+      const int m = item * SUM_ROWS + r;
+      if (m >= M) continue;
+      const int4* a = reinterpret_cast<const int4*>(A + size_t(m) * K);
+      const int chunks = K / 16;
+      int acc = 0;
+      int i = lane;
+      for (; i + 15 * 32 < chunks; i += 16 * 32) {
+        int4 v[16];
+#pragma unroll
+        for (int u = 0; u < 16; ++u) v[u] = __ldg(a + i + u * 32);
+#pragma unroll
+        for (int u = 0; u < 16; ++u) {
+          acc = __dp4a(v[u].x, 0x01010101, acc);
+          acc = __dp4a(v[u].y, 0x01010101, acc);
+          acc = __dp4a(v[u].z, 0x01010101, acc);
+          acc = __dp4a(v[u].w, 0x01010101, acc);
+        }
+      }
+      for (; i < chunks; i += 32) {
+        const int4 v = __ldg(a + i);
+        acc = __dp4a(v.x, 0x01010101, acc);
+        acc = __dp4a(v.y, 0x01010101, acc);
+        acc = __dp4a(v.z, 0x01010101, acc);
+        acc = __dp4a(v.w, 0x01010101, acc);
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+      if (lane == 0) row_sum[m] = acc;
+    }
   }
+  __threadfence();
+  epilogue_bar();
+  if (et == 0) asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(flags + pos), "r"(epoch) : "memory");
+}
+
+// Whether the sums this CTA's part of tile (tm, tn) needs are published: its 128 rows (eight
+// row items) and the tile's 256 columns (four column items).  Called by one full warp.
+__device__ __forceinline__ bool tile_sums_ready(int tm, int tn, int rank, int row_items, int col_items,
+                                                const unsigned* flags, unsigned epoch, int lane) {
+  int pos = -1;
+  if (lane < 8) {
+    const int i = (tm * 256 + rank * 128) / SUM_ROWS + lane;
+    if (i < row_items) pos = pos_of_row_item(i, row_items, col_items);
+  } else if (lane < 12) {
+    const int c = tn * (256 / SUM_COLS) + (lane - 8);
+    if (c < col_items) pos = pos_of_col_item(c, row_items);
+  }
+  bool ready = true;
+  if (pos >= 0) {
+    unsigned seen;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(flags + pos) : "memory");
+    ready = seen == epoch;
+  }
+  return __all_sync(0xffffffffu, ready);
 }
 
 // ---------------------------------------------------- tensor path, CTA pairs
@@ -646,7 +665,7 @@ __global__ void __launch_bounds__(MMA_THREADS, 1)
                      int K, Quant q, int tiles_m, int tiles_n, int c_vector_ok, int* status,
                      const int8_t* __restrict__ A_raw, const int8_t* __restrict__ B_raw,
                      int* row_sum_w, int* col_sum_w, int col_items, int row_items,
-                     unsigned* items_done, unsigned items_expected) {
+                     unsigned* item_flags, unsigned epoch) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~uintptr_t(1023));
@@ -776,27 +795,57 @@ __global__ void __launch_bounds__(MMA_THREADS, 1)
     // Everything this kernel reads may have been written by the grid ahead of it in the stream
     // (no effect without a programmatic dependency).
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    // Row / column sums: computed here, by the epilogue warps of all CTAs, while the first
-    // tile's MMAs run (see epilogue_sums above).
-    if (col_items + row_items > 0) {
-      const int et = threadIdx.x - 64;
-      int(*part)[SUM_COLS + 1] =
-          reinterpret_cast<int(*)[SUM_COLS + 1]>(smem + P_STAGES * P_STAGE_BYTES + 256);
-      const int mine = epilogue_sums(A_raw, B_raw, row_sum_w, col_sum_w, M, N, K, col_items,
-                                     row_items, part, et);
-      __threadfence();
-      epilogue_bar();
-      if (et == 0 && mine > 0) atomicAdd(items_done, unsigned(mine));
-      // (a pair that owns no tile was only here to help with the sums: nothing to wait for)
-      if (lane == 0 && cluster_id < num_tiles)
-        ok = wait_items(items_done, items_expected, abort_flag, status);
-      ok = __shfl_sync(0xffffffffu, ok, 0);
-      __threadfence();
-      epilogue_bar();  // `part` doubles as the all-gather staging area of the drains below
-    }
+    // Row / column sums: computed by the epilogue warps of all CTAs in the gaps of their own
+    // work (see epilogue_sum_item above).  Decisions that steer all eight warps (they meet at
+    // named barriers inside an item) are taken by the first of them and passed through shared
+    // memory.
+    const int et = threadIdx.x - 64;
+    const int total_items = col_items + row_items;
+    int next_item = blockIdx.x;  // this CTA's next position in the processing order
+    int(*part)[SUM_COLS + 1] =
+        reinterpret_cast<int(*)[SUM_COLS + 1]>(smem + P_STAGES * P_STAGE_BYTES + 256);
+    volatile int* decision = reinterpret_cast<volatile int*>(smem + P_STAGES * P_STAGE_BYTES + 256 + ES_PART_BYTES);
+    int round = 0;  // alternates the two decision words, so that one barrier per decision suffices
     for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
       int tm, tn;
       pair_tile_coords(tile, tiles_m, tiles_n, tm, tn);
+      if (total_items > 0) {
+        // until the accumulator is complete AND this tile's sums are published: own items
+        const long long start = clock64();
+        while (true) {
+          if (ew == 0) {
+            int d = 0;  // 0 = wait, 1 = go on to the drain, 2 = do an item, 3 = give up
+            const bool acc_ready = mbar_try_wait(&bars->acc_full[acc], acc_phase);
+            const bool sums_ready = tile_sums_ready(tm, tn, int(rank), row_items, col_items, item_flags, epoch, lane);
+            if (acc_ready && sums_ready) d = 1;
+            else if (next_item < total_items) d = 2;
+            else if (*abort_flag) d = 3;
+            else if (clock64() - start > WAIT_BUDGET_CLOCKS) {
+              d = 3;
+              *abort_flag = 1;
+              if (status) atomicCAS(status, 0, acc_ready ? STATUS_TIMEOUT_FLAG : STATUS_TIMEOUT_TMEM_FULL);
+            }
+            if (lane == 0) decision[round & 1] = d;
+          }
+          epilogue_bar();
+          const int d = decision[round & 1];
+          ++round;
+          if (d == 1) break;
+          if (d == 3) {
+            ok = false;
+            break;
+          }
+          if (d == 2) {
+            epilogue_sum_item(next_item, A_raw, B_raw, row_sum_w, col_sum_w, M, N, K, col_items, row_items,
+                              part, et, item_flags, epoch);
+            next_item += gridDim.x;
+          } else {
+            __nanosleep(100);
+          }
+        }
+        if (!ok) break;
+        __threadfence();
+      }
       ok = mbar_wait(&bars->acc_full[acc], acc_phase, abort_flag, status, STATUS_TIMEOUT_TMEM_FULL);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
@@ -815,6 +864,13 @@ __global__ void __launch_bounds__(MMA_THREADS, 1)
         acc = 0;
         acc_phase ^= 1;
       }
+    }
+    // whatever is left of this CTA's share of the sums (other CTAs' later tiles wait for it; a
+    // pair that owns no tile does all of its share here)
+    while (ok && next_item < total_items) {
+      epilogue_sum_item(next_item, A_raw, B_raw, row_sum_w, col_sum_w, M, N, K, col_items, row_items, part,
+                        et, item_flags, epoch);
+      next_item += gridDim.x;
     }
   }
 
@@ -935,11 +991,14 @@ static bool launch_tensor(DeviceCtx& ctx, const int8_t* A, const int8_t* B, int8
   }
   const int tiles_n = (N + BN - 1) / BN;
   const int np = tiles_n * BN;
-  // Scratch: row_sum[M] | col_sum[np] (int32).
+  // Scratch: row_sum[M] | col_sum[np] (int32); one flag per sum item in an array of its own.
   const size_t row_bytes = (size_t(M) * 4 + 255) & ~size_t(255);
   int* row_sum = static_cast<int*>(device_scratch(ctx, row_bytes + size_t(np) * 4));
   if (!row_sum) return false;
   int* col_sum = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(row_sum) + row_bytes);
+  unsigned* item_flags = device_item_flags(
+      ctx, size_t((M + SUM_ROWS - 1) / SUM_ROWS + (N + SUM_COLS - 1) / SUM_COLS) * sizeof(unsigned));
+  if (!item_flags) return false;
   // 16-byte row stores need aligned rows of the output (H [M, N/2] in the SwiGLU form, FP16
   // [M, N] in the dequantising form)
   int c_vector_ok = (reinterpret_cast<uintptr_t>(C) & 15) == 0 &&
@@ -969,10 +1028,9 @@ static bool launch_tensor(DeviceCtx& ctx, const int8_t* A, const int8_t* B, int8
     const int tiles_m = (M + 255) / 256;
     const int col_items = sums_q.za != 0 ? (N + SUM_COLS - 1) / SUM_COLS : 0;
     const int row_items = sums_q.zb != 0 ? (M + SUM_ROWS - 1) / SUM_ROWS : 0;
-    // the value the device-wide item counter will show once this call's items are done
-    unsigned* items_done = reinterpret_cast<unsigned*>(ctx.status + STATUS_WORD_ITEMS_DONE);
-    ctx.items_expected += unsigned(col_items + row_items);
-    const unsigned items_expected = ctx.items_expected;
+    // a finished item is marked with this call's epoch number: never zero, never used twice
+    if (++ctx.sums_epoch == 0) ++ctx.sums_epoch;
+    const unsigned epoch = ctx.sums_epoch;
     cudaLaunchConfig_t cfg = {};
     // One pair per tile up to what the device holds; a small problem gets extra pairs that own
     // no tile and only help with the sums (one item per CTA: an item is one memory round trip),
@@ -995,13 +1053,12 @@ static bool launch_tensor(DeviceCtx& ctx, const int8_t* A, const int8_t* B, int8
     const cudaError_t err =
         K <= 33025 ? cudaLaunchKernelEx(&cfg, umma_pair_kernel<false>, map_a, map_b, C, rs, cs, M, N, K, q,
                                         tiles_m, tiles_n, c_vector_ok, ctx.status, A, B, row_sum, col_sum,
-                                        col_items, row_items, items_done, items_expected)
+                                        col_items, row_items, item_flags, epoch)
                    : cudaLaunchKernelEx(&cfg, umma_pair_kernel<true>, map_a, map_b, C, rs, cs, M, N, K, q,
                                         tiles_m, tiles_n, c_vector_ok, ctx.status, A, B, row_sum, col_sum,
-                                        col_items, row_items, items_done, items_expected);
+                                        col_items, row_items, item_flags, epoch);
     if (err != cudaSuccess) {
       cudaGetLastError();
-      ctx.items_expected -= unsigned(col_items + row_items);  // nothing will count them
       profile_stop(slot);
       note_host_error(STATUS_LAUNCH_FAILED);
       return false;  // the caller falls back to the generic kernel
