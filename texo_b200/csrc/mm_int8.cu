@@ -540,12 +540,12 @@ __device__ __forceinline__ void epilogue_sum_item(int pos, const int8_t* __restr
         int4 v[16];
 #pragma unroll
         for (int u = 0; u < 16; ++u)
-          v[u] = __ldg(reinterpret_cast<const int4*>(col + size_t(k + u * ES_KLANES) * N));
+          v[u] = __ldcs(reinterpret_cast<const int4*>(col + size_t(k + u * ES_KLANES) * N));
 #pragma unroll
         for (int u = 0; u < 16; ++u) add_bytes(acc, v[u]);
       }
       for (; k < K; k += ES_KLANES)
-        add_bytes(acc, __ldg(reinterpret_cast<const int4*>(col + size_t(k) * N)));
+        add_bytes(acc, __ldcs(reinterpret_cast<const int4*>(col + size_t(k) * N)));
     }
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
@@ -577,7 +577,7 @@ __device__ __forceinline__ void epilogue_sum_item(int pos, const int8_t* __restr
       for (; i + 15 * 32 < chunks; i += 16 * 32) {
         int4 v[16];
 #pragma unroll
-        for (int u = 0; u < 16; ++u) v[u] = __ldg(a + i + u * 32);
+        for (int u = 0; u < 16; ++u) v[u] = __ldcs(a + i + u * 32);
 #pragma unroll
         for (int u = 0; u < 16; ++u) {
           acc = __dp4a(v[u].x, 0x01010101, acc);
@@ -587,7 +587,7 @@ __device__ __forceinline__ void epilogue_sum_item(int pos, const int8_t* __restr
         }
       }
       for (; i < chunks; i += 32) {
-        const int4 v = __ldg(a + i);
+        const int4 v = __ldcs(a + i);
         acc = __dp4a(v.x, 0x01010101, acc);
         acc = __dp4a(v.y, 0x01010101, acc);
         acc = __dp4a(v.z, 0x01010101, acc);
@@ -806,19 +806,27 @@ __global__ void __launch_bounds__(MMA_THREADS, 1)
         reinterpret_cast<int(*)[SUM_COLS + 1]>(smem + P_STAGES * P_STAGE_BYTES + 256);
     volatile int* decision = reinterpret_cast<volatile int*>(smem + P_STAGES * P_STAGE_BYTES + 256 + ES_PART_BYTES);
     int round = 0;  // alternates the two decision words, so that one barrier per decision suffices
+    int items_done = 0;
     for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
       int tm, tn;
       pair_tile_coords(tile, tiles_m, tiles_n, tm, tn);
       if (total_items > 0) {
-        // until the accumulator is complete AND this tile's sums are published: own items
+        // Until the accumulator is complete AND this tile's sums are published.  The first two
+        // items of a CTA (what the first waves of tiles need) are done at once; after that one
+        // item per tile keeps ahead of the need (the order of the items is the order of need)
+        // and spreads the extra memory traffic over the run instead of piling it onto the
+        // first wave's own loads - except when this tile's sums are missing: then the CTA
+        // works through its items without pause (it must never sit idle on a flag while it
+        // still owes items to others).
         const long long start = clock64();
+        bool item_this_tile = false;
         while (true) {
           if (ew == 0) {
             int d = 0;  // 0 = wait, 1 = go on to the drain, 2 = do an item, 3 = give up
             const bool acc_ready = mbar_try_wait(&bars->acc_full[acc], acc_phase);
             const bool sums_ready = tile_sums_ready(tm, tn, int(rank), row_items, col_items, item_flags, epoch, lane);
             if (acc_ready && sums_ready) d = 1;
-            else if (next_item < total_items) d = 2;
+            else if (next_item < total_items && (items_done < 2 || !sums_ready || !item_this_tile)) d = 2;
             else if (*abort_flag) d = 3;
             else if (clock64() - start > WAIT_BUDGET_CLOCKS) {
               d = 3;
@@ -839,6 +847,8 @@ __global__ void __launch_bounds__(MMA_THREADS, 1)
             epilogue_sum_item(next_item, A_raw, B_raw, row_sum_w, col_sum_w, M, N, K, col_items, row_items,
                               part, et, item_flags, epoch);
             next_item += gridDim.x;
+            ++items_done;
+            item_this_tile = true;
           } else {
             __nanosleep(100);
           }
