@@ -115,6 +115,23 @@ void texo_mm_int8_solve_per_channel(const int8_t* A, const int8_t* B, int8_t* C,
                                     float scale_A, const float* scale_B, float scale_C,
                                     int zero_point_A, const int* zero_point_B, int zero_point_C);
 
+/* mm_int8 with per-group weight scales (no counterpart in the reference: its INT8 operator is
+ * per-tensor, src/mm_int8.cu:533-535; its per-group scheme is the FP16 one of
+ * src/mm_int4.cu:309-317): scale_B [K / group_size, N] FP32 on the device, one scale per scale
+ * group of group_size consecutive k and output column; group_size divides K.  With dot_g the
+ * exact integer dot of group g:
+ *   acc = 0; for g ascending: acc = fma(RN(float(dot_g) * scale_A), scale_B[g, n], acc)  (FP32)
+ *   C[m, n] = clamp(rint(acc / scale_C) + zero_point_C, -128, 127)
+ * (one group = the per-channel form).  Runs a SIMT kernel on every shape. */
+void texo_mm_int8_solve_per_group(const int8_t* A, const int8_t* B, int8_t* C, int M, int N, int K,
+                                  int group_size, float scale_A, const float* scale_B, float scale_C,
+                                  int zero_point_A, int zero_point_B, int zero_point_C);
+/* The same for packed-INT4 weights: scale_B [N, K / group_size] FP32 on the device (the layout of
+ * the reference's W4A16 scales, src/mm_int4.cu:5-6, in FP32). */
+void texo_mm_int4a8_solve_per_group(const int8_t* A, const uint8_t* w_q, int8_t* C, int M, int N, int K,
+                                    int group_size, float scale_A, const float* scale_B, float scale_C,
+                                    int zero_point_A, int zero_point_B, int zero_point_C);
+
 /* Gate/up projection with the SwiGLU consumer fused into the epilogue (no counterpart in the
  * reference as one operator; it fuses its INT8 matmul, src/mm_int8.cu, with the formula of its
  * src/swiglu.cu:15-18).  B_gu [K, 2F] int8 holds gate and up weight columns interleaved

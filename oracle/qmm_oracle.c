@@ -158,6 +158,38 @@ int oracle_mm_int8_per_channel_rows(const int8_t *A, const int8_t *B, int8_t *C_
   return 0;
 }
 
+/* Per-group weight scales (no reference counterpart; composed from the pinned exact integer dot
+ * and FP32 steps): sb [groups][N] with groups = K / G.  acc = fmaf(RN((float)dot_g * sa),
+ * sb[g][n], acc) over the groups in ascending order, then acc / sc, round to nearest even,
+ * + zc, clamp - all FP32.  With one group this is oracle_mm_int8_per_channel_rows (zb scalar). */
+int oracle_mm_int8_per_group_rows(const int8_t *A, const int8_t *B, int8_t *C_rows, int M, int N,
+                                  int K, int G, float sa, const float *sb, float sc, int za, int zb,
+                                  int zc, int row0, int row1) {
+  if (M <= 0 || N <= 0 || K <= 0 || G <= 0 || (K % G) || !sb || row0 < 0 || row1 > M || row0 > row1)
+    return -1;
+  int8_t *bt = transpose_b(B, K, N);
+  if (!bt) return -1;
+  const int groups = K / G;
+#pragma omp parallel for schedule(dynamic, 1)
+  for (int m = row0; m < row1; ++m)
+    for (int n = 0; n < N; ++n) {
+      volatile float acc = 0.0f;
+      for (int g = 0; g < groups; ++g) {
+        int64_t dot = dot_zp(A + (size_t)m * K + (size_t)g * G, bt + (size_t)n * K + (size_t)g * G, G, za, zb);
+        volatile float t = (float)dot;
+        t = t * sa;
+        acc = fmaf(t, sb[(size_t)g * N + n], acc);
+      }
+      volatile float v = acc / sc;
+      v = nearbyintf(v) + (float)zc;
+      if (v > 127.0f) v = 127.0f;
+      if (v < -128.0f) v = -128.0f;
+      C_rows[(size_t)(m - row0) * N + n] = (int8_t)v;
+    }
+  free(bt);
+  return 0;
+}
+
 /* Gate/up projection with fused SwiGLU (no reference counterpart; composed from the pinned
  * integer dot of mm_int8 and the formula of src/swiglu.cu:15-18, x2 * x1 / (1 + exp(-x1))).
  * B is [K, 2F] with column 2j = gate j and 2j+1 = up j.  gate and up are dequantised in FP32

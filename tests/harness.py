@@ -65,6 +65,19 @@ class Oracle:
         assert rc == 0
         return out
 
+    def mm_int8_per_group(self, A, B, M, N, K, G, sa, sb, sc, za, zb, zc, rows=None):
+        """sb: float32 [K/G, N] (one scale per scale group and output column)."""
+        r0, r1 = rows if rows else (0, M)
+        A = np.ascontiguousarray(A, dtype=np.int8)
+        B = np.ascontiguousarray(B, dtype=np.int8)
+        sb = np.ascontiguousarray(sb, dtype=np.float32)
+        assert sb.shape == (K // G, N)
+        out = np.empty((r1 - r0, N), dtype=np.int8)
+        rc = self.lib.oracle_mm_int8_per_group_rows(_p(A), _p(B), _p(out), M, N, K, G, _f(sa), _p(sb), _f(sc),
+                                                    za, zb, zc, r0, r1)
+        assert rc == 0
+        return out
+
     def mm_int8_swiglu(self, A, B, M, F, K, sa, s_gate, s_up, s_out, za, z_gate, z_up, rows=None):
         """Returns h / s_out before rounding, float64 [rows, F]."""
         r0, r1 = rows if rows else (0, M)

@@ -278,3 +278,28 @@ def test_per_channel_weight_quantisation(lib, oracle, shape, forces):
     torch.cuda.synchronize()
     assert torch.equal(C1, C2)
     assert lib.texo_mm_int4a8_status() == 0
+
+
+@pytest.mark.parametrize("shape", [(64, 96, 256, 64), (130, 200, 1024, 128), (17, 19, 96, 32), (5, 7, 30, 30)])
+def test_per_group_weight_scales(lib, oracle, shape):
+    """Per-group scales for packed INT4 weights (scale_B [N, K/G]): bit-exact against the
+    per-group INT8 oracle applied to the weights unpacked in the reference's nibble order."""
+    m, n, k, g = shape
+    rng = np.random.default_rng(m + n + k)
+    a = rng.integers(-128, 128, (m, k), dtype=np.int8)
+    w = rng.integers(0, 256, (n, k // 2), dtype=np.uint8)
+    unpacked = np.empty((n, k), dtype=np.int8)
+    unpacked[:, 0::2] = (w >> 4).astype(np.int8) - 8
+    unpacked[:, 1::2] = (w & 15).astype(np.int8) - 8
+    sa, za, zb, zc = 0.021, 3, -2, 1
+    sb = rng.uniform(0.005, 0.05, (n, k // g)).astype(np.float32)
+    sc = float(np.float32(sa * 0.03 * (340 * np.sqrt(k) + 12 * k) / 60))
+    want = oracle.mm_int8_per_group(a, np.ascontiguousarray(unpacked.T), m, n, k, g, sa,
+                                    np.ascontiguousarray(sb.T), sc, za, zb, zc)
+    A, W, S = _dev(a), _dev(w), torch.from_numpy(sb).cuda()
+    C = torch.full((m, n), 77, dtype=torch.int8, device="cuda")
+    lib.texo_mm_int4a8_solve_per_group(A.data_ptr(), W.data_ptr(), C.data_ptr(), m, n, k, g, sa, S.data_ptr(), sc,
+                                       za, zb, zc)
+    torch.cuda.synchronize()
+    assert np.array_equal(C.cpu().numpy(), want), shape
+    assert lib.texo_mm_int4a8_status() == 0

@@ -696,3 +696,25 @@ def test_fused_allgather_stores_into_every_copy(lib, oracle, shape, paths):
     assert lib.texo_mm_int8_solve_allgather(A.data_ptr(), B.data_ptr(), ctypes.cast(bad, ctypes.c_void_p),
                                             1, m, n, k, ld, off, *q) == -1
     assert lib.texo_mm_int8_status() == 16  # bad argument, reported and cleared
+
+
+@pytest.mark.parametrize("shape", [(64, 96, 256, 64), (300, 200, 1024, 128), (17, 19, 96, 32), (5, 7, 30, 30)])
+def test_per_group_weight_scales(lib, oracle, shape):
+    """One weight scale per scale group and output column (scale_B [K/G, N]): bit-exact against
+    the per-group oracle (exact group dots, FP32 fma over the groups in order)."""
+    m, n, k, g = shape
+    rng = np.random.default_rng(m + n + k)
+    a = rng.integers(-128, 128, (m, k), dtype=np.int8)
+    b = rng.integers(-128, 128, (k, n), dtype=np.int8)
+    sa, za, zb, zc = 0.021, 3, -5, -2
+    sb = rng.uniform(0.005, 0.05, (k // g, n)).astype(np.float32)
+    sc = float(np.float32(sa * 0.03 * 128 * np.sqrt(k) * 127 / 100))
+    want = oracle.mm_int8_per_group(a, b, m, n, k, g, sa, sb, sc, za, zb, zc)
+    assert np.count_nonzero(np.abs(want.astype(int)) < 127) > want.size // 2
+    A, B, S = _dev(a), _dev(b), torch.from_numpy(sb).cuda()
+    C = torch.full((m, n), 77, dtype=torch.int8, device="cuda")
+    lib.texo_mm_int8_solve_per_group(A.data_ptr(), B.data_ptr(), C.data_ptr(), m, n, k, g, sa, S.data_ptr(), sc,
+                                     za, zb, zc)
+    torch.cuda.synchronize()
+    assert np.array_equal(C.cpu().numpy(), want), shape
+    assert lib.texo_mm_int8_status() == 0

@@ -22,6 +22,10 @@ _SIGNATURES = {
                                   _c_float, _c_float, _c_float, _c_int, _c_int, _c_int]),
     "texo_mm_int8_solve_per_channel": (None, [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int,
                                               _c_float, _c_ptr, _c_float, _c_int, _c_ptr, _c_int]),
+    "texo_mm_int8_solve_per_group": (None, [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int,
+                                            _c_float, _c_ptr, _c_float, _c_int, _c_int, _c_int]),
+    "texo_mm_int4a8_solve_per_group": (None, [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int,
+                                              _c_float, _c_ptr, _c_float, _c_int, _c_int, _c_int]),
     "texo_mm_int8_swiglu_solve": (None, [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int,
                                          _c_float, _c_float, _c_float, _c_float,
                                          _c_int, _c_int, _c_int, _c_int]),

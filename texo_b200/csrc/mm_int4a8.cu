@@ -629,6 +629,78 @@ extern "C" void texo_mm_int4a8_solve_per_channel(const int8_t* A, const uint8_t*
                          scale_B, zero_point_B);
 }
 
+// W4A8 with one weight scale per (output column, scale group): scale_B [N, K / group_size] FP32
+// on the device - the layout of the reference's W4A16 scales (src/mm_int4.cu:5-6 of
+// frezcirno/Texo), in FP32.  Arithmetic as texo_mm_int8_solve_per_group (mm_int8.cu):
+//   acc = fma(RN(float(dot_g) * scale_A), scale_B[n, g], acc) over the groups in order, then
+//   C[m, n] = clamp(rint(acc / scale_C) + zC, -128, 127).
+// SIMT kernel for every shape (see there for why no tensor-core path is offered).
+namespace texo {
+namespace w4a8 {
+__global__ void __launch_bounds__(256)
+    per_group_kernel(const int8_t* __restrict__ A, const uint8_t* __restrict__ W, int8_t* __restrict__ C,
+                     int M, int N, int K, int G, const float* __restrict__ scale_B, Quant q) {
+  __shared__ int8_t As[16][64 + 4];
+  __shared__ uint8_t Ws[16][32 + 4];
+  const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
+  const int n = blockIdx.x * 16 + tx, m = blockIdx.y * 16 + ty;
+  const int groups = K / G;
+  float acc = 0.f;
+  long long dot = 0;
+  for (int k0 = 0; k0 < K; k0 += 64) {
+    for (int i = threadIdx.x; i < 16 * 64; i += 256) {
+      const int r = i / 64, c = i % 64;
+      const int mm = blockIdx.y * 16 + r, k = k0 + c;
+      As[r][c] = (mm < M && k < K) ? A[size_t(mm) * K + k] : int8_t(0);
+    }
+    for (int i = threadIdx.x; i < 16 * 32; i += 256) {
+      const int r = i / 32, c = i % 32;
+      const int nn = blockIdx.x * 16 + r, k = k0 + 2 * c;
+      Ws[r][c] = (nn < N && k < K) ? W[size_t(nn) * (K / 2) + k / 2] : uint8_t(0);
+    }
+    __syncthreads();
+    if (n < N) {
+      const int kend = min(64, K - k0);
+      for (int c = 0; c < kend; ++c) {
+        const int k = k0 + c;
+        const int byte = Ws[tx][c / 2];
+        const int wq = ((c & 1) == 0 ? byte >> 4 : byte & 15) - 8;  // high nibble = even k
+        dot += (long long)(int(As[ty][c]) - q.za) * (wq - q.zb);
+        if ((k + 1) % G == 0) {
+          const float t = __fmul_rn(float(dot), q.sa);
+          acc = __fmaf_rn(t, scale_B[size_t(n) * groups + k / G], acc);
+          dot = 0;
+        }
+      }
+    }
+    __syncthreads();
+  }
+  if (m < M && n < N) {
+    float v = __fdiv_rn(acc, q.sc);
+    v = __fadd_rn(rintf(v), float(q.zc));
+    C[size_t(m) * N + n] = int8_t(__float2int_rn(fminf(fmaxf(v, -128.f), 127.f)));
+  }
+}
+}  // namespace w4a8
+}  // namespace texo
+
+extern "C" void texo_mm_int4a8_solve_per_group(const int8_t* A, const uint8_t* w_q, int8_t* C, int M, int N,
+                                               int K, int group_size, float scale_A, const float* scale_B,
+                                               float scale_C, int zero_point_A, int zero_point_B,
+                                               int zero_point_C) {
+  using namespace texo;
+  using namespace texo::w4a8;
+  if (M <= 0 || N <= 0) return;
+  if (K <= 0 || K % 2 != 0 || group_size <= 0 || K % group_size != 0 || !A || !w_q || !C || !scale_B) {
+    note_host_error(STATUS_BAD_ARGUMENT);
+    return;
+  }
+  const i8::Quant q = i8::make_quant(scale_A, 1.0f, scale_C, zero_point_A, zero_point_B, zero_point_C, K);
+  per_group_kernel<<<dim3((N + 15) / 16, (M + 15) / 16), 256>>>(A, w_q, C, M, N, K, group_size, scale_B, q);
+  ++launch_counter();
+  last_path() = PATH_GENERIC;
+}
+
 extern "C" int texo_mm_int4a8_last_path() { return texo::w4a8::last_path(); }
 extern "C" void texo_mm_int4a8_force_path(int path) { texo::w4a8::forced_path() = path; }
 extern "C" int texo_mm_int4a8_status() { return texo::read_and_clear_status(); }

@@ -1323,6 +1323,76 @@ extern "C" void texo_mm_int8_solve_per_channel(const int8_t* A, const int8_t* B,
   solve_with(A, B, C, M, N, K, q);
 }
 
+// --------------------------------------------------- per-group weight scales
+// One weight scale per (scale group of `group_size` consecutive k, output column):
+// scale_B [K / group_size, N] FP32 on the device (row g holds the scales of k in
+// [g * group_size, (g + 1) * group_size)).  With dot_g the exact integer dot of group g,
+//   acc = 0;  for g = 0, 1, ...:  acc = fma(RN(float(dot_g) * scale_A), scale_B[g, n], acc)
+//   C[m, n] = clamp(rint(acc / scale_C) + zC, -128, 127)
+// all in FP32, groups in ascending order.  With a single group (group_size == K) this is
+// exactly the per-channel form ((float(dot) * sA) * sB[n]) / sC.  No counterpart in the
+// reference (its mm_int8 is per-tensor, src/mm_int8.cu:533-535; its per-group handling is the
+// FP16 path of src/mm_int4.cu:309-317).  This form runs on a SIMT kernel for every shape: a
+// tensor-core path would have to drain the accumulator once per group, which tensor-memory
+// bandwidth makes two to three times as expensive as the MMAs themselves at group_size = 128
+// (measured on the W4A16 kernel), so it is left out rather than shipped slow and complex.
+namespace texo {
+namespace i8 {
+__global__ void __launch_bounds__(256)
+    per_group_kernel(const int8_t* __restrict__ A, const int8_t* __restrict__ B, int8_t* __restrict__ C,
+                     int M, int N, int K, int G, const float* __restrict__ scale_B, Quant q) {
+  __shared__ int8_t As[16][64 + 4];
+  const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
+  const int n = blockIdx.x * 16 + tx, m = blockIdx.y * 16 + ty;
+  float acc = 0.f;
+  long long dot = 0;
+  for (int k0 = 0; k0 < K; k0 += 64) {
+    for (int i = threadIdx.x; i < 16 * 64; i += 256) {
+      const int r = i / 64, c = i % 64;
+      const int mm = blockIdx.y * 16 + r, k = k0 + c;
+      As[r][c] = (mm < M && k < K) ? A[size_t(mm) * K + k] : int8_t(0);
+    }
+    __syncthreads();
+    if (n < N) {
+      const int kend = min(64, K - k0);
+      for (int c = 0; c < kend; ++c) {
+        const int k = k0 + c;
+        dot += (long long)(int(As[ty][c]) - q.za) * (int(B[size_t(k) * N + n]) - q.zb);
+        if ((k + 1) % G == 0) {  // the group ends here
+          const float t = __fmul_rn(float(dot), q.sa);
+          acc = __fmaf_rn(t, scale_B[size_t(k / G) * N + n], acc);
+          dot = 0;
+        }
+      }
+    }
+    __syncthreads();
+  }
+  if (m < M && n < N) {
+    float v = __fdiv_rn(acc, q.sc);
+    v = __fadd_rn(rintf(v), float(q.zc));
+    C[size_t(m) * N + n] = int8_t(__float2int_rn(fminf(fmaxf(v, -128.f), 127.f)));
+  }
+}
+}  // namespace i8
+}  // namespace texo
+
+extern "C" void texo_mm_int8_solve_per_group(const int8_t* A, const int8_t* B, int8_t* C, int M, int N,
+                                             int K, int group_size, float scale_A, const float* scale_B,
+                                             float scale_C, int zero_point_A, int zero_point_B,
+                                             int zero_point_C) {
+  using namespace texo;
+  using namespace texo::i8;
+  if (M <= 0 || N <= 0) return;
+  if (K <= 0 || group_size <= 0 || K % group_size != 0 || !A || !B || !C || !scale_B) {
+    note_host_error(STATUS_BAD_ARGUMENT);
+    return;
+  }
+  const Quant q = make_quant(scale_A, 1.0f, scale_C, zero_point_A, zero_point_B, zero_point_C, K);
+  per_group_kernel<<<dim3((N + 15) / 16, (M + 15) / 16), 256>>>(A, B, C, M, N, K, group_size, scale_B, q);
+  ++launch_counter();
+  last_path() = PATH_GENERIC;
+}
+
 // ------------------------------------------------------------ prepared weights
 // Inference calls the same weights with new activations again and again; colsum(B) depends
 // on the weights only.  The reference recomputes it (together with a transposed copy of B)

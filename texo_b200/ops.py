@@ -11,7 +11,8 @@ import torch
 
 from . import _lib
 
-__all__ = ["mm_int8", "mm_int8_per_channel", "mm_int8_swiglu", "mm_int8_dequant", "mm_int4", "mm_int4a8", "mm_int4a8_per_channel", "dequantization", "rms_norm_w_residual",
+__all__ = ["mm_int8", "mm_int8_per_channel", "mm_int8_per_group", "mm_int8_swiglu", "mm_int8_dequant", "mm_int4",
+           "mm_int4a8", "mm_int4a8_per_channel", "mm_int4a8_per_group", "dequantization", "rms_norm_w_residual",
            "rms_norm_quant", "mm_int8_host", "Int8Weights", "last_path", "status", "force_path"]
 
 
@@ -241,6 +242,58 @@ def mm_int4a8_per_channel(A: torch.Tensor, w_q: torch.Tensor, scale_A: float, sc
             A.data_ptr() if K else None, w_q.data_ptr() if K else None, out.data_ptr(), M, N, K,
             scale_A, scale_B.data_ptr(), scale_C, zero_point_A,
             zero_point_B.data_ptr() if zero_point_B is not None else None, zero_point_C)
+    return out
+
+
+def mm_int8_per_group(A: torch.Tensor, B: torch.Tensor, group_size: int, scale_A: float,
+                      scale_B: torch.Tensor, scale_C: float, zero_point_A: int, zero_point_B: int,
+                      zero_point_C: int) -> torch.Tensor:
+    """mm_int8 with one weight scale per scale group of `group_size` consecutive k and output
+    column: scale_B fp32 [K / group_size, N] on the device; see include/texo_b200.h."""
+    _check_cuda("A", A, torch.int8)
+    _check_cuda("B", B, torch.int8)
+    _check_cuda("scale_B", scale_B, torch.float32)
+    if A.dim() != 2 or B.dim() != 2 or A.shape[1] != B.shape[0]:
+        raise ValueError("A must be [M, K] and B [K, N]")
+    M, K = A.shape
+    N = B.shape[1]
+    if M <= 0 or N <= 0 or K <= 0 or group_size <= 0 or K % group_size:
+        raise ValueError("M, N, K must be positive and group_size must divide K")
+    if tuple(scale_B.shape) != (K // group_size, N):
+        raise ValueError("scale_B must be [K / group_size, N]")
+    out = torch.empty((M, N), dtype=torch.int8, device=A.device)
+    lib = _lib.load()
+    with torch.cuda.device(A.device), _DefaultStreamOrder(A.device):
+        lib.texo_mm_int8_solve_per_group(A.data_ptr(), B.data_ptr(), out.data_ptr(), M, N, K, group_size,
+                                         scale_A, scale_B.data_ptr(), scale_C, zero_point_A, zero_point_B,
+                                         zero_point_C)
+    return out
+
+
+def mm_int4a8_per_group(A: torch.Tensor, w_q: torch.Tensor, group_size: int, scale_A: float,
+                        scale_B: torch.Tensor, scale_C: float, zero_point_A: int, zero_point_B: int,
+                        zero_point_C: int) -> torch.Tensor:
+    """mm_int4a8 with per-group weight scales: scale_B fp32 [N, K / group_size] on the device (the
+    layout of the reference's W4A16 scales); see include/texo_b200.h."""
+    _check_cuda("A", A, torch.int8)
+    _check_cuda("w_q", w_q, torch.uint8)
+    _check_cuda("scale_B", scale_B, torch.float32)
+    if A.dim() != 2 or w_q.dim() != 2:
+        raise ValueError("A and w_q must be matrices")
+    M, K = A.shape
+    N = w_q.shape[0]
+    if K <= 0 or K % 2 or w_q.shape[1] != K // 2:
+        raise ValueError("w_q must be [N, K/2] with even K > 0")
+    if M <= 0 or N <= 0 or group_size <= 0 or K % group_size:
+        raise ValueError("M, N must be positive and group_size must divide K")
+    if tuple(scale_B.shape) != (N, K // group_size):
+        raise ValueError("scale_B must be [N, K / group_size]")
+    out = torch.empty((M, N), dtype=torch.int8, device=A.device)
+    lib = _lib.load()
+    with torch.cuda.device(A.device), _DefaultStreamOrder(A.device):
+        lib.texo_mm_int4a8_solve_per_group(A.data_ptr(), w_q.data_ptr(), out.data_ptr(), M, N, K, group_size,
+                                           scale_A, scale_B.data_ptr(), scale_C, zero_point_A, zero_point_B,
+                                           zero_point_C)
     return out
 
 
