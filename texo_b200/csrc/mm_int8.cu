@@ -501,11 +501,29 @@ __global__ void __launch_bounds__(MMA_THREADS, 1)
 constexpr int ES_THREADS = EPI_WARPS * 32;                        // 256 epilogue threads
 constexpr int ES_KLANES = ES_THREADS / SUM_TX;                    // k lanes of a column item
 constexpr int ES_PART_BYTES = EPI_WARPS * (SUM_COLS + 1) * 4;     // partials of a column item
-constexpr int P_AUX_SMEM_BYTES = 2304;                            // >= ES_PART_BYTES + the decision words
-static_assert(ES_PART_BYTES + 64 <= P_AUX_SMEM_BYTES, "sums partials outgrew their shared-memory reserve");
+// Shared memory of the epilogue warps behind the ring and the barriers: 64 bytes of decision
+// words (aliased with nothing: warps read them while others have already gone on), then
+//   plain call:   128 column sums per epilogue warp (4 KiB) | partials of a column item
+//   fused gather: one 4 KiB staging tile per epilogue warp, whose first bytes double as the
+//                 partials of a column item (inside an item all eight warps are between the
+//                 same barriers, none of them drains)
+constexpr int P_DECISION_BYTES = 64;
+constexpr int P_COLSUM_SMEM_BYTES = EPI_WARPS * 512;
+constexpr int P_AUX_SMEM_BYTES = P_DECISION_BYTES + P_COLSUM_SMEM_BYTES + ((ES_PART_BYTES + 127) & ~127);
 constexpr int ES_FIRST_ROW_ITEMS = P_GROUP_M * 256 / SUM_ROWS;    // row items of the first eight tile rows
 
+constexpr int ES_ROW_THREADS = ES_THREADS / SUM_ROWS;             // threads per row of a row item
+static_assert(ES_ROW_THREADS == 16, "a row item is sixteen rows by sixteen threads");
+
 __device__ __forceinline__ void epilogue_bar() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+
+// Sum of the sixteen signed bytes of v, added to acc.
+__device__ __forceinline__ int sum_bytes(const int4& v, int acc) {
+  acc = __dp4a(v.x, 0x01010101, acc);
+  acc = __dp4a(v.y, 0x01010101, acc);
+  acc = __dp4a(v.z, 0x01010101, acc);
+  return __dp4a(v.w, 0x01010101, acc);
+}
 
 // Position of a row / column item in the processing order described above.
 __device__ __forceinline__ int pos_of_row_item(int i, int row_items, int col_items) {
@@ -544,6 +562,14 @@ __device__ __forceinline__ void epilogue_sum_item(int pos, const int8_t* __restr
 #pragma unroll
         for (int u = 0; u < 16; ++u) add_bytes(acc, v[u]);
       }
+      for (; k + 3 * ES_KLANES < K; k += 4 * ES_KLANES) {
+        int4 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          v[u] = __ldcs(reinterpret_cast<const int4*>(col + size_t(k + u * ES_KLANES) * N));
+#pragma unroll
+        for (int u = 0; u < 4; ++u) add_bytes(acc, v[u]);
+      }
       for (; k < K; k += ES_KLANES)
         add_bytes(acc, __ldcs(reinterpret_cast<const int4*>(col + size_t(k) * N)));
     }
@@ -566,39 +592,38 @@ __device__ __forceinline__ void epilogue_sum_item(int pos, const int8_t* __restr
       if (out < N) col_sum[out] = total;
     }
   } else {
+    // sixteen threads per row, all sixteen rows at once: every load of a short row is in
+    // flight before the first is used (a row of 1024 bytes is four loads per thread)
     const int item = pos < first_rows ? pos : pos - col_items;
-    for (int r = warp; r < SUM_ROWS; r += EPI_WARPS) {
-      const int m = item * SUM_ROWS + r;
-      if (m >= M) continue;
+    const int sub = et % ES_ROW_THREADS;
+    const int m = item * SUM_ROWS + et / ES_ROW_THREADS;
+    int acc = 0;
+    if (m < M) {
       const int4* a = reinterpret_cast<const int4*>(A + size_t(m) * K);
       const int chunks = K / 16;
-      int acc = 0;
-      int i = lane;
-      for (; i + 15 * 32 < chunks; i += 16 * 32) {
+      int i = sub;
+      for (; i + 15 * ES_ROW_THREADS < chunks; i += 16 * ES_ROW_THREADS) {
         int4 v[16];
 #pragma unroll
-        for (int u = 0; u < 16; ++u) v[u] = __ldcs(a + i + u * 32);
+        for (int u = 0; u < 16; ++u) v[u] = __ldcs(a + i + u * ES_ROW_THREADS);
 #pragma unroll
-        for (int u = 0; u < 16; ++u) {
-          acc = __dp4a(v[u].x, 0x01010101, acc);
-          acc = __dp4a(v[u].y, 0x01010101, acc);
-          acc = __dp4a(v[u].z, 0x01010101, acc);
-          acc = __dp4a(v[u].w, 0x01010101, acc);
-        }
+        for (int u = 0; u < 16; ++u) acc = sum_bytes(v[u], acc);
       }
-      for (; i < chunks; i += 32) {
-        const int4 v = __ldcs(a + i);
-        acc = __dp4a(v.x, 0x01010101, acc);
-        acc = __dp4a(v.y, 0x01010101, acc);
-        acc = __dp4a(v.z, 0x01010101, acc);
-        acc = __dp4a(v.w, 0x01010101, acc);
-      }
+      for (; i + 3 * ES_ROW_THREADS < chunks; i += 4 * ES_ROW_THREADS) {
+        int4 v[4];
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-      if (lane == 0) row_sum[m] = acc;
+        for (int u = 0; u < 4; ++u) v[u] = __ldcs(a + i + u * ES_ROW_THREADS);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) acc = sum_bytes(v[u], acc);
+      }
+      for (; i < chunks; i += ES_ROW_THREADS) acc = sum_bytes(__ldcs(a + i), acc);
     }
+#pragma unroll
+    for (int o = ES_ROW_THREADS / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (sub == 0 && m < M) row_sum[m] = acc;
   }
-  __threadfence();
+  // (the barrier orders every thread's stores before the release of the first thread, which is
+  // cumulative over them: no fence per thread)
   epilogue_bar();
   if (et == 0) asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(flags + pos), "r"(epoch) : "memory");
 }
@@ -646,7 +671,9 @@ constexpr int P_A_BYTES = BM * BK;   // 128 rows x 128 k-bytes
 constexpr int P_B_BYTES = BK * 128;  // 128 k-rows x 128 n-bytes (this CTA's half of the columns)
 constexpr int P_STAGE_BYTES = P_A_BYTES + P_B_BYTES;
 constexpr int P_SMEM_BYTES = P_STAGES * P_STAGE_BYTES + 1024 + 256;
-constexpr int P_GATHER_SMEM_BYTES = EPI_WARPS * 4096;  // staging tiles of the fused all-gather
+constexpr int P_GATHER_SMEM_BYTES = P_DECISION_BYTES + EPI_WARPS * 4096;  // staging tiles of the fused all-gather
+static_assert(ES_PART_BYTES <= 4096, "the partials of a column item must fit the first staging tile");
+static_assert(P_SMEM_BYTES + P_GATHER_SMEM_BYTES <= 232448, "CTA-pair kernel: shared memory over the limit");
 
 struct PairBarriers {
   uint64_t full[P_STAGES];  // used in the even CTA: bytes of both CTAs' loads
@@ -678,6 +705,12 @@ __global__ void __launch_bounds__(MMA_THREADS, 1)
   const int num_tiles = tiles_m * tiles_n;
   const int num_kb = (K + BK - 1) / BK;
 
+  // The next grid in the stream may be scheduled from now on (it matters when that grid was
+  // launched with programmatic stream serialisation, as this one is): its CTAs take the SMs
+  // this grid's CTAs leave, set up their barriers and tensor memory, and wait in
+  // griddepcontrol.wait until this grid has completed and its writes are visible.
+  asm volatile("griddepcontrol.launch_dependents;");
+
   if (threadIdx.x == 0) {
     for (int s = 0; s < P_STAGES; ++s) mbar_init(&bars->full[s], 1);
     for (int r = 0; r < P_RING; ++r) mbar_init(&bars->ring[r], 1);
@@ -706,6 +739,8 @@ __global__ void __launch_bounds__(MMA_THREADS, 1)
     int g = 0;          // global k-block number of the next load
     int observed = -1;  // highest commit number seen complete
     bool ok = true;
+    // the operands may have been written by the grid ahead of this one
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
       int tm, tn;
       pair_tile_coords(tile, tiles_m, tiles_n, tm, tn);
@@ -792,8 +827,8 @@ __global__ void __launch_bounds__(MMA_THREADS, 1)
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
-    // Everything this kernel reads may have been written by the grid ahead of it in the stream
-    // (no effect without a programmatic dependency).
+    // Everything this kernel reads or writes may be in use by the grid ahead of it in the
+    // stream until that grid has completed.
     asm volatile("griddepcontrol.wait;" ::: "memory");
     // Row / column sums: computed by the epilogue warps of all CTAs in the gaps of their own
     // work (see epilogue_sum_item above).  Decisions that steer all eight warps (they meet at
@@ -802,11 +837,23 @@ __global__ void __launch_bounds__(MMA_THREADS, 1)
     const int et = threadIdx.x - 64;
     const int total_items = col_items + row_items;
     int next_item = blockIdx.x;  // this CTA's next position in the processing order
-    int(*part)[SUM_COLS + 1] =
-        reinterpret_cast<int(*)[SUM_COLS + 1]>(smem + P_STAGES * P_STAGE_BYTES + 256);
-    volatile int* decision = reinterpret_cast<volatile int*>(smem + P_STAGES * P_STAGE_BYTES + 256 + ES_PART_BYTES);
+    uint8_t* const aux = smem + P_STAGES * P_STAGE_BYTES + 256;
+    volatile int* decision = reinterpret_cast<volatile int*>(aux);
+    const bool gathering = q.n_peers > 0;
+    int(*part)[SUM_COLS + 1] = reinterpret_cast<int(*)[SUM_COLS + 1]>(
+        aux + P_DECISION_BYTES + (gathering ? 0 : P_COLSUM_SMEM_BYTES));
+    // 128 column sums per epilogue warp (plain calls), or a 4 KiB staging tile per warp (fused
+    // all-gather; the host sizes the launch accordingly)
+    int4* colsum_stage = gathering ? nullptr : reinterpret_cast<int4*>(aux + P_DECISION_BYTES) + ew * 32;
+    uint8_t* gather_stage = gathering ? aux + P_DECISION_BYTES + ew * 4096 : nullptr;
     int round = 0;  // alternates the two decision words, so that one barrier per decision suffices
     int items_done = 0;
+    if (next_item < total_items) {  // the first item needs no decision: nothing else can be ready yet
+      epilogue_sum_item(next_item, A_raw, B_raw, row_sum_w, col_sum_w, M, N, K, col_items, row_items, part,
+                        et, item_flags, epoch);
+      next_item += gridDim.x;
+      ++items_done;
+    }
     for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
       int tm, tn;
       pair_tile_coords(tile, tiles_m, tiles_n, tm, tn);
@@ -861,12 +908,9 @@ __global__ void __launch_bounds__(MMA_THREADS, 1)
       if (!ok) break;
       tc_fence_after_sync();
       const int m = tm * 256 + int(rank) * 128 + quarter * 32 + lane;
-      // fused all-gather: a 4 KiB tile per epilogue warp behind the barriers (the host adds
-      // P_GATHER_SMEM_BYTES to the launch for such calls)
-      uint8_t* gather_stage =
-          q.n_peers > 0 ? smem + P_STAGES * P_STAGE_BYTES + 256 + ew * 4096 : nullptr;
       drain_half<WIDE>(tmem_base + acc * ACC_COLS + (uint32_t(quarter * 32) << 16), half * 128,
-                       tn * 256, m, m < M, C, row_sum, col_sum, N, K, q, c_vector_ok, gather_stage);
+                       tn * 256, m, m < M, C, row_sum, col_sum, N, K, q, c_vector_ok, gather_stage,
+                       colsum_stage);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&bars->acc_empty[acc]), 0));
@@ -1051,13 +1095,17 @@ static bool launch_tensor(DeviceCtx& ctx, const int8_t* A, const int8_t* B, int8
     cfg.blockDim = dim3(MMA_THREADS);
     cfg.dynamicSmemBytes = P_SMEM_BYTES + (q.n_peers > 0 ? P_GATHER_SMEM_BYTES : P_AUX_SMEM_BYTES);
     cfg.stream = 0;
-    cudaLaunchAttribute attrs[1];
+    cudaLaunchAttribute attrs[2];
     attrs[0].id = cudaLaunchAttributeClusterDimension;
     attrs[0].val.clusterDim.x = 2;
     attrs[0].val.clusterDim.y = 1;
     attrs[0].val.clusterDim.z = 1;
+    // may be scheduled while the grid ahead of it drains (the kernel waits in
+    // griddepcontrol.wait before it touches memory)
+    attrs[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attrs;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = 2;
     const int* rs = row_sum;
     const int* cs = col_sum;
     const cudaError_t err =

@@ -95,15 +95,18 @@ __device__ __forceinline__ float div_rn_inrange(float x, float sc, float rsc) {
   return __fmaf_rn(r1, rsc, q1);
 }
 
-// Requantisation with that division and the tail done in integers: cvt.rni.s32
-// (saturating) -> saturating add of zC; the caller saturates to int8.  Identical to the FP32
-// tail whenever |zC| <= 2^22: if |rint(acc)| < 2^24 the float add is exact and the two
-// agree; beyond that both forms saturate to the same end of [-128, 127].
+// rint(acc) + zC in integers, for |zC| <= 2^22: `rounded` is cvt.rni.s32 of acc (saturating).
+// Clamped to +-2^24 first, so that the sum cannot wrap; the caller saturates to int8.
+// Identical to the FP32 tail: if |rint(acc)| <= 2^24 the float add is exact (or lands far
+// outside [-128, 127] on the same side); beyond that both forms saturate to the same end.
+__device__ __forceinline__ int add_zero_point(int rounded, int zc) {
+  return max(-(1 << 24), min(rounded, 1 << 24)) + zc;
+}
+
+// Requantisation with that division and the tail done in integers.
 __device__ __forceinline__ int requantize_fast(float dot, const Quant& q) {
   const float acc = div_rn_inrange(__fmul_rn(__fmul_rn(dot, q.sa), q.sb), q.sc, q.rsc);
-  int r;
-  asm("add.sat.s32 %0, %1, %2;" : "=r"(r) : "r"(__float2int_rn(acc)), "r"(q.zc));
-  return r;
+  return add_zero_point(__float2int_rn(acc), q.zc);
 }
 __device__ __forceinline__ uint32_t pack_sat_s8(int r0, int r1, int r2, int r3) {
   uint32_t hi, out;
@@ -119,8 +122,8 @@ __device__ __forceinline__ bool channel_in_fast_range(float sb, int zb) {
 }
 
 // One thread's 32 consecutive accumulator columns -> 32 int8 in eight words: zero-point
-// identity, then requantisation.  `col_sum_at` points at colsum(B) of the first column
-// (read through L2: another grid may have produced it while this one was running), `rt_row`
+// identity, then requantisation.  `col_sums` holds colsum(B) of the 32 columns (zeros when
+// the activation zero point is zero), `rt_row`
 // is K*zA - rowsum(A)[m] for this thread's row, so that
 //   dot = raw + zB * rt_row - zA * colsum(B)[n].
 // PC: per-channel weight scale / zero point, read from q.sb_vec / q.zb_vec at column n0 + ...
@@ -128,7 +131,7 @@ __device__ __forceinline__ bool channel_in_fast_range(float sb, int zb) {
 // the matrix as a whole).
 template <bool WIDE, bool FAST, bool PC>
 __device__ __forceinline__ void requantize_chunk(
-    const uint32_t (&v)[32], const int* __restrict__ col_sum_at,
+    const uint32_t (&v)[32], const int4 (&col_sums)[8],
     typename std::conditional<WIDE, long long, unsigned>::type rt_row, const Quant& q, int n0, int N,
     uint32_t (&packed)[8]) {
   using Wide = typename std::conditional<WIDE, long long, unsigned>::type;
@@ -137,9 +140,7 @@ __device__ __forceinline__ void requantize_chunk(
   const Wide tensor_term = Wide(Signed(q.zb)) * rt_row;
 #pragma unroll
   for (int g = 0; g < 8; ++g) {
-    int4 cs = make_int4(0, 0, 0, 0);
-    if (q.za != 0) cs = __ldcg(reinterpret_cast<const int4*>(col_sum_at + g * 4));
-    const int csv[4] = {cs.x, cs.y, cs.z, cs.w};
+    const int csv[4] = {col_sums[g].x, col_sums[g].y, col_sums[g].z, col_sums[g].w};
     float sbv[4] = {q.sb, q.sb, q.sb, q.sb};
     int zbv[4] = {q.zb_bias, q.zb_bias, q.zb_bias, q.zb_bias};
     if (PC && n0 + g * 4 < N) {
@@ -158,7 +159,7 @@ __device__ __forceinline__ void requantize_chunk(
       const float x = float(Signed(dot));
       if (FAST) {
         const float acc = div_rn_inrange(__fmul_rn(__fmul_rn(x, q.sa), sbv[e]), q.sc, q.rsc);
-        asm("add.sat.s32 %0, %1, %2;" : "=r"(r[e]) : "r"(__float2int_rn(acc)), "r"(q.zc));
+        r[e] = add_zero_point(__float2int_rn(acc), q.zc);
       } else {
         r[e] = requantize(x, q.sa, sbv[e], q.sc, zc);
       }
@@ -186,19 +187,19 @@ __device__ __forceinline__ bool chunk_channels_fast(const Quant& q, int n0, int 
 // Picks the form of requantize_chunk for one chunk.
 template <bool WIDE>
 __device__ __forceinline__ void requantize_chunk_auto(
-    const uint32_t (&v)[32], const int* __restrict__ col_sum_at,
+    const uint32_t (&v)[32], const int4 (&col_sums)[8],
     typename std::conditional<WIDE, long long, unsigned>::type rt_row, const Quant& q, int n0, int N,
     uint32_t (&packed)[8]) {
   if (q.sb_vec == nullptr) {
     if (q.fast_div)
-      requantize_chunk<WIDE, true, false>(v, col_sum_at, rt_row, q, n0, N, packed);
+      requantize_chunk<WIDE, true, false>(v, col_sums, rt_row, q, n0, N, packed);
     else
-      requantize_chunk<WIDE, false, false>(v, col_sum_at, rt_row, q, n0, N, packed);
+      requantize_chunk<WIDE, false, false>(v, col_sums, rt_row, q, n0, N, packed);
   } else {
     if (q.fast_div && chunk_channels_fast(q, n0, N))
-      requantize_chunk<WIDE, true, true>(v, col_sum_at, rt_row, q, n0, N, packed);
+      requantize_chunk<WIDE, true, true>(v, col_sums, rt_row, q, n0, N, packed);
     else
-      requantize_chunk<WIDE, false, true>(v, col_sum_at, rt_row, q, n0, N, packed);
+      requantize_chunk<WIDE, false, true>(v, col_sums, rt_row, q, n0, N, packed);
   }
 }
 
@@ -364,7 +365,8 @@ __device__ __forceinline__ void drain_half(uint32_t tmem_row_addr, int col0, int
                                            const int* __restrict__ row_sum,
                                            const int* __restrict__ col_sum, int N, int K,
                                            const Quant& q, int c_vector_ok,
-                                           uint8_t* gather_stage = nullptr) {
+                                           uint8_t* gather_stage = nullptr,
+                                           int4* colsum_stage = nullptr) {
   if (q.swiglu) {
     drain_half_swiglu<WIDE>(tmem_row_addr, col0, n_tile0, m, row_ok, C, row_sum, col_sum, N, K, q,
                             c_vector_ok);
@@ -384,17 +386,33 @@ __device__ __forceinline__ void drain_half(uint32_t tmem_row_addr, int col0, int
   const bool staged = q.n_peers > 0 && gather_stage != nullptr && c_vector_ok &&
                       n_tile0 + col0 + 128 <= N;  // warp-uniform
   const int lane = threadIdx.x % 32;
+  // Column sums (col_sum is padded to a multiple of the tile width: never out of bounds; read
+  // through L2: other CTAs of this grid may have produced them).  With a staging area the warp
+  // fetches the 128 sums of its half in one load, four per lane, and every chunk reads its 32
+  // from shared memory: one trip to L2 per drain instead of one per chunk.
+  const bool staged_sums = colsum_stage != nullptr && q.za != 0;
+  if (staged_sums) {
+    __syncwarp();  // the previous drain's readers are done
+    colsum_stage[lane] = __ldcg(reinterpret_cast<const int4*>(col_sum + n_tile0 + col0) + lane);
+    __syncwarp();
+  }
 #pragma unroll 1
   for (int chunk = 0; chunk < 4; ++chunk) {
     const int col = col0 + chunk * 32;
     const int n0 = n_tile0 + col;
     uint32_t v[32];
     tmem_ld_32x32(tmem_row_addr + col, v);
+    // the chunk's column sums travel while the accumulator columns do
+    int4 col_sums[8];
+#pragma unroll
+    for (int g = 0; g < 8; ++g)
+      col_sums[g] = staged_sums ? colsum_stage[chunk * 8 + g]
+                    : q.za != 0 ? __ldcg(reinterpret_cast<const int4*>(col_sum + n0 + g * 4))
+                                : make_int4(0, 0, 0, 0);
     tmem_ld_wait();
     if (n0 >= N) continue;  // warp-uniform
     uint32_t packed[8];
-    // col_sum is padded to a multiple of the tile width: never out of bounds.
-    requantize_chunk_auto<WIDE>(v, col_sum + n0, rt_row, q, n0, N, packed);
+    requantize_chunk_auto<WIDE>(v, col_sums, rt_row, q, n0, N, packed);
     if (staged) {
       // row `lane` of the tile, 16-byte pieces 2*chunk and 2*chunk+1, XOR-swizzled by the row
       uint8_t* row = gather_stage + lane * 128;

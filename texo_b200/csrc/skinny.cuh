@@ -227,9 +227,7 @@ __device__ __forceinline__ void skinny_store_rows(const uint32_t (&v)[32], const
     const long long dot = (long long)int(v[m]) + (long long)zb_n * (kza - row_sum[m]) - col_term;
     if (FAST) {
       const float acc = div_rn_inrange(__fmul_rn(__fmul_rn(float(dot), q.sa), sb_n), q.sc, q.rsc);
-      int t;
-      asm("add.sat.s32 %0, %1, %2;" : "=r"(t) : "r"(__float2int_rn(acc)), "r"(q.zc));
-      r[m] = min(max(t, -128), 127);
+      r[m] = min(max(add_zero_point(__float2int_rn(acc), q.zc), -128), 127);
     } else {
       r[m] = requantize(float(dot), q.sa, sb_n, q.sc, zc);
     }
