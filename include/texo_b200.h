@@ -242,7 +242,7 @@ int texo_mm_int8_status(void);
 /* mm_int4: 1 = generic FP32 kernel, 2 = tcgen05 kind::f16 CTA-pair kernel with a TMEM drain
  * per scale group (needs 16-byte aligned x / w_q, K % 64 == 0, group_size 16, 32, 64 or 128),
  * 4 = the same pipeline with the scale folded exactly into the weight operand (FP16 hi + lo,
- * two MMAs per k step, one drain per tile; the default for group_size <= 32),
+ * two MMAs per k step, one drain per tile; the default for group_size <= 64),
  * 3 = streaming (decode) kernel
  * (M <= 16, group_size 128, K % 128 == 0, aligned x / w_q): packed weights read once from HBM
  * straight into registers, mma.sync on 16-row activation tiles. */

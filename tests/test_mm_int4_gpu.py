@@ -104,7 +104,7 @@ def test_tensor_path_full_matrix(lib, oracle, shape):
     x, w, s = oracle.int4_inputs(m, n, k, g, 100 + m)
     want = oracle.mm_int4(x, w, s, m, n, k, g)
     # 2 = a TMEM drain per scale group (any of the four group sizes); 4 = scale folded into the
-    # weight operand as an exact FP16 hi + lo pair, one drain per tile (G <= 32, where it is the
+    # weight operand as an exact FP16 hi + lo pair, one drain per tile (G <= 64, where it is the
     # default).  Forcing either also keeps few-row shapes off the decode kernel.
     for force in ((2, 4) if g <= 64 else (2,)):
         lib.texo_mm_int4_force_path(force)

@@ -491,7 +491,7 @@ __global__ void __launch_bounds__(T_THREADS, 1)
   }
 }
 
-// ------------------------------- tensor path for small scale groups (G <= 32)
+// ------------------------------- tensor path for small scale groups (G <= 64)
 // With a drain per scale group the kernel above is bound by tensor-memory traffic: every group
 // moves the whole 128 x 256 FP32 accumulator out through tcgen05.ld (about as long as a
 // 128-k group's MMAs take, and the two do not overlap), so at G = 32 / 16 the drains cost 4x /
