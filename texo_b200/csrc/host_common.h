@@ -135,6 +135,26 @@ inline int read_and_clear_status() {
   return code;
 }
 
+// Launch on the legacy default stream with programmatic stream serialisation: the grid may be
+// scheduled while the grid ahead of it drains (its CTAs take SMs as they become free and run
+// up to their grid_dependency_wait, ptx.cuh).  Only for kernels that execute that wait before
+// touching global memory.
+template <typename... Params, typename... Args>
+inline cudaError_t launch_overlapping_predecessor(void (*kernel)(Params...), dim3 grid, dim3 block,
+                                                  size_t smem_bytes, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem_bytes;
+  cfg.stream = 0;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, Params(args)...);
+}
+
 // ------------------------------------------------------------ instrumentation
 // Cumulative number of kernels this library has launched (all devices).
 inline long long& launch_counter() {

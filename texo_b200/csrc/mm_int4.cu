@@ -202,6 +202,7 @@ __global__ void __launch_bounds__(T_THREADS, 1)
                   const __half* __restrict__ scales, __half* __restrict__ y, int M, int N, int K,
                   int G, int tiles_n, int tiles_m, int* status) {
   extern __shared__ uint8_t smem_raw[];
+  grid_dependency_trigger();  // the next grid may set itself up while this one runs
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~uintptr_t(1023));
   TensorBarriers* bars = reinterpret_cast<TensorBarriers*>(smem + T_STAGES * T_STAGE_BYTES);
@@ -235,6 +236,9 @@ __global__ void __launch_bounds__(T_THREADS, 1)
   cluster_sync_all();
   tc_fence_after_sync();
   const uint32_t tmem_base = bars->tmem_base;
+  // set-up done while the grid ahead of this one may still be running; nothing below touches
+  // global memory before that grid has completed
+  grid_dependency_wait();
 
   // Commit numbering: scale groups are numbered globally over the tiles this pair processes;
   // the MMA warp issues one tcgen05.commit per group, number c, onto group_done[c % T_RING].
@@ -526,6 +530,7 @@ __global__ void __launch_bounds__(T_THREADS, 1)
                         const __half* __restrict__ scales, __half* __restrict__ y, int M, int N, int K,
                         int G, int tiles_n, int tiles_m, int* status) {
   extern __shared__ uint8_t smem_raw[];
+  grid_dependency_trigger();  // the next grid may set itself up while this one runs
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~uintptr_t(1023));
   SplitBarriers* bars = reinterpret_cast<SplitBarriers*>(smem + S_STAGES * S_STAGE_BYTES);
@@ -561,6 +566,9 @@ __global__ void __launch_bounds__(T_THREADS, 1)
   cluster_sync_all();
   tc_fence_after_sync();
   const uint32_t tmem_base = bars->tmem_base;
+  // set-up done while the grid ahead of this one may still be running; nothing below touches
+  // global memory before that grid has completed
+  grid_dependency_wait();
 
   if (warp < T_CONV_WARP0) {
    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(S_REGS_CONTROL));
@@ -780,13 +788,15 @@ static bool launch_tensor_split(DeviceCtx& ctx, const __half* x, const uint8_t* 
   cfg.blockDim = dim3(T_THREADS);
   cfg.dynamicSmemBytes = S_SMEM_BYTES;
   cfg.stream = 0;
-  cudaLaunchAttribute attr;
-  attr.id = cudaLaunchAttributeClusterDimension;
-  attr.val.clusterDim.x = 2;
-  attr.val.clusterDim.y = 1;
-  attr.val.clusterDim.z = 1;
-  cfg.attrs = &attr;
-  cfg.numAttrs = 1;
+  cudaLaunchAttribute attrs[2];
+  attrs[0].id = cudaLaunchAttributeClusterDimension;
+  attrs[0].val.clusterDim.x = 2;
+  attrs[0].val.clusterDim.y = 1;
+  attrs[0].val.clusterDim.z = 1;
+  attrs[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;  // see grid_dependency_wait in the kernel
+  attrs[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attrs;
+  cfg.numAttrs = 2;
   if (!configured[ctx.device]) {
     configured[ctx.device] = true;
     cudaFuncSetAttribute(tensor_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S_SMEM_BYTES);
@@ -831,13 +841,15 @@ static bool launch_tensor(DeviceCtx& ctx, const __half* x, const uint8_t* w_q, c
   cfg.blockDim = dim3(T_THREADS);
   cfg.dynamicSmemBytes = T_SMEM_BYTES;
   cfg.stream = 0;
-  cudaLaunchAttribute attr;
-  attr.id = cudaLaunchAttributeClusterDimension;
-  attr.val.clusterDim.x = 2;
-  attr.val.clusterDim.y = 1;
-  attr.val.clusterDim.z = 1;
-  cfg.attrs = &attr;
-  cfg.numAttrs = 1;
+  cudaLaunchAttribute attrs[2];
+  attrs[0].id = cudaLaunchAttributeClusterDimension;
+  attrs[0].val.clusterDim.x = 2;
+  attrs[0].val.clusterDim.y = 1;
+  attrs[0].val.clusterDim.z = 1;
+  attrs[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;  // see grid_dependency_wait in the kernel
+  attrs[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attrs;
+  cfg.numAttrs = 2;
   if (!configured[ctx.device]) {
     configured[ctx.device] = true;
     cudaFuncSetAttribute(tensor_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T_SMEM_BYTES);
@@ -902,8 +914,8 @@ static bool launch_decode(DeviceCtx& ctx, const __half* x, const uint8_t* w_q, c
   if (rowgroups == 0) return false;
   const int grid = (N + 32 * rowgroups - 1) / (32 * rowgroups);
   const int slot = profile_start();
-  decode_kernel<<<grid, D_THREADS, D_SMEM_BYTES>>>(x, w_q, scales, y, M, N, K, rowgroups);
-  if (cudaPeekAtLastError() != cudaSuccess) {
+  if (launch_overlapping_predecessor(decode_kernel, dim3(grid), dim3(D_THREADS), D_SMEM_BYTES, x, w_q, scales, y,
+                                     M, N, K, rowgroups) != cudaSuccess) {
     cudaGetLastError();
     profile_stop(slot);
     note_host_error(STATUS_LAUNCH_FAILED);

@@ -540,8 +540,8 @@ static bool launch_decode(DeviceCtx& ctx, const int8_t* A, const uint8_t* w_q, i
   if (rowgroups == 0) return false;
   const int grid = (N + 32 * rowgroups - 1) / (32 * rowgroups);
   const int slot = profile_start();
-  decode_kernel<<<grid, E_THREADS, E_SMEM_BYTES>>>(A, w_q, C, M, N, K, q, rowgroups);
-  if (cudaPeekAtLastError() != cudaSuccess) {
+  if (launch_overlapping_predecessor(decode_kernel, dim3(grid), dim3(E_THREADS), E_SMEM_BYTES, A, w_q, C, M, N, K,
+                                     q, rowgroups) != cudaSuccess) {
     cudaGetLastError();
     profile_stop(slot);
     note_host_error(STATUS_LAUNCH_FAILED);

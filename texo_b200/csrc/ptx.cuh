@@ -39,6 +39,14 @@ __device__ __forceinline__ bool elect_one() {
   return pred != 0;
 }
 
+// Programmatic dependent launch.  A kernel launched with programmatic stream serialisation
+// may be scheduled as soon as every CTA of the grid ahead of it in the stream has executed
+// grid_dependency_trigger (or exited); it must execute grid_dependency_wait before it touches
+// global memory: the wait returns when that grid has completed and its writes are visible.
+// Both are no-ops in a launch without the attribute.
+__device__ __forceinline__ void grid_dependency_trigger() { asm volatile("griddepcontrol.launch_dependents;"); }
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // ------------------------------------------------------------------ mbarrier
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count)

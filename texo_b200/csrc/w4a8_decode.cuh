@@ -82,6 +82,9 @@ __global__ void __launch_bounds__(E_THREADS, 1)
     decode_kernel(const int8_t* __restrict__ A, const uint8_t* __restrict__ w_q, int8_t* __restrict__ C,
                   int M, int N, int K, i8::Quant q, int rowgroups) {
   extern __shared__ uint8_t smem_raw[];
+  // scheduled while the grid ahead of it drains; nothing is read before that grid is complete
+  grid_dependency_trigger();
+  grid_dependency_wait();
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   const int r = lane / 4, j = lane % 4;
