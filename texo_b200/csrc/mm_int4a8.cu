@@ -92,50 +92,6 @@ __global__ void __launch_bounds__(GT * GT)
   }
 }
 
-// ------------------------------------------------------------ sums pre-pass
-// One warp per row: rows 0..M-1 are rows of A (signed byte sums), rows M..M+N-1 are weight
-// rows (sums of the unsigned nibbles).  16-byte loads; the tensor path guarantees alignment.
-constexpr int SUM_WARPS = 8;
-
-__global__ void __launch_bounds__(SUM_WARPS * 32)
-    sums_kernel(const int8_t* __restrict__ A, const uint8_t* __restrict__ W, int* __restrict__ row_sum,
-                int* __restrict__ w_sum, int M, int N, int K, int first_row, int rows) {
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  const int r = first_row + blockIdx.x * SUM_WARPS + threadIdx.x / 32;
-  const int lane = threadIdx.x % 32;
-  if (r >= first_row + rows) return;
-  int acc = 0;
-  if (r < M) {
-    const int4* src = reinterpret_cast<const int4*>(A + size_t(r) * K);
-    for (int i = lane; i < K / 16; i += 32) {
-      const int4 v = __ldg(src + i);
-      acc = __dp4a(v.x, 0x01010101, acc);
-      acc = __dp4a(v.y, 0x01010101, acc);
-      acc = __dp4a(v.z, 0x01010101, acc);
-      acc = __dp4a(v.w, 0x01010101, acc);
-    }
-  } else {
-    const uint4* src = reinterpret_cast<const uint4*>(W + size_t(r - M) * (K / 2));
-    for (int i = lane; i < K / 32; i += 32) {
-      const uint4 v = __ldg(src + i);
-      const uint32_t words[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-      for (int w = 0; w < 4; ++w) {
-        const uint32_t both = (words[w] & 0x0f0f0f0fu) + ((words[w] >> 4) & 0x0f0f0f0fu);
-        acc = int(__dp4a(both, 0x01010101u, unsigned(acc)));  // bytes <= 30, unsigned
-      }
-    }
-  }
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-  if (lane == 0) {
-    if (r < M)
-      row_sum[r] = acc;
-    else
-      w_sum[r - M] = acc;
-  }
-}
-
 // --------------------------------------------------------------- tensor path
 constexpr int BK = 128;    // k per stage = one 128-byte swizzle row of int8
 constexpr int UMMA_K = 32;  // k per kind::i8 instruction
@@ -175,12 +131,114 @@ __device__ __forceinline__ void unpack32(const uint4& packed, uint4& first, uint
   second = make_uint4(out[4], out[5], out[6], out[7]);
 }
 
+// ----------------------------------------------- sums inside the pair kernel
+// rowsum(A) (signed bytes, needed when the effective weight zero point zB + 8 is non-zero) and
+// the per-row sums of the unsigned nibbles of W (needed when zA is non-zero) are computed by
+// the epilogue warps of this kernel, exactly as the INT8 CTA-pair kernel computes its sums
+// (mm_int8.cu, "sums inside the CTA-pair kernel"): items of sixteen rows (sixteen threads per
+// row), ordered as the raster needs them - the A rows of the first eight tile rows, all weight
+// rows, the remaining A rows -, dealt round robin over the CTAs of the grid, each published by
+// a release store of the call's epoch number into the item's flag; a tile is drained when the
+// flags of its 8 + 16 items carry the epoch.  A CTA blocks on a flag only when it has no item
+// left to do, and every wait is bounded.
+constexpr int QS_ROWS = 16;                          // rows per item
+constexpr int QS_FIRST_A_ITEMS = 8 * 256 / QS_ROWS;  // A items of the first eight tile rows
+constexpr int Q_DECISION_BYTES = 64;
+constexpr int Q_AUX_SMEM_BYTES = Q_DECISION_BYTES + Q_EPI_WARPS * 512;  // + 128 nibble sums per epilogue warp
+static_assert(Q_SMEM_BYTES + Q_AUX_SMEM_BYTES <= 232448, "W4A8 pair kernel: shared memory over the limit");
+
+__device__ __forceinline__ void epilogue_bar() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+
+// Sum of the 32 unsigned nibbles of v, added to acc.
+__device__ __forceinline__ int sum_nibbles(const int4& v, int acc) {
+  const uint32_t words[4] = {uint32_t(v.x), uint32_t(v.y), uint32_t(v.z), uint32_t(v.w)};
+#pragma unroll
+  for (int w = 0; w < 4; ++w) {
+    const uint32_t both = (words[w] & 0x0f0f0f0fu) + ((words[w] >> 4) & 0x0f0f0f0fu);  // bytes <= 30
+    acc = int(__dp4a(both, 0x01010101u, unsigned(acc)));
+  }
+  return acc;
+}
+
+// Sixteen rows of `row_bytes` bytes each (a multiple of 16), sixteen threads per row, up to
+// sixteen 16-byte streaming loads in flight per thread; out[row] = sum of the signed bytes
+// (NIBBLES = false) or of the unsigned nibbles (true).  `et` = index among the 256 epilogue
+// threads.
+template <bool NIBBLES>
+__device__ __forceinline__ void sum_sixteen_rows(const uint8_t* __restrict__ base, int row_bytes, int rows_total,
+                                                 int item, int* __restrict__ out, int et) {
+  const int sub = et % 16, r = item * QS_ROWS + et / 16;
+  int acc = 0;
+  if (r < rows_total) {
+    const int4* src = reinterpret_cast<const int4*>(base + size_t(r) * row_bytes);
+    const int chunks = row_bytes / 16;
+    auto add = [](const int4& v, int a) { return NIBBLES ? sum_nibbles(v, a) : i8::sum_bytes(v, a); };
+    int i = sub;
+    for (; i + 15 * 16 < chunks; i += 16 * 16) {
+      int4 v[16];
+#pragma unroll
+      for (int u = 0; u < 16; ++u) v[u] = __ldcs(src + i + u * 16);
+#pragma unroll
+      for (int u = 0; u < 16; ++u) acc = add(v[u], acc);
+    }
+    for (; i + 3 * 16 < chunks; i += 4 * 16) {
+      int4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) v[u] = __ldcs(src + i + u * 16);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) acc = add(v[u], acc);
+    }
+    for (; i < chunks; i += 16) acc = add(__ldcs(src + i), acc);
+  }
+#pragma unroll
+  for (int o = 8; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if (sub == 0 && r < rows_total) out[r] = acc;
+}
+
+// Computes the item at position `pos` of the processing order and publishes it.
+__device__ __forceinline__ void epilogue_sum_item(int pos, const int8_t* __restrict__ A,
+                                                  const uint8_t* __restrict__ W, int* __restrict__ row_sum,
+                                                  int* __restrict__ w_sum, int M, int N, int K, int a_items,
+                                                  int w_items, int et, unsigned* flags, unsigned epoch) {
+  const int first_a = min(a_items, QS_FIRST_A_ITEMS);
+  if (pos >= first_a && pos < first_a + w_items)
+    sum_sixteen_rows<true>(W, K / 2, N, pos - first_a, w_sum, et);
+  else
+    sum_sixteen_rows<false>(reinterpret_cast<const uint8_t*>(A), K, M, pos < first_a ? pos : pos - w_items,
+                            row_sum, et);
+  epilogue_bar();  // orders every thread's stores before the first thread's (cumulative) release
+  if (et == 0) asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(flags + pos), "r"(epoch) : "memory");
+}
+
+// Whether the sums this CTA's part of tile (tm, tn) needs are published: its 128 rows of A
+// (eight items) and the tile's 256 weight rows (sixteen items).  Called by one full warp.
+__device__ __forceinline__ bool tile_sums_ready(int tm, int tn, int rank, int a_items, int w_items,
+                                                const unsigned* flags, unsigned epoch, int lane) {
+  const int first_a = min(a_items, QS_FIRST_A_ITEMS);
+  int pos = -1;
+  if (lane < 8) {
+    const int i = (tm * 256 + rank * 128) / QS_ROWS + lane;
+    if (i < a_items) pos = i < first_a ? i : i + w_items;
+  } else if (lane < 24) {
+    const int j = tn * (256 / QS_ROWS) + (lane - 8);
+    if (j < w_items) pos = first_a + j;
+  }
+  bool ready = true;
+  if (pos >= 0) {
+    unsigned seen;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(flags + pos) : "memory");
+    ready = seen == epoch;
+  }
+  return __all_sync(0xffffffffu, ready);
+}
+
 template <bool WIDE>
 __global__ void __launch_bounds__(Q_THREADS, 1)
     pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_raw,
-                int8_t* __restrict__ C, const int* __restrict__ row_sum,
-                const int* __restrict__ w_sum, int M, int N, int K, Quant q, int tiles_m, int tiles_n,
-                int c_vector_ok, int* status) {
+                int8_t* __restrict__ C, int* row_sum, int* w_sum, int M, int N, int K, Quant q,
+                int tiles_m, int tiles_n, int c_vector_ok, int* status, const int8_t* __restrict__ A_raw,
+                const uint8_t* __restrict__ W_raw, int a_items, int w_items, unsigned* item_flags,
+                unsigned epoch) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~uintptr_t(1023));
@@ -191,6 +249,7 @@ __global__ void __launch_bounds__(Q_THREADS, 1)
   const int cluster_id = blockIdx.x / 2, num_clusters = gridDim.x / 2;
   const int num_tiles = tiles_m * tiles_n;
   const int num_kb = (K + BK - 1) / BK;
+  grid_dependency_trigger();  // the next grid may set itself up while this one runs
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < Q_STAGES; ++s) {
@@ -227,6 +286,7 @@ __global__ void __launch_bounds__(Q_THREADS, 1)
     int g = 0;          // global k-block number of the next load
     int observed = -1;  // highest commit number seen complete
     bool ok = true;
+    grid_dependency_wait();  // the operands may have been written by the grid ahead of this one
     for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
       int tm, tn;
       i8::pair_tile_coords(tile, tiles_m, tiles_n, tm, tn);
@@ -351,19 +411,74 @@ __global__ void __launch_bounds__(Q_THREADS, 1)
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
-    // The sums come from the pre-pass grid, which may still be running when this kernel was
-    // launched behind it with programmatic stream serialisation.
-    asm volatile("griddepcontrol.wait;" ::: "memory");
+    // Everything this kernel reads or writes may be in use by the grid ahead of it in the
+    // stream until that grid has completed.
+    grid_dependency_wait();
+    const int et = threadIdx.x - Q_EPI_WARP0 * 32;
+    const int total_items = a_items + w_items;
+    int next_item = blockIdx.x;  // this CTA's next position in the processing order
+    uint8_t* const aux = smem + Q_STAGES * Q_STAGE_BYTES + 256;
+    volatile int* decision = reinterpret_cast<volatile int*>(aux);
+    int4* colsum_stage = reinterpret_cast<int4*>(aux + Q_DECISION_BYTES) + ew * 32;
+    int round = 0;  // alternates the two decision words, so that one barrier per decision suffices
+    int items_done = 0;
+    if (next_item < total_items) {  // the first item needs no decision: nothing else can be ready yet
+      epilogue_sum_item(next_item, A_raw, W_raw, row_sum, w_sum, M, N, K, a_items, w_items, et, item_flags, epoch);
+      next_item += gridDim.x;
+      ++items_done;
+    }
     for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
       int tm, tn;
       i8::pair_tile_coords(tile, tiles_m, tiles_n, tm, tn);
+      if (total_items > 0) {
+        // Until the accumulator is complete AND this tile's sums are published: the second item
+        // at once, then one item per tile, all remaining ones without pause if this tile's
+        // sums are missing (a CTA never sits idle on a flag while it still owes items).
+        const long long start = clock64();
+        bool item_this_tile = false;
+        while (true) {
+          if (ew == 0) {
+            int d = 0;  // 0 = wait, 1 = go on to the drain, 2 = do an item, 3 = give up
+            const bool acc_ready = mbar_try_wait(&bars->acc_full[acc], acc_phase);
+            const bool sums_ready = tile_sums_ready(tm, tn, int(rank), a_items, w_items, item_flags, epoch, lane);
+            if (acc_ready && sums_ready) d = 1;
+            else if (next_item < total_items && (items_done < 2 || !sums_ready || !item_this_tile)) d = 2;
+            else if (*abort_flag) d = 3;
+            else if (clock64() - start > WAIT_BUDGET_CLOCKS) {
+              d = 3;
+              *abort_flag = 1;
+              if (status) atomicCAS(status, 0, acc_ready ? STATUS_TIMEOUT_FLAG : STATUS_TIMEOUT_TMEM_FULL);
+            }
+            if (lane == 0) decision[round & 1] = d;
+          }
+          epilogue_bar();
+          const int d = decision[round & 1];
+          ++round;
+          if (d == 1) break;
+          if (d == 3) {
+            ok = false;
+            break;
+          }
+          if (d == 2) {
+            epilogue_sum_item(next_item, A_raw, W_raw, row_sum, w_sum, M, N, K, a_items, w_items, et, item_flags,
+                              epoch);
+            next_item += gridDim.x;
+            ++items_done;
+            item_this_tile = true;
+          } else {
+            __nanosleep(100);
+          }
+        }
+        if (!ok) break;
+        __threadfence();
+      }
       ok = mbar_wait(&bars->acc_full[acc], acc_phase, abort_flag, status, STATUS_TIMEOUT_TMEM_FULL);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after_sync();
       const int m = tm * 256 + int(rank) * 128 + quarter * 32 + lane;
       i8::drain_half<WIDE>(tmem_base + acc * Q_ACC_COLS + (uint32_t(quarter * 32) << 16), half * 128,
-                           tn * 256, m, m < M, C, row_sum, w_sum, N, K, q, c_vector_ok);
+                           tn * 256, m, m < M, C, row_sum, w_sum, N, K, q, c_vector_ok, nullptr, colsum_stage);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&bars->acc_empty[acc]), 0));
@@ -371,6 +486,12 @@ __global__ void __launch_bounds__(Q_THREADS, 1)
         acc = 0;
         acc_phase ^= 1;
       }
+    }
+    // whatever is left of this CTA's share of the sums (other CTAs' later tiles wait for it; a
+    // pair that owns no tile does all of its share here)
+    while (ok && next_item < total_items) {
+      epilogue_sum_item(next_item, A_raw, W_raw, row_sum, w_sum, M, N, K, a_items, w_items, et, item_flags, epoch);
+      next_item += gridDim.x;
     }
   }
 
@@ -410,14 +531,14 @@ static int max_active_pairs(DeviceCtx& ctx) {
   static bool known[MAX_DEVICES] = {};
   if (!known[ctx.device]) {
     known[ctx.device] = true;
-    cudaFuncSetAttribute(pair_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Q_SMEM_BYTES);
-    cudaFuncSetAttribute(pair_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Q_SMEM_BYTES);
-    cudaFuncSetAttribute(sums_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
-                         cudaSharedmemCarveoutMaxShared);
+    cudaFuncSetAttribute(pair_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         Q_SMEM_BYTES + Q_AUX_SMEM_BYTES);
+    cudaFuncSetAttribute(pair_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         Q_SMEM_BYTES + Q_AUX_SMEM_BYTES);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2 * ctx.sm_count);
     cfg.blockDim = dim3(Q_THREADS);
-    cfg.dynamicSmemBytes = Q_SMEM_BYTES;
+    cfg.dynamicSmemBytes = Q_SMEM_BYTES + Q_AUX_SMEM_BYTES;
     cudaLaunchAttribute attr;
     attr.id = cudaLaunchAttributeClusterDimension;
     attr.val.clusterDim.x = 2;
@@ -453,48 +574,40 @@ static bool launch_tensor(DeviceCtx& ctx, const int8_t* A, const uint8_t* W, int
   int* row_sum = scratch;
   int* w_sum = scratch + m_pad;
   // rows of A are needed when the effective weight zero point (zB + 8) is non-zero, the
-  // nibble sums when zA is
+  // nibble sums when zA is; the kernel's epilogue warps compute both (no pre-pass)
   const bool need_rows = q.zb != 0 || q.sb_vec != nullptr;  // per-channel zero points: unknown here
-  const int first = need_rows ? 0 : M;
-  const int rows = (need_rows ? M : 0) + (q.za != 0 ? N : 0);
-  bool sums_launched = false;
-  if (rows > 0) {
-    sums_kernel<<<(rows + SUM_WARPS - 1) / SUM_WARPS, SUM_WARPS * 32>>>(A, W, row_sum, w_sum, M, N, K,
-                                                                         first, rows);
-    ++launch_counter();
-    sums_launched = true;
-  }
+  const int a_items = need_rows ? (M + QS_ROWS - 1) / QS_ROWS : 0;
+  const int w_items = q.za != 0 ? (N + QS_ROWS - 1) / QS_ROWS : 0;
+  unsigned* item_flags = device_item_flags(ctx, size_t(std::max(a_items + w_items, 1)) * sizeof(unsigned));
+  if (!item_flags) return false;
+  // a finished item is marked with this call's epoch number: never zero, never used twice
+  if (++ctx.sums_epoch == 0) ++ctx.sums_epoch;
+  const unsigned epoch = ctx.sums_epoch;
   const int slot = profile_start();
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(2 * std::min(tiles_m * tiles_n, pairs));
+  // one pair per tile up to what the device holds; a small problem gets extra pairs that own
+  // no tile and only help with the sums
+  const int helper_pairs = (a_items + w_items + 1) / 2;
+  cfg.gridDim = dim3(2 * std::min(std::max(tiles_m * tiles_n, helper_pairs), pairs));
   cfg.blockDim = dim3(Q_THREADS);
-  cfg.dynamicSmemBytes = Q_SMEM_BYTES;
+  cfg.dynamicSmemBytes = Q_SMEM_BYTES + Q_AUX_SMEM_BYTES;
   cfg.stream = 0;
   cudaLaunchAttribute attrs[2];
   attrs[0].id = cudaLaunchAttributeClusterDimension;
   attrs[0].val.clusterDim.x = 2;
   attrs[0].val.clusterDim.y = 1;
   attrs[0].val.clusterDim.z = 1;
-  // Start while the sums pre-pass is still running (the epilogue waits for it).
+  // may be scheduled while the grid ahead of it drains (the kernel waits before it touches memory)
   attrs[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attrs[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attrs;
+  cfg.numAttrs = 2;
   const int c_vector_ok = (reinterpret_cast<uintptr_t>(C) & 15) == 0 && N % 16 == 0;
-  const int* rs = row_sum;
-  const int* ws = w_sum;
-  static bool overlap_ok = true;
-  cudaError_t err = cudaSuccess;
-  for (int attempt = 0; attempt < 2; ++attempt) {
-    const bool overlap = sums_launched && overlap_ok && attempt == 0;
-    cfg.numAttrs = overlap ? 2 : 1;
-    err = wide ? cudaLaunchKernelEx(&cfg, pair_kernel<true>, map_a, map_raw, C, rs, ws, M, N, K, q,
-                                    tiles_m, tiles_n, c_vector_ok, ctx.status)
-               : cudaLaunchKernelEx(&cfg, pair_kernel<false>, map_a, map_raw, C, rs, ws, M, N, K, q,
-                                    tiles_m, tiles_n, c_vector_ok, ctx.status);
-    if (err == cudaSuccess || !overlap) break;
-    cudaGetLastError();  // the attribute was refused: launch again, fully serialised
-    overlap_ok = false;
-  }
+  const cudaError_t err =
+      wide ? cudaLaunchKernelEx(&cfg, pair_kernel<true>, map_a, map_raw, C, row_sum, w_sum, M, N, K, q, tiles_m,
+                                tiles_n, c_vector_ok, ctx.status, A, W, a_items, w_items, item_flags, epoch)
+           : cudaLaunchKernelEx(&cfg, pair_kernel<false>, map_a, map_raw, C, row_sum, w_sum, M, N, K, q, tiles_m,
+                                tiles_n, c_vector_ok, ctx.status, A, W, a_items, w_items, item_flags, epoch);
   if (err != cudaSuccess) {
     cudaGetLastError();
     profile_stop(slot);

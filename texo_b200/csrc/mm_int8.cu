@@ -517,13 +517,7 @@ static_assert(ES_ROW_THREADS == 16, "a row item is sixteen rows by sixteen threa
 
 __device__ __forceinline__ void epilogue_bar() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
-// Sum of the sixteen signed bytes of v, added to acc.
-__device__ __forceinline__ int sum_bytes(const int4& v, int acc) {
-  acc = __dp4a(v.x, 0x01010101, acc);
-  acc = __dp4a(v.y, 0x01010101, acc);
-  acc = __dp4a(v.z, 0x01010101, acc);
-  return __dp4a(v.w, 0x01010101, acc);
-}
+
 
 // Position of a row / column item in the processing order described above.
 __device__ __forceinline__ int pos_of_row_item(int i, int row_items, int col_items) {

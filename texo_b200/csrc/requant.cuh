@@ -227,6 +227,14 @@ __device__ __forceinline__ void multimem_st_16(void* mc_addr, const int4& v) {
 
 constexpr int P_GROUP_M = 8;  // pair-tile rows per raster group
 
+// Sum of the sixteen signed bytes of v, added to acc.
+__device__ __forceinline__ int sum_bytes(const int4& v, int acc) {
+  acc = __dp4a(v.x, 0x01010101, acc);
+  acc = __dp4a(v.y, 0x01010101, acc);
+  acc = __dp4a(v.z, 0x01010101, acc);
+  return __dp4a(v.w, 0x01010101, acc);
+}
+
 __device__ __forceinline__ void pair_tile_coords(int tile, int tiles_m, int tiles_n, int& tm,
                                                  int& tn) {
   const int group_tiles = P_GROUP_M * tiles_n;
