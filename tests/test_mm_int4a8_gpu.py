@@ -303,3 +303,25 @@ def test_per_group_weight_scales(lib, oracle, shape):
     torch.cuda.synchronize()
     assert np.array_equal(C.cpu().numpy(), want), shape
     assert lib.texo_mm_int4a8_status() == 0
+
+
+def test_pair_path_is_one_launch(lib, oracle):
+    """The CTA-pair kernel computes rowsum(A) and the nibble sums of W itself (its epilogue warps):
+    a call with both zero points is a single launch, and repeated calls with different
+    operands on the same scratch and flag array stay bit-exact."""
+    rng = np.random.default_rng(78)
+    for (m, n, k), q in (((512, 512, 1024), (0.02, 0.03, 0.5, 3, -5, 1)),
+                         ((300, 1008, 1056), (0.02, 0.03, 2.0, -7, 6, -2)),
+                         ((2048, 272, 4096), (0.01, 0.02, 2.0, 0, 4, 0)),
+                         ((1000, 2064, 512), (0.01, 0.02, 0.5, 5, -8, 3))):
+        a = rng.integers(-128, 128, (m, k), dtype=np.int8)
+        w = rng.integers(0, 256, (n, k // 2), dtype=np.uint8)
+        A, W = _dev(a), _dev(w)
+        C = torch.full((m, n), 55, dtype=torch.int8, device="cuda")
+        before = lib.texo_kernel_launches()
+        lib.texo_mm_int4a8_solve(A.data_ptr(), W.data_ptr(), C.data_ptr(), m, n, k, *q)
+        torch.cuda.synchronize()
+        assert lib.texo_mm_int4a8_last_path() == 2
+        assert lib.texo_kernel_launches() - before == 1
+        assert np.array_equal(C.cpu().numpy(), oracle.mm_int4a8(a, w, m, n, k, q)), (m, n, k)
+    assert lib.texo_mm_int4a8_status() == 0
