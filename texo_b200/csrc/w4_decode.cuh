@@ -61,11 +61,13 @@ __device__ __forceinline__ void cp_async_16(void* smem_dst, const void* src, boo
 // fragment layout described above; part p's i-th 128-k block lands at block p * (span/128) + i.
 __device__ __forceinline__ void stage_x(uint8_t* buf, const __half* __restrict__ x, int M, int K,
                                         int k_first, int part_k, int ksplit, int span) {
+  // (ksplit and span are powers of two: shifts and masks, no integer divisions)
   const int pieces_per_part = span / 8;  // 16-byte pieces (8 halves) per row and part
   const int pieces_per_row = ksplit * pieces_per_part;
+  const int part_log = 31 - __clz(pieces_per_part), row_log = 31 - __clz(pieces_per_row);
   for (int i = threadIdx.x; i < 16 * pieces_per_row; i += D_THREADS) {
-    const int m = i / pieces_per_row, piece = i % pieces_per_row;
-    const int p = piece / pieces_per_part, within = (piece % pieces_per_part) * 8;
+    const int m = i >> row_log, piece = i & (pieces_per_row - 1);
+    const int p = piece >> part_log, within = (piece & (pieces_per_part - 1)) * 8;
     const int k_in_part = k_first + within;
     const int kk = p * span + within;  // k index inside the staged chunk
     uint8_t* dst = buf + (kk / 128) * D_XBLK_BYTES + ((kk % 128) / 32) * D_JBLK_BYTES + m * 64 + (kk % 32) * 2;
@@ -91,9 +93,10 @@ __global__ void __launch_bounds__(D_THREADS, 1)
   const int rg = warp % rowgroups, part = warp / rowgroups;
   const int part_k = K / ksplit;        // a multiple of 128
   const int span = D_CHUNK_K / ksplit;  // k per part per staged chunk, a multiple of 128
-  const int ipc = span / 128;           // iterations per chunk
+  const int ipc = span / 128;           // iterations per chunk (a power of two)
+  const int ipc_log = 31 - __clz(ipc);
   const int iters = part_k / 128;       // 128-k iterations (= scale groups) of this warp
-  const int chunks = (iters + ipc - 1) / ipc;
+  const int chunks = (iters + ipc - 1) >> ipc_log;
   const int groups = K / 128;
   const int n_base = (blockIdx.x * rowgroups + rg) * 32;
 
@@ -134,8 +137,8 @@ __global__ void __launch_bounds__(D_THREADS, 1)
     for (int d = 0; d < D_DEPTH; ++d) {
       const int it = it0 + d;
       if (it >= iters) break;  // uniform over the CTA
-      const int c = it / ipc;
-      if (it % ipc == 0) {  // entering chunk c (uniform over the CTA)
+      const int c = it >> ipc_log;
+      if ((it & (ipc - 1)) == 0) {  // entering chunk c (uniform over the CTA)
         __syncthreads();    // everyone is done with chunk c - 1, whose buffer is refilled now
         if (c + 1 < chunks)
           stage_x(smem + ((c + 1) & 1) * D_X_BYTES, x, M, K, (c + 1) * span, part_k, ksplit, span);
@@ -144,7 +147,7 @@ __global__ void __launch_bounds__(D_THREADS, 1)
         __syncthreads();  // chunk c has landed for every thread
       }
       // x fragments of this 128-k block: rows r and r + 8, this lane's 64 bytes of each
-      const uint8_t* xb = smem + (c & 1) * D_X_BYTES + (part * ipc + it % ipc) * D_XBLK_BYTES + j * D_JBLK_BYTES;
+      const uint8_t* xb = smem + (c & 1) * D_X_BYTES + (part * ipc + (it & (ipc - 1))) * D_XBLK_BYTES + j * D_JBLK_BYTES;
       const uint4* x_lo = reinterpret_cast<const uint4*>(xb + r * 64);
       const uint4* x_hi = reinterpret_cast<const uint4*>(xb + (r + 8) * 64);
       float acc[D_TILES][4];

@@ -62,11 +62,13 @@ __device__ __forceinline__ void e_cp_async_16(void* smem_dst, const void* src, b
 // p's i-th 128-k block lands at block p * (span/128) + i, rows in natural byte order.
 __device__ __forceinline__ void stage_a(uint8_t* buf, const int8_t* __restrict__ A, int M, int K,
                                         int k_first, int part_k, int ksplit, int span) {
+  // (ksplit and span are powers of two: shifts and masks, no integer divisions)
   const int pieces_per_part = span / 16;
   const int pieces_per_row = ksplit * pieces_per_part;
+  const int part_log = 31 - __clz(pieces_per_part), row_log = 31 - __clz(pieces_per_row);
   for (int i = threadIdx.x; i < 16 * pieces_per_row; i += E_THREADS) {
-    const int m = i / pieces_per_row, piece = i % pieces_per_row;
-    const int p = piece / pieces_per_part, within = (piece % pieces_per_part) * 16;
+    const int m = i >> row_log, piece = i & (pieces_per_row - 1);
+    const int p = piece >> part_log, within = (piece & (pieces_per_part - 1)) * 16;
     const int k_in_part = k_first + within;
     const int kk = p * span + within;
     uint8_t* dst = buf + (kk / 128) * E_ABLK_BYTES + m * E_ROW_BYTES + (kk % 128);
@@ -92,9 +94,10 @@ __global__ void __launch_bounds__(E_THREADS, 1)
   const int rg = warp % rowgroups, part = warp / rowgroups;
   const int part_k = K / ksplit;        // a multiple of 128
   const int span = E_CHUNK_K / ksplit;  // k per part per staged chunk, a multiple of 128
-  const int ipc = span / 128;           // iterations per chunk
+  const int ipc = span / 128;           // iterations per chunk (a power of two)
+  const int ipc_log = 31 - __clz(ipc);
   const int iters = part_k / 128;
-  const int chunks = (iters + ipc - 1) / ipc;
+  const int chunks = (iters + ipc - 1) >> ipc_log;
   const int n_base = (blockIdx.x * rowgroups + rg) * 32;
 
   uint32_t w_off[E_TILES];
@@ -130,8 +133,8 @@ __global__ void __launch_bounds__(E_THREADS, 1)
     for (int d = 0; d < E_DEPTH; ++d) {
       const int it = it0 + d;
       if (it >= iters) break;  // uniform over the CTA
-      const int c = it / ipc;
-      if (it % ipc == 0) {  // entering chunk c (uniform over the CTA)
+      const int c = it >> ipc_log;
+      if ((it & (ipc - 1)) == 0) {  // entering chunk c (uniform over the CTA)
         __syncthreads();    // everyone is done with chunk c - 1, whose buffer is refilled now
         if (c + 1 < chunks)
           stage_a(smem + ((c + 1) & 1) * E_A_BYTES, A, M, K, (c + 1) * span, part_k, ksplit, span);
@@ -140,7 +143,7 @@ __global__ void __launch_bounds__(E_THREADS, 1)
         __syncthreads();  // chunk c has landed for every thread
       }
       // this lane's 32 bytes of activation rows r and r + 8 in this 128-k block
-      const uint8_t* ab = smem + (c & 1) * E_A_BYTES + (part * ipc + it % ipc) * E_ABLK_BYTES + j * 32;
+      const uint8_t* ab = smem + (c & 1) * E_A_BYTES + (part * ipc + (it & (ipc - 1))) * E_ABLK_BYTES + j * 32;
       const uint4* a_lo = reinterpret_cast<const uint4*>(ab + r * E_ROW_BYTES);
       const uint4* a_hi = reinterpret_cast<const uint4*>(ab + (r + 8) * E_ROW_BYTES);
 #pragma unroll
