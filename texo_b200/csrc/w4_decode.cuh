@@ -9,10 +9,9 @@
 // for the weights), D_DEPTH such loads in flight per thread and tile.  The MMA's k slots are a
 // free permutation as long as both operands agree on it: lane j of a quad supplies, in MMA
 // step s, its own nibbles 4s..4s+3, i.e. k = k0 + 32j + 4s + {0,1,2,3}; the matching x values
-// are 4 consecutive halves of an x row, read as 16-byte pieces (two steps each) from a
-// shared-memory copy of x laid out [128-k block][j][row][32 halves] (+16 bytes per [j] block,
-// which makes the quad's 16-byte reads bank-conflict free).  One x fragment feeds the MMAs of
-// all four tiles.  Nibbles become the exact FP16 integers q - 8 by the byte-permute + one
+// are 4 consecutive halves of rows r and r + 8 of x, kept in shared memory in exactly the
+// order of the MMA's A operand (see stage_x): one 16-byte load per step is the operand, and
+// it feeds the MMAs of all four tiles.  Nibbles become the exact FP16 integers q - 8 by the byte-permute + one
 // HFMA2 conversion of mm_int4.cu (unpack8); per scale group (= one 128-k iteration) each
 // tile's 16x8 FP32 partial is folded into the running result with the group's scale,
 // acc += s[n,g] * partial, so the only roundings are FP32 accumulations (the property the
@@ -34,8 +33,8 @@ constexpr int D_WARPS = 16;
 constexpr int D_THREADS = D_WARPS * 32;
 constexpr int D_TILES = 4;   // n8 tiles (32 weight rows) per warp
 constexpr int D_DEPTH = 2;   // 128-k loads in flight per thread and tile
-constexpr int D_JBLK_BYTES = 16 * 64 + 16;        // 16 rows x 32 halves of one j, + bank-shift pad
-constexpr int D_XBLK_BYTES = 4 * D_JBLK_BYTES;    // one 128-k block of x
+constexpr int D_GROUP_BYTES = 32 * 16;            // one 16-byte x fragment of every lane
+constexpr int D_XBLK_BYTES = 8 * D_GROUP_BYTES;   // one 128-k block of x (16 rows) = eight fragments per lane
 constexpr int D_CHUNK_K = 2048;                   // k of x staged per buffer, over all k parts of the CTA
 constexpr int D_X_BYTES = (D_CHUNK_K / 128) * D_XBLK_BYTES;
 constexpr int D_RED_BYTES = D_WARPS * D_TILES * 4 * 32 * 4;  // FP32 partial results of every warp
@@ -51,14 +50,19 @@ __device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* src, bool valid) {
+__device__ __forceinline__ void cp_async_4(void* smem_dst, const void* src, bool valid) {
   const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst));
-  const int bytes = valid ? 16 : 0;  // zero-fill: rows past M, k past K
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+  const int bytes = valid ? 4 : 0;  // zero-fill: rows past M, k past K
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
 }
 
-// Stages x[:, p * part_k + k_first + [0, span)) for every k part p of the CTA into `buf`, in the
-// fragment layout described above; part p's i-th 128-k block lands at block p * (span/128) + i.
+// Stages x[:, p * part_k + k_first + [0, span)) for every k part p of the CTA into `buf`; part
+// p's i-th 128-k block lands at block p * (span/128) + i.  Inside a block the halves are laid
+// out as the MMA wants them: lane (r, j) uses, in MMA step s = 0..7, the A fragment
+// {row r: its k 4s, 4s+1 | row r + 8: the same k | row r: k 4s+2, 4s+3 | row r + 8: the same}
+// (its k = 32 j + ...), one 16-byte piece at [step s][lane][16 bytes]: a conflict-free
+// 16-byte shared load yields the operand's four registers in order, with no register
+// shuffling in front of the MMA.
 __device__ __forceinline__ void stage_x(uint8_t* buf, const __half* __restrict__ x, int M, int K,
                                         int k_first, int part_k, int ksplit, int span) {
   // (ksplit and span are powers of two: shifts and masks, no integer divisions)
@@ -69,10 +73,16 @@ __device__ __forceinline__ void stage_x(uint8_t* buf, const __half* __restrict__
     const int m = i >> row_log, piece = i & (pieces_per_row - 1);
     const int p = piece >> part_log, within = (piece & (pieces_per_part - 1)) * 8;
     const int k_in_part = k_first + within;
-    const int kk = p * span + within;  // k index inside the staged chunk
-    uint8_t* dst = buf + (kk / 128) * D_XBLK_BYTES + ((kk % 128) / 32) * D_JBLK_BYTES + m * 64 + (kk % 32) * 2;
+    const int kk = p * span + within;  // k index inside the staged chunk, a multiple of 8
+    // 8 halves of row m = two steps' worth of one lane: k = 32 j + 8 q + (0..7)
+    const int j = (kk >> 5) & 3, q = (kk >> 3) & 3;
+    uint8_t* dst = buf + (kk >> 7) * D_XBLK_BYTES + (2 * q) * D_GROUP_BYTES + ((m & 7) * 4 + j) * 16 + (m >> 3) * 4;
     const bool valid = m < M && k_in_part < part_k;
-    cp_async_16(dst, x + (valid ? size_t(m) * K + size_t(p) * part_k + k_in_part : 0), valid);
+    const __half* src = x + (valid ? size_t(m) * K + size_t(p) * part_k + k_in_part : 0);
+    cp_async_4(dst, src, valid);                          // k 0, 1 -> step 2q, slot of this row
+    cp_async_4(dst + 8, src + 2, valid);                  // k 2, 3 -> step 2q, second pair
+    cp_async_4(dst + D_GROUP_BYTES, src + 4, valid);      // k 4, 5 -> step 2q + 1
+    cp_async_4(dst + D_GROUP_BYTES + 8, src + 6, valid);  // k 6, 7
   }
 }
 
@@ -146,24 +156,23 @@ __global__ void __launch_bounds__(D_THREADS, 1)
         asm volatile("cp.async.wait_group 1;" ::: "memory");
         __syncthreads();  // chunk c has landed for every thread
       }
-      // x fragments of this 128-k block: rows r and r + 8, this lane's 64 bytes of each
-      const uint8_t* xb = smem + (c & 1) * D_X_BYTES + (part * ipc + (it & (ipc - 1))) * D_XBLK_BYTES + j * D_JBLK_BYTES;
-      const uint4* x_lo = reinterpret_cast<const uint4*>(xb + r * 64);
-      const uint4* x_hi = reinterpret_cast<const uint4*>(xb + (r + 8) * 64);
+      // this lane's eight x fragments of this 128-k block (see stage_x)
+      const uint8_t* xb = smem + (c & 1) * D_X_BYTES + (part * ipc + (it & (ipc - 1))) * D_XBLK_BYTES + lane * 16;
       float acc[D_TILES][4];
 #pragma unroll
       for (int t = 0; t < D_TILES; ++t)
 #pragma unroll
         for (int e = 0; e < 4; ++e) acc[t][e] = 0.f;
 #pragma unroll
-      for (int q4 = 0; q4 < 4; ++q4) {  // 16 bytes of x per row = two MMA steps
-        const uint4 lo = x_lo[q4], hi = x_hi[q4];
+      for (int q4 = 0; q4 < 4; ++q4) {  // one packed word per tile = two MMA steps
+        const uint4 f0 = *reinterpret_cast<const uint4*>(xb + (2 * q4) * D_GROUP_BYTES);
+        const uint4 f1 = *reinterpret_cast<const uint4*>(xb + (2 * q4 + 1) * D_GROUP_BYTES);
 #pragma unroll
         for (int t = 0; t < D_TILES; ++t) {
           const uint32_t word = q4 == 0 ? ring[d][t].x : q4 == 1 ? ring[d][t].y : q4 == 2 ? ring[d][t].z : ring[d][t].w;
           const uint4 b = unpack8(word);  // 8 nibbles -> halves (k0,k1) (k2,k3) (k4,k5) (k6,k7)
-          mma_16816(acc[t], lo.x, hi.x, lo.y, hi.y, b.x, b.y);
-          mma_16816(acc[t], lo.z, hi.z, lo.w, hi.w, b.z, b.w);
+          mma_16816(acc[t], f0.x, f0.y, f0.z, f0.w, b.x, b.y);
+          mma_16816(acc[t], f1.x, f1.y, f1.z, f1.w, b.z, b.w);
         }
       }
       // this slot's next load: D_DEPTH iterations ahead
