@@ -70,7 +70,11 @@ __device__ __forceinline__ void stage_x(uint8_t* buf, const __half* __restrict__
   const int pieces_per_row = ksplit * pieces_per_part;
   const int part_log = 31 - __clz(pieces_per_part), row_log = 31 - __clz(pieces_per_row);
   for (int i = threadIdx.x; i < 16 * pieces_per_row; i += D_THREADS) {
-    const int m = i >> row_log, piece = i & (pieces_per_row - 1);
+    // (a warp copies sixteen consecutive pieces of two neighbouring rows per step: contiguous
+    // global reads, and the 4-byte shared-memory writes of one instruction spread over eight
+    // banks, the most this layout allows)
+    const int piece = (i >> 1) & (pieces_per_row - 1);
+    const int m = ((i >> (row_log + 1)) << 1) | (i & 1);
     const int p = piece >> part_log, within = (piece & (pieces_per_part - 1)) * 8;
     const int k_in_part = k_first + within;
     const int kk = p * span + within;  // k index inside the staged chunk, a multiple of 8
