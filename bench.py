@@ -72,7 +72,7 @@ NCU_TRAFFIC = {
     "int8_8192_presummed": 395.0e6,
     "int8_decode": 239.0e6,
     "int4_w4a16": 328.5e6,
-    "int4_w4a8": 106.9e6,
+    "int4_w4a8": 119.9e6,
     "dequant": 482.8e6,
     "rmsnorm_quant": 826.5e6,
 }
