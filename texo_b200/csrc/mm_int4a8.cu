@@ -136,13 +136,13 @@ __device__ __forceinline__ void unpack32(const uint4& packed, uint4& first, uint
 // the per-row sums of the unsigned nibbles of W (needed when zA is non-zero) are computed by
 // the epilogue warps of this kernel, exactly as the INT8 CTA-pair kernel computes its sums
 // (mm_int8.cu, "sums inside the CTA-pair kernel"): items of sixteen rows (sixteen threads per
-// row), ordered as the raster needs them - the A rows of the first eight tile rows, all weight
+// row), ordered as the raster needs them - the A rows of the first raster group of tile rows, all weight
 // rows, the remaining A rows -, dealt round robin over the CTAs of the grid, each published by
 // a release store of the call's epoch number into the item's flag; a tile is drained when the
 // flags of its 8 + 16 items carry the epoch.  A CTA blocks on a flag only when it has no item
 // left to do, and every wait is bounded.
 constexpr int QS_ROWS = 16;                          // rows per item
-constexpr int QS_FIRST_A_ITEMS = 8 * 256 / QS_ROWS;  // A items of the first eight tile rows
+constexpr int QS_FIRST_A_ITEMS = i8::P_GROUP_M * 256 / QS_ROWS;  // A items of the first raster group
 constexpr int Q_DECISION_BYTES = 64;
 constexpr int Q_AUX_SMEM_BYTES = Q_DECISION_BYTES + Q_EPI_WARPS * 512;  // + 128 nibble sums per epilogue warp
 static_assert(Q_SMEM_BYTES + Q_AUX_SMEM_BYTES <= 232448, "W4A8 pair kernel: shared memory over the limit");
@@ -238,7 +238,7 @@ __global__ void __launch_bounds__(Q_THREADS, 1)
                 int8_t* __restrict__ C, int* row_sum, int* w_sum, int M, int N, int K, Quant q,
                 int tiles_m, int tiles_n, int c_vector_ok, int* status, const int8_t* __restrict__ A_raw,
                 const uint8_t* __restrict__ W_raw, int a_items, int w_items, unsigned* item_flags,
-                unsigned epoch) {
+                unsigned epoch, int raster_rows) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~uintptr_t(1023));
@@ -289,7 +289,7 @@ __global__ void __launch_bounds__(Q_THREADS, 1)
     grid_dependency_wait();  // the operands may have been written by the grid ahead of this one
     for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
       int tm, tn;
-      i8::pair_tile_coords(tile, tiles_m, tiles_n, tm, tn);
+      i8::pair_tile_coords(tile, tiles_m, tiles_n, raster_rows, tm, tn);
       const int m0 = tm * 256 + int(rank) * 128;
       const int n0 = tn * 256 + int(rank) * 128;
       for (int kb = 0; kb < num_kb && ok; ++kb, ++g) {
@@ -429,7 +429,7 @@ __global__ void __launch_bounds__(Q_THREADS, 1)
     }
     for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
       int tm, tn;
-      i8::pair_tile_coords(tile, tiles_m, tiles_n, tm, tn);
+      i8::pair_tile_coords(tile, tiles_m, tiles_n, raster_rows, tm, tn);
       if (total_items > 0) {
         // Until the accumulator is complete AND this tile's sums are published: the second item
         // at once, then one item per tile, all remaining ones without pause if this tile's
@@ -605,9 +605,11 @@ static bool launch_tensor(DeviceCtx& ctx, const int8_t* A, const uint8_t* W, int
   const int c_vector_ok = (reinterpret_cast<uintptr_t>(C) & 15) == 0 && N % 16 == 0;
   const cudaError_t err =
       wide ? cudaLaunchKernelEx(&cfg, pair_kernel<true>, map_a, map_raw, C, row_sum, w_sum, M, N, K, q, tiles_m,
-                                tiles_n, c_vector_ok, ctx.status, A, W, a_items, w_items, item_flags, epoch)
+                                tiles_n, c_vector_ok, ctx.status, A, W, a_items, w_items, item_flags, epoch,
+                                i8::raster_group_rows(K))
            : cudaLaunchKernelEx(&cfg, pair_kernel<false>, map_a, map_raw, C, row_sum, w_sum, M, N, K, q, tiles_m,
-                                tiles_n, c_vector_ok, ctx.status, A, W, a_items, w_items, item_flags, epoch);
+                                tiles_n, c_vector_ok, ctx.status, A, W, a_items, w_items, item_flags, epoch,
+                                i8::raster_group_rows(K));
   if (err != cudaSuccess) {
     cudaGetLastError();
     profile_stop(slot);

@@ -487,8 +487,8 @@ __global__ void __launch_bounds__(MMA_THREADS, 1)
 // colsum(B) themselves, in the time they would otherwise spend waiting for accumulators.  The
 // work is cut into items (64 columns of B over all K, or 16 rows of A: the access pattern of
 // sums_kernel; the bytes are the ones the TMA producer is pulling through L2 anyway), put in
-// the order in which the tiles need them - the rows of the first eight tile rows, then the
-// column items from left to right (the raster walks eight tile rows column by column), then
+// the order in which the tiles need them - the rows of the first raster group of tile rows, then
+// the column items from left to right (the raster walks a group's tile rows column by column), then
 // the remaining rows - and dealt round robin over all CTAs of the grid (position blockIdx.x,
 // += gridDim.x).  Every finished item is published by storing the call's epoch number into
 // its flag (the flags are never cleared: an epoch is used once).  Before it drains a tile an
@@ -510,7 +510,7 @@ constexpr int ES_PART_BYTES = EPI_WARPS * (SUM_COLS + 1) * 4;     // partials of
 constexpr int P_DECISION_BYTES = 64;
 constexpr int P_COLSUM_SMEM_BYTES = EPI_WARPS * 512;
 constexpr int P_AUX_SMEM_BYTES = P_DECISION_BYTES + P_COLSUM_SMEM_BYTES + ((ES_PART_BYTES + 127) & ~127);
-constexpr int ES_FIRST_ROW_ITEMS = P_GROUP_M * 256 / SUM_ROWS;    // row items of the first eight tile rows
+constexpr int ES_FIRST_ROW_ITEMS = P_GROUP_M * 256 / SUM_ROWS;    // row items of the first raster group
 
 constexpr int ES_ROW_THREADS = ES_THREADS / SUM_ROWS;             // threads per row of a row item
 static_assert(ES_ROW_THREADS == 16, "a row item is sixteen rows by sixteen threads");
@@ -686,7 +686,7 @@ __global__ void __launch_bounds__(MMA_THREADS, 1)
                      int K, Quant q, int tiles_m, int tiles_n, int c_vector_ok, int* status,
                      const int8_t* __restrict__ A_raw, const int8_t* __restrict__ B_raw,
                      int* row_sum_w, int* col_sum_w, int col_items, int row_items,
-                     unsigned* item_flags, unsigned epoch) {
+                     unsigned* item_flags, unsigned epoch, int raster_rows) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~uintptr_t(1023));
@@ -737,7 +737,7 @@ __global__ void __launch_bounds__(MMA_THREADS, 1)
     asm volatile("griddepcontrol.wait;" ::: "memory");
     for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
       int tm, tn;
-      pair_tile_coords(tile, tiles_m, tiles_n, tm, tn);
+      pair_tile_coords(tile, tiles_m, tiles_n, raster_rows, tm, tn);
       const int m0 = tm * 256 + int(rank) * 128;
       const int n0 = tn * 256 + int(rank) * 128;
       for (int kb = 0; kb < num_kb && ok; ++kb, ++g) {
@@ -850,7 +850,7 @@ __global__ void __launch_bounds__(MMA_THREADS, 1)
     }
     for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
       int tm, tn;
-      pair_tile_coords(tile, tiles_m, tiles_n, tm, tn);
+      pair_tile_coords(tile, tiles_m, tiles_n, raster_rows, tm, tn);
       if (total_items > 0) {
         // Until the accumulator is complete AND this tile's sums are published.  The first two
         // items of a CTA (what the first waves of tiles need) are done at once; after that one
@@ -1105,10 +1105,10 @@ static bool launch_tensor(DeviceCtx& ctx, const int8_t* A, const int8_t* B, int8
     const cudaError_t err =
         K <= 33025 ? cudaLaunchKernelEx(&cfg, umma_pair_kernel<false>, map_a, map_b, C, rs, cs, M, N, K, q,
                                         tiles_m, tiles_n, c_vector_ok, ctx.status, A, B, row_sum, col_sum,
-                                        col_items, row_items, item_flags, epoch)
+                                        col_items, row_items, item_flags, epoch, raster_group_rows(K))
                    : cudaLaunchKernelEx(&cfg, umma_pair_kernel<true>, map_a, map_b, C, rs, cs, M, N, K, q,
                                         tiles_m, tiles_n, c_vector_ok, ctx.status, A, B, row_sum, col_sum,
-                                        col_items, row_items, item_flags, epoch);
+                                        col_items, row_items, item_flags, epoch, raster_group_rows(K));
     if (err != cudaSuccess) {
       cudaGetLastError();
       profile_stop(slot);

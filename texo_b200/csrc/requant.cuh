@@ -225,7 +225,29 @@ __device__ __forceinline__ void multimem_st_16(void* mc_addr, const int4& v) {
                : "memory");
 }
 
-constexpr int P_GROUP_M = 8;  // pair-tile rows per raster group
+// Raster of the CTA-pair kernels: tile rows are taken in groups, a group's tiles are walked
+// column by column, so the CTAs running at one time share a group's rows of A and a few
+// columns of B in L2.  Measured on B200 (stateless INT8 call): 8192^3 409 / 402 / 395 / 411 us
+// and 4096^3 65 / 74 / 65 / 65 us for groups of 4 / 8 / 16 / 32 tile rows; with K = 28672 a
+// group of 16 (117 MB of A) no longer fits L2 and 8 is faster again.  The host picks the
+// group size (raster_group_rows) and passes it to the kernel.
+constexpr int P_GROUP_M = 16;  // largest group; also orders the sums' items (any order is correct)
+
+// Tile rows per raster group for rows of `row_bytes` bytes of A: sixteen while a group's rows
+// of A stay within 48 MB, else eight.
+inline int raster_group_rows(long long row_bytes) {
+  return 16LL * 256 * row_bytes <= (48LL << 20) ? 16 : 8;
+}
+
+__device__ __forceinline__ void pair_tile_coords(int tile, int tiles_m, int tiles_n, int group_rows, int& tm,
+                                                 int& tn) {
+  const int group_tiles = group_rows * tiles_n;
+  const int first_m = tile / group_tiles * group_rows;
+  const int group_m = min(tiles_m - first_m, group_rows);
+  const int in_group = tile % group_tiles;
+  tm = first_m + in_group % group_m;
+  tn = in_group / group_m;
+}
 
 // Sum of the sixteen signed bytes of v, added to acc.
 __device__ __forceinline__ int sum_bytes(const int4& v, int acc) {
@@ -235,15 +257,6 @@ __device__ __forceinline__ int sum_bytes(const int4& v, int acc) {
   return __dp4a(v.w, 0x01010101, acc);
 }
 
-__device__ __forceinline__ void pair_tile_coords(int tile, int tiles_m, int tiles_n, int& tm,
-                                                 int& tn) {
-  const int group_tiles = P_GROUP_M * tiles_n;
-  const int first_m = tile / group_tiles * P_GROUP_M;
-  const int group_m = min(tiles_m - first_m, P_GROUP_M);
-  const int in_group = tile % group_tiles;
-  tm = first_m + in_group % group_m;
-  tn = in_group / group_m;
-}
 
 // up * silu(gate), requantised: the arithmetic of the reference's src/swiglu.cu:15-18
 // (x2 * x1 / (1 + __expf(-x1)), FP32, same operation order) on the dequantised gate and up
