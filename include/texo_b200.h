@@ -259,6 +259,11 @@ int texo_selftest_wait_timeout(void);
  * shape seen before skips the driver's descriptor encoding); either pointer may be null. */
 void texo_tensor_map_cache_stats(long long* hits, long long* misses);
 
+/* Sets the per-device epoch counter with which the CTA-pair kernels (mm_int8, mm_int4a8) mark
+ * finished row / column sums (diagnostic, no reference counterpart): lets a test drive the
+ * counter across its 32-bit wrap, where the library clears the flags. */
+void texo_set_sums_epoch(unsigned value);
+
 /* Number of kernels the library has launched so far in this process. */
 long long texo_kernel_launches(void);
 /* CUDA-event bracket around the dominant kernel of each following call (for roofline

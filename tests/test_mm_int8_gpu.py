@@ -718,3 +718,40 @@ def test_per_group_weight_scales(lib, oracle, shape):
     torch.cuda.synchronize()
     assert np.array_equal(C.cpu().numpy(), want), shape
     assert lib.texo_mm_int8_status() == 0
+
+
+def test_sums_epoch_counter_wraps_cleanly(lib, oracle):
+    """The CTA-pair kernels mark finished row / column sums with a per-device call counter;
+    when its 32 bits wrap the library clears the flags, so a mark left by an earlier call with
+    the same number cannot pass for a fresh one.  Drive the counter across the wrap (a large
+    problem first, so that high flag positions carry old numbers, then small and large calls
+    on both sides of the wrap) and require every result bit-exact."""
+    rng = np.random.default_rng(91)
+    q = (0.02, 0.03, 12.0, 3, -5, 1)
+    big = (1024, 1040, 512)
+    small = (300, 272, 256)
+    cases = {}
+    for shape in (big, small):
+        m, n, k = shape
+        a = rng.integers(-128, 128, (m, k), dtype=np.int8)
+        b = rng.integers(-128, 128, (k, n), dtype=np.int8)
+        cases[shape] = (_dev(a), _dev(b), oracle.mm_int8(a, b, m, n, k, q))
+
+    def run(shape):
+        m, n, k = shape
+        A, B, want = cases[shape]
+        C = torch.full((m, n), 55, dtype=torch.int8, device="cuda")
+        lib.texo_mm_int8_solve(A.data_ptr(), B.data_ptr(), C.data_ptr(), m, n, k, *q)
+        torch.cuda.synchronize()
+        assert lib.texo_mm_int8_last_path() == 4
+        assert np.array_equal(C.cpu().numpy(), want), shape
+
+    try:
+        lib.texo_set_sums_epoch(2)   # the next call marks its items with 3
+        run(big)
+        lib.texo_set_sums_epoch(0xFFFFFFFD)
+        for shape in (small, small, small, big, small, big):  # ..FE, ..FF, wrap to 1, 2, 3, 4
+            run(shape)
+    finally:
+        lib.texo_set_sums_epoch(1000)
+    assert lib.texo_mm_int8_status() == 0

@@ -26,6 +26,7 @@ _SIGNATURES = {
                                             _c_float, _c_ptr, _c_float, _c_int, _c_int, _c_int]),
     "texo_mm_int4a8_solve_per_group": (None, [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int,
                                               _c_float, _c_ptr, _c_float, _c_int, _c_int, _c_int]),
+    "texo_set_sums_epoch": (None, [ctypes.c_uint]),
     "texo_mm_int8_swiglu_solve": (None, [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int,
                                          _c_float, _c_float, _c_float, _c_float,
                                          _c_int, _c_int, _c_int, _c_int]),

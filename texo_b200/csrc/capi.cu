@@ -76,3 +76,8 @@ extern "C" void texo_tensor_map_cache_stats(long long* hits, long long* misses) 
   if (hits) *hits = cache.hits;
   if (misses) *misses = cache.misses;
 }
+
+// Sets the epoch counter of the current device's sums flags (host_common.h, next_sums_epoch),
+// so that a test can drive the counter across its 32-bit wrap.  Diagnostic; no counterpart in
+// the reference.
+extern "C" void texo_set_sums_epoch(unsigned value) { texo::device_ctx().sums_epoch = value; }

@@ -30,8 +30,8 @@ struct DeviceCtx {
   // (the kernel that consumes it cleans up after itself); zeroed when (re)allocated.
   void* workspace = nullptr;
   size_t workspace_bytes = 0;
-  // Epoch number of the last INT8 CTA-pair call: its epilogues mark finished sum items in the
-  // scratch with it (flags are compared, never cleared; the scratch is zeroed when allocated).
+  // Epoch number of the last CTA-pair call (INT8 or W4A8): its epilogues mark finished sum items
+  // in the flag array with it (flags are compared, not cleared per call; see next_sums_epoch).
   unsigned sums_epoch = 0;
   void* item_flags = nullptr;  // used by nothing else, so that no other data can pass for an epoch
   size_t item_flag_bytes = 0;
@@ -97,6 +97,17 @@ inline unsigned* device_item_flags(DeviceCtx& ctx, size_t bytes) {
     ctx.item_flag_bytes = want;
   }
   return static_cast<unsigned*>(ctx.item_flags);
+}
+
+// The epoch number of the next call that publishes sums through the flag array: never zero,
+// and when the 32-bit counter wraps the flags are cleared (on the stream, ahead of the kernel)
+// so that a flag left behind 2^32 calls ago cannot pass for a fresh one.
+inline unsigned next_sums_epoch(DeviceCtx& ctx) {
+  if (++ctx.sums_epoch == 0) {
+    if (ctx.item_flags) cudaMemsetAsync(ctx.item_flags, 0, ctx.item_flag_bytes, 0);
+    ctx.sums_epoch = 1;
+  }
+  return ctx.sums_epoch;
 }
 
 // Grow-only, zero-initialised workspace (see DeviceCtx::workspace).

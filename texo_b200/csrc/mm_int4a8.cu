@@ -581,8 +581,7 @@ static bool launch_tensor(DeviceCtx& ctx, const int8_t* A, const uint8_t* W, int
   unsigned* item_flags = device_item_flags(ctx, size_t(std::max(a_items + w_items, 1)) * sizeof(unsigned));
   if (!item_flags) return false;
   // a finished item is marked with this call's epoch number: never zero, never used twice
-  if (++ctx.sums_epoch == 0) ++ctx.sums_epoch;
-  const unsigned epoch = ctx.sums_epoch;
+  const unsigned epoch = next_sums_epoch(ctx);
   const int slot = profile_start();
   cudaLaunchConfig_t cfg = {};
   // one pair per tile up to what the device holds; a small problem gets extra pairs that own

@@ -1077,8 +1077,7 @@ static bool launch_tensor(DeviceCtx& ctx, const int8_t* A, const int8_t* B, int8
     const int col_items = sums_q.za != 0 ? (N + SUM_COLS - 1) / SUM_COLS : 0;
     const int row_items = sums_q.zb != 0 ? (M + SUM_ROWS - 1) / SUM_ROWS : 0;
     // a finished item is marked with this call's epoch number: never zero, never used twice
-    if (++ctx.sums_epoch == 0) ++ctx.sums_epoch;
-    const unsigned epoch = ctx.sums_epoch;
+    const unsigned epoch = next_sums_epoch(ctx);
     cudaLaunchConfig_t cfg = {};
     // One pair per tile up to what the device holds; a small problem gets extra pairs that own
     // no tile and only help with the sums (one item per CTA: an item is one memory round trip),
