@@ -485,7 +485,7 @@ __global__ void __launch_bounds__(MMA_THREADS, 1)
 // ------------------------------------------- sums inside the CTA-pair kernel
 // The CTA-pair kernel needs no pre-pass: its eight epilogue warps compute rowsum(A) /
 // colsum(B) themselves, in the time they would otherwise spend waiting for accumulators.  The
-// work is cut into items (64 columns of B over all K, or 16 rows of A: the access pattern of
+// work is cut into items (128 columns of B over all K, or 16 rows of A: the access pattern of
 // sums_kernel; the bytes are the ones the TMA producer is pulling through L2 anyway), put in
 // the order in which the tiles need them - the rows of the first raster group of tile rows, then
 // the column items from left to right (the raster walks a group's tile rows column by column), then
@@ -499,8 +499,13 @@ __global__ void __launch_bounds__(MMA_THREADS, 1)
 // every item's owner is running.  The items the first wave of tiles needs are finished
 // within the first few microseconds, long before the first accumulators are.
 constexpr int ES_THREADS = EPI_WARPS * 32;                        // 256 epilogue threads
-constexpr int ES_KLANES = ES_THREADS / SUM_TX;                    // k lanes of a column item
-constexpr int ES_PART_BYTES = EPI_WARPS * (SUM_COLS + 1) * 4;     // partials of a column item
+// Columns of a column item: 128, i.e. whole 128-byte lines of B per k row.  Measured on the
+// stateless 8192^3 call (same box): 32 columns 406 us, 64 columns 400 us, 128 columns 394 us,
+// 256 columns 396 us (items of 256 columns are few and long).
+constexpr int ES_COLS = 128;
+constexpr int ES_TX = ES_COLS / 16;                               // threads across the columns
+constexpr int ES_KLANES = ES_THREADS / ES_TX;                     // k lanes of a column item
+constexpr int ES_PART_BYTES = EPI_WARPS * (ES_COLS + 1) * 4;      // partials of a column item
 // Shared memory of the epilogue warps behind the ring and the barriers: 64 bytes of decision
 // words (aliased with nothing: warps read them while others have already gone on), then
 //   plain call:   128 column sums per epilogue warp (4 KiB) | partials of a column item
@@ -533,15 +538,15 @@ __device__ __forceinline__ int pos_of_col_item(int c, int row_items) {
 __device__ __forceinline__ void epilogue_sum_item(int pos, const int8_t* __restrict__ A,
                                                   const int8_t* __restrict__ B, int* __restrict__ row_sum,
                                                   int* __restrict__ col_sum, int M, int N, int K,
-                                                  int col_items, int row_items, int (*part)[SUM_COLS + 1],
+                                                  int col_items, int row_items, int (*part)[ES_COLS + 1],
                                                   int et, unsigned* flags, unsigned epoch) {
   const int warp = et / 32, lane = et % 32;
   const int first_rows = min(row_items, ES_FIRST_ROW_ITEMS);
   const bool is_col = pos >= first_rows && pos < first_rows + col_items;
   if (is_col) {
     const int item = pos - first_rows;
-    const int tx = et % SUM_TX, ty = et / SUM_TX;
-    const int n = item * SUM_COLS + tx * 16;
+    const int tx = et % ES_TX, ty = et / ES_TX;
+    const int n = item * ES_COLS + tx * 16;
     int acc[16] = {};
     if (n < N) {
       // (sixteen 16-byte loads in flight per thread: an item is bound by load latency under
@@ -570,19 +575,19 @@ __device__ __forceinline__ void epilogue_sum_item(int pos, const int8_t* __restr
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
 #pragma unroll
-      for (int o = SUM_TX; o < 32; o <<= 1) acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], o);
+      for (int o = ES_TX; o < 32; o <<= 1) acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], o);
     }
     epilogue_bar();  // the previous item's readers are done with `part`
-    if (lane < SUM_TX) {
+    if (lane < ES_TX) {
 #pragma unroll
       for (int i = 0; i < 16; ++i) part[warp][tx * 16 + i] = acc[i];
     }
     epilogue_bar();
-    if (et < SUM_COLS) {
+    if (et < ES_COLS) {
       int total = 0;
 #pragma unroll
       for (int r = 0; r < EPI_WARPS; ++r) total += part[r][et];
-      const int out = item * SUM_COLS + et;
+      const int out = item * ES_COLS + et;
       if (out < N) col_sum[out] = total;
     }
   } else {
@@ -623,15 +628,15 @@ __device__ __forceinline__ void epilogue_sum_item(int pos, const int8_t* __restr
 }
 
 // Whether the sums this CTA's part of tile (tm, tn) needs are published: its 128 rows (eight
-// row items) and the tile's 256 columns (four column items).  Called by one full warp.
+// row items) and the tile's 256 columns (two column items).  Called by one full warp.
 __device__ __forceinline__ bool tile_sums_ready(int tm, int tn, int rank, int row_items, int col_items,
                                                 const unsigned* flags, unsigned epoch, int lane) {
   int pos = -1;
   if (lane < 8) {
     const int i = (tm * 256 + rank * 128) / SUM_ROWS + lane;
     if (i < row_items) pos = pos_of_row_item(i, row_items, col_items);
-  } else if (lane < 12) {
-    const int c = tn * (256 / SUM_COLS) + (lane - 8);
+  } else if (lane < 8 + 256 / ES_COLS) {
+    const int c = tn * (256 / ES_COLS) + (lane - 8);
     if (c < col_items) pos = pos_of_col_item(c, row_items);
   }
   bool ready = true;
@@ -666,7 +671,7 @@ constexpr int P_B_BYTES = BK * 128;  // 128 k-rows x 128 n-bytes (this CTA's hal
 constexpr int P_STAGE_BYTES = P_A_BYTES + P_B_BYTES;
 constexpr int P_SMEM_BYTES = P_STAGES * P_STAGE_BYTES + 1024 + 256;
 constexpr int P_GATHER_SMEM_BYTES = P_DECISION_BYTES + EPI_WARPS * 4096;  // staging tiles of the fused all-gather
-static_assert(ES_PART_BYTES <= 4096, "the partials of a column item must fit the first staging tile");
+static_assert(ES_PART_BYTES <= EPI_WARPS * 4096, "the partials of a column item must fit the staging tiles");
 static_assert(P_SMEM_BYTES + P_GATHER_SMEM_BYTES <= 232448, "CTA-pair kernel: shared memory over the limit");
 
 struct PairBarriers {
@@ -834,7 +839,7 @@ __global__ void __launch_bounds__(MMA_THREADS, 1)
     uint8_t* const aux = smem + P_STAGES * P_STAGE_BYTES + 256;
     volatile int* decision = reinterpret_cast<volatile int*>(aux);
     const bool gathering = q.n_peers > 0;
-    int(*part)[SUM_COLS + 1] = reinterpret_cast<int(*)[SUM_COLS + 1]>(
+    int(*part)[ES_COLS + 1] = reinterpret_cast<int(*)[ES_COLS + 1]>(
         aux + P_DECISION_BYTES + (gathering ? 0 : P_COLSUM_SMEM_BYTES));
     // 128 column sums per epilogue warp (plain calls), or a 4 KiB staging tile per warp (fused
     // all-gather; the host sizes the launch accordingly)
@@ -1045,7 +1050,7 @@ static bool launch_tensor(DeviceCtx& ctx, const int8_t* A, const int8_t* B, int8
   if (!row_sum) return false;
   int* col_sum = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(row_sum) + row_bytes);
   unsigned* item_flags = device_item_flags(
-      ctx, size_t((M + SUM_ROWS - 1) / SUM_ROWS + (N + SUM_COLS - 1) / SUM_COLS) * sizeof(unsigned));
+      ctx, size_t((M + SUM_ROWS - 1) / SUM_ROWS + (N + ES_COLS - 1) / ES_COLS) * sizeof(unsigned));
   if (!item_flags) return false;
   // 16-byte row stores need aligned rows of the output (H [M, N/2] in the SwiGLU form, FP16
   // [M, N] in the dequantising form)
@@ -1074,7 +1079,7 @@ static bool launch_tensor(DeviceCtx& ctx, const int8_t* A, const int8_t* B, int8
   const int slot = profile_start();
   if (pairs > 0) {
     const int tiles_m = (M + 255) / 256;
-    const int col_items = sums_q.za != 0 ? (N + SUM_COLS - 1) / SUM_COLS : 0;
+    const int col_items = sums_q.za != 0 ? (N + ES_COLS - 1) / ES_COLS : 0;
     const int row_items = sums_q.zb != 0 ? (M + SUM_ROWS - 1) / SUM_ROWS : 0;
     // a finished item is marked with this call's epoch number: never zero, never used twice
     const unsigned epoch = next_sums_epoch(ctx);
