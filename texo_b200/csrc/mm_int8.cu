@@ -501,10 +501,9 @@ __global__ void __launch_bounds__(MMA_THREADS, 1)
 constexpr int ES_THREADS = EPI_WARPS * 32;                        // 256 epilogue threads
 // Columns of a column item: 128, i.e. whole 128-byte lines of B per k row.  Measured on the
 // stateless 8192^3 call (same box): 32 columns 406 us, 64 columns 400 us, 128 columns 394 us,
-// 256 columns 396 us (items of 256 columns are few and long).
-constexpr int ES_COLS = 128;
-constexpr int ES_TX = ES_COLS / 16;                               // threads across the columns
-constexpr int ES_KLANES = ES_THREADS / ES_TX;                     // k lanes of a column item
+// 256 columns 396 us (items of 256 columns are few and long).  For K > 12288 the host asks for
+// 64 columns: an item must stay shorter than the MMAs of a tile, or the drain behind it is late.
+constexpr int ES_COLS = 128;                                      // widest column item
 constexpr int ES_PART_BYTES = EPI_WARPS * (ES_COLS + 1) * 4;      // partials of a column item
 // Shared memory of the epilogue warps behind the ring and the barriers: 64 bytes of decision
 // words (aliased with nothing: warps read them while others have already gone on), then
@@ -533,63 +532,72 @@ __device__ __forceinline__ int pos_of_col_item(int c, int row_items) {
   return min(row_items, ES_FIRST_ROW_ITEMS) + c;
 }
 
+// One column item: colsum(B) of COLS columns over all K, by the 256 epilogue threads (COLS / 16
+// threads across the columns, the rest along k; partials of the eight warps meet in `part`).
+template <int COLS>
+__device__ __forceinline__ void column_sum_item(int item, const int8_t* __restrict__ B, int* __restrict__ col_sum,
+                                                int N, int K, int (*part)[ES_COLS + 1], int et) {
+  constexpr int TX = COLS / 16, KLANES = ES_THREADS / TX;
+  const int warp = et / 32, lane = et % 32;
+  const int tx = et % TX, ty = et / TX;
+  const int n = item * COLS + tx * 16;
+  int acc[16] = {};
+  if (n < N) {
+    // (sixteen 16-byte loads in flight per thread: an item is bound by load latency under
+    // the tensor kernel's own L2 traffic, not by the additions)
+    const int8_t* col = B + n;
+    int k = ty;
+    for (; k + 15 * KLANES < K; k += 16 * KLANES) {
+      int4 v[16];
+#pragma unroll
+      for (int u = 0; u < 16; ++u) v[u] = __ldcs(reinterpret_cast<const int4*>(col + size_t(k + u * KLANES) * N));
+#pragma unroll
+      for (int u = 0; u < 16; ++u) add_bytes(acc, v[u]);
+    }
+    for (; k + 3 * KLANES < K; k += 4 * KLANES) {
+      int4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) v[u] = __ldcs(reinterpret_cast<const int4*>(col + size_t(k + u * KLANES) * N));
+#pragma unroll
+      for (int u = 0; u < 4; ++u) add_bytes(acc, v[u]);
+    }
+    for (; k < K; k += KLANES) add_bytes(acc, __ldcs(reinterpret_cast<const int4*>(col + size_t(k) * N)));
+  }
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+#pragma unroll
+    for (int o = TX; o < 32; o <<= 1) acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], o);
+  }
+  epilogue_bar();  // the previous item's readers are done with `part`
+  if (lane < TX) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) part[warp][tx * 16 + i] = acc[i];
+  }
+  epilogue_bar();
+  if (et < COLS) {
+    int total = 0;
+#pragma unroll
+    for (int r = 0; r < EPI_WARPS; ++r) total += part[r][et];
+    const int out = item * COLS + et;
+    if (out < N) col_sum[out] = total;
+  }
+}
+
 // Computes the item at position `pos` with the 256 epilogue threads of this CTA (`et` = index
-// among them) and publishes it.
+// among them) and publishes it.  `col_cols` = columns per column item (64 or 128).
 __device__ __forceinline__ void epilogue_sum_item(int pos, const int8_t* __restrict__ A,
                                                   const int8_t* __restrict__ B, int* __restrict__ row_sum,
                                                   int* __restrict__ col_sum, int M, int N, int K,
-                                                  int col_items, int row_items, int (*part)[ES_COLS + 1],
-                                                  int et, unsigned* flags, unsigned epoch) {
-  const int warp = et / 32, lane = et % 32;
+                                                  int col_items, int row_items, int col_cols,
+                                                  int (*part)[ES_COLS + 1], int et, unsigned* flags,
+                                                  unsigned epoch) {
   const int first_rows = min(row_items, ES_FIRST_ROW_ITEMS);
   const bool is_col = pos >= first_rows && pos < first_rows + col_items;
   if (is_col) {
-    const int item = pos - first_rows;
-    const int tx = et % ES_TX, ty = et / ES_TX;
-    const int n = item * ES_COLS + tx * 16;
-    int acc[16] = {};
-    if (n < N) {
-      // (sixteen 16-byte loads in flight per thread: an item is bound by load latency under
-      // the tensor kernel's own L2 traffic, not by the additions)
-      const int8_t* col = B + n;
-      int k = ty;
-      for (; k + 15 * ES_KLANES < K; k += 16 * ES_KLANES) {
-        int4 v[16];
-#pragma unroll
-        for (int u = 0; u < 16; ++u)
-          v[u] = __ldcs(reinterpret_cast<const int4*>(col + size_t(k + u * ES_KLANES) * N));
-#pragma unroll
-        for (int u = 0; u < 16; ++u) add_bytes(acc, v[u]);
-      }
-      for (; k + 3 * ES_KLANES < K; k += 4 * ES_KLANES) {
-        int4 v[4];
-#pragma unroll
-        for (int u = 0; u < 4; ++u)
-          v[u] = __ldcs(reinterpret_cast<const int4*>(col + size_t(k + u * ES_KLANES) * N));
-#pragma unroll
-        for (int u = 0; u < 4; ++u) add_bytes(acc, v[u]);
-      }
-      for (; k < K; k += ES_KLANES)
-        add_bytes(acc, __ldcs(reinterpret_cast<const int4*>(col + size_t(k) * N)));
-    }
-#pragma unroll
-    for (int i = 0; i < 16; ++i) {
-#pragma unroll
-      for (int o = ES_TX; o < 32; o <<= 1) acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], o);
-    }
-    epilogue_bar();  // the previous item's readers are done with `part`
-    if (lane < ES_TX) {
-#pragma unroll
-      for (int i = 0; i < 16; ++i) part[warp][tx * 16 + i] = acc[i];
-    }
-    epilogue_bar();
-    if (et < ES_COLS) {
-      int total = 0;
-#pragma unroll
-      for (int r = 0; r < EPI_WARPS; ++r) total += part[r][et];
-      const int out = item * ES_COLS + et;
-      if (out < N) col_sum[out] = total;
-    }
+    if (col_cols == 128)
+      column_sum_item<128>(pos - first_rows, B, col_sum, N, K, part, et);
+    else
+      column_sum_item<64>(pos - first_rows, B, col_sum, N, K, part, et);
   } else {
     // sixteen threads per row, all sixteen rows at once: every load of a short row is in
     // flight before the first is used (a row of 1024 bytes is four loads per thread)
@@ -628,15 +636,15 @@ __device__ __forceinline__ void epilogue_sum_item(int pos, const int8_t* __restr
 }
 
 // Whether the sums this CTA's part of tile (tm, tn) needs are published: its 128 rows (eight
-// row items) and the tile's 256 columns (two column items).  Called by one full warp.
+// row items) and the tile's 256 columns (two or four column items).  Called by one full warp.
 __device__ __forceinline__ bool tile_sums_ready(int tm, int tn, int rank, int row_items, int col_items,
-                                                const unsigned* flags, unsigned epoch, int lane) {
+                                                int col_cols, const unsigned* flags, unsigned epoch, int lane) {
   int pos = -1;
   if (lane < 8) {
     const int i = (tm * 256 + rank * 128) / SUM_ROWS + lane;
     if (i < row_items) pos = pos_of_row_item(i, row_items, col_items);
-  } else if (lane < 8 + 256 / ES_COLS) {
-    const int c = tn * (256 / ES_COLS) + (lane - 8);
+  } else if (lane < 8 + 256 / col_cols) {
+    const int c = tn * (256 / col_cols) + (lane - 8);
     if (c < col_items) pos = pos_of_col_item(c, row_items);
   }
   bool ready = true;
@@ -691,7 +699,7 @@ __global__ void __launch_bounds__(MMA_THREADS, 1)
                      int K, Quant q, int tiles_m, int tiles_n, int c_vector_ok, int* status,
                      const int8_t* __restrict__ A_raw, const int8_t* __restrict__ B_raw,
                      int* row_sum_w, int* col_sum_w, int col_items, int row_items,
-                     unsigned* item_flags, unsigned epoch, int raster_rows) {
+                     unsigned* item_flags, unsigned epoch, int raster_rows, int col_cols) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~uintptr_t(1023));
@@ -848,8 +856,8 @@ __global__ void __launch_bounds__(MMA_THREADS, 1)
     int round = 0;  // alternates the two decision words, so that one barrier per decision suffices
     int items_done = 0;
     if (next_item < total_items) {  // the first item needs no decision: nothing else can be ready yet
-      epilogue_sum_item(next_item, A_raw, B_raw, row_sum_w, col_sum_w, M, N, K, col_items, row_items, part,
-                        et, item_flags, epoch);
+      epilogue_sum_item(next_item, A_raw, B_raw, row_sum_w, col_sum_w, M, N, K, col_items, row_items, col_cols,
+                        part, et, item_flags, epoch);
       next_item += gridDim.x;
       ++items_done;
     }
@@ -870,7 +878,7 @@ __global__ void __launch_bounds__(MMA_THREADS, 1)
           if (ew == 0) {
             int d = 0;  // 0 = wait, 1 = go on to the drain, 2 = do an item, 3 = give up
             const bool acc_ready = mbar_try_wait(&bars->acc_full[acc], acc_phase);
-            const bool sums_ready = tile_sums_ready(tm, tn, int(rank), row_items, col_items, item_flags, epoch, lane);
+            const bool sums_ready = tile_sums_ready(tm, tn, int(rank), row_items, col_items, col_cols, item_flags, epoch, lane);
             if (acc_ready && sums_ready) d = 1;
             else if (next_item < total_items && (items_done < 2 || !sums_ready || !item_this_tile)) d = 2;
             else if (*abort_flag) d = 3;
@@ -891,7 +899,7 @@ __global__ void __launch_bounds__(MMA_THREADS, 1)
           }
           if (d == 2) {
             epilogue_sum_item(next_item, A_raw, B_raw, row_sum_w, col_sum_w, M, N, K, col_items, row_items,
-                              part, et, item_flags, epoch);
+                              col_cols, part, et, item_flags, epoch);
             next_item += gridDim.x;
             ++items_done;
             item_this_tile = true;
@@ -921,8 +929,8 @@ __global__ void __launch_bounds__(MMA_THREADS, 1)
     // whatever is left of this CTA's share of the sums (other CTAs' later tiles wait for it; a
     // pair that owns no tile does all of its share here)
     while (ok && next_item < total_items) {
-      epilogue_sum_item(next_item, A_raw, B_raw, row_sum_w, col_sum_w, M, N, K, col_items, row_items, part,
-                        et, item_flags, epoch);
+      epilogue_sum_item(next_item, A_raw, B_raw, row_sum_w, col_sum_w, M, N, K, col_items, row_items, col_cols,
+                        part, et, item_flags, epoch);
       next_item += gridDim.x;
     }
   }
@@ -1050,7 +1058,7 @@ static bool launch_tensor(DeviceCtx& ctx, const int8_t* A, const int8_t* B, int8
   if (!row_sum) return false;
   int* col_sum = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(row_sum) + row_bytes);
   unsigned* item_flags = device_item_flags(
-      ctx, size_t((M + SUM_ROWS - 1) / SUM_ROWS + (N + ES_COLS - 1) / ES_COLS) * sizeof(unsigned));
+      ctx, size_t((M + SUM_ROWS - 1) / SUM_ROWS + (N + 63) / 64) * sizeof(unsigned));
   if (!item_flags) return false;
   // 16-byte row stores need aligned rows of the output (H [M, N/2] in the SwiGLU form, FP16
   // [M, N] in the dequantising form)
@@ -1079,7 +1087,9 @@ static bool launch_tensor(DeviceCtx& ctx, const int8_t* A, const int8_t* B, int8
   const int slot = profile_start();
   if (pairs > 0) {
     const int tiles_m = (M + 255) / 256;
-    const int col_items = sums_q.za != 0 ? (N + ES_COLS - 1) / ES_COLS : 0;
+    // column items of 128 columns, unless K makes such an item longer than a tile's MMAs take
+    const int col_cols = K <= 12288 ? 128 : 64;
+    const int col_items = sums_q.za != 0 ? (N + col_cols - 1) / col_cols : 0;
     const int row_items = sums_q.zb != 0 ? (M + SUM_ROWS - 1) / SUM_ROWS : 0;
     // a finished item is marked with this call's epoch number: never zero, never used twice
     const unsigned epoch = next_sums_epoch(ctx);
@@ -1109,10 +1119,10 @@ static bool launch_tensor(DeviceCtx& ctx, const int8_t* A, const int8_t* B, int8
     const cudaError_t err =
         K <= 33025 ? cudaLaunchKernelEx(&cfg, umma_pair_kernel<false>, map_a, map_b, C, rs, cs, M, N, K, q,
                                         tiles_m, tiles_n, c_vector_ok, ctx.status, A, B, row_sum, col_sum,
-                                        col_items, row_items, item_flags, epoch, raster_group_rows(K))
+                                        col_items, row_items, item_flags, epoch, raster_group_rows(K), col_cols)
                    : cudaLaunchKernelEx(&cfg, umma_pair_kernel<true>, map_a, map_b, C, rs, cs, M, N, K, q,
                                         tiles_m, tiles_n, c_vector_ok, ctx.status, A, B, row_sum, col_sum,
-                                        col_items, row_items, item_flags, epoch, raster_group_rows(K));
+                                        col_items, row_items, item_flags, epoch, raster_group_rows(K), col_cols);
     if (err != cudaSuccess) {
       cudaGetLastError();
       profile_stop(slot);
