@@ -123,7 +123,7 @@ constexpr int T_THREADS = 512;
 // 128 * (32 + 64) + 256 * 208 = 65536, the SM's register file.
 constexpr int T_REGS_CONTROL = 32, T_REGS_UNPACK = 64, T_REGS_EPILOGUE = 208;
 constexpr int T_SMEM_BYTES = T_STAGES * T_STAGE_BYTES + 1024 + 512;
-constexpr int T_GROUP_M = 8;
+
 
 struct TensorBarriers {
   uint64_t ready[T_STAGES];     // even CTA: x bytes of both CTAs landed AND all unpack warps arrived
@@ -171,11 +171,21 @@ __device__ __forceinline__ void fold32(unsigned long long* acc, int first, const
   }
 }
 
-__device__ __forceinline__ void w4_tile_coords(int tile, int tiles_n, int tiles_m, int& tn, int& tm) {
-  // groups of T_GROUP_M weight-row tiles walked along m, so that a wave shares x rows in L2
-  const int group_tiles = T_GROUP_M * tiles_m;
-  const int first_n = tile / group_tiles * T_GROUP_M;
-  const int group_n = min(tiles_n - first_n, T_GROUP_M);
+// Weight-row tiles per raster group for K weights per row: 32 while a group's packed rows stay
+// within 48 MB, else 16 or 8 (measured at 4096 x 8192 x 8192, G = 128: 502 / 491 / 487 / 486 us
+// for groups of 4 / 8 / 16 / 32).
+inline int w4_raster_group(int K) {
+  for (int g = 32; g > 8; g /= 2)
+    if ((long long)g * 256 * (K / 2) <= (48LL << 20)) return g;
+  return 8;
+}
+
+__device__ __forceinline__ void w4_tile_coords(int tile, int tiles_n, int tiles_m, int group, int& tn, int& tm) {
+  // groups of `group` weight-row tiles walked along m, so that a wave shares x rows and a
+  // group's weights in L2
+  const int group_tiles = group * tiles_m;
+  const int first_n = tile / group_tiles * group;
+  const int group_n = min(tiles_n - first_n, group);
   const int in_group = tile % group_tiles;
   tn = first_n + in_group % group_n;
   tm = in_group / group_n;
@@ -200,7 +210,7 @@ __device__ __forceinline__ void w4_tile_coords(int tile, int tiles_n, int tiles_
 __global__ void __launch_bounds__(T_THREADS, 1)
     tensor_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_raw,
                   const __half* __restrict__ scales, __half* __restrict__ y, int M, int N, int K,
-                  int G, int tiles_n, int tiles_m, int* status) {
+                  int G, int tiles_n, int tiles_m, int* status, int raster_group) {
   extern __shared__ uint8_t smem_raw[];
   grid_dependency_trigger();  // the next grid may set itself up while this one runs
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -255,7 +265,7 @@ __global__ void __launch_bounds__(T_THREADS, 1)
     PROBE_DECL;
     for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
       int tn, tm;
-      w4_tile_coords(tile, tiles_n, tiles_m, tn, tm);
+      w4_tile_coords(tile, tiles_n, tiles_m, raster_group, tn, tm);
       const int n0 = tn * 256 + int(rank) * 128;
       const int m0 = tm * 256 + int(rank) * 128;
       for (int kb = 0; kb < num_kb && ok; ++kb, ++kbg) {
@@ -423,7 +433,7 @@ __global__ void __launch_bounds__(T_THREADS, 1)
     PROBE_DECL;
     for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
       int tn, tm;
-      w4_tile_coords(tile, tiles_n, tiles_m, tn, tm);
+      w4_tile_coords(tile, tiles_n, tiles_m, raster_group, tn, tm);
       const int n = tn * 256 + int(rank) * 128 + quarter * 32 + lane;
       const bool n_ok = n < N;
       const __half* s_row = scales + size_t(n_ok ? n : 0) * groups;
@@ -528,7 +538,7 @@ struct SplitBarriers {
 __global__ void __launch_bounds__(T_THREADS, 1)
     tensor_split_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_raw,
                         const __half* __restrict__ scales, __half* __restrict__ y, int M, int N, int K,
-                        int G, int tiles_n, int tiles_m, int* status) {
+                        int G, int tiles_n, int tiles_m, int* status, int raster_group) {
   extern __shared__ uint8_t smem_raw[];
   grid_dependency_trigger();  // the next grid may set itself up while this one runs
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -579,7 +589,7 @@ __global__ void __launch_bounds__(T_THREADS, 1)
     bool ok = true;
     for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
       int tn, tm;
-      w4_tile_coords(tile, tiles_n, tiles_m, tn, tm);
+      w4_tile_coords(tile, tiles_n, tiles_m, raster_group, tn, tm);
       const int n0 = tn * 256 + int(rank) * 128;
       const int m0 = tm * 256 + int(rank) * 128;
       for (int kb = 0; kb < num_kb && ok; ++kb) {
@@ -662,7 +672,7 @@ __global__ void __launch_bounds__(T_THREADS, 1)
     bool ok = true;
     for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
       int tn, tm;
-      w4_tile_coords(tile, tiles_n, tiles_m, tn, tm);
+      w4_tile_coords(tile, tiles_n, tiles_m, raster_group, tn, tm);
       const int n = min(tn * 256 + int(rank) * 128 + row, N - 1);
       const __half* s_row = scales + size_t(n) * groups;
       for (int kb = 0; kb < num_kb && ok; ++kb) {
@@ -719,7 +729,7 @@ __global__ void __launch_bounds__(T_THREADS, 1)
     bool ok = true;
     for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
       int tn, tm;
-      w4_tile_coords(tile, tiles_n, tiles_m, tn, tm);
+      w4_tile_coords(tile, tiles_n, tiles_m, raster_group, tn, tm);
       const int n = tn * 256 + int(rank) * 128 + quarter * 32 + lane;
       ok = mbar_wait(&bars->acc_full[acc], acc_phase, abort_flag, status, STATUS_TIMEOUT_TMEM_FULL);
       ok = __all_sync(0xffffffffu, ok);
@@ -821,7 +831,7 @@ static bool launch_tensor_split(DeviceCtx& ctx, const __half* x, const uint8_t* 
   cfg.gridDim = dim3(2 * std::min(tiles_n * tiles_m, pairs[ctx.device]));
   const int slot = profile_start();
   if (cudaLaunchKernelEx(&cfg, tensor_split_kernel, map_x, map_raw, scales, y, M, N, K, G, tiles_n, tiles_m,
-                         ctx.status) != cudaSuccess) {
+                         ctx.status, w4_raster_group(K)) != cudaSuccess) {
     cudaGetLastError();
     profile_stop(slot);
     note_host_error(STATUS_LAUNCH_FAILED);
@@ -874,7 +884,7 @@ static bool launch_tensor(DeviceCtx& ctx, const __half* x, const uint8_t* w_q, c
   cfg.gridDim = dim3(2 * std::min(tiles_n * tiles_m, pairs[ctx.device]));
   const int slot = profile_start();
   if (cudaLaunchKernelEx(&cfg, tensor_kernel, map_x, map_raw, scales, y, M, N, K, G, tiles_n, tiles_m,
-                         ctx.status) != cudaSuccess) {
+                         ctx.status, w4_raster_group(K)) != cudaSuccess) {
     cudaGetLastError();
     profile_stop(slot);
     note_host_error(STATUS_LAUNCH_FAILED);
