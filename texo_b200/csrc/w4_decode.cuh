@@ -65,24 +65,31 @@ __device__ __forceinline__ void cp_async_4(void* smem_dst, const void* src, bool
 // shuffling in front of the MMA.
 __device__ __forceinline__ void stage_x(uint8_t* buf, const __half* __restrict__ x, int M, int K,
                                         int k_first, int part_k, int ksplit, int span) {
-  // (ksplit and span are powers of two: shifts and masks, no integer divisions)
+  // A staged chunk is D_CHUNK_K halves = D_THREADS / 2 sixteen-byte pieces per row, whatever
+  // the k split: a thread owns one piece position and the rows of one parity.  (A warp so
+  // copies sixteen consecutive pieces of two neighbouring rows per step: contiguous global
+  // reads, and the 4-byte shared-memory writes of one instruction spread over eight banks,
+  // the most this layout allows.)  ksplit and span are powers of two.
+  static_assert(D_CHUNK_K / 8 == D_THREADS / 2, "one piece position per thread pair");
   const int pieces_per_part = span / 8;  // 16-byte pieces (8 halves) per row and part
-  const int pieces_per_row = ksplit * pieces_per_part;
-  const int part_log = 31 - __clz(pieces_per_part), row_log = 31 - __clz(pieces_per_row);
-  for (int i = threadIdx.x; i < 16 * pieces_per_row; i += D_THREADS) {
-    // (a warp copies sixteen consecutive pieces of two neighbouring rows per step: contiguous
-    // global reads, and the 4-byte shared-memory writes of one instruction spread over eight
-    // banks, the most this layout allows)
-    const int piece = (i >> 1) & (pieces_per_row - 1);
-    const int m = ((i >> (row_log + 1)) << 1) | (i & 1);
-    const int p = piece >> part_log, within = (piece & (pieces_per_part - 1)) * 8;
-    const int k_in_part = k_first + within;
-    const int kk = p * span + within;  // k index inside the staged chunk, a multiple of 8
-    // 8 halves of row m = two steps' worth of one lane: k = 32 j + 8 q + (0..7)
-    const int j = (kk >> 5) & 3, q = (kk >> 3) & 3;
-    uint8_t* dst = buf + (kk >> 7) * D_XBLK_BYTES + (2 * q) * D_GROUP_BYTES + ((m & 7) * 4 + j) * 16 + (m >> 3) * 4;
-    const bool valid = m < M && k_in_part < part_k;
-    const __half* src = x + (valid ? size_t(m) * K + size_t(p) * part_k + k_in_part : 0);
+  const int part_log = 31 - __clz(pieces_per_part);
+  const int piece = threadIdx.x >> 1, parity = threadIdx.x & 1;
+  const int p = piece >> part_log, within = (piece & (pieces_per_part - 1)) * 8;
+  const int k_in_part = k_first + within;
+  const int kk = p * span + within;  // k index inside the staged chunk, a multiple of 8
+  // 8 halves of a row = two steps' worth of one lane: k = 32 j + 8 q + (0..7)
+  const int j = (kk >> 5) & 3, q = (kk >> 3) & 3;
+  uint8_t* const dst0 = buf + (kk >> 7) * D_XBLK_BYTES + (2 * q) * D_GROUP_BYTES + j * 16;
+  const bool k_valid = k_in_part < part_k;
+  const __half* const src0 = x + (k_valid ? size_t(p) * part_k + k_in_part : 0);
+  // rows at and beyond M rounded up to even were zeroed once, when the kernel started
+#pragma unroll
+  for (int pair = 0; pair < 8; ++pair) {
+    const int m = 2 * pair + parity;
+    if (2 * pair >= M) break;
+    uint8_t* dst = dst0 + (m & 7) * 64 + (m >> 3) * 4;
+    const bool valid = k_valid && m < M;
+    const __half* src = src0 + (valid ? size_t(m) * K : 0);
     cp_async_4(dst, src, valid);                          // k 0, 1 -> step 2q, slot of this row
     cp_async_4(dst + 8, src + 2, valid);                  // k 2, 3 -> step 2q, second pair
     cp_async_4(dst + D_GROUP_BYTES, src + 4, valid);      // k 4, 5 -> step 2q + 1
@@ -142,6 +149,11 @@ __global__ void __launch_bounds__(D_THREADS, 1)
       ring[d][t] = d < iters ? __ldcs(reinterpret_cast<const uint4*>(w_q + w_off[t] + d * 64))
                              : make_uint4(0, 0, 0, 0);
 
+  if (M < 15) {  // rows that are never staged must read as zero in both buffers
+    for (int i = threadIdx.x; i < 2 * D_X_BYTES / 16; i += D_THREADS)
+      reinterpret_cast<uint4*>(smem)[i] = make_uint4(0, 0, 0, 0);
+    __syncthreads();
+  }
   stage_x(smem, x, M, K, 0, part_k, ksplit, span);
   asm volatile("cp.async.commit_group;" ::: "memory");
 

@@ -62,18 +62,26 @@ __device__ __forceinline__ void e_cp_async_16(void* smem_dst, const void* src, b
 // p's i-th 128-k block lands at block p * (span/128) + i, rows in natural byte order.
 __device__ __forceinline__ void stage_a(uint8_t* buf, const int8_t* __restrict__ A, int M, int K,
                                         int k_first, int part_k, int ksplit, int span) {
-  // (ksplit and span are powers of two: shifts and masks, no integer divisions)
+  // A staged chunk is E_CHUNK_K bytes = E_THREADS / 2 sixteen-byte pieces per row, whatever
+  // the k split: a thread owns one piece position and the rows of one parity (consecutive
+  // lanes copy consecutive pieces of a row).  ksplit and span are powers of two.
+  static_assert(E_CHUNK_K / 16 == E_THREADS / 2, "one piece position per thread pair");
   const int pieces_per_part = span / 16;
-  const int pieces_per_row = ksplit * pieces_per_part;
-  const int part_log = 31 - __clz(pieces_per_part), row_log = 31 - __clz(pieces_per_row);
-  for (int i = threadIdx.x; i < 16 * pieces_per_row; i += E_THREADS) {
-    const int m = i >> row_log, piece = i & (pieces_per_row - 1);
-    const int p = piece >> part_log, within = (piece & (pieces_per_part - 1)) * 16;
-    const int k_in_part = k_first + within;
-    const int kk = p * span + within;
-    uint8_t* dst = buf + (kk / 128) * E_ABLK_BYTES + m * E_ROW_BYTES + (kk % 128);
-    const bool valid = m < M && k_in_part < part_k;
-    e_cp_async_16(dst, A + (valid ? size_t(m) * K + size_t(p) * part_k + k_in_part : 0), valid);
+  const int part_log = 31 - __clz(pieces_per_part);
+  const int piece = threadIdx.x & (E_THREADS / 2 - 1), parity = threadIdx.x / (E_THREADS / 2);
+  const int p = piece >> part_log, within = (piece & (pieces_per_part - 1)) * 16;
+  const int k_in_part = k_first + within;
+  const int kk = p * span + within;
+  uint8_t* const dst0 = buf + (kk >> 7) * E_ABLK_BYTES + (kk & 127);
+  const bool k_valid = k_in_part < part_k;
+  const int8_t* const src0 = A + (k_valid ? size_t(p) * part_k + k_in_part : 0);
+  // rows at and beyond M rounded up to even were zeroed once, when the kernel started
+#pragma unroll
+  for (int pair = 0; pair < 8; ++pair) {
+    const int m = 2 * pair + parity;
+    if (2 * pair >= M) break;
+    const bool valid = k_valid && m < M;
+    e_cp_async_16(dst0 + m * E_ROW_BYTES, src0 + (valid ? size_t(m) * K : 0), valid);
   }
 }
 
@@ -124,6 +132,11 @@ __global__ void __launch_bounds__(E_THREADS, 1)
       ring[d][t] = d < iters ? __ldcs(reinterpret_cast<const uint4*>(w_q + w_off[t] + d * 64))
                              : make_uint4(0, 0, 0, 0);
 
+  if (M < 15) {  // rows that are never staged must read as zero in both buffers
+    for (int i = threadIdx.x; i < 2 * E_A_BYTES / 16; i += E_THREADS)
+      reinterpret_cast<uint4*>(smem)[i] = make_uint4(0, 0, 0, 0);
+    __syncthreads();
+  }
   stage_a(smem, A, M, K, 0, part_k, ksplit, span);
   asm volatile("cp.async.commit_group;" ::: "memory");
 
