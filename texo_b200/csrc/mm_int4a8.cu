@@ -19,11 +19,12 @@
 // weights; the offset moves into the zero point:
 //   sum (a-zA)(q-zB) = sum a*u - (zB+8)*rowsum(A) - zA*rowsum(u) + K*zA*(zB+8),   u = q + 8.
 // The epilogue is the INT8 operator's TMEM drain (zero-point identity, requantisation,
-// 32-byte row stores).  rowsum(A) and the nibble sums come from a small pre-pass that the
-// pair kernel overlaps by programmatic dependent launch.
+// 32-byte row stores).  rowsum(A) and the nibble sums are computed inside the same kernel by
+// its epilogue warps (one launch per call).
 //
-// Decode path (M <= 32): the INT8 operator's streaming kernel (skinny.cuh) in its packed-weight
-// form - w_q crosses HBM once, four extra warps unpack it next to the tensor core.
+// Decode paths: M <= 16 (K a multiple of 128): a register-streaming mma.sync kernel
+// (w4a8_decode.cuh); M <= 32: the INT8 operator's streaming kernel (skinny.cuh) in its
+// packed-weight form - w_q crosses HBM once, four extra warps unpack it next to the tensor core.
 // Generic path: any shape with even K, any alignment, K = 0: SIMT tiles with int64 totals.
 #include <algorithm>
 #include <cmath>
